@@ -1,0 +1,147 @@
+// Shared pieces of the paged-decode kernels: the launch parameter block, the
+// partial-state format, and the small PTX wrappers.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace loom_decode {
+
+// log2(e): scores are kept in base-2 units so the softmax uses ex2.
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+// Partial state of one (sequence, query head, partition): value_head_size
+// floats of sum_i exp(s_i - max) * v_i, then max (natural-log units of the
+// scaled score), then sum_i exp(s_i - max). The reference keeps the same triple
+// (crates/loom-cuda-sys/cuda/src/paged_decode_attention.cu:551,685,701,743).
+__host__ __device__ inline uint32_t state_stride(uint32_t value_head_size) {
+  return value_head_size + 2u;
+}
+
+struct DecodeParams {
+  const void* query;
+  const void* key_cache;
+  const void* value_cache;
+  const float* key_scales;    // FP8 cache only
+  const float* value_scales;  // FP8 cache only
+  const int32_t* block_tables;
+  const int32_t* sequence_lengths;
+  void* output;      // [sequences, query_heads, Dv] of the query type, or F32 states
+  float* partials;   // workspace [sequences*query_heads, max_partitions, Dv+2] or null
+  uint32_t sequences, query_heads, kv_heads, group;  // group = query_heads / kv_heads
+  uint32_t head_size, value_head_size;
+  uint32_t num_blocks, block_size, max_blocks_per_sequence, max_sequence_length;
+  uint32_t partition_tokens;  // tokens per partition (whole context when partials == null)
+  uint32_t max_partitions;
+  uint32_t scale_stride;
+  uint32_t emit_state;  // final rows are F32 states instead of normalised output
+  uint64_t k_block, k_page, k_head, v_block, v_page, v_head;  // element strides
+  uint64_t q_token, q_head;                                   // element strides of the query
+  float scale_log2;  // softmax scale * log2(e)
+};
+
+// ---------------------------------------------------------------- PTX
+
+__device__ __forceinline__ uint32_t smem_address(const void* pointer) {
+  return (uint32_t)__cvta_generic_to_shared(pointer);
+}
+
+// 16-byte asynchronous global->shared copy that bypasses L1; `bytes` of 0
+// writes zeros without touching global memory.
+__device__ __forceinline__ void cp_async_16(uint32_t smem, const void* global, uint32_t bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem), "l"(global), "r"(bytes)
+               : "memory");
+}
+
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+
+template <int kPending>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(kPending) : "memory");
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t smem) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem));
+}
+
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t smem) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem));
+}
+
+// Warp-wide transpose of an 8x8 matrix of 16-bit elements held one 32-bit
+// register per lane.
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t value) {
+  uint32_t out;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(out) : "r"(value));
+  return out;
+}
+
+__device__ __forceinline__ void mma_16816_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
+                                               uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ void mma_16816_f16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
+                                              uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Four E4M3 bytes -> two f16x2 registers (bytes 0,1 and bytes 2,3). Exact:
+// every E4M3 value is an F16 value.
+__device__ __forceinline__ void e4m3x4_to_f16x2x2(uint32_t packed, uint32_t& low, uint32_t& high) {
+  asm("{\n"
+      ".reg .b16 lo, hi;\n"
+      "mov.b32 {lo, hi}, %2;\n"
+      "cvt.rn.f16x2.e4m3x2 %0, lo;\n"
+      "cvt.rn.f16x2.e4m3x2 %1, hi;\n"
+      "}\n"
+      : "=r"(low), "=r"(high)
+      : "r"(packed));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float low, float high) {
+  __nv_bfloat162 pair = __floats2bfloat162_rn(low, high);
+  return *reinterpret_cast<uint32_t*>(&pair);
+}
+
+__device__ __forceinline__ uint32_t pack_f16x2(float low, float high) {
+  __half2 pair = __floats2half2_rn(low, high);
+  return *reinterpret_cast<uint32_t*>(&pair);
+}
+
+// Physical block of a logical block, clamped so that a corrupt table entry can
+// never turn into an address outside the cache allocation.
+__device__ __forceinline__ uint32_t clamp_block(int32_t block, uint32_t num_blocks) {
+  const uint32_t unsigned_block = (uint32_t)block;
+  return unsigned_block < num_blocks ? unsigned_block : num_blocks - 1u;
+}
+
+// Length of a sequence, clamped into [0, max_sequence_length].
+__device__ __forceinline__ uint32_t clamp_length(int32_t length, uint32_t maximum) {
+  if (length <= 0) return 0u;
+  return (uint32_t)length < maximum ? (uint32_t)length : maximum;
+}
+
+}  // namespace loom_decode

@@ -1,0 +1,441 @@
+// Tensor-core paged decode kernel for 16-bit queries (F16/BF16) over a native
+// 16-bit or an FP8 E4M3 cache.
+//
+// Replaces the reference's three decode kernels
+// (crates/loom-cuda-sys/cuda/src/paged_decode_attention.cu: one head per CTA
+// :164-264, 2/4 packed GQA heads :269-501, split-K partials :509-747), all of
+// which are scalar CUDA-core loops capped at 1024 tokens.
+//
+// Shape of the computation. One CTA owns one (sequence, KV head, KV partition)
+// and ALL query heads of that KV head's group, so every K/V byte is fetched
+// from HBM once however large the group is. Each of the 4 warps streams its
+// own 16-token chunks (warp w takes chunks w, w+4, ...) through a private
+// multi-stage cp.async ring in shared memory; there is no CTA-wide barrier in
+// the main loop. Per chunk a warp computes, with m16n8k16 MMAs,
+//     S^T[16 tokens x 8 heads]  = K[16 x D]   . Q^T[D x 8]
+//     O^T[Dv x 8 heads]        += V^T[Dv x 16] . P^T[16 x 8]
+// i.e. tokens (then value dims) ride the M side and the query heads ride N = 8,
+// which is what makes a GQA group of 4..8 heads a dense tile; a group of 16
+// uses two N tiles. K is the row-major A operand straight from ldmatrix, V^T is
+// the same shared tile read with ldmatrix.trans, Q^T lives in registers for the
+// whole CTA, and P^T is produced from the S^T accumulators by one movmatrix
+// transpose per 8 tokens (no shared-memory round trip). The online softmax
+// keeps (max, sum) per head in registers; max and sum cross lanes with xor
+// shuffles.
+//
+// Memory. The hot loop is bound by HBM: 2*D*sizeof(cache element) bytes per
+// (token, KV head). Rows are fetched as 16-byte cp.async.cg pieces (L1
+// bypassed) into an XOR-swizzled tile, so both ldmatrix flavours are
+// bank-conflict free. Each warp keeps kStages-1 chunks in flight; two CTAs per
+// SM give about 128 KB in flight per SM, above the ~45 KB the measured
+// bandwidth-latency product needs.
+//
+// FP8 cache. Bytes are staged as they are. ldmatrix moves them as 16-bit
+// pairs; a byte permute plus cvt.rn.f16x2.e4m3x2 (exact) turns them into F16
+// MMA operands in registers. The reduction dimension of QK^T and the row
+// dimension of O^T are permuted to match what ldmatrix delivers, Q is loaded
+// with the same permutation, and the epilogue un-permutes O. The K scale is
+// folded into the softmax scale and the V scale into the final normalisation,
+// so dequantisation costs no multiply per element.
+#pragma once
+
+#include "decode_common.cuh"
+
+namespace loom_decode {
+
+constexpr int kMmaWarps = 4;
+constexpr int kMmaThreads = kMmaWarps * 32;
+
+template <bool kFp8, int kD>
+struct MmaTile {
+  static constexpr int kRowBytes = kD * (kFp8 ? 1 : 2);
+  static constexpr int kSegs = kRowBytes / 16;       // 16-byte pieces per row
+  static constexpr int kTileBytes = 16 * kRowBytes;  // one K or V chunk
+  static constexpr int kStageBytes = 2 * kTileBytes;
+  static constexpr int kWanted = (96 * 1024) / (kMmaWarps * kStageBytes);
+  static constexpr int kStages = kWanted < 2 ? 2 : (kWanted > 8 ? 8 : kWanted);
+  static constexpr int kRowsPerPass = 32 / kSegs;
+  static constexpr int kPasses = 16 / kRowsPerPass;
+  static_assert(kSegs >= 4 && kSegs <= 32, "row width out of range");
+};
+
+template <int kNT, int kD>
+constexpr int mma_merge_bytes() {
+  // per warp: 8*kNT heads x (kD + 4) floats of O, plus max and sum
+  return kMmaWarps * (8 * kNT) * (kD + 4 + 2) * 4;
+}
+
+template <bool kFp8, int kD, int kNT>
+constexpr int mma_smem_bytes() {
+  constexpr int pipeline = kMmaWarps * MmaTile<kFp8, kD>::kStages * MmaTile<kFp8, kD>::kStageBytes;
+  constexpr int merge = mma_merge_bytes<kNT, kD>();
+  return pipeline > merge ? pipeline : merge;
+}
+
+// Byte offset of 16-byte piece `col` of row `row` inside a swizzled tile.
+template <int kSegs>
+__device__ __forceinline__ uint32_t swizzled(uint32_t row, uint32_t col) {
+  if constexpr (kSegs >= 8) {
+    return row * (kSegs * 16) + ((col ^ (row & 7u)) << 4);
+  } else {
+    return row * (kSegs * 16) + ((col ^ ((row >> 1) & 3u)) << 4);
+  }
+}
+
+__device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t packed) {
+  const float2 wide = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&packed));
+  return pack_f16x2(wide.x, wide.y);
+}
+
+template <typename QT, bool kFp8, int kD, int kNT>
+__global__ void __launch_bounds__(kMmaThreads, 2) decode_mma_kernel(const DecodeParams p) {
+  using Tile = MmaTile<kFp8, kD>;
+  constexpr bool kBf16Mma = !kFp8 && std::is_same<QT, __nv_bfloat16>::value;
+  constexpr int kHeads = 8 * kNT;
+  constexpr int kKSteps = kD / 16;
+
+  extern __shared__ __align__(128) uint8_t smem[];
+
+  const uint32_t warp = threadIdx.x >> 5;
+  const uint32_t lane = threadIdx.x & 31u;
+  const uint32_t g = lane >> 2;
+  const uint32_t t = lane & 3u;
+
+  const uint32_t head_chunks = (p.group + kHeads - 1) / kHeads;
+  const uint32_t seq = blockIdx.x / p.max_partitions;
+  const uint32_t part = blockIdx.x % p.max_partitions;
+  const uint32_t kv_head = blockIdx.y / head_chunks;
+  const uint32_t first_head = (blockIdx.y % head_chunks) * kHeads;  // within the group
+
+  const uint32_t length = clamp_length(p.sequence_lengths[seq], p.max_sequence_length);
+  const uint32_t part_begin = part * p.partition_tokens;
+  if (part_begin >= length && part != 0) return;  // empty partition
+  const uint32_t part_end = min(length, part_begin + p.partition_tokens);
+  const uint32_t n_parts = length == 0 ? 1u : (length + p.partition_tokens - 1) / p.partition_tokens;
+  const uint32_t n_chunks = part_end > part_begin ? (part_end - part_begin + 15u) / 16u : 0u;
+  const uint32_t my_chunks = n_chunks > warp ? (n_chunks - warp + kMmaWarps - 1) / kMmaWarps : 0u;
+
+  // ---- Q^T fragments, resident for the whole CTA -----------------------
+  uint32_t qf[kNT][kKSteps][2];
+  {
+    const QT* query = static_cast<const QT*>(p.query);
+#pragma unroll
+    for (int nt = 0; nt < kNT; ++nt) {
+      const uint32_t head_in_group = first_head + nt * 8 + g;
+      const bool live = head_in_group < p.group;
+      const QT* row = query + (uint64_t)seq * p.q_token +
+                      ((uint64_t)kv_head * p.group + (live ? head_in_group : 0u)) * p.q_head;
+#pragma unroll
+      for (int ks = 0; ks < kKSteps; ++ks) {
+        uint32_t b0 = 0, b1 = 0;
+        if (live) {
+          if constexpr (kFp8) {
+            // reduction index permuted to the byte order ldmatrix delivers
+            const uint2 four = *reinterpret_cast<const uint2*>(row + ks * 16 + t * 4);
+            b0 = four.x;
+            b1 = four.y;
+            if constexpr (std::is_same<QT, __nv_bfloat16>::value) {
+              b0 = bf16x2_to_f16x2(b0);
+              b1 = bf16x2_to_f16x2(b1);
+            }
+          } else {
+            b0 = *reinterpret_cast<const uint32_t*>(row + ks * 16 + t * 2);
+            b1 = *reinterpret_cast<const uint32_t*>(row + ks * 16 + 8 + t * 2);
+          }
+        }
+        qf[nt][ks][0] = b0;
+        qf[nt][ks][1] = b1;
+      }
+    }
+  }
+
+  float score_scale = p.scale_log2;
+  if constexpr (kFp8) score_scale *= p.key_scales[(uint64_t)kv_head * p.scale_stride];
+
+  // ---- running state ------------------------------------------------------
+  float o[kNT][kKSteps][4];
+  float row_max[kNT][2], row_sum[kNT][2];
+#pragma unroll
+  for (int nt = 0; nt < kNT; ++nt) {
+    row_max[nt][0] = row_max[nt][1] = -INFINITY;
+    row_sum[nt][0] = row_sum[nt][1] = 0.0f;
+#pragma unroll
+    for (int mt = 0; mt < kKSteps; ++mt) {
+      o[nt][mt][0] = o[nt][mt][1] = o[nt][mt][2] = o[nt][mt][3] = 0.0f;
+    }
+  }
+
+  // ---- producer side: page-table driven 16-byte copies --------------------
+  const uint8_t* key_bytes = static_cast<const uint8_t*>(p.key_cache);
+  const uint8_t* value_bytes = static_cast<const uint8_t*>(p.value_cache);
+  constexpr uint32_t kElem = kFp8 ? 1 : 2;
+  const bool page16 = (p.block_size % 16u) == 0;
+  const int32_t* table = p.block_tables + (uint64_t)seq * p.max_blocks_per_sequence;
+  const uint32_t smem_base = smem_address(smem) + warp * (Tile::kStages * Tile::kStageBytes);
+  const uint32_t copy_row = lane / Tile::kSegs;
+  const uint32_t copy_col = lane % Tile::kSegs;
+  const uint64_t k_head_offset = (uint64_t)kv_head * p.k_head * kElem + copy_col * 16;
+  const uint64_t v_head_offset = (uint64_t)kv_head * p.v_head * kElem + copy_col * 16;
+
+  uint32_t cached_blocks = 0;  // block ids of 32 consecutive chunks of this warp (page16 only)
+
+  auto issue_chunk = [&](uint32_t index) {
+    // index counts this warp's chunks; the stage is index % kStages
+    const uint32_t token0 = part_begin + (warp + index * kMmaWarps) * 16u;
+    const uint32_t stage = smem_base + (index % Tile::kStages) * Tile::kStageBytes;
+    if (page16) {
+      if ((index & 31u) == 0) {
+        const uint32_t ahead = part_begin + (warp + (index + lane) * kMmaWarps) * 16u;
+        cached_blocks = ahead < part_end ? clamp_block(__ldg(table + ahead / p.block_size), p.num_blocks) : 0u;
+      }
+      const uint32_t block = __shfl_sync(0xffffffffu, cached_blocks, index & 31u);
+      const uint32_t page0 = token0 % p.block_size;
+      const uint8_t* k_row = key_bytes + ((uint64_t)block * p.k_block + (uint64_t)(page0 + copy_row) * p.k_page) * kElem + k_head_offset;
+      const uint8_t* v_row = value_bytes + ((uint64_t)block * p.v_block + (uint64_t)(page0 + copy_row) * p.v_page) * kElem + v_head_offset;
+      const uint64_t k_step = (uint64_t)Tile::kRowsPerPass * p.k_page * kElem;
+      const uint64_t v_step = (uint64_t)Tile::kRowsPerPass * p.v_page * kElem;
+#pragma unroll
+      for (int pass = 0; pass < Tile::kPasses; ++pass) {
+        const uint32_t row = copy_row + pass * Tile::kRowsPerPass;
+        const uint32_t bytes = (token0 + row) < part_end ? 16u : 0u;
+        cp_async_16(stage + swizzled<Tile::kSegs>(row, copy_col), bytes ? k_row + pass * k_step : key_bytes, bytes);
+      }
+#pragma unroll
+      for (int pass = 0; pass < Tile::kPasses; ++pass) {
+        const uint32_t row = copy_row + pass * Tile::kRowsPerPass;
+        const uint32_t bytes = (token0 + row) < part_end ? 16u : 0u;
+        cp_async_16(stage + Tile::kTileBytes + swizzled<Tile::kSegs>(row, copy_col),
+                    bytes ? v_row + pass * v_step : value_bytes, bytes);
+      }
+    } else {
+      // any block size: every row looks its own block up
+#pragma unroll
+      for (int pass = 0; pass < Tile::kPasses; ++pass) {
+        const uint32_t row = copy_row + pass * Tile::kRowsPerPass;
+        const uint32_t token = token0 + row;
+        const bool live = token < part_end;
+        const uint8_t* k_row = key_bytes;
+        const uint8_t* v_row = value_bytes;
+        if (live) {
+          const uint32_t block = clamp_block(__ldg(table + token / p.block_size), p.num_blocks);
+          const uint32_t page = token % p.block_size;
+          k_row = key_bytes + ((uint64_t)block * p.k_block + (uint64_t)page * p.k_page) * kElem + k_head_offset;
+          v_row = value_bytes + ((uint64_t)block * p.v_block + (uint64_t)page * p.v_page) * kElem + v_head_offset;
+        }
+        cp_async_16(stage + swizzled<Tile::kSegs>(row, copy_col), k_row, live ? 16u : 0u);
+        cp_async_16(stage + Tile::kTileBytes + swizzled<Tile::kSegs>(row, copy_col), v_row, live ? 16u : 0u);
+      }
+    }
+  };
+
+#pragma unroll
+  for (int s = 0; s < Tile::kStages - 1; ++s) {
+    if ((uint32_t)s < my_chunks) issue_chunk(s);
+    cp_async_commit();
+  }
+
+  // ldmatrix lane roles
+  const uint32_t ld_row_a = (lane & 7u) + ((lane >> 3) & 1u) * 8u;  // matrices 0..3 = (r0,c0)(r8,c0)(r0,c1)(r8,c1)
+  const uint32_t ld_col_a = lane >> 4;
+  const uint32_t ld_row_t = (lane & 7u) + (lane >> 4) * 8u;         // matrices 0..3 = (r0,c0)(r0,c1)(r8,c0)(r8,c1)
+  const uint32_t ld_col_t = (lane >> 3) & 1u;
+
+  for (uint32_t i = 0; i < my_chunks; ++i) {
+    cp_async_wait<Tile::kStages - 2>();
+    __syncwarp();
+    {
+      const uint32_t next = i + Tile::kStages - 1;
+      if (next < my_chunks) issue_chunk(next);
+      cp_async_commit();
+    }
+    const uint32_t stage = smem_base + (i % Tile::kStages) * Tile::kStageBytes;
+    const uint32_t k_tile = stage;
+    const uint32_t v_tile = stage + Tile::kTileBytes;
+    const uint32_t token0 = part_begin + (warp + i * kMmaWarps) * 16u;
+    const uint32_t live_rows = part_end - token0;  // >= 1; rows beyond it are zero filled
+
+    // ---- S^T = K . Q^T ----------------------------------------------------
+    float s[kNT][4];
+#pragma unroll
+    for (int nt = 0; nt < kNT; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f;
+
+    if constexpr (!kFp8) {
+#pragma unroll
+      for (int ks = 0; ks < kKSteps; ++ks) {
+        uint32_t a[4];
+        ldmatrix_x4(a, k_tile + swizzled<Tile::kSegs>(ld_row_a, 2 * ks + ld_col_a));
+#pragma unroll
+        for (int nt = 0; nt < kNT; ++nt) {
+          if constexpr (kBf16Mma) mma_16816_bf16(s[nt], a, qf[nt][ks][0], qf[nt][ks][1]);
+          else mma_16816_f16(s[nt], a, qf[nt][ks][0], qf[nt][ks][1]);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int pair = 0; pair < kKSteps / 2; ++pair) {
+        uint32_t r[4];
+        ldmatrix_x4(r, k_tile + swizzled<Tile::kSegs>(ld_row_a, 2 * pair + ld_col_a));
+        uint32_t a[4];
+        e4m3x4_to_f16x2x2(r[0], a[0], a[2]);
+        e4m3x4_to_f16x2x2(r[1], a[1], a[3]);
+#pragma unroll
+        for (int nt = 0; nt < kNT; ++nt) mma_16816_f16(s[nt], a, qf[nt][2 * pair][0], qf[nt][2 * pair][1]);
+        e4m3x4_to_f16x2x2(r[2], a[0], a[2]);
+        e4m3x4_to_f16x2x2(r[3], a[1], a[3]);
+#pragma unroll
+        for (int nt = 0; nt < kNT; ++nt) mma_16816_f16(s[nt], a, qf[nt][2 * pair + 1][0], qf[nt][2 * pair + 1][1]);
+      }
+    }
+
+    // ---- online softmax over this chunk's 16 tokens -----------------------
+    uint32_t pb[kNT][2];
+#pragma unroll
+    for (int nt = 0; nt < kNT; ++nt) {
+      const bool low_live = g < live_rows;
+      const bool high_live = (g + 8u) < live_rows;
+      const float s0 = low_live ? s[nt][0] * score_scale : -INFINITY;
+      const float s1 = low_live ? s[nt][1] * score_scale : -INFINITY;
+      const float s2 = high_live ? s[nt][2] * score_scale : -INFINITY;
+      const float s3 = high_live ? s[nt][3] * score_scale : -INFINITY;
+      float max0 = fmaxf(s0, s2), max1 = fmaxf(s1, s3);
+#pragma unroll
+      for (int offset = 4; offset < 32; offset <<= 1) {
+        max0 = fmaxf(max0, __shfl_xor_sync(0xffffffffu, max0, offset));
+        max1 = fmaxf(max1, __shfl_xor_sync(0xffffffffu, max1, offset));
+      }
+      const float new0 = fmaxf(row_max[nt][0], max0);
+      const float new1 = fmaxf(row_max[nt][1], max1);
+      const float alpha0 = fast_exp2(row_max[nt][0] - new0);
+      const float alpha1 = fast_exp2(row_max[nt][1] - new1);
+      row_max[nt][0] = new0;
+      row_max[nt][1] = new1;
+      const float p0 = fast_exp2(s0 - new0), p1 = fast_exp2(s1 - new1);
+      const float p2 = fast_exp2(s2 - new0), p3 = fast_exp2(s3 - new1);
+      row_sum[nt][0] = row_sum[nt][0] * alpha0 + (p0 + p2);
+      row_sum[nt][1] = row_sum[nt][1] * alpha1 + (p1 + p3);
+#pragma unroll
+      for (int mt = 0; mt < kKSteps; ++mt) {
+        o[nt][mt][0] *= alpha0;
+        o[nt][mt][1] *= alpha1;
+        o[nt][mt][2] *= alpha0;
+        o[nt][mt][3] *= alpha1;
+      }
+      if constexpr (kBf16Mma) {
+        pb[nt][0] = movmatrix_trans(pack_bf16x2(p0, p1));
+        pb[nt][1] = movmatrix_trans(pack_bf16x2(p2, p3));
+      } else {
+        pb[nt][0] = movmatrix_trans(pack_f16x2(p0, p1));
+        pb[nt][1] = movmatrix_trans(pack_f16x2(p2, p3));
+      }
+    }
+
+    // ---- O^T += V^T . P^T ---------------------------------------------------
+    if constexpr (!kFp8) {
+#pragma unroll
+      for (int mt = 0; mt < kKSteps; ++mt) {
+        uint32_t a[4];
+        ldmatrix_x4_trans(a, v_tile + swizzled<Tile::kSegs>(ld_row_t, 2 * mt + ld_col_t));
+#pragma unroll
+        for (int nt = 0; nt < kNT; ++nt) {
+          if constexpr (kBf16Mma) mma_16816_bf16(o[nt][mt], a, pb[nt][0], pb[nt][1]);
+          else mma_16816_f16(o[nt][mt], a, pb[nt][0], pb[nt][1]);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int pair = 0; pair < kKSteps / 2; ++pair) {
+        // matrices: (tokens 0-7, col c)(tokens 8-15, col c)(tokens 0-7, col c+1)(tokens 8-15, col c+1)
+        uint32_t r[4];
+        ldmatrix_x4_trans(r, v_tile + swizzled<Tile::kSegs>(ld_row_a, 2 * pair + ld_col_a));
+        uint32_t a[4];
+        e4m3x4_to_f16x2x2(__byte_perm(r[0], 0u, 0x3120u), a[0], a[1]);
+        e4m3x4_to_f16x2x2(__byte_perm(r[1], 0u, 0x3120u), a[2], a[3]);
+#pragma unroll
+        for (int nt = 0; nt < kNT; ++nt) mma_16816_f16(o[nt][2 * pair], a, pb[nt][0], pb[nt][1]);
+        e4m3x4_to_f16x2x2(__byte_perm(r[2], 0u, 0x3120u), a[0], a[1]);
+        e4m3x4_to_f16x2x2(__byte_perm(r[3], 0u, 0x3120u), a[2], a[3]);
+#pragma unroll
+        for (int nt = 0; nt < kNT; ++nt) mma_16816_f16(o[nt][2 * pair + 1], a, pb[nt][0], pb[nt][1]);
+      }
+    }
+  }
+  cp_async_wait<0>();
+
+  // ---- finish the per-warp sums, then merge the four warps ----------------
+#pragma unroll
+  for (int nt = 0; nt < kNT; ++nt) {
+#pragma unroll
+    for (int offset = 4; offset < 32; offset <<= 1) {
+      row_sum[nt][0] += __shfl_xor_sync(0xffffffffu, row_sum[nt][0], offset);
+      row_sum[nt][1] += __shfl_xor_sync(0xffffffffu, row_sum[nt][1], offset);
+    }
+  }
+  __syncthreads();  // every warp is done with its ring; reuse the memory
+
+  constexpr int kORow = kD + 4;
+  float* merge_o = reinterpret_cast<float*>(smem);                    // [warps][kHeads][kORow]
+  float* merge_max = merge_o + kMmaWarps * kHeads * kORow;            // [warps][kHeads]
+  float* merge_sum = merge_max + kMmaWarps * kHeads;                  // [warps][kHeads]
+#pragma unroll
+  for (int nt = 0; nt < kNT; ++nt) {
+    const uint32_t head0 = nt * 8 + 2 * t;
+    float* base0 = merge_o + ((size_t)warp * kHeads + head0) * kORow;
+    float* base1 = base0 + kORow;
+#pragma unroll
+    for (int mt = 0; mt < kKSteps; ++mt) {
+      const uint32_t dv_a = kFp8 ? mt * 16 + 2 * g : mt * 16 + g;
+      const uint32_t dv_b = kFp8 ? dv_a + 1 : dv_a + 8;
+      base0[dv_a] = o[nt][mt][0];
+      base1[dv_a] = o[nt][mt][1];
+      base0[dv_b] = o[nt][mt][2];
+      base1[dv_b] = o[nt][mt][3];
+    }
+    if (g == 0) {
+      merge_max[warp * kHeads + head0] = row_max[nt][0];
+      merge_max[warp * kHeads + head0 + 1] = row_max[nt][1];
+      merge_sum[warp * kHeads + head0] = row_sum[nt][0];
+      merge_sum[warp * kHeads + head0 + 1] = row_sum[nt][1];
+    }
+  }
+  __syncthreads();
+
+  float value_scale = 1.0f;
+  if constexpr (kFp8) value_scale = p.value_scales[(uint64_t)kv_head * p.scale_stride];
+  const uint32_t live_heads = min((uint32_t)kHeads, p.group - first_head);
+  const bool final_rows = n_parts == 1;
+  const uint32_t stride = state_stride(kD);
+  for (uint32_t index = threadIdx.x; index < live_heads * kD; index += kMmaThreads) {
+    const uint32_t head = index / kD;
+    const uint32_t dv = index % kD;
+    float top = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kMmaWarps; ++w) top = fmaxf(top, merge_max[w * kHeads + head]);
+    float acc = 0.0f, total = 0.0f;
+    if (top > -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < kMmaWarps; ++w) {
+        const float factor = fast_exp2(merge_max[w * kHeads + head] - top);
+        acc += merge_o[((size_t)w * kHeads + head) * kORow + dv] * factor;
+        total += merge_sum[w * kHeads + head] * factor;
+      }
+    }
+    acc *= value_scale;
+    const uint64_t query_row = (uint64_t)seq * p.query_heads + (uint64_t)kv_head * p.group + first_head + head;
+    if (final_rows && !p.emit_state) {
+      const float result = total > 0.0f ? acc / total : 0.0f;
+      QT* out = static_cast<QT*>(p.output) + query_row * kD;
+      if constexpr (std::is_same<QT, __nv_bfloat16>::value) out[dv] = __float2bfloat16_rn(result);
+      else out[dv] = __float2half_rn(result);
+    } else {
+      float* state = final_rows ? static_cast<float*>(p.output) + query_row * stride
+                                : p.partials + (query_row * p.max_partitions + part) * stride;
+      state[dv] = acc;
+      if (dv == 0) {
+        state[kD] = top * kLn2;
+        state[kD + 1] = total;
+      }
+    }
+  }
+}
+
+}  // namespace loom_decode

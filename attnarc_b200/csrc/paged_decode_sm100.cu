@@ -1,0 +1,663 @@
+// Paged MQA/GQA decode attention for sm_100a: route selection, the scalar
+// fallback kernel, the log-sum-exp merge kernel and the exported symbols.
+//
+// Replaces crates/loom-cuda-sys/cuda/src/paged_decode_attention.cu behind the
+// same `loom_cuda_paged_decode_attention_*` symbols (host gate :988-1152,
+// split-K sizing :89-162,1156-1166, merge kernel :749-853) and adds the
+// strided / FP8-cache / partial-state entry points declared in
+// include/loom_launch.h.
+//
+// Three kernels:
+//   decode_mma_kernel      (decode_mma.cuh) 16-bit queries, head size 64 or
+//                          128, 16-byte aligned cache rows: the fast path.
+//   decode_scalar_kernel   everything else (F32, odd head sizes, unaligned
+//                          views): one query head per CTA, CUDA cores.
+//   merge_states_kernel    second, light kernel: combines the partial
+//                          (O, max, sum) states of the KV partitions of a
+//                          sequence, or of several GPUs.
+// A sequence that fits one partition is finished by the first kernel, so the
+// merge kernel only touches the sequences that were actually split.
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cmath>
+#include <cstdint>
+#include <limits>
+#include <type_traits>
+
+#include "../../include/loom_launch.h"
+#include "decode_common.cuh"
+#include "decode_mma.cuh"
+
+namespace loom_decode {
+
+// ============================================================ scalar path
+
+constexpr int kScalarWarps = 4;
+constexpr int kScalarThreads = kScalarWarps * 32;
+constexpr int kScalarMaxValueRegs = 16;  // value_head_size <= 512
+
+template <typename T>
+__device__ __forceinline__ float widen(T value);
+template <>
+__device__ __forceinline__ float widen<float>(float value) { return value; }
+template <>
+__device__ __forceinline__ float widen<__half>(__half value) { return __half2float(value); }
+template <>
+__device__ __forceinline__ float widen<__nv_bfloat16>(__nv_bfloat16 value) { return __bfloat162float(value); }
+template <>
+__device__ __forceinline__ float widen<uint8_t>(uint8_t value) {
+  // E4M3 byte -> F16 (exact) -> F32
+  const __half_raw raw = __nv_cvt_fp8_to_halfraw(value, __NV_E4M3);
+  return __half2float(__half(raw));
+}
+
+template <typename T>
+__device__ __forceinline__ void narrow_store(T* out, float value);
+template <>
+__device__ __forceinline__ void narrow_store<float>(float* out, float value) { *out = value; }
+template <>
+__device__ __forceinline__ void narrow_store<__half>(__half* out, float value) { *out = __float2half_rn(value); }
+template <>
+__device__ __forceinline__ void narrow_store<__nv_bfloat16>(__nv_bfloat16* out, float value) {
+  *out = __float2bfloat16_rn(value);
+}
+
+__device__ __forceinline__ float warp_sum(float value) {
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) value += __shfl_xor_sync(0xffffffffu, value, offset);
+  return value;
+}
+
+__device__ __forceinline__ float warp_max(float value) {
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) value = fmaxf(value, __shfl_xor_sync(0xffffffffu, value, offset));
+  return value;
+}
+
+// One CTA per (sequence, partition, query head); each warp walks every fourth
+// token with a lane-strided dot product and keeps its own online softmax.
+template <typename QT, typename CT>
+__global__ void __launch_bounds__(kScalarThreads) decode_scalar_kernel(const DecodeParams p) {
+  constexpr bool kFp8 = std::is_same<CT, uint8_t>::value;
+  extern __shared__ __align__(16) float scalar_smem[];
+  float* q_shared = scalar_smem;                                 // [head_size]
+  float* merge_o = q_shared + p.head_size;                       // [warps][value_head_size]
+  float* merge_max = merge_o + kScalarWarps * p.value_head_size; // [warps]
+  float* merge_sum = merge_max + kScalarWarps;                   // [warps]
+
+  const uint32_t warp = threadIdx.x >> 5;
+  const uint32_t lane = threadIdx.x & 31u;
+  const uint32_t seq = blockIdx.x / p.max_partitions;
+  const uint32_t part = blockIdx.x % p.max_partitions;
+  const uint32_t query_head = blockIdx.y;
+  const uint32_t kv_head = query_head / p.group;
+
+  const uint32_t length = clamp_length(p.sequence_lengths[seq], p.max_sequence_length);
+  const uint32_t part_begin = part * p.partition_tokens;
+  if (part_begin >= length && part != 0) return;
+  const uint32_t part_end = min(length, part_begin + p.partition_tokens);
+  const uint32_t n_parts = length == 0 ? 1u : (length + p.partition_tokens - 1) / p.partition_tokens;
+
+  const QT* query = static_cast<const QT*>(p.query) + (uint64_t)seq * p.q_token + (uint64_t)query_head * p.q_head;
+  for (uint32_t d = threadIdx.x; d < p.head_size; d += kScalarThreads) q_shared[d] = widen<QT>(query[d]);
+  __syncthreads();
+
+  const CT* keys = static_cast<const CT*>(p.key_cache);
+  const CT* values = static_cast<const CT*>(p.value_cache);
+  const int32_t* table = p.block_tables + (uint64_t)seq * p.max_blocks_per_sequence;
+  float score_scale = p.scale_log2;
+  if (kFp8) score_scale *= p.key_scales[(uint64_t)kv_head * p.scale_stride];
+
+  float running_max = -INFINITY, running_sum = 0.0f;
+  float acc[kScalarMaxValueRegs];
+#pragma unroll
+  for (int j = 0; j < kScalarMaxValueRegs; ++j) acc[j] = 0.0f;
+
+  for (uint32_t token = part_begin + warp; token < part_end; token += kScalarWarps) {
+    const uint32_t block = clamp_block(__ldg(table + token / p.block_size), p.num_blocks);
+    const uint32_t page = token % p.block_size;
+    const CT* k_row = keys + (uint64_t)block * p.k_block + (uint64_t)page * p.k_page + (uint64_t)kv_head * p.k_head;
+    const CT* v_row = values + (uint64_t)block * p.v_block + (uint64_t)page * p.v_page + (uint64_t)kv_head * p.v_head;
+    float dot = 0.0f;
+    for (uint32_t d = lane; d < p.head_size; d += 32) dot = fmaf(q_shared[d], widen<CT>(k_row[d]), dot);
+    const float score = warp_sum(dot) * score_scale;
+    const float new_max = fmaxf(running_max, score);
+    const float alpha = exp2f(running_max - new_max);
+    const float weight = exp2f(score - new_max);
+    running_max = new_max;
+    running_sum = running_sum * alpha + weight;
+#pragma unroll
+    for (int j = 0; j < kScalarMaxValueRegs; ++j) {
+      const uint32_t dv = lane + 32 * j;
+      if (dv < p.value_head_size) acc[j] = acc[j] * alpha + weight * widen<CT>(v_row[dv]);
+    }
+  }
+
+#pragma unroll
+  for (int j = 0; j < kScalarMaxValueRegs; ++j) {
+    const uint32_t dv = lane + 32 * j;
+    if (dv < p.value_head_size) merge_o[warp * p.value_head_size + dv] = acc[j];
+  }
+  if (lane == 0) {
+    merge_max[warp] = running_max;
+    merge_sum[warp] = running_sum;
+  }
+  __syncthreads();
+
+  float top = -INFINITY;
+#pragma unroll
+  for (int w = 0; w < kScalarWarps; ++w) top = fmaxf(top, merge_max[w]);
+  float factor[kScalarWarps];
+  float total = 0.0f;
+#pragma unroll
+  for (int w = 0; w < kScalarWarps; ++w) {
+    factor[w] = top > -INFINITY ? exp2f(merge_max[w] - top) : 0.0f;
+    total += merge_sum[w] * factor[w];
+  }
+  float value_scale = 1.0f;
+  if (kFp8) value_scale = p.value_scales[(uint64_t)kv_head * p.scale_stride];
+  const bool final_rows = n_parts == 1;
+  const uint32_t stride = state_stride(p.value_head_size);
+  const uint64_t query_row = (uint64_t)seq * p.query_heads + query_head;
+  for (uint32_t dv = threadIdx.x; dv < p.value_head_size; dv += kScalarThreads) {
+    float sum = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kScalarWarps; ++w) sum += merge_o[w * p.value_head_size + dv] * factor[w];
+    sum *= value_scale;
+    if (final_rows && !p.emit_state) {
+      narrow_store<QT>(static_cast<QT*>(p.output) + query_row * p.value_head_size + dv,
+                       total > 0.0f ? sum / total : 0.0f);
+    } else {
+      float* state = final_rows ? static_cast<float*>(p.output) + query_row * stride
+                                : p.partials + (query_row * p.max_partitions + part) * stride;
+      state[dv] = sum;
+      if (dv == 0) {
+        state[p.value_head_size] = top * kLn2;
+        state[p.value_head_size + 1] = total;
+      }
+    }
+  }
+}
+
+// ============================================================= merge kernel
+
+constexpr int kMergeThreads = 128;
+
+__device__ __forceinline__ float block_reduce(float value, bool take_max, float* scratch) {
+  value = take_max ? warp_max(value) : warp_sum(value);
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+  __syncthreads();  // scratch may still be read from the previous reduction
+  if (lane == 0) scratch[warp] = value;
+  __syncthreads();
+  float out = scratch[0];
+#pragma unroll
+  for (int w = 1; w < kMergeThreads / 32; ++w) out = take_max ? fmaxf(out, scratch[w]) : out + scratch[w];
+  return out;
+}
+
+// One CTA per output row. Part `i` of row `r` lives at
+// states + r*row_stride + i*part_stride. With sequence_lengths the part count
+// is ceil(length / partition_tokens) and rows with a single part are skipped
+// (the decode kernel finished them); without, `fixed_parts` is used.
+template <typename OT>
+__global__ void __launch_bounds__(kMergeThreads)
+merge_states_kernel(const float* __restrict__ states, uint64_t row_stride, uint64_t part_stride,
+                    uint32_t value_head_size, uint32_t fixed_parts,
+                    const int32_t* __restrict__ sequence_lengths, uint32_t rows_per_sequence,
+                    uint32_t partition_tokens, uint32_t max_sequence_length, void* output,
+                    uint32_t emit_state) {
+  __shared__ float scratch[kMergeThreads / 32];
+  const uint32_t row = blockIdx.x;
+  uint32_t parts = fixed_parts;
+  if (sequence_lengths != nullptr) {
+    const uint32_t length = clamp_length(sequence_lengths[row / rows_per_sequence], max_sequence_length);
+    parts = (length + partition_tokens - 1) / partition_tokens;
+    if (parts <= 1) return;
+  }
+  const float* base = states + (uint64_t)row * row_stride;
+
+  float top = -INFINITY;
+  for (uint32_t i = threadIdx.x; i < parts; i += kMergeThreads) {
+    const float* state = base + (uint64_t)i * part_stride;
+    if (state[value_head_size + 1] > 0.0f) top = fmaxf(top, state[value_head_size]);
+  }
+  top = block_reduce(top, true, scratch);
+
+  float total = 0.0f;
+  if (top > -INFINITY) {
+    for (uint32_t i = threadIdx.x; i < parts; i += kMergeThreads) {
+      const float* state = base + (uint64_t)i * part_stride;
+      const float sum = state[value_head_size + 1];
+      if (sum > 0.0f) total += sum * exp2f((state[value_head_size] - top) * kLog2e);
+    }
+  }
+  total = block_reduce(total, false, scratch);
+
+  for (uint32_t dv = threadIdx.x; dv < value_head_size; dv += kMergeThreads) {
+    float acc = 0.0f;
+    if (top > -INFINITY) {
+      for (uint32_t i = 0; i < parts; ++i) {
+        const float* state = base + (uint64_t)i * part_stride;
+        if (state[value_head_size + 1] > 0.0f) {
+          acc += state[dv] * exp2f((state[value_head_size] - top) * kLog2e);
+        }
+      }
+    }
+    if (emit_state) {
+      float* out = static_cast<float*>(output) + (uint64_t)row * state_stride(value_head_size);
+      out[dv] = acc;
+      if (dv == 0) {
+        out[value_head_size] = top;
+        out[value_head_size + 1] = total;
+      }
+    } else {
+      narrow_store<OT>(static_cast<OT*>(output) + (uint64_t)row * value_head_size + dv,
+                       total > 0.0f ? acc / total : 0.0f);
+    }
+  }
+}
+
+// ================================================================= host
+
+thread_local const char* g_last_route = "none";
+
+bool aligned16(const void* pointer) { return (reinterpret_cast<uintptr_t>(pointer) & 15u) == 0; }
+
+// Raises a kernel's dynamic shared memory limit once per device.
+template <typename Kernel>
+cudaError_t ensure_smem(Kernel kernel, int bytes, std::atomic<uint64_t>& done_mask) {
+  int device = 0;
+  cudaError_t status = cudaGetDevice(&device);
+  if (status != cudaSuccess) return status;
+  const uint64_t bit = 1ull << (device & 63);
+  if (device < 64 && (done_mask.load(std::memory_order_acquire) & bit)) return cudaSuccess;
+  status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (status == cudaSuccess && device < 64) done_mask.fetch_or(bit, std::memory_order_release);
+  return status;
+}
+
+template <typename QT, bool kFp8, int kD, int kNT>
+int launch_mma(const DecodeParams& p, cudaStream_t stream) {
+  static std::atomic<uint64_t> configured{0};
+  constexpr int kBytes = mma_smem_bytes<kFp8, kD, kNT>();
+  auto kernel = decode_mma_kernel<QT, kFp8, kD, kNT>;
+  if (ensure_smem(kernel, kBytes, configured) != cudaSuccess) return LOOM_CUDA_LAUNCH_ERROR;
+  const uint32_t head_chunks = (p.group + 8 * kNT - 1) / (8 * kNT);
+  const dim3 grid(p.sequences * p.max_partitions, p.kv_heads * head_chunks, 1);
+  kernel<<<grid, kMmaThreads, kBytes, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? LOOM_CUDA_SUCCESS : LOOM_CUDA_LAUNCH_ERROR;
+}
+
+template <typename QT, bool kFp8>
+int launch_mma_shape(const DecodeParams& p, cudaStream_t stream) {
+  const bool wide = p.group > 8;
+  if (p.head_size == 128) {
+    return wide ? launch_mma<QT, kFp8, 128, 2>(p, stream) : launch_mma<QT, kFp8, 128, 1>(p, stream);
+  }
+  return wide ? launch_mma<QT, kFp8, 64, 2>(p, stream) : launch_mma<QT, kFp8, 64, 1>(p, stream);
+}
+
+template <typename QT, typename CT>
+int launch_scalar(const DecodeParams& p, cudaStream_t stream) {
+  const size_t bytes =
+      ((size_t)p.head_size + (size_t)kScalarWarps * p.value_head_size + 2 * kScalarWarps) * sizeof(float);
+  if (bytes > 48 * 1024) return LOOM_CUDA_UNSUPPORTED;
+  const dim3 grid(p.sequences * p.max_partitions, p.query_heads, 1);
+  decode_scalar_kernel<QT, CT><<<grid, kScalarThreads, bytes, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? LOOM_CUDA_SUCCESS : LOOM_CUDA_LAUNCH_ERROR;
+}
+
+bool mma_route_fits(const LoomDecodeArgs& a, bool fp8) {
+  if (a.dtype != 1 && a.dtype != 2) return false;
+  if (a.head_size != a.value_head_size || (a.head_size != 64 && a.head_size != 128)) return false;
+  const uint64_t elem = fp8 ? 1 : 2;
+  const auto row_ok = [elem](uint64_t stride) { return (stride * elem) % 16 == 0; };
+  if (!aligned16(a.query) || !aligned16(a.key_cache) || !aligned16(a.value_cache)) return false;
+  if ((a.query_token_stride * 2) % 16 != 0 || (a.query_head_stride * 2) % 16 != 0) return false;
+  if (!row_ok(a.key_block_stride) || !row_ok(a.key_page_stride) || !row_ok(a.key_head_stride) ||
+      !row_ok(a.value_block_stride) || !row_ok(a.value_page_stride) || !row_ok(a.value_head_stride)) {
+    return false;
+  }
+  const uint32_t group = a.query_heads / a.kv_heads;
+  const uint32_t heads_per_cta = group > 8 ? 16 : 8;
+  const uint64_t grid_y = (uint64_t)a.kv_heads * ((group + heads_per_cta - 1) / heads_per_cta);
+  return grid_y <= 65535;
+}
+
+uint32_t ceil_div(uint32_t a, uint32_t b) { return (a + b - 1) / b; }
+
+// Partition length the library picks when the caller does not: the longest of
+// {2048, ..., 64} that still yields enough CTAs to fill 148 SMs a few times
+// over, assuming every sequence were as long as the maximum.
+uint32_t default_partition_tokens(uint32_t sequences, uint32_t kv_heads, uint32_t max_sequence_length) {
+  constexpr uint64_t kWantedCtas = 148ull * 2 * 4;
+  const uint64_t heads = (uint64_t)sequences * kv_heads;
+  for (uint32_t tokens = 2048; tokens > 64; tokens >>= 1) {
+    if (heads * ceil_div(max_sequence_length, tokens) >= kWantedCtas) return tokens;
+  }
+  return 64;
+}
+
+uint64_t workspace_elements(uint32_t sequences, uint32_t query_heads, uint32_t value_head_size,
+                            uint32_t max_sequence_length, uint32_t partition_tokens) {
+  if (sequences == 0 || query_heads == 0 || value_head_size == 0 || max_sequence_length == 0 ||
+      partition_tokens == 0 || partition_tokens % 16 != 0) {
+    return 0;
+  }
+  uint64_t total = (uint64_t)sequences * query_heads;  // < 2^64
+  const uint64_t parts = ceil_div(max_sequence_length, partition_tokens);
+  const uint64_t per_row = parts * ((uint64_t)value_head_size + 2);
+  if (per_row != 0 && total > std::numeric_limits<uint64_t>::max() / per_row) return 0;
+  return total * per_row;
+}
+
+bool product_fits_u64(std::initializer_list<uint64_t> dims) {
+  uint64_t product = 1;
+  for (uint64_t d : dims) {
+    if (d != 0 && product > std::numeric_limits<uint64_t>::max() / d) return false;
+    product *= d;
+  }
+  return true;
+}
+
+int launch_decode(const LoomDecodeArgs& a) {
+  const bool fp8 = a.cache_encoding == LOOM_CUDA_KV_CACHE_FP8_E4M3;
+  // The argument rules of the reference launcher
+  // (paged_decode_attention.cu:1018-1049) without its 1024-token cap.
+  if (a.dtype > 2 || a.cache_encoding > 1 || a.query == nullptr || a.key_cache == nullptr ||
+      a.value_cache == nullptr || a.block_tables == nullptr || a.sequence_lengths == nullptr ||
+      a.output == nullptr || a.sequences == 0 || a.query_heads == 0 || a.kv_heads == 0 ||
+      a.head_size == 0 || a.value_head_size == 0 || a.num_blocks == 0 || a.block_size == 0 ||
+      a.max_blocks_per_sequence == 0 || a.query_heads % a.kv_heads != 0 ||
+      a.max_sequence_length == 0 || a.max_sequence_length > (1u << 30) ||
+      a.max_sequence_length > (uint64_t)a.block_size * a.max_blocks_per_sequence ||
+      !std::isfinite(a.scale) || a.scale <= 0.0f ||
+      (fp8 && (a.key_scales == nullptr || a.value_scales == nullptr || a.scale_stride > 1)) ||
+      !product_fits_u64({a.sequences, a.query_heads, a.head_size}) ||
+      !product_fits_u64({a.sequences, a.query_heads, a.value_head_size}) ||
+      !product_fits_u64({a.num_blocks, a.block_size, a.kv_heads, a.head_size}) ||
+      !product_fits_u64({a.num_blocks, a.block_size, a.kv_heads, a.value_head_size}) ||
+      !product_fits_u64({a.sequences, a.max_blocks_per_sequence}) ||
+      a.key_block_stride == 0 || a.key_page_stride == 0 || a.key_head_stride == 0 ||
+      a.value_block_stride == 0 || a.value_page_stride == 0 || a.value_head_stride == 0 ||
+      ((a.query_token_stride == 0) != (a.query_head_stride == 0)) ||
+      (a.query_head_stride != 0 && a.query_head_stride < a.head_size)) {
+    return LOOM_CUDA_INVALID_ARGUMENT;
+  }
+
+  DecodeParams p{};
+  p.query = a.query;
+  p.key_cache = a.key_cache;
+  p.value_cache = a.value_cache;
+  p.key_scales = a.key_scales;
+  p.value_scales = a.value_scales;
+  p.block_tables = a.block_tables;
+  p.sequence_lengths = a.sequence_lengths;
+  p.output = a.output;
+  p.sequences = a.sequences;
+  p.query_heads = a.query_heads;
+  p.kv_heads = a.kv_heads;
+  p.group = a.query_heads / a.kv_heads;
+  p.head_size = a.head_size;
+  p.value_head_size = a.value_head_size;
+  p.num_blocks = a.num_blocks;
+  p.block_size = a.block_size;
+  p.max_blocks_per_sequence = a.max_blocks_per_sequence;
+  p.max_sequence_length = a.max_sequence_length;
+  p.scale_stride = fp8 ? a.scale_stride : 0;
+  p.emit_state = a.emit_state ? 1 : 0;
+  p.k_block = a.key_block_stride;
+  p.k_page = a.key_page_stride;
+  p.k_head = a.key_head_stride;
+  p.v_block = a.value_block_stride;
+  p.v_page = a.value_page_stride;
+  p.v_head = a.value_head_stride;
+  const bool dense_query = a.query_token_stride == 0 && a.query_head_stride == 0;
+  p.q_head = dense_query ? a.head_size : a.query_head_stride;
+  p.q_token = dense_query ? (uint64_t)a.query_heads * a.head_size : a.query_token_stride;
+  p.scale_log2 = a.scale * kLog2e;
+
+  const bool partitioned = a.workspace != nullptr || a.workspace_elements != 0;
+  if (partitioned) {
+    const uint32_t tokens = a.partition_tokens != 0
+                                ? a.partition_tokens
+                                : default_partition_tokens(a.sequences, a.kv_heads, a.max_sequence_length);
+    const uint64_t needed =
+        workspace_elements(a.sequences, a.query_heads, a.value_head_size, a.max_sequence_length, tokens);
+    if (a.workspace == nullptr || needed == 0 || a.workspace_elements < needed ||
+        (reinterpret_cast<uintptr_t>(a.workspace) & 3u) != 0) {
+      return LOOM_CUDA_INVALID_ARGUMENT;
+    }
+    p.partials = a.workspace;
+    p.partition_tokens = tokens;
+    p.max_partitions = ceil_div(a.max_sequence_length, tokens);
+  } else {
+    p.partials = nullptr;
+    p.partition_tokens = (a.max_sequence_length + 15u) & ~15u;
+    p.max_partitions = 1;
+  }
+  if ((uint64_t)p.sequences * p.max_partitions > 0x7fffffffull) return LOOM_CUDA_INVALID_ARGUMENT;
+
+  cudaStream_t stream = static_cast<cudaStream_t>(a.stream);
+  int status;
+  if (mma_route_fits(a, fp8)) {
+    g_last_route = fp8 ? "mma16-fp8" : "mma16";
+    if (a.dtype == 1) {
+      status = fp8 ? launch_mma_shape<__half, true>(p, stream) : launch_mma_shape<__half, false>(p, stream);
+    } else {
+      status = fp8 ? launch_mma_shape<__nv_bfloat16, true>(p, stream)
+                   : launch_mma_shape<__nv_bfloat16, false>(p, stream);
+    }
+  } else {
+    if (a.value_head_size > 32u * kScalarMaxValueRegs || a.query_heads > 65535u) return LOOM_CUDA_UNSUPPORTED;
+    g_last_route = fp8 ? "scalar-fp8" : "scalar";
+    switch (a.dtype) {
+      case 0:
+        status = fp8 ? launch_scalar<float, uint8_t>(p, stream) : launch_scalar<float, float>(p, stream);
+        break;
+      case 1:
+        status = fp8 ? launch_scalar<__half, uint8_t>(p, stream) : launch_scalar<__half, __half>(p, stream);
+        break;
+      default:
+        status = fp8 ? launch_scalar<__nv_bfloat16, uint8_t>(p, stream)
+                     : launch_scalar<__nv_bfloat16, __nv_bfloat16>(p, stream);
+        break;
+    }
+  }
+  if (status != LOOM_CUDA_SUCCESS || !partitioned || p.max_partitions <= 1) return status;
+
+  // Second kernel: merge the partitions of every sequence that had several.
+  const uint64_t rows = (uint64_t)p.sequences * p.query_heads;
+  if (rows > 0x7fffffffull) return LOOM_CUDA_INVALID_ARGUMENT;
+  const uint64_t part_stride = state_stride(p.value_head_size);
+  const uint64_t row_stride = part_stride * p.max_partitions;
+  const uint32_t grid = (uint32_t)rows;
+#define LOOM_MERGE(type)                                                                        \
+  merge_states_kernel<type><<<grid, kMergeThreads, 0, stream>>>(                               \
+      p.partials, row_stride, part_stride, p.value_head_size, 0u, p.sequence_lengths,          \
+      p.query_heads, p.partition_tokens, p.max_sequence_length, p.output, p.emit_state)
+  if (p.emit_state || a.dtype == 0) LOOM_MERGE(float);
+  else if (a.dtype == 1) LOOM_MERGE(__half);
+  else LOOM_MERGE(__nv_bfloat16);
+#undef LOOM_MERGE
+  return cudaGetLastError() == cudaSuccess ? LOOM_CUDA_SUCCESS : LOOM_CUDA_LAUNCH_ERROR;
+}
+
+// The reference ABI: dense-inner NHD caches, block stride free.
+int launch_reference_abi(uint32_t dtype, const void* query, const void* key_cache, const void* value_cache,
+                         const int32_t* block_tables, const int32_t* sequence_lengths, void* output,
+                         float* workspace, uint64_t workspace_elements, uint32_t sequences,
+                         uint32_t query_heads, uint32_t kv_heads, uint32_t head_size,
+                         uint32_t value_head_size, uint32_t num_blocks, uint32_t block_size,
+                         uint64_t key_block_stride, uint64_t value_block_stride,
+                         uint32_t max_blocks_per_sequence, uint32_t max_sequence_length, float scale,
+                         void* stream) {
+  // paged_decode_attention.cu:1035-1048: a block stride must cover one block.
+  const uint64_t key_block = (uint64_t)block_size * kv_heads * head_size;
+  const uint64_t value_block = (uint64_t)block_size * kv_heads * value_head_size;
+  if (key_block_stride < key_block || value_block_stride < value_block) return LOOM_CUDA_INVALID_ARGUMENT;
+  LoomDecodeArgs a{};
+  a.struct_size = sizeof(LoomDecodeArgs);
+  a.dtype = dtype;
+  a.cache_encoding = LOOM_CUDA_KV_CACHE_NATIVE;
+  a.query = query;
+  a.key_cache = key_cache;
+  a.value_cache = value_cache;
+  a.block_tables = block_tables;
+  a.sequence_lengths = sequence_lengths;
+  a.output = output;
+  a.workspace = workspace;
+  a.workspace_elements = workspace_elements;
+  a.sequences = sequences;
+  a.query_heads = query_heads;
+  a.kv_heads = kv_heads;
+  a.head_size = head_size;
+  a.value_head_size = value_head_size;
+  a.num_blocks = num_blocks;
+  a.block_size = block_size;
+  a.max_blocks_per_sequence = max_blocks_per_sequence;
+  a.max_sequence_length = max_sequence_length;
+  a.key_block_stride = key_block_stride;
+  a.key_page_stride = (uint64_t)kv_heads * head_size;
+  a.key_head_stride = head_size;
+  a.value_block_stride = value_block_stride;
+  a.value_page_stride = (uint64_t)kv_heads * value_head_size;
+  a.value_head_stride = value_head_size;
+  a.scale = scale;
+  a.stream = stream;
+  return launch_decode(a);
+}
+
+}  // namespace loom_decode
+
+// ================================================================ C ABI
+
+extern "C" const char* loom_cuda_status_string(int status) {
+  switch (status) {
+    case LOOM_CUDA_SUCCESS: return "success";
+    case LOOM_CUDA_INVALID_ARGUMENT: return "invalid argument";
+    case LOOM_CUDA_UNSUPPORTED: return "unsupported";
+    case LOOM_CUDA_LAUNCH_ERROR: return "CUDA launch error";
+    case LOOM_CUDA_UNAVAILABLE: return "CUDA unavailable";
+    default: return "unknown Loom CUDA status";
+  }
+}
+
+#define LOOM_DEFINE_DECODE(suffix, scalar, code)                                                   \
+  extern "C" int loom_cuda_paged_decode_attention_##suffix(                                        \
+      const scalar* query, const scalar* key_cache, const scalar* value_cache,                    \
+      const int32_t* block_tables, const int32_t* sequence_lengths, scalar* output,               \
+      uint32_t sequences, uint32_t query_heads, uint32_t kv_heads, uint32_t head_size,            \
+      uint32_t value_head_size, uint32_t num_blocks, uint32_t block_size,                         \
+      uint64_t key_block_stride, uint64_t value_block_stride, uint32_t max_blocks_per_sequence,   \
+      uint32_t max_sequence_length, float scale, void* stream) {                                  \
+    return loom_decode::launch_reference_abi(                                                     \
+        code, query, key_cache, value_cache, block_tables, sequence_lengths, output, nullptr, 0,  \
+        sequences, query_heads, kv_heads, head_size, value_head_size, num_blocks, block_size,     \
+        key_block_stride, value_block_stride, max_blocks_per_sequence, max_sequence_length,       \
+        scale, stream);                                                                           \
+  }                                                                                               \
+  extern "C" int loom_cuda_paged_decode_attention_split_k_##suffix(                                \
+      const scalar* query, const scalar* key_cache, const scalar* value_cache,                    \
+      const int32_t* block_tables, const int32_t* sequence_lengths, scalar* output,               \
+      float* workspace, uint64_t workspace_elements, uint32_t sequences, uint32_t query_heads,    \
+      uint32_t kv_heads, uint32_t head_size, uint32_t value_head_size, uint32_t num_blocks,       \
+      uint32_t block_size, uint64_t key_block_stride, uint64_t value_block_stride,                \
+      uint32_t max_blocks_per_sequence, uint32_t max_sequence_length, float scale,                \
+      void* stream) {                                                                             \
+    if (workspace == nullptr || workspace_elements == 0) return LOOM_CUDA_INVALID_ARGUMENT;       \
+    return loom_decode::launch_reference_abi(                                                     \
+        code, query, key_cache, value_cache, block_tables, sequence_lengths, output, workspace,   \
+        workspace_elements, sequences, query_heads, kv_heads, head_size, value_head_size,         \
+        num_blocks, block_size, key_block_stride, value_block_stride, max_blocks_per_sequence,    \
+        max_sequence_length, scale, stream);                                                      \
+  }
+
+LOOM_DEFINE_DECODE(f32, float, 0u)
+LOOM_DEFINE_DECODE(f16, uint16_t, 1u)
+LOOM_DEFINE_DECODE(bf16, uint16_t, 2u)
+
+extern "C" uint64_t loom_cuda_paged_decode_attention_split_k_workspace_elements(
+    uint32_t sequences, uint32_t query_heads, uint32_t kv_heads, uint32_t head_size,
+    uint32_t value_head_size, uint32_t max_sequence_length) {
+  if (sequences == 0 || query_heads == 0 || kv_heads == 0 || head_size == 0 || value_head_size == 0 ||
+      max_sequence_length == 0 || query_heads % kv_heads != 0) {
+    return 0;
+  }
+  const uint32_t tokens = loom_decode::default_partition_tokens(sequences, kv_heads, max_sequence_length);
+  if (max_sequence_length <= tokens) return 0;  // one partition: use the workspace-free entry point
+  return loom_decode::workspace_elements(sequences, query_heads, value_head_size, max_sequence_length, tokens);
+}
+
+extern "C" uint32_t loom_cuda_paged_decode_default_partition_tokens(uint32_t sequences, uint32_t kv_heads,
+                                                                    uint32_t max_sequence_length) {
+  if (sequences == 0 || kv_heads == 0 || max_sequence_length == 0) return 0;
+  return loom_decode::default_partition_tokens(sequences, kv_heads, max_sequence_length);
+}
+
+extern "C" uint64_t loom_cuda_paged_decode_workspace_elements(uint32_t sequences, uint32_t query_heads,
+                                                              uint32_t value_head_size,
+                                                              uint32_t max_sequence_length,
+                                                              uint32_t partition_tokens) {
+  return loom_decode::workspace_elements(sequences, query_heads, value_head_size, max_sequence_length,
+                                         partition_tokens);
+}
+
+extern "C" int loom_cuda_paged_decode_attention_ex(const LoomDecodeArgs* args) {
+  if (args == nullptr || args->struct_size != sizeof(LoomDecodeArgs)) return LOOM_CUDA_INVALID_ARGUMENT;
+  if (args->partition_tokens % 16 != 0) return LOOM_CUDA_INVALID_ARGUMENT;
+  return loom_decode::launch_decode(*args);
+}
+
+extern "C" int loom_cuda_merge_decode_states(const float* states, uint32_t parts, uint32_t rows,
+                                             uint32_t value_head_size, uint32_t out_dtype, void* output,
+                                             void* stream) {
+  using namespace loom_decode;
+  if (states == nullptr || output == nullptr || parts == 0 || rows == 0 || value_head_size == 0 ||
+      out_dtype > 2 || rows > 0x7fffffffu) {
+    return LOOM_CUDA_INVALID_ARGUMENT;
+  }
+  const uint64_t row_stride = state_stride(value_head_size);
+  const uint64_t part_stride = row_stride * rows;
+  cudaStream_t cuda_stream = static_cast<cudaStream_t>(stream);
+#define LOOM_MERGE(type)                                                                      \
+  merge_states_kernel<type><<<rows, kMergeThreads, 0, cuda_stream>>>(                        \
+      states, row_stride, part_stride, value_head_size, parts, nullptr, 1u, 1u, 0u, output, 0u)
+  if (out_dtype == 0) LOOM_MERGE(float);
+  else if (out_dtype == 1) LOOM_MERGE(__half);
+  else LOOM_MERGE(__nv_bfloat16);
+#undef LOOM_MERGE
+  return cudaGetLastError() == cudaSuccess ? LOOM_CUDA_SUCCESS : LOOM_CUDA_LAUNCH_ERROR;
+}
+
+extern "C" int loom_cuda_supports_paged_decode(uint32_t dtype, uint32_t cache_encoding, uint32_t sequences,
+                                               uint32_t query_heads, uint32_t kv_heads, uint32_t head_size,
+                                               uint32_t value_head_size, uint32_t num_blocks,
+                                               uint32_t block_size, uint32_t max_blocks_per_sequence,
+                                               uint32_t max_sequence_length, const char** reason) {
+  const char* why = nullptr;
+  if (dtype > 2) {
+    why = "B200 paged decode attention supports F32, FP16, and BF16 queries";
+  } else if (cache_encoding > 1) {
+    why = "B200 paged decode attention reads native or FP8 E4M3 caches";
+  } else if (sequences == 0 || query_heads == 0 || kv_heads == 0 || head_size == 0 ||
+             value_head_size == 0 || num_blocks == 0 || block_size == 0 ||
+             max_blocks_per_sequence == 0 || max_sequence_length == 0 || query_heads % kv_heads != 0) {
+    why = "paged decode attention contract is not well formed";
+  } else if (max_sequence_length > (1u << 30) ||
+             (uint64_t)sequences * query_heads > 0x7fffffffull || query_heads > 65535u) {
+    why = "paged decode attention shape exceeds the CUDA ABI";
+  } else if (value_head_size > 32u * loom_decode::kScalarMaxValueRegs &&
+             !(head_size == value_head_size && (head_size == 64 || head_size == 128))) {
+    why = "B200 paged decode attention supports value heads of at most 512 elements";
+  }
+  if (reason != nullptr) *reason = why != nullptr ? why : "supported";
+  return why == nullptr ? 1 : 0;
+}
+
+extern "C" const char* loom_cuda_last_decode_route(void) { return loom_decode::g_last_route; }

@@ -1,0 +1,458 @@
+"""PyTorch-facing operators of the paged-decode path.
+
+Same names, arguments and error behaviour as the reference's Python API
+(python/src/loom_kernels/ops/attention.py, ops/rope_kv.py, ops/telemetry.py),
+so its tests read the same against this package. The differences are
+additions: contexts are not capped at 1024 tokens, the decode accepts any cache
+stride order and FP8 E4M3 caches (``paged_decode_attention_ex``), and partial
+states can be produced and merged. torch is used for device memory and streams
+only; all work happens in ``libloom_cuda_bridge.so``.
+"""
+
+from __future__ import annotations
+
+import enum
+import math
+
+import torch
+
+from . import _native
+from ._native import BridgeError, check, library
+
+_DTYPE_CODES = {torch.float32: _native.F32, torch.float16: _native.F16, torch.bfloat16: _native.BF16}
+_DTYPE_NAMES = _DTYPE_CODES  # membership test used by the predicates
+
+
+class Operator(enum.IntEnum):
+    """Launch-counter ids (loom_cuda_bridge.h:28-40)."""
+
+    RMS_NORM = 0
+    ADD_RMS_NORM = 1
+    RMS_NORM_DYNAMIC_FP8 = 2
+    SILU_AND_MUL = 3
+    SILU_AND_MUL_DYNAMIC_FP8 = 4
+    ROPE_PAGED_KV_WRITE = 5
+    GREEDY_SAMPLE_LOGPROBS = 6
+    SELECTED_TOKEN_LOGPROBS = 7
+    MIN_P_FILTER = 8
+    PAGED_DECODE_ATTENTION = 9
+    GREEDY_SPECULATIVE_VERIFY = 10
+
+
+def launch_count(operator: Operator) -> int:
+    """Successful launches of one operator since the last reset."""
+    count = _native.u64(0)
+    check(library().loom_cuda_bridge_launch_count(int(operator), count), "launch count")
+    return int(count.value)
+
+
+def reset_launch_count(operator: Operator) -> None:
+    check(library().loom_cuda_bridge_reset_launch_count(int(operator)), "launch count reset")
+
+
+def last_decode_route() -> str:
+    """Kernel family chosen by the last decode launch on this thread."""
+    return library().loom_cuda_last_decode_route().decode()
+
+
+def _require_inference_tensors(*tensors: torch.Tensor) -> None:
+    for tensor in tensors:
+        if tensor.requires_grad:
+            raise ValueError("Loom operators are inference-only; detach tensors that require grad")
+
+
+def _stream(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _span(tensor: torch.Tensor) -> int:
+    """Elements from the first to one past the last addressed element."""
+    if tensor.numel() == 0:
+        return 0
+    return 1 + sum((size - 1) * stride for size, stride in zip(tensor.shape, tensor.stride()))
+
+
+def _has_dense_nhd_inner_strides(tensor: torch.Tensor) -> bool:
+    if tensor.dim() != 4:
+        return False
+    _, block_size, heads, width = tensor.shape
+    return bool(
+        tensor.stride(3) == 1
+        and tensor.stride(2) == width
+        and tensor.stride(1) == heads * width
+        and tensor.stride(0) >= block_size * heads * width
+    )
+
+
+# ------------------------------------------------------------------ decode
+
+def supports_paged_decode_attention(
+    query: torch.Tensor,
+    key_cache: torch.Tensor,
+    value_cache: torch.Tensor,
+    block_tables: torch.Tensor,
+    sequence_lengths: torch.Tensor,
+    *,
+    max_sequence_length: int,
+) -> bool:
+    """Whether the tensors fit the reference-shaped decode entry point."""
+    if (
+        query.dim() != 3 or key_cache.dim() != 4 or value_cache.dim() != 4
+        or block_tables.dim() != 2 or sequence_lengths.dim() != 1
+        or query.numel() == 0 or key_cache.numel() == 0 or value_cache.numel() == 0
+        or isinstance(max_sequence_length, bool) or not isinstance(max_sequence_length, int)
+    ):
+        return False
+    sequences, query_heads, head_size = query.shape
+    num_blocks, block_size, kv_heads, key_head_size = key_cache.shape
+    if not (
+        query.device.type == "cuda"
+        and all(t.device == query.device for t in (key_cache, value_cache, block_tables, sequence_lengths))
+        and query.dtype in _DTYPE_NAMES
+        and key_cache.dtype == query.dtype and value_cache.dtype == query.dtype
+        and block_tables.dtype == torch.int32 and sequence_lengths.dtype == torch.int32
+        and query.is_contiguous()
+        and _has_dense_nhd_inner_strides(key_cache) and _has_dense_nhd_inner_strides(value_cache)
+        and block_tables.is_contiguous() and sequence_lengths.is_contiguous()
+        and not query.requires_grad and not key_cache.requires_grad and not value_cache.requires_grad
+        and head_size == key_head_size
+        and tuple(value_cache.shape[:3]) == (num_blocks, block_size, kv_heads)
+        and value_cache.shape[3] > 0
+        and kv_heads > 0 and query_heads % kv_heads == 0
+        and block_tables.shape[0] == sequences and block_tables.shape[1] > 0
+        and sequence_lengths.shape[0] == sequences
+        and 0 < max_sequence_length <= block_tables.shape[1] * block_size
+    ):
+        return False
+    return bool(
+        library().loom_cuda_bridge_supports_paged_decode(
+            _DTYPE_CODES[query.dtype], _native.KV_CACHE_NATIVE, sequences, query_heads, kv_heads,
+            head_size, value_cache.shape[3], num_blocks, block_size, block_tables.shape[1],
+            max_sequence_length, 1.0,
+        )
+    )
+
+
+def _check_decode_tensors(query, key_cache, value_cache, block_tables, sequence_lengths, output,
+                          strided_query=False):
+    if query.dim() != 3 or key_cache.dim() != 4 or value_cache.dim() != 4:
+        raise RuntimeError("Loom paged decode expects query [B,Hq,D] and caches [blocks,block,Hkv,D]")
+    if block_tables.dim() != 2 or sequence_lengths.dim() != 1:
+        raise RuntimeError("Loom paged decode expects block_tables [B,max_blocks] and lengths [B]")
+    if query.device.type != "cuda" or any(
+        t.device != query.device for t in (key_cache, value_cache, block_tables, sequence_lengths, output)
+    ):
+        raise RuntimeError("Loom paged decode tensors must share one CUDA device")
+    if query.dtype not in _DTYPE_CODES:
+        raise RuntimeError("Loom paged decode supports float32, float16 and bfloat16 queries")
+    if block_tables.dtype != torch.int32 or sequence_lengths.dtype != torch.int32:
+        raise RuntimeError("Loom paged decode metadata must be int32")
+    query_ok = query.stride(2) == 1 if strided_query else query.is_contiguous()
+    if not (query_ok and output.is_contiguous() and block_tables.is_contiguous()
+            and sequence_lengths.is_contiguous()):
+        raise RuntimeError("Loom paged decode query, output and metadata must be contiguous")
+
+
+def decode_workspace_elements(query: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor,
+                              block_tables: torch.Tensor, *, max_sequence_length: int,
+                              scale: float = 1.0) -> int:
+    """F32 workspace elements the reference-shaped decode call expects (0 = none)."""
+    elements = _native.u64(0)
+    check(
+        library().loom_cuda_bridge_paged_decode_workspace_elements(
+            _DTYPE_CODES[query.dtype], query.shape[0], query.shape[1], key_cache.shape[2], query.shape[2],
+            value_cache.shape[3], key_cache.shape[0], key_cache.shape[1], block_tables.shape[1],
+            int(max_sequence_length), float(scale), elements,
+        ),
+        "paged decode workspace query",
+    )
+    return int(elements.value)
+
+
+def paged_decode_attention_out(
+    query: torch.Tensor,
+    key_cache: torch.Tensor,
+    value_cache: torch.Tensor,
+    block_tables: torch.Tensor,
+    sequence_lengths: torch.Tensor,
+    output: torch.Tensor,
+    *,
+    max_sequence_length: int,
+    scale: float | None = None,
+    workspace: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """Paged MQA/GQA decode into caller-owned output (dense-inner NHD caches)."""
+    _require_inference_tensors(query, key_cache, value_cache, output)
+    _check_decode_tensors(query, key_cache, value_cache, block_tables, sequence_lengths, output)
+    if not (_has_dense_nhd_inner_strides(key_cache) and _has_dense_nhd_inner_strides(value_cache)):
+        raise RuntimeError("Loom paged decode caches must be dense-inner NHD; use paged_decode_attention_ex")
+    if scale is None:
+        scale = query.shape[-1] ** -0.5
+    with torch.cuda.device(query.device):
+        needed = decode_workspace_elements(query, key_cache, value_cache, block_tables,
+                                           max_sequence_length=max_sequence_length, scale=scale)
+        if needed and (workspace is None or workspace.numel() != needed):
+            workspace = torch.empty(needed, device=query.device, dtype=torch.float32)
+        status = library().loom_cuda_bridge_paged_decode_attention(
+            _DTYPE_CODES[query.dtype], query.data_ptr(), query.numel(), key_cache.data_ptr(),
+            _span(key_cache), value_cache.data_ptr(), _span(value_cache), block_tables.data_ptr(),
+            block_tables.numel(), sequence_lengths.data_ptr(), sequence_lengths.numel(),
+            output.data_ptr(), output.numel(), workspace.data_ptr() if needed else None, needed,
+            query.shape[0], query.shape[1], key_cache.shape[2], query.shape[2], value_cache.shape[3],
+            key_cache.shape[0], key_cache.shape[1], key_cache.stride(0), value_cache.stride(0),
+            block_tables.shape[1], int(max_sequence_length), float(scale), _stream(query.device),
+        )
+    check(status, "paged decode attention")
+    return output
+
+
+def paged_decode_attention(
+    query: torch.Tensor,
+    key_cache: torch.Tensor,
+    value_cache: torch.Tensor,
+    block_tables: torch.Tensor,
+    sequence_lengths: torch.Tensor,
+    *,
+    max_sequence_length: int,
+    scale: float | None = None,
+) -> torch.Tensor:
+    """Paged MQA/GQA decode for one query token per sequence."""
+    if query.dim() != 3 or value_cache.dim() != 4:
+        raise ValueError("paged decode query/value cache must have ranks 3 and 4")
+    output = torch.empty((query.shape[0], query.shape[1], value_cache.shape[3]),
+                         device=query.device, dtype=query.dtype)
+    return paged_decode_attention_out(query, key_cache, value_cache, block_tables, sequence_lengths,
+                                      output, max_sequence_length=max_sequence_length, scale=scale)
+
+
+def decode_workspace_elements_ex(sequences: int, query_heads: int, kv_heads: int, value_head_size: int,
+                                 max_sequence_length: int, partition_tokens: int = 0) -> tuple[int, int]:
+    """(workspace elements, partition tokens) of a partitioned decode."""
+    elements, tokens = _native.u64(0), _native.u32(0)
+    check(
+        library().loom_cuda_bridge_paged_decode_workspace_elements_ex(
+            sequences, query_heads, kv_heads, value_head_size, max_sequence_length, partition_tokens,
+            elements, tokens,
+        ),
+        "paged decode workspace query",
+    )
+    return int(elements.value), int(tokens.value)
+
+
+def paged_decode_attention_ex(
+    query: torch.Tensor,
+    key_cache: torch.Tensor,
+    value_cache: torch.Tensor,
+    block_tables: torch.Tensor,
+    sequence_lengths: torch.Tensor,
+    *,
+    max_sequence_length: int,
+    scale: float | None = None,
+    key_scales: torch.Tensor | None = None,
+    value_scales: torch.Tensor | None = None,
+    workspace: torch.Tensor | None = None,
+    partition_tokens: int = 0,
+    split: bool | None = None,
+    emit_state: bool = False,
+    output: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """Decode over caches of any stride order, native or FP8 E4M3.
+
+    ``key_cache``/``value_cache`` are logical ``[blocks, block_size, kv_heads,
+    dim]`` views (permute an HND allocation to get one); only the last stride
+    must be 1. ``uint8`` caches are FP8 E4M3 and need ``key_scales`` and
+    ``value_scales`` (one element, or one per KV head). ``split`` chooses the
+    partitioned path (default: when the context spans several partitions);
+    ``emit_state`` returns F32 ``[B, Hq, Dv + 2]`` partial states. ``query``
+    may be a strided view (unit innermost stride), e.g. the rotated Q inside a
+    packed QKV row.
+    """
+    _require_inference_tensors(query, key_cache, value_cache)
+    sequences, query_heads, head_size = query.shape
+    num_blocks, block_size, kv_heads, _ = key_cache.shape
+    value_head_size = value_cache.shape[3]
+    fp8 = key_cache.dtype == torch.uint8
+    if scale is None:
+        scale = head_size ** -0.5
+    if key_cache.stride(3) != 1 or value_cache.stride(3) != 1:
+        raise RuntimeError("Loom paged decode caches need a unit innermost stride")
+    if output is None:
+        shape = (sequences, query_heads, value_head_size + 2) if emit_state else (sequences, query_heads, value_head_size)
+        output = torch.empty(shape, device=query.device, dtype=torch.float32 if emit_state else query.dtype)
+    _check_decode_tensors(query, key_cache, value_cache, block_tables, sequence_lengths, output,
+                          strided_query=True)
+    with torch.cuda.device(query.device):
+        needed, tokens = decode_workspace_elements_ex(sequences, query_heads, kv_heads, value_head_size,
+                                                      int(max_sequence_length), partition_tokens)
+        if split is None:
+            split = max_sequence_length > tokens
+        if split:
+            if workspace is None or workspace.numel() < needed:
+                workspace = torch.empty(needed, device=query.device, dtype=torch.float32)
+        else:
+            workspace = None
+        scales = (key_scales, value_scales) if fp8 else (None, None)
+        status = library().loom_cuda_bridge_paged_decode_attention_ex(
+            _DTYPE_CODES[query.dtype], _native.KV_CACHE_FP8_E4M3 if fp8 else _native.KV_CACHE_NATIVE,
+            query.data_ptr(), _span(query), key_cache.data_ptr(), _span(key_cache),
+            value_cache.data_ptr(), _span(value_cache),
+            scales[0].data_ptr() if scales[0] is not None else None,
+            scales[0].numel() if scales[0] is not None else 0,
+            scales[1].data_ptr() if scales[1] is not None else None,
+            scales[1].numel() if scales[1] is not None else 0,
+            block_tables.data_ptr(), block_tables.numel(), sequence_lengths.data_ptr(),
+            sequence_lengths.numel(), output.data_ptr(), output.numel(),
+            workspace.data_ptr() if workspace is not None else None,
+            workspace.numel() if workspace is not None else 0,
+            sequences, query_heads, kv_heads, head_size, value_head_size, num_blocks, block_size,
+            key_cache.stride(0), key_cache.stride(1), key_cache.stride(2),
+            value_cache.stride(0), value_cache.stride(1), value_cache.stride(2),
+            block_tables.shape[1], int(max_sequence_length), tokens if split else 0, float(scale),
+            1 if emit_state else 0,
+            0 if query.is_contiguous() else query.stride(0), 0 if query.is_contiguous() else query.stride(1),
+            _stream(query.device),
+        )
+    check(status, "paged decode attention")
+    return output
+
+
+def merge_decode_states(states: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """Merges ``[parts, rows, Dv + 2]`` F32 states into ``[rows, Dv]`` outputs."""
+    if states.dim() != 3 or states.dtype != torch.float32 or not states.is_contiguous():
+        raise RuntimeError("decode states must be a contiguous float32 [parts, rows, Dv + 2] tensor")
+    parts, rows, width = states.shape
+    output = torch.empty((rows, width - 2), device=states.device, dtype=out_dtype)
+    with torch.cuda.device(states.device):
+        status = library().loom_cuda_bridge_merge_decode_states(
+            states.data_ptr(), states.numel(), parts, rows, width - 2, _DTYPE_CODES[out_dtype],
+            output.data_ptr(), output.numel(), _stream(states.device),
+        )
+    check(status, "decode state merge")
+    return output
+
+
+# -------------------------------------------------------------------- RoPE
+
+def supports_rope_paged_kv_write(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    positions: torch.Tensor,
+    cos_sin_cache: torch.Tensor,
+    kv_cache: torch.Tensor,
+    key_scales: torch.Tensor,
+    value_scales: torch.Tensor,
+    slot_mapping: torch.Tensor,
+) -> bool:
+    """Whether the tensors fit the fused RoPE + paged-KV write."""
+    if query.dim() != 3 or key.dim() != 3 or value.dim() != 3 or cos_sin_cache.dim() != 2:
+        return False
+    if query.numel() == 0 or key.numel() == 0 or value.numel() == 0 or kv_cache.dim() != 5:
+        return False
+    rotary_dim = cos_sin_cache.shape[1]
+    others = (key, value, positions, cos_sin_cache, kv_cache, key_scales, value_scales, slot_mapping)
+    span = (kv_cache.shape[2] - 1) * kv_cache.stride(2) + (kv_cache.shape[3] - 1) * kv_cache.stride(3) + kv_cache.shape[4]
+    return bool(
+        query.device.type == "cuda"
+        and all(t.device == query.device for t in others)
+        and query.dtype in _DTYPE_NAMES
+        and key.dtype == query.dtype and value.dtype == query.dtype and cos_sin_cache.dtype == query.dtype
+        and kv_cache.dtype in (query.dtype, torch.uint8)
+        and key_scales.dtype == torch.float32 and value_scales.dtype == torch.float32
+        and key_scales.numel() == value_scales.numel() and key_scales.numel() in (1, key.shape[1])
+        and key_scales.is_contiguous() and value_scales.is_contiguous()
+        and positions.dtype == torch.int64 and slot_mapping.dtype == torch.int64
+        and query.shape[0] == key.shape[0] == value.shape[0]
+        and query.shape[2] == key.shape[2]
+        and key.shape[1] == value.shape[1] and key.shape[2] == value.shape[2]
+        and positions.dim() == 1 and positions.numel() == query.shape[0]
+        and slot_mapping.dim() == 1 and 0 < slot_mapping.numel() <= query.shape[0]
+        and cos_sin_cache.shape[0] > 0 and rotary_dim > 0 and rotary_dim % 2 == 0
+        and rotary_dim <= query.shape[2]
+        and kv_cache.shape[0] > 0 and kv_cache.shape[1] == 2 and kv_cache.shape[2] > 0
+        and tuple(kv_cache.shape[3:]) == tuple(key.shape[1:])
+        and query.stride(2) == 1 and key.stride(2) == 1 and value.stride(2) == 1
+        and all(s > 0 for s in query.stride()[:2]) and all(s > 0 for s in key.stride()[:2])
+        and all(s > 0 for s in value.stride()[:2])
+        and positions.is_contiguous() and cos_sin_cache.is_contiguous() and slot_mapping.is_contiguous()
+        and kv_cache.stride(4) == 1 and all(s > 0 for s in kv_cache.stride()[:4])
+        and kv_cache.stride(1) >= span and kv_cache.stride(0) >= kv_cache.stride(1) + span
+        and not any(t.requires_grad for t in (query, key, value, cos_sin_cache))
+    )
+
+
+def rope_paged_kv_write_(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    positions: torch.Tensor,
+    cos_sin_cache: torch.Tensor,
+    kv_cache: torch.Tensor,
+    key_scales: torch.Tensor,
+    value_scales: torch.Tensor,
+    slot_mapping: torch.Tensor,
+    is_neox: bool = True,
+) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Rotates Q/K in place and writes K/V into a packed paged cache.
+
+    ``kv_cache`` is ``[blocks, 2, block_size, kv_heads, head_size]`` with any
+    positive strides (vLLM's NHD and HND layouts both qualify); ``uint8``
+    storage selects the static FP8 E4M3 encoding with the given scales.
+    """
+    _require_inference_tensors(query, key, value, cos_sin_cache, kv_cache, key_scales, value_scales)
+    if query.dim() != 3 or key.dim() != 3 or value.dim() != 3 or kv_cache.dim() != 5 or kv_cache.shape[1] != 2:
+        raise RuntimeError(
+            "Loom RoPE+paged-KV expects [tokens, heads, dim] sources and a "
+            "[blocks, 2, block_size, kv_heads, head_size] cache"
+        )
+    if query.dtype not in _DTYPE_CODES:
+        raise RuntimeError("Loom RoPE+paged-KV supports float32, float16 and bfloat16 sources")
+    if query.stride(2) != 1 or key.stride(2) != 1 or value.stride(2) != 1 or kv_cache.stride(4) != 1:
+        raise RuntimeError("Loom RoPE+paged-KV needs unit innermost strides")
+    fp8 = kv_cache.dtype == torch.uint8
+    view_span = (
+        (kv_cache.shape[0] - 1) * kv_cache.stride(0) + (kv_cache.shape[2] - 1) * kv_cache.stride(2)
+        + (kv_cache.shape[3] - 1) * kv_cache.stride(3) + kv_cache.shape[4]
+    )
+    key_cache_pointer = kv_cache.data_ptr()
+    value_cache_pointer = key_cache_pointer + kv_cache.stride(1) * kv_cache.element_size()
+    with torch.cuda.device(query.device):
+        status = library().loom_cuda_bridge_rope_paged_kv_write(
+            _DTYPE_CODES[query.dtype], _native.KV_CACHE_FP8_E4M3 if fp8 else _native.KV_CACHE_NATIVE,
+            query.data_ptr(), _span(query), key.data_ptr(), _span(key), value.data_ptr(), _span(value),
+            positions.data_ptr(), positions.numel(), cos_sin_cache.data_ptr(), cos_sin_cache.numel(),
+            key_cache_pointer, view_span, value_cache_pointer, view_span,
+            key_scales.data_ptr(), key_scales.numel(), value_scales.data_ptr(), value_scales.numel(),
+            slot_mapping.data_ptr(), slot_mapping.numel(),
+            query.shape[0], slot_mapping.numel(), query.shape[1], key.shape[1], query.shape[2],
+            value.shape[2], cos_sin_cache.shape[1], cos_sin_cache.shape[0], kv_cache.shape[0],
+            kv_cache.shape[2],
+            query.stride(0), query.stride(1), key.stride(0), key.stride(1), value.stride(0), value.stride(1),
+            kv_cache.stride(0), kv_cache.stride(2), kv_cache.stride(3),
+            kv_cache.stride(0), kv_cache.stride(2), kv_cache.stride(3),
+            1 if is_neox else 0, _stream(query.device),
+        )
+    check(status, "RoPE+paged-KV")
+    return query, key, kv_cache
+
+
+def default_scale(head_size: int) -> float:
+    return 1.0 / math.sqrt(head_size)
+
+
+__all__ = [
+    "BridgeError",
+    "Operator",
+    "decode_workspace_elements",
+    "decode_workspace_elements_ex",
+    "last_decode_route",
+    "launch_count",
+    "merge_decode_states",
+    "paged_decode_attention",
+    "paged_decode_attention_ex",
+    "paged_decode_attention_out",
+    "reset_launch_count",
+    "rope_paged_kv_write_",
+    "supports_paged_decode_attention",
+    "supports_rope_paged_kv_write",
+]

@@ -1,0 +1,230 @@
+/*
+ * Launch ABI of the B200 paged-decode library (plain C, no framework types).
+ *
+ * Part 1 re-declares, symbol for symbol, the hot-path entry points of the
+ * reference's internal launch header
+ * (crates/loom-cuda-sys/cuda/include/loom_cuda.h): its dispatch layer
+ * (crates/loom-cuda/src/{attention_dispatch,rope_kv_dispatch}.rs) binds to
+ * exactly these names and argument lists, so it links against this library
+ * unchanged. Part 2 adds entry points in the same style for what the reference
+ * does not have: any cache stride order (HND as well as NHD), FP8 E4M3 caches
+ * read with the dequantisation fused into the load, contexts of any length,
+ * partial (O, max, sum) states and their merge.
+ *
+ * Conventions shared by every function here:
+ *  - all pointers are device pointers valid on the current device;
+ *  - 16-bit element types travel as uint16_t*; strides count ELEMENTS;
+ *  - the call only enqueues work on `stream`; it never allocates, frees or
+ *    synchronises;
+ *  - the return value is a LoomCudaStatus;
+ *  - device metadata (lengths, block ids, positions, slots) is trusted engine
+ *    state; the kernels only guard against reading or writing out of bounds.
+ */
+#ifndef LOOM_LAUNCH_H_
+#define LOOM_LAUNCH_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* loom_cuda.h:10-16 */
+enum LoomCudaStatus {
+  LOOM_CUDA_SUCCESS = 0,
+  LOOM_CUDA_INVALID_ARGUMENT = 1,
+  LOOM_CUDA_UNSUPPORTED = 2,
+  LOOM_CUDA_LAUNCH_ERROR = 3,
+  LOOM_CUDA_UNAVAILABLE = 4,
+};
+
+/* loom_cuda.h:18-21 */
+enum LoomCudaKvCacheEncoding {
+  LOOM_CUDA_KV_CACHE_NATIVE = 0,
+  LOOM_CUDA_KV_CACHE_FP8_E4M3 = 1,
+};
+
+/* loom_cuda.h:23 */
+const char* loom_cuda_status_string(int status);
+
+/* ====================================================================== *
+ * Part 1: the reference's symbols
+ * ====================================================================== */
+
+/*
+ * Paged MQA/GQA decode, one query token per sequence (loom_cuda.h:182-210).
+ * query/output: contiguous [sequences, query_heads, dim]. Caches: dense-inner
+ * NHD [block_size, kv_heads, dim] with a free element stride between blocks.
+ * block_tables [sequences, max_blocks_per_sequence] and sequence_lengths
+ * [sequences] are int32. Unlike the reference there is no 1024-token cap:
+ * max_sequence_length is bounded only by the table capacity.
+ */
+#define LOOM_DECLARE_DECODE(suffix, scalar)                                     \
+  int loom_cuda_paged_decode_attention_##suffix(                                \
+      const scalar* query, const scalar* key_cache, const scalar* value_cache,  \
+      const int32_t* block_tables, const int32_t* sequence_lengths,             \
+      scalar* output, uint32_t sequences, uint32_t query_heads,                 \
+      uint32_t kv_heads, uint32_t head_size, uint32_t value_head_size,          \
+      uint32_t num_blocks, uint32_t block_size, uint64_t key_block_stride,      \
+      uint64_t value_block_stride, uint32_t max_blocks_per_sequence,            \
+      uint32_t max_sequence_length, float scale, void* stream);
+LOOM_DECLARE_DECODE(f32, float)
+LOOM_DECLARE_DECODE(f16, uint16_t)
+LOOM_DECLARE_DECODE(bf16, uint16_t)
+#undef LOOM_DECLARE_DECODE
+
+/*
+ * Split-K sizing (loom_cuda.h:217-220). Returns the F32 element count of the
+ * caller-owned workspace that the split-K entry points below need for this
+ * shape, or 0 when the shape should use the workspace-free entry points above
+ * (a context so short that one partition covers it).
+ */
+uint64_t loom_cuda_paged_decode_attention_split_k_workspace_elements(
+    uint32_t sequences, uint32_t query_heads, uint32_t kv_heads,
+    uint32_t head_size, uint32_t value_head_size, uint32_t max_sequence_length);
+
+/*
+ * Split-K decode (loom_cuda.h:222-250): a partial kernel over KV partitions
+ * followed by a log-sum-exp merge kernel. `workspace` holds at least
+ * `workspace_elements` floats as reported by the sizing function.
+ */
+#define LOOM_DECLARE_DECODE_SPLIT_K(suffix, scalar)                             \
+  int loom_cuda_paged_decode_attention_split_k_##suffix(                        \
+      const scalar* query, const scalar* key_cache, const scalar* value_cache,  \
+      const int32_t* block_tables, const int32_t* sequence_lengths,             \
+      scalar* output, float* workspace, uint64_t workspace_elements,            \
+      uint32_t sequences, uint32_t query_heads, uint32_t kv_heads,              \
+      uint32_t head_size, uint32_t value_head_size, uint32_t num_blocks,        \
+      uint32_t block_size, uint64_t key_block_stride,                           \
+      uint64_t value_block_stride, uint32_t max_blocks_per_sequence,            \
+      uint32_t max_sequence_length, float scale, void* stream);
+LOOM_DECLARE_DECODE_SPLIT_K(f32, float)
+LOOM_DECLARE_DECODE_SPLIT_K(f16, uint16_t)
+LOOM_DECLARE_DECODE_SPLIT_K(bf16, uint16_t)
+#undef LOOM_DECLARE_DECODE_SPLIT_K
+
+/*
+ * Fused in-place RoPE on Q and K plus the paged write of the rotated K and of
+ * V (loom_cuda.h:264-312). Q/K/V are [tokens, heads, dim] views with unit dim
+ * stride and explicit token/head strides (packed QKV needs no copy).
+ * cos_sin_cache is contiguous [max_position, rotary_dim], cosines then sines.
+ * The caches are [blocks, block_size, kv_heads, dim] with explicit strides, so
+ * NHD and HND both fit. slot_mapping has cache_tokens <= tokens entries; a
+ * negative slot, or a token beyond cache_tokens, is rotated but not written.
+ * cache_encoding is a LoomCudaKvCacheEncoding; for FP8 the stored byte is
+ * e4m3(round_to_storage(x) / scale), scale_stride 0 = one scale, 1 = per head.
+ */
+#define LOOM_DECLARE_ROPE_WRITE(suffix, scalar)                                 \
+  int loom_cuda_rope_paged_kv_write_##suffix(                                   \
+      scalar* query, scalar* key, const scalar* value,                          \
+      const int64_t* positions, const scalar* cos_sin_cache, void* key_cache,   \
+      void* value_cache, const float* key_scales, const float* value_scales,    \
+      const int64_t* slot_mapping, uint32_t tokens, uint32_t cache_tokens,      \
+      uint32_t query_heads, uint32_t kv_heads, uint32_t head_size,              \
+      uint32_t value_head_size, uint32_t rotary_dim, uint32_t max_position,     \
+      uint32_t num_blocks, uint32_t block_size, uint32_t cache_encoding,        \
+      uint32_t scale_stride, uint64_t query_token_stride,                       \
+      uint64_t query_head_stride, uint64_t key_token_stride,                    \
+      uint64_t key_head_stride, uint64_t value_token_stride,                    \
+      uint64_t value_head_stride, uint64_t key_cache_block_stride,              \
+      uint64_t key_cache_page_stride, uint64_t key_cache_head_stride,           \
+      uint64_t value_cache_block_stride, uint64_t value_cache_page_stride,      \
+      uint64_t value_cache_head_stride, uint32_t is_neox, void* stream);
+LOOM_DECLARE_ROPE_WRITE(f32, float)
+LOOM_DECLARE_ROPE_WRITE(f16, uint16_t)
+LOOM_DECLARE_ROPE_WRITE(bf16, uint16_t)
+#undef LOOM_DECLARE_ROPE_WRITE
+
+/* ====================================================================== *
+ * Part 2: additions (no counterpart in the reference; same conventions)
+ * ====================================================================== */
+
+/*
+ * Everything a decode launch needs, in one plain struct, so that the additive
+ * entry points do not multiply into one symbol per combination. Zero-fill it,
+ * then set the fields; `struct_size` must be sizeof(LoomDecodeArgs).
+ */
+typedef struct LoomDecodeArgs {
+  uint32_t struct_size;
+  uint32_t dtype;          /* 0 = F32, 1 = F16, 2 = BF16: query/output type */
+  uint32_t cache_encoding; /* LoomCudaKvCacheEncoding */
+  uint32_t scale_stride;   /* FP8 only: 0 = per tensor, 1 = per KV head */
+  const void* query;       /* [sequences, query_heads, head_size]; see strides below */
+  const void* key_cache;   /* native: same type as query; FP8: bytes */
+  const void* value_cache;
+  const float* key_scales; /* FP8 only */
+  const float* value_scales;
+  const int32_t* block_tables;     /* [sequences, max_blocks_per_sequence] */
+  const int32_t* sequence_lengths; /* [sequences] */
+  void* output;            /* [sequences, query_heads, value_head_size], or   */
+                           /* F32 states when `emit_state` is set            */
+  float* workspace;        /* null = single pass over each sequence */
+  uint64_t workspace_elements;
+  uint32_t sequences, query_heads, kv_heads, head_size, value_head_size;
+  uint32_t num_blocks, block_size, max_blocks_per_sequence, max_sequence_length;
+  uint32_t partition_tokens; /* 0 = let the library choose; else multiple of 16 */
+  uint64_t key_block_stride, key_page_stride, key_head_stride;
+  uint64_t value_block_stride, value_page_stride, value_head_stride;
+  /* Element strides of `query` between sequences and between heads; 0 and 0
+   * mean contiguous. A rotated Q that is still a view of a packed QKV row can
+   * be read in place this way. */
+  uint64_t query_token_stride, query_head_stride;
+  float scale;
+  uint32_t emit_state;     /* 1 = write [sequences, query_heads, Dv + 2] F32   */
+                           /* states (O unnormalised, max, sum) instead of O  */
+  void* stream;
+} LoomDecodeArgs;
+
+/* Partition length (tokens) the library would choose for this shape. */
+uint32_t loom_cuda_paged_decode_default_partition_tokens(
+    uint32_t sequences, uint32_t kv_heads, uint32_t max_sequence_length);
+
+/*
+ * F32 workspace elements for a partitioned decode with the given partition
+ * length: sequences * query_heads * ceil(max_sequence_length / partition) *
+ * (value_head_size + 2). Returns 0 if the arguments are invalid or overflow.
+ */
+uint64_t loom_cuda_paged_decode_workspace_elements(
+    uint32_t sequences, uint32_t query_heads, uint32_t value_head_size,
+    uint32_t max_sequence_length, uint32_t partition_tokens);
+
+/* General decode: any stride order, native or FP8 cache, optional workspace. */
+int loom_cuda_paged_decode_attention_ex(const LoomDecodeArgs* args);
+
+/*
+ * Merge of `parts` partial states per row into normalised output rows.
+ * states: [parts, rows, value_head_size + 2] F32, each row holding the
+ * unnormalised O (value_head_size floats), then the running maximum of the
+ * scaled scores (natural-log units) and the sum of exp(score - max). A part
+ * whose sum is 0 is ignored. out_dtype as in LoomDecodeArgs.dtype; output is
+ * [rows, value_head_size]. This is the kernel the multi-GPU long-context mode
+ * runs after gathering every GPU's states.
+ */
+int loom_cuda_merge_decode_states(const float* states, uint32_t parts,
+                                  uint32_t rows, uint32_t value_head_size,
+                                  uint32_t out_dtype, void* output,
+                                  void* stream);
+
+/*
+ * Capability query (crates/loom-cuda/src/cuda_backend.rs:112-145 answers the
+ * same question for the reference). Returns 1 if the decode shape runs here,
+ * 0 if not; `reason`, when non-null, receives a short static string.
+ */
+int loom_cuda_supports_paged_decode(uint32_t dtype, uint32_t cache_encoding,
+                                    uint32_t sequences, uint32_t query_heads,
+                                    uint32_t kv_heads, uint32_t head_size,
+                                    uint32_t value_head_size,
+                                    uint32_t num_blocks, uint32_t block_size,
+                                    uint32_t max_blocks_per_sequence,
+                                    uint32_t max_sequence_length,
+                                    const char** reason);
+
+/* Name of the kernel family the last decode launch on this thread selected
+ * ("mma16", "scalar", ...); for tests and profiling notes. */
+const char* loom_cuda_last_decode_route(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* LOOM_LAUNCH_H_ */

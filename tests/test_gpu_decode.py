@@ -1,0 +1,364 @@
+"""GPU parity of the paged decode against the CPU oracle, through the C ABI.
+
+Every case runs the CUDA path (``attnarc_b200.ops`` -> bridge ABI ->
+dispatch -> launch ABI -> kernels) and compares with the oracle on identical
+seeded inputs. Tolerances: rtol = atol = 1e-4 for F32 and 1e-2 for F16/BF16.
+The shape matrix is the one the reference's Python tests use
+(python/tests/test_paged_decode_attention.py:110-137); the two fixtures of its
+Rust wrapper tests (crates/loom-cuda/src/attention_dispatch.rs:487-606) are
+replayed as well.
+"""
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from tests import helpers
+from attnarc_b200 import workloads
+
+pytestmark = pytest.mark.gpu
+
+DEVICE = "cuda"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from attnarc_b200 import ops as module
+
+    return module
+
+
+def make_case(dtype, sequences, query_heads, kv_heads, head_size, value_head_size, block_size, lengths,
+              seed, interleaved=False):
+    generator = torch.Generator().manual_seed(seed)
+    max_blocks = math.ceil(max(lengths) / block_size)
+    num_blocks = sequences * max_blocks + 7
+    query = torch.randn((sequences, query_heads, head_size), generator=generator).to(dtype)
+    if interleaved:
+        kv = torch.randn((num_blocks, 2, block_size, kv_heads, head_size), generator=generator).to(dtype)
+        kv = kv.to(DEVICE)
+        key_cache, value_cache = kv[:, 0], kv[:, 1]
+    else:
+        key_cache = torch.randn((num_blocks, block_size, kv_heads, head_size), generator=generator).to(dtype).to(DEVICE)
+        value_cache = torch.randn((num_blocks, block_size, kv_heads, value_head_size), generator=generator).to(dtype).to(DEVICE)
+    tables = torch.randperm(num_blocks, generator=generator)[: sequences * max_blocks]
+    tables = tables.reshape(sequences, max_blocks).to(torch.int32)
+    return (query.to(DEVICE), key_cache, value_cache, tables.to(DEVICE),
+            torch.tensor(lengths, dtype=torch.int32, device=DEVICE))
+
+
+REFERENCE_SHAPES = [
+    (3, 8, 1, 32, 24, 16, [1, 17, 31]),
+    (4, 8, 2, 64, 64, 16, [16, 33, 64, 7]),
+    (3, 12, 4, 80, 48, 32, [63, 129, 255]),
+    (2, 8, 2, 128, 96, 32, [257, 511]),
+    (16, 32, 8, 32, 24, 16, list(range(17, 33))),
+    (2, 8, 2, 33, 17, 8, [17, 23]),
+    (2, 14, 2, 64, 64, 16, [17, 32]),
+    (64, 14, 2, 64, 64, 16, list(range(17, 33)) * 4),
+    (1, 32, 8, 128, 128, 16, [128]),
+    (4, 32, 8, 128, 128, 16, [512, 501, 489, 477]),
+    (8, 32, 8, 128, 128, 32, list(range(491, 499))),
+    (2, 14, 2, 128, 128, 16, [129, 256]),
+    (1, 8, 8, 128, 128, 16, [257]),
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", REFERENCE_SHAPES, ids=[str(i) for i in range(len(REFERENCE_SHAPES))])
+def test_reference_shape_matrix(ops, dtype, shape):
+    sequences, query_heads, kv_heads, head_size, value_head_size, block_size, lengths = shape
+    query, key_cache, value_cache, tables, seq_lens = make_case(
+        dtype, sequences, query_heads, kv_heads, head_size, value_head_size, block_size, lengths, seed=len(lengths))
+    scale = head_size ** -0.5
+    expected = helpers.oracle_decode(query, key_cache, value_cache, tables, seq_lens, scale=scale,
+                                     max_sequence_length=max(lengths))
+    assert ops.supports_paged_decode_attention(query, key_cache, value_cache, tables, seq_lens,
+                                               max_sequence_length=max(lengths))
+    actual = ops.paged_decode_attention(query, key_cache, value_cache, tables, seq_lens,
+                                        max_sequence_length=max(lengths), scale=scale)
+    helpers.assert_close(actual, expected, dtype, "reference-shaped entry point")
+    # the same case through the partitioned path with a small partition
+    split = ops.paged_decode_attention_ex(query, key_cache, value_cache, tables, seq_lens,
+                                          max_sequence_length=max(lengths), scale=scale,
+                                          partition_tokens=64, split=True)
+    helpers.assert_close(split, expected, dtype, "partitioned path")
+
+
+def test_expected_kernel_routes(ops):
+    query, key_cache, value_cache, tables, seq_lens = make_case(torch.bfloat16, 2, 8, 2, 128, 128, 16, [40, 70], 1)
+    ops.paged_decode_attention(query, key_cache, value_cache, tables, seq_lens, max_sequence_length=70)
+    assert ops.last_decode_route() == "mma16"
+    query, key_cache, value_cache, tables, seq_lens = make_case(torch.float32, 2, 8, 2, 128, 128, 16, [40, 70], 1)
+    ops.paged_decode_attention(query, key_cache, value_cache, tables, seq_lens, max_sequence_length=70)
+    assert ops.last_decode_route() == "scalar"
+    query, key_cache, value_cache, tables, seq_lens = make_case(torch.float16, 2, 8, 2, 80, 48, 16, [40, 70], 1)
+    ops.paged_decode_attention(query, key_cache, value_cache, tables, seq_lens, max_sequence_length=70)
+    assert ops.last_decode_route() == "scalar"
+
+
+def test_rust_wrapper_fixture_base(ops):
+    # attention_dispatch.rs:487-540, tolerance 2e-5 there.
+    q = torch.tensor([(i - 9.0) * 0.07 for i in range(32)], dtype=torch.float32).reshape(2, 4, 4)
+    k = torch.tensor([(np.float32(i) % np.float32(13.0) - 6.0) * 0.11 for i in range(64)], dtype=torch.float32)
+    v = torch.tensor([(np.float32(i) % np.float32(17.0) - 8.0) * 0.09 for i in range(48)], dtype=torch.float32)
+    k, v = k.reshape(4, 2, 2, 4).to(DEVICE), v.reshape(4, 2, 2, 3).to(DEVICE)
+    tables = torch.tensor([[2, 0], [1, 3]], dtype=torch.int32, device=DEVICE)
+    lens = torch.tensor([3, 2], dtype=torch.int32, device=DEVICE)
+    expected = helpers.oracle_decode(q, k, v, tables, lens, scale=0.5, max_sequence_length=4)
+    actual = ops.paged_decode_attention(q.to(DEVICE), k, v, tables, lens, max_sequence_length=4, scale=0.5)
+    assert (actual.cpu() - expected).abs().max().item() <= 2.0e-5
+
+
+def test_rust_wrapper_fixture_split_k(ops):
+    # attention_dispatch.rs:542-606, tolerance 2e-4 there.
+    q = torch.tensor([(i % 29 - 14.0) * 0.013 for i in range(512)], dtype=torch.float32).reshape(1, 4, 128)
+    k = torch.tensor([(i % 37 - 18.0) * 0.011 for i in range(8 * 16 * 128)], dtype=torch.float32)
+    v = torch.tensor([(i % 41 - 20.0) * 0.009 for i in range(8 * 16 * 128)], dtype=torch.float32)
+    k, v = k.reshape(8, 16, 1, 128).to(DEVICE), v.reshape(8, 16, 1, 128).to(DEVICE)
+    tables = torch.arange(8, dtype=torch.int32, device=DEVICE).reshape(1, 8)
+    lens = torch.tensor([128], dtype=torch.int32, device=DEVICE)
+    expected = helpers.oracle_decode(q, k, v, tables, lens, scale=0.125, max_sequence_length=128)
+    actual = ops.paged_decode_attention_ex(q.to(DEVICE), k, v, tables, lens, max_sequence_length=128,
+                                           scale=0.125, partition_tokens=32, split=True)
+    assert (actual.cpu() - expected).abs().max().item() <= 2.0e-4
+
+
+def test_vllm_interleaved_cache_views(ops):
+    # K and V are views of one [blocks, 2, block, heads, D] allocation
+    # (python/tests/test_paged_decode_attention.py:186-230).
+    for dtype in (torch.float16, torch.bfloat16, torch.float32):
+        query, key_cache, value_cache, tables, seq_lens = make_case(
+            dtype, 3, 8, 2, 128, 128, 16, [5, 130, 300], seed=9, interleaved=True)
+        expected = helpers.oracle_decode(query, key_cache, value_cache, tables, seq_lens, scale=0.09,
+                                         max_sequence_length=300)
+        actual = ops.paged_decode_attention(query, key_cache, value_cache, tables, seq_lens,
+                                            max_sequence_length=300, scale=0.09)
+        helpers.assert_close(actual, expected, dtype, "interleaved K/V views")
+
+
+def test_runs_on_a_caller_stream(ops):
+    query, key_cache, value_cache, tables, seq_lens = make_case(torch.bfloat16, 2, 8, 2, 128, 128, 16, [100, 200], 2)
+    expected = helpers.oracle_decode(query, key_cache, value_cache, tables, seq_lens, scale=0.1,
+                                     max_sequence_length=200)
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        actual = ops.paged_decode_attention(query, key_cache, value_cache, tables, seq_lens,
+                                            max_sequence_length=200, scale=0.1)
+    stream.synchronize()
+    helpers.assert_close(actual, expected, torch.bfloat16, "side stream")
+
+
+@pytest.mark.parametrize("layout", ["NHD", "HND"])
+@pytest.mark.parametrize("dtype", ["bf16", "f16", "f32"])
+@pytest.mark.parametrize("group", [(8, 8), (12, 2), (32, 8), (64, 8), (32, 2), (4, 4)])
+def test_layouts_groups_and_partitions(ops, layout, dtype, group):
+    query_heads, kv_heads = group
+    config = workloads.DecodeConfig("t", 5, query_heads, kv_heads, dtype=dtype, layout=layout,
+                                    lengths=("fixed", [1, 16, 257, 512, 700]))
+    case = workloads.build_case(config, DEVICE, seed=query_heads + kv_heads)
+    key_cache, value_cache = case.cache_views()
+    query = case.query.contiguous()
+    expected = helpers.oracle_decode(query, key_cache, value_cache, case.block_tables, case.sequence_lengths,
+                                     scale=case.scale, max_sequence_length=case.max_sequence_length)
+    for partition in (0, 128, 256):
+        actual = ops.paged_decode_attention_ex(query, key_cache, value_cache, case.block_tables,
+                                               case.sequence_lengths,
+                                               max_sequence_length=case.max_sequence_length, scale=case.scale,
+                                               partition_tokens=partition, split=partition != 0)
+        helpers.assert_close(actual, expected, config.torch_dtype, f"{layout} partition={partition}")
+
+
+@pytest.mark.parametrize("granularity", ["tensor", "head"])
+@pytest.mark.parametrize("dtype", ["bf16", "f16", "f32"])
+@pytest.mark.parametrize("layout", ["NHD", "HND"])
+def test_fp8_cache_dequantised_on_load(ops, granularity, dtype, layout):
+    config = workloads.DecodeConfig("t", 4, 16, 2, dtype=dtype, cache="fp8", fp8_granularity=granularity,
+                                    layout=layout, lengths=("fixed", [3, 64, 300, 1000]))
+    case = workloads.build_case(config, DEVICE, seed=4)
+    key_cache, value_cache = case.cache_views()
+    query = case.query.contiguous()
+    expected = helpers.oracle_decode(query, key_cache, value_cache, case.block_tables, case.sequence_lengths,
+                                     scale=case.scale, max_sequence_length=case.max_sequence_length,
+                                     key_scales=case.key_scales, value_scales=case.value_scales)
+    for partition in (0, 256):
+        actual = ops.paged_decode_attention_ex(query, key_cache, value_cache, case.block_tables,
+                                               case.sequence_lengths,
+                                               max_sequence_length=case.max_sequence_length, scale=case.scale,
+                                               key_scales=case.key_scales, value_scales=case.value_scales,
+                                               partition_tokens=partition, split=partition != 0)
+        helpers.assert_close(actual, expected, config.torch_dtype, f"fp8 {granularity} partition={partition}")
+    expected_route = "scalar-fp8" if dtype == "f32" else "mma16-fp8"
+    assert ops.last_decode_route() == expected_route
+
+
+@pytest.mark.parametrize("head_size", [64, 128])
+@pytest.mark.parametrize("block_size", [8, 16, 32, 48])
+def test_block_sizes_and_head_sizes(ops, head_size, block_size):
+    lengths = [block_size - 1, block_size, block_size + 1, 5 * block_size + 3, 333]
+    query, key_cache, value_cache, tables, seq_lens = make_case(
+        torch.bfloat16, 5, 8, 2, head_size, head_size, block_size, lengths, seed=block_size)
+    expected = helpers.oracle_decode(query, key_cache, value_cache, tables, seq_lens, scale=0.1,
+                                     max_sequence_length=max(lengths))
+    actual = ops.paged_decode_attention(query, key_cache, value_cache, tables, seq_lens,
+                                        max_sequence_length=max(lengths), scale=0.1)
+    assert ops.last_decode_route() == "mma16"
+    helpers.assert_close(actual, expected, torch.bfloat16, f"block_size={block_size}")
+
+
+def test_unused_cache_slots_do_not_leak(ops):
+    # Slots past the sequence length hold NaN; they must never reach the output.
+    query, key_cache, value_cache, tables, seq_lens = make_case(torch.bfloat16, 3, 8, 2, 128, 128, 16, [1, 17, 40], 3)
+    expected = helpers.oracle_decode(query, key_cache, value_cache, tables, seq_lens, scale=0.1,
+                                     max_sequence_length=40)
+    poisoned_k, poisoned_v = key_cache.clone(), value_cache.clone()
+    for s, length in enumerate([1, 17, 40]):
+        block = int(tables[s, (length - 1) // 16])
+        poisoned_k[block, length % 16 if length % 16 else 16:] = float("nan")
+        poisoned_v[block, length % 16 if length % 16 else 16:] = float("nan")
+    actual = ops.paged_decode_attention(query, poisoned_k, poisoned_v, tables, seq_lens,
+                                        max_sequence_length=40, scale=0.1)
+    helpers.assert_close(actual, expected, torch.bfloat16, "poisoned tail slots")
+
+
+def test_partial_states_merge_to_the_same_answer(ops):
+    # Split a batch's context into two block ranges, decode each range to
+    # (O, max, sum) states, merge: must equal the single-shot decode. This is
+    # the arithmetic of the multi-GPU long-context mode on one device.
+    config = workloads.DecodeConfig("t", 3, 32, 8, dtype="bf16", lengths=("fixed", [2048, 900, 4096]))
+    case = workloads.build_case(config, DEVICE, seed=12)
+    key_cache, value_cache = case.cache_views()
+    query = case.query.contiguous()
+    expected = helpers.oracle_decode(query, key_cache, value_cache, case.block_tables, case.sequence_lengths,
+                                     scale=case.scale, max_sequence_length=case.max_sequence_length)
+    tables = case.block_tables
+    half_blocks = tables.shape[1] // 2
+    lengths = case.sequence_lengths
+    first_len = torch.clamp(lengths, max=half_blocks * 16)
+    second_len = torch.clamp(lengths - half_blocks * 16, min=0)
+    states = []
+    for sub_tables, sub_len in ((tables[:, :half_blocks].contiguous(), first_len),
+                                (tables[:, half_blocks:].contiguous(), second_len)):
+        states.append(ops.paged_decode_attention_ex(
+            query, key_cache, value_cache, sub_tables, sub_len.to(torch.int32),
+            max_sequence_length=sub_tables.shape[1] * 16, scale=case.scale, emit_state=True,
+            partition_tokens=256, split=True))
+    stacked = torch.stack([s.reshape(-1, s.shape[-1]) for s in states]).contiguous()
+    merged = ops.merge_decode_states(stacked, torch.bfloat16).reshape(expected.shape)
+    helpers.assert_close(merged, expected, torch.bfloat16, "merged states")
+    # single-pass state emission agrees too
+    whole = ops.paged_decode_attention_ex(query, key_cache, value_cache, tables, lengths,
+                                          max_sequence_length=case.max_sequence_length, scale=case.scale,
+                                          emit_state=True, split=False)
+    merged_one = ops.merge_decode_states(whole.reshape(1, -1, whole.shape[-1]).contiguous(), torch.bfloat16)
+    helpers.assert_close(merged_one.reshape(expected.shape), expected, torch.bfloat16, "single state")
+
+
+def test_cfg1_f32_oracle_case(ops):
+    case = workloads.build_case(workloads.CONFIGS["cfg1"], DEVICE, seed=1)
+    key_cache, value_cache = case.cache_views()
+    query = case.query.contiguous()
+    expected = helpers.oracle_decode(query, key_cache, value_cache, case.block_tables, case.sequence_lengths,
+                                     scale=case.scale, max_sequence_length=case.max_sequence_length)
+    actual = ops.paged_decode_attention(query, key_cache, value_cache, case.block_tables,
+                                        case.sequence_lengths, max_sequence_length=case.max_sequence_length,
+                                        scale=case.scale)
+    helpers.assert_close(actual, expected, torch.float32, "cfg1")
+
+
+def test_cfg2_full_size_against_the_oracle(ops):
+    # The benchmark workload itself: 64 sequences of 512..4096 tokens, BF16.
+    case = workloads.build_case(workloads.CONFIGS["cfg2"], DEVICE, seed=2)
+    key_cache, value_cache = case.cache_views()
+    query = case.query.contiguous()
+    expected = helpers.oracle_decode(query, key_cache, value_cache, case.block_tables, case.sequence_lengths,
+                                     scale=case.scale, max_sequence_length=case.max_sequence_length)
+    for split in (False, True):
+        actual = ops.paged_decode_attention_ex(query, key_cache, value_cache, case.block_tables,
+                                               case.sequence_lengths,
+                                               max_sequence_length=case.max_sequence_length, scale=case.scale,
+                                               split=split)
+        helpers.assert_close(actual, expected, torch.bfloat16, f"cfg2 split={split}")
+
+
+@pytest.mark.parametrize("name", ["cfg3", "cfg4", "cfg5"])
+def test_large_configs_on_a_sequence_subset(ops, name):
+    # Full-size caches are too slow for the F64 oracle; draw the configuration's
+    # lengths, keep its geometry, and check a handful of its sequences
+    # (including the longest) against the oracle.
+    config = workloads.CONFIGS[name]
+    rng = np.random.default_rng(5)
+    lengths = workloads.sample_lengths(config, rng)
+    keep = np.argsort(lengths)[[0, len(lengths) // 2, -1]]
+    if name == "cfg5":
+        keep = np.argsort(lengths)[[0, -1]]
+        chosen = np.minimum(lengths[keep], 20000)  # the 131072-token row is checked by properties below
+    else:
+        chosen = lengths[keep]
+    small = workloads.scaled(config, batch=len(chosen), lengths=("fixed", chosen.tolist()))
+    case = workloads.build_case(small, DEVICE, seed=6)
+    key_cache, value_cache = case.cache_views()
+    query = case.query.contiguous()
+    scales = dict(key_scales=case.key_scales, value_scales=case.value_scales) if config.cache == "fp8" else {}
+    expected = helpers.oracle_decode(query, key_cache, value_cache, case.block_tables, case.sequence_lengths,
+                                     scale=case.scale, max_sequence_length=case.max_sequence_length, **scales)
+    actual = ops.paged_decode_attention_ex(query, key_cache, value_cache, case.block_tables,
+                                           case.sequence_lengths,
+                                           max_sequence_length=case.max_sequence_length, scale=case.scale,
+                                           partition_tokens=config.partition_tokens, split=True, **scales)
+    helpers.assert_close(actual, expected, config.torch_dtype, name)
+
+
+def test_long_context_properties_at_full_length(ops):
+    # 131072 tokens, size-independent checks: (1) if every V row equals one
+    # vector the output is that vector whatever the scores; (2) the split path
+    # equals the single pass; (3) permuting which physical blocks hold the
+    # tokens (with the table following) changes nothing.
+    length, heads, kv_heads, dim = 131072, 32, 8, 128
+    blocks = length // 16
+    generator = torch.Generator(device=DEVICE).manual_seed(7)
+    key_cache = torch.randn((blocks + 3, 16, kv_heads, dim), device=DEVICE, dtype=torch.bfloat16, generator=generator)
+    constant = torch.randn((kv_heads, dim), device=DEVICE, dtype=torch.bfloat16, generator=generator)
+    value_cache = constant.expand(blocks + 3, 16, kv_heads, dim).contiguous()
+    query = torch.randn((1, heads, dim), device=DEVICE, dtype=torch.bfloat16, generator=generator)
+    tables = torch.randperm(blocks + 3, device=DEVICE)[:blocks].to(torch.int32).reshape(1, blocks)
+    lens = torch.tensor([length], dtype=torch.int32, device=DEVICE)
+    out = ops.paged_decode_attention_ex(query, key_cache, value_cache, tables, lens, max_sequence_length=length,
+                                        partition_tokens=512, split=True)
+    want = constant.repeat_interleave(heads // kv_heads, dim=0).unsqueeze(0)
+    helpers.assert_close(out, want, torch.bfloat16, "constant V")
+
+    value_cache = torch.randn((blocks + 3, 16, kv_heads, dim), device=DEVICE, dtype=torch.bfloat16, generator=generator)
+    split = ops.paged_decode_attention_ex(query, key_cache, value_cache, tables, lens, max_sequence_length=length,
+                                          partition_tokens=512, split=True)
+    single = ops.paged_decode_attention_ex(query, key_cache, value_cache, tables, lens, max_sequence_length=length,
+                                           split=False)
+    helpers.assert_close(split, single, torch.bfloat16, "split vs single pass")
+
+    shuffle = torch.randperm(blocks + 3, device=DEVICE)
+    moved_k, moved_v = torch.empty_like(key_cache), torch.empty_like(value_cache)
+    moved_k[shuffle] = key_cache
+    moved_v[shuffle] = value_cache
+    moved_tables = shuffle[tables.long()].to(torch.int32)
+    moved = ops.paged_decode_attention_ex(query, moved_k, moved_v, moved_tables, lens, max_sequence_length=length,
+                                          partition_tokens=512, split=True)
+    assert torch.equal(moved, split), "block placement must not change the result"
+
+
+def test_launch_counter_and_error_text(ops):
+    query, key_cache, value_cache, tables, seq_lens = make_case(torch.bfloat16, 2, 8, 2, 128, 128, 16, [100, 200], 2)
+    ops.reset_launch_count(ops.Operator.PAGED_DECODE_ATTENTION)
+    ops.paged_decode_attention(query, key_cache, value_cache, tables, seq_lens, max_sequence_length=200)
+    assert ops.launch_count(ops.Operator.PAGED_DECODE_ATTENTION) == 1
+    with pytest.raises(RuntimeError, match="maximum sequence length 100000 exceeds block-table capacity"):
+        ops.paged_decode_attention(query, key_cache, value_cache, tables, seq_lens, max_sequence_length=100000)
+    with pytest.raises(RuntimeError, match="query head count 8 must be divisible by KV head count 3"):
+        ops.paged_decode_attention(query, key_cache[:, :, :1].repeat(1, 1, 3, 1), value_cache[:, :, :1].repeat(1, 1, 3, 1),
+                                   tables, seq_lens, max_sequence_length=200)
+    with pytest.raises(RuntimeError, match="regions output and query must not overlap"):
+        ops.paged_decode_attention_out(query, key_cache, value_cache, tables, seq_lens, query,
+                                       max_sequence_length=200)
+    assert ops.launch_count(ops.Operator.PAGED_DECODE_ATTENTION) == 1  # failures are not counted
