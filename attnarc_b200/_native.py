@@ -81,7 +81,7 @@ def _declare(lib):
     lib.loom_cuda_paged_decode_attention_split_k_workspace_elements.restype = u64
     lib.loom_cuda_paged_decode_attention_split_k_workspace_elements.argtypes = [u32] * 6
     lib.loom_cuda_paged_decode_workspace_elements.restype = u64
-    lib.loom_cuda_paged_decode_workspace_elements.argtypes = [u32] * 5
+    lib.loom_cuda_paged_decode_workspace_elements.argtypes = [u32] * 6
     lib.loom_cuda_merge_decode_states.argtypes = [ptr, u32, u32, u32, u32, ptr, ptr]
     # partitioner
     i64p, u32p, u64p = ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(u32), ctypes.POINTER(u64)

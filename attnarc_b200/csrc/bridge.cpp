@@ -316,12 +316,9 @@ int loom_cuda_bridge_paged_decode_workspace_elements_ex(uint32_t sequences, uint
     if (partition_tokens % 16 != 0) {
       throw invalid("paged decode partition length must be a multiple of 16 tokens");
     }
-    const uint32_t tokens =
-        partition_tokens != 0
-            ? partition_tokens
-            : loom_cuda_paged_decode_default_partition_tokens(sequences, kv_heads, max_sequence_length);
+    const uint32_t tokens = partition_tokens;  // 0 = the library chooses at launch
     const uint64_t elements = loom_cuda_paged_decode_workspace_elements(
-        sequences, query_heads, value_head_size, max_sequence_length, tokens);
+        sequences, query_heads, kv_heads, value_head_size, max_sequence_length, tokens);
     if (elements == 0) throw invalid("paged decode workspace size overflows the CUDA ABI");
     *workspace_elements = elements;
     if (chosen_partition_tokens != nullptr) *chosen_partition_tokens = tokens;

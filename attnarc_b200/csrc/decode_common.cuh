@@ -32,6 +32,7 @@ struct DecodeParams {
   const int32_t* sequence_lengths;
   void* output;      // [sequences, query_heads, Dv] of the query type, or F32 states
   float* partials;   // workspace [sequences*query_heads, max_partitions, Dv+2] or null
+  uint32_t* item_meta;  // balanced kernel only: (first CTA, CTA count) per work item
   uint32_t sequences, query_heads, kv_heads, group;  // group = query_heads / kv_heads
   uint32_t head_size, value_head_size;
   uint32_t num_blocks, block_size, max_blocks_per_sequence, max_sequence_length;

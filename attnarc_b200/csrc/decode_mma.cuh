@@ -1,34 +1,30 @@
-// Tensor-core paged decode kernel for 16-bit queries (F16/BF16) over a native
-// 16-bit or an FP8 E4M3 cache.
+// Tensor-core building blocks of the paged decode kernels (16-bit queries over
+// a native 16-bit or an FP8 E4M3 cache) and the fixed-partition kernel.
 //
 // Replaces the reference's three decode kernels
 // (crates/loom-cuda-sys/cuda/src/paged_decode_attention.cu: one head per CTA
 // :164-264, 2/4 packed GQA heads :269-501, split-K partials :509-747), all of
 // which are scalar CUDA-core loops capped at 1024 tokens.
 //
-// Shape of the computation. One CTA owns one (sequence, KV head, KV partition)
-// and ALL query heads of that KV head's group, so every K/V byte is fetched
-// from HBM once however large the group is. Each of the 4 warps streams its
-// own 16-token chunks (warp w takes chunks w, w+4, ...) through a private
-// multi-stage cp.async ring in shared memory; there is no CTA-wide barrier in
-// the main loop. Per chunk a warp computes, with m16n8k16 MMAs,
+// Shape of the computation. A warp owns 16-token chunks of one (sequence, KV
+// head) and ALL query heads of that KV head's group, so every K/V byte is
+// fetched from HBM once however large the group is. Per chunk a warp computes,
+// with m16n8k16 MMAs,
 //     S^T[16 tokens x 8 heads]  = K[16 x D]   . Q^T[D x 8]
 //     O^T[Dv x 8 heads]        += V^T[Dv x 16] . P^T[16 x 8]
 // i.e. tokens (then value dims) ride the M side and the query heads ride N = 8,
 // which is what makes a GQA group of 4..8 heads a dense tile; a group of 16
 // uses two N tiles. K is the row-major A operand straight from ldmatrix, V^T is
-// the same shared tile read with ldmatrix.trans, Q^T lives in registers for the
-// whole CTA, and P^T is produced from the S^T accumulators by one movmatrix
-// transpose per 8 tokens (no shared-memory round trip). The online softmax
-// keeps (max, sum) per head in registers; max and sum cross lanes with xor
-// shuffles.
+// the same kind of shared tile read with ldmatrix.trans, Q^T lives in registers,
+// and P^T is produced from the S^T accumulators by one movmatrix transpose per
+// 8 tokens (no shared-memory round trip). The online softmax keeps (max, sum)
+// per head in registers; max and sum cross lanes with xor shuffles.
 //
 // Memory. The hot loop is bound by HBM: 2*D*sizeof(cache element) bytes per
 // (token, KV head). Rows are fetched as 16-byte cp.async.cg pieces (L1
-// bypassed) into an XOR-swizzled tile, so both ldmatrix flavours are
-// bank-conflict free. Each warp keeps kStages-1 chunks in flight; two CTAs per
-// SM give about 128 KB in flight per SM, above the ~45 KB the measured
-// bandwidth-latency product needs.
+// bypassed) into XOR-swizzled tiles, so both ldmatrix flavours are free of bank
+// conflicts. Each warp runs its own multi-stage ring; there is no CTA-wide
+// barrier in the streaming loop.
 //
 // FP8 cache. Bytes are staged as they are. ldmatrix moves them as 16-bit
 // pairs; a byte permute plus cvt.rn.f16x2.e4m3x2 (exact) turns them into F16
@@ -38,6 +34,8 @@
 // folded into the softmax scale and the V scale into the final normalisation,
 // so dequantisation costs no multiply per element.
 #pragma once
+
+#include <type_traits>
 
 #include "decode_common.cuh"
 
@@ -59,9 +57,10 @@ struct MmaTile {
   static_assert(kSegs >= 4 && kSegs <= 32, "row width out of range");
 };
 
+// Shared memory the cross-warp merge needs: per warp 8*kNT heads of kD + 4
+// floats of O, plus one max and one sum per head.
 template <int kNT, int kD>
 constexpr int mma_merge_bytes() {
-  // per warp: 8*kNT heads x (kD + 4) floats of O, plus max and sum
   return kMmaWarps * (8 * kNT) * (kD + 4 + 2) * 4;
 }
 
@@ -82,17 +81,318 @@ __device__ __forceinline__ uint32_t swizzled(uint32_t row, uint32_t col) {
   }
 }
 
+// The same for a tile that TMA wrote with its 128-byte (64-byte for 64-byte
+// rows) swizzle: identical for rows of up to 128 bytes; a 256-byte row arrives
+// as two 128-byte boxes, so the tile is two half-tiles of [16 rows x 128 B].
+template <int kSegs, bool kTmaLayout>
+__device__ __forceinline__ uint32_t tile_offset(uint32_t row, uint32_t col) {
+  if constexpr (kTmaLayout && kSegs == 16) {
+    return (col >> 3) * 2048u + row * 128u + (((col & 7u) ^ (row & 7u)) << 4);
+  } else {
+    return swizzled<kSegs>(row, col);
+  }
+}
+
 __device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t packed) {
   const float2 wide = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&packed));
   return pack_f16x2(wide.x, wide.y);
 }
 
+// Everything one warp carries for one (sequence, KV head): the Q^T fragments and
+// the running softmax state of its query heads.
+template <int kD, int kNT>
+struct WarpState {
+  static constexpr int kKSteps = kD / 16;
+  uint32_t qf[kNT][kKSteps][2];
+  float o[kNT][kKSteps][4];
+  float row_max[kNT][2];
+  float row_sum[kNT][2];
+
+  __device__ __forceinline__ void reset() {
+#pragma unroll
+    for (int nt = 0; nt < kNT; ++nt) {
+      row_max[nt][0] = row_max[nt][1] = -INFINITY;
+      row_sum[nt][0] = row_sum[nt][1] = 0.0f;
+#pragma unroll
+      for (int mt = 0; mt < kKSteps; ++mt) o[nt][mt][0] = o[nt][mt][1] = o[nt][mt][2] = o[nt][mt][3] = 0.0f;
+    }
+  }
+};
+
+// Loads the Q^T fragments of up to 8*kNT heads starting at `first_row` (a
+// pointer to the first head's row; rows are `head_stride` elements apart).
+// Heads at or beyond `live_heads` read as zero.
+template <typename QT, bool kFp8, int kD, int kNT>
+__device__ __forceinline__ void load_query(WarpState<kD, kNT>& state, const QT* first_row,
+                                           uint64_t head_stride, uint32_t live_heads, uint32_t g,
+                                           uint32_t t) {
+  constexpr int kKSteps = kD / 16;
+#pragma unroll
+  for (int nt = 0; nt < kNT; ++nt) {
+    const uint32_t head = nt * 8 + g;
+    const bool live = head < live_heads;
+    const QT* row = first_row + (uint64_t)(live ? head : 0u) * head_stride;
+#pragma unroll
+    for (int ks = 0; ks < kKSteps; ++ks) {
+      uint32_t b0 = 0, b1 = 0;
+      if (live) {
+        if constexpr (kFp8) {
+          // reduction index permuted to the byte order ldmatrix delivers
+          const uint2 four = *reinterpret_cast<const uint2*>(row + ks * 16 + t * 4);
+          b0 = four.x;
+          b1 = four.y;
+          if constexpr (std::is_same<QT, __nv_bfloat16>::value) {
+            b0 = bf16x2_to_f16x2(b0);
+            b1 = bf16x2_to_f16x2(b1);
+          }
+        } else {
+          b0 = *reinterpret_cast<const uint32_t*>(row + ks * 16 + t * 2);
+          b1 = *reinterpret_cast<const uint32_t*>(row + ks * 16 + 8 + t * 2);
+        }
+      }
+      state.qf[nt][ks][0] = b0;
+      state.qf[nt][ks][1] = b1;
+    }
+  }
+}
+
+// S^T = K . Q^T for one 16-token chunk staged at shared address `k_tile`.
+template <typename QT, bool kFp8, int kD, int kNT, bool kTmaLayout = false>
+__device__ __forceinline__ void chunk_scores(float (&s)[kNT][4], const WarpState<kD, kNT>& state,
+                                             uint32_t k_tile, uint32_t lane) {
+  using Tile = MmaTile<kFp8, kD>;
+  constexpr bool kBf16Mma = !kFp8 && std::is_same<QT, __nv_bfloat16>::value;
+  constexpr int kKSteps = kD / 16;
+  // ldmatrix lane roles: matrices 0..3 = (rows 0-7, col c)(rows 8-15, col c)(rows 0-7, col c+1)(rows 8-15, col c+1)
+  const uint32_t ld_row = (lane & 7u) + ((lane >> 3) & 1u) * 8u;
+  const uint32_t ld_col = lane >> 4;
+#pragma unroll
+  for (int nt = 0; nt < kNT; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f;
+  if constexpr (!kFp8) {
+#pragma unroll
+    for (int ks = 0; ks < kKSteps; ++ks) {
+      uint32_t a[4];
+      ldmatrix_x4(a, k_tile + tile_offset<Tile::kSegs, kTmaLayout>(ld_row, 2 * ks + ld_col));
+#pragma unroll
+      for (int nt = 0; nt < kNT; ++nt) {
+        if constexpr (kBf16Mma) mma_16816_bf16(s[nt], a, state.qf[nt][ks][0], state.qf[nt][ks][1]);
+        else mma_16816_f16(s[nt], a, state.qf[nt][ks][0], state.qf[nt][ks][1]);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int pair = 0; pair < kKSteps / 2; ++pair) {
+      uint32_t r[4];
+      ldmatrix_x4(r, k_tile + tile_offset<Tile::kSegs, kTmaLayout>(ld_row, 2 * pair + ld_col));
+      uint32_t a[4];
+      e4m3x4_to_f16x2x2(r[0], a[0], a[2]);
+      e4m3x4_to_f16x2x2(r[1], a[1], a[3]);
+#pragma unroll
+      for (int nt = 0; nt < kNT; ++nt) mma_16816_f16(s[nt], a, state.qf[nt][2 * pair][0], state.qf[nt][2 * pair][1]);
+      e4m3x4_to_f16x2x2(r[2], a[0], a[2]);
+      e4m3x4_to_f16x2x2(r[3], a[1], a[3]);
+#pragma unroll
+      for (int nt = 0; nt < kNT; ++nt) {
+        mma_16816_f16(s[nt], a, state.qf[nt][2 * pair + 1][0], state.qf[nt][2 * pair + 1][1]);
+      }
+    }
+  }
+}
+
+// Online softmax over the chunk's 16 tokens: updates max/sum, rescales O, and
+// returns P^T as MMA B fragments. Rows at or beyond `live_rows` are masked.
+template <typename QT, bool kFp8, int kD, int kNT>
+__device__ __forceinline__ void chunk_softmax(uint32_t (&pb)[kNT][2], const float (&s)[kNT][4],
+                                              WarpState<kD, kNT>& state, float score_scale,
+                                              uint32_t live_rows, uint32_t g) {
+  constexpr bool kBf16Mma = !kFp8 && std::is_same<QT, __nv_bfloat16>::value;
+  constexpr int kKSteps = kD / 16;
+  const bool low_live = g < live_rows;
+  const bool high_live = (g + 8u) < live_rows;
+#pragma unroll
+  for (int nt = 0; nt < kNT; ++nt) {
+    const float s0 = low_live ? s[nt][0] * score_scale : -INFINITY;
+    const float s1 = low_live ? s[nt][1] * score_scale : -INFINITY;
+    const float s2 = high_live ? s[nt][2] * score_scale : -INFINITY;
+    const float s3 = high_live ? s[nt][3] * score_scale : -INFINITY;
+    float max0 = fmaxf(s0, s2), max1 = fmaxf(s1, s3);
+#pragma unroll
+    for (int offset = 4; offset < 32; offset <<= 1) {
+      max0 = fmaxf(max0, __shfl_xor_sync(0xffffffffu, max0, offset));
+      max1 = fmaxf(max1, __shfl_xor_sync(0xffffffffu, max1, offset));
+    }
+    const float new0 = fmaxf(state.row_max[nt][0], max0);
+    const float new1 = fmaxf(state.row_max[nt][1], max1);
+    const float alpha0 = fast_exp2(state.row_max[nt][0] - new0);
+    const float alpha1 = fast_exp2(state.row_max[nt][1] - new1);
+    state.row_max[nt][0] = new0;
+    state.row_max[nt][1] = new1;
+    const float p0 = fast_exp2(s0 - new0), p1 = fast_exp2(s1 - new1);
+    const float p2 = fast_exp2(s2 - new0), p3 = fast_exp2(s3 - new1);
+    state.row_sum[nt][0] = state.row_sum[nt][0] * alpha0 + (p0 + p2);
+    state.row_sum[nt][1] = state.row_sum[nt][1] * alpha1 + (p1 + p3);
+#pragma unroll
+    for (int mt = 0; mt < kKSteps; ++mt) {
+      state.o[nt][mt][0] *= alpha0;
+      state.o[nt][mt][1] *= alpha1;
+      state.o[nt][mt][2] *= alpha0;
+      state.o[nt][mt][3] *= alpha1;
+    }
+    if constexpr (kBf16Mma) {
+      pb[nt][0] = movmatrix_trans(pack_bf16x2(p0, p1));
+      pb[nt][1] = movmatrix_trans(pack_bf16x2(p2, p3));
+    } else {
+      pb[nt][0] = movmatrix_trans(pack_f16x2(p0, p1));
+      pb[nt][1] = movmatrix_trans(pack_f16x2(p2, p3));
+    }
+  }
+}
+
+// O^T += V^T . P^T for the chunk staged at shared address `v_tile`.
+template <typename QT, bool kFp8, int kD, int kNT, bool kTmaLayout = false>
+__device__ __forceinline__ void chunk_values(WarpState<kD, kNT>& state, const uint32_t (&pb)[kNT][2],
+                                             uint32_t v_tile, uint32_t lane) {
+  using Tile = MmaTile<kFp8, kD>;
+  constexpr bool kBf16Mma = !kFp8 && std::is_same<QT, __nv_bfloat16>::value;
+  constexpr int kKSteps = kD / 16;
+  if constexpr (!kFp8) {
+    // matrices 0..3 = (tokens 0-7, col c)(tokens 0-7, col c+1)(tokens 8-15, col c)(tokens 8-15, col c+1)
+    const uint32_t ld_row = (lane & 7u) + (lane >> 4) * 8u;
+    const uint32_t ld_col = (lane >> 3) & 1u;
+#pragma unroll
+    for (int mt = 0; mt < kKSteps; ++mt) {
+      uint32_t a[4];
+      ldmatrix_x4_trans(a, v_tile + tile_offset<Tile::kSegs, kTmaLayout>(ld_row, 2 * mt + ld_col));
+#pragma unroll
+      for (int nt = 0; nt < kNT; ++nt) {
+        if constexpr (kBf16Mma) mma_16816_bf16(state.o[nt][mt], a, pb[nt][0], pb[nt][1]);
+        else mma_16816_f16(state.o[nt][mt], a, pb[nt][0], pb[nt][1]);
+      }
+    }
+  } else {
+    // matrices 0..3 = (tokens 0-7, col c)(tokens 8-15, col c)(tokens 0-7, col c+1)(tokens 8-15, col c+1)
+    const uint32_t ld_row = (lane & 7u) + ((lane >> 3) & 1u) * 8u;
+    const uint32_t ld_col = lane >> 4;
+#pragma unroll
+    for (int pair = 0; pair < kKSteps / 2; ++pair) {
+      uint32_t r[4];
+      ldmatrix_x4_trans(r, v_tile + tile_offset<Tile::kSegs, kTmaLayout>(ld_row, 2 * pair + ld_col));
+      uint32_t a[4];
+      e4m3x4_to_f16x2x2(__byte_perm(r[0], 0u, 0x3120u), a[0], a[1]);
+      e4m3x4_to_f16x2x2(__byte_perm(r[1], 0u, 0x3120u), a[2], a[3]);
+#pragma unroll
+      for (int nt = 0; nt < kNT; ++nt) mma_16816_f16(state.o[nt][2 * pair], a, pb[nt][0], pb[nt][1]);
+      e4m3x4_to_f16x2x2(__byte_perm(r[2], 0u, 0x3120u), a[0], a[1]);
+      e4m3x4_to_f16x2x2(__byte_perm(r[3], 0u, 0x3120u), a[2], a[3]);
+#pragma unroll
+      for (int nt = 0; nt < kNT; ++nt) mma_16816_f16(state.o[nt][2 * pair + 1], a, pb[nt][0], pb[nt][1]);
+    }
+  }
+}
+
+// Layout of the cross-warp merge area.
+template <int kD, int kNT>
+struct MergeArea {
+  static constexpr int kHeads = 8 * kNT;
+  static constexpr int kORow = kD + 4;
+  float* o;    // [warps][kHeads][kORow]
+  float* max;  // [warps][kHeads]
+  float* sum;  // [warps][kHeads]
+  __device__ __forceinline__ explicit MergeArea(void* base) {
+    o = reinterpret_cast<float*>(base);
+    max = o + kMmaWarps * kHeads * kORow;
+    sum = max + kMmaWarps * kHeads;
+  }
+};
+
+// Completes a warp's row sums and parks its state in the merge area. The
+// caller brackets this with CTA barriers.
+template <bool kFp8, int kD, int kNT>
+__device__ __forceinline__ void park_warp_state(MergeArea<kD, kNT> area, WarpState<kD, kNT>& state,
+                                                uint32_t warp, uint32_t g, uint32_t t) {
+  constexpr int kHeads = 8 * kNT;
+  constexpr int kORow = kD + 4;
+  constexpr int kKSteps = kD / 16;
+#pragma unroll
+  for (int nt = 0; nt < kNT; ++nt) {
+#pragma unroll
+    for (int offset = 4; offset < 32; offset <<= 1) {
+      state.row_sum[nt][0] += __shfl_xor_sync(0xffffffffu, state.row_sum[nt][0], offset);
+      state.row_sum[nt][1] += __shfl_xor_sync(0xffffffffu, state.row_sum[nt][1], offset);
+    }
+    const uint32_t head0 = nt * 8 + 2 * t;
+    float* base0 = area.o + ((size_t)warp * kHeads + head0) * kORow;
+    float* base1 = base0 + kORow;
+#pragma unroll
+    for (int mt = 0; mt < kKSteps; ++mt) {
+      // un-permute the value dimension of the FP8 path
+      const uint32_t dv_a = kFp8 ? mt * 16 + 2 * g : mt * 16 + g;
+      const uint32_t dv_b = kFp8 ? dv_a + 1 : dv_a + 8;
+      base0[dv_a] = state.o[nt][mt][0];
+      base1[dv_a] = state.o[nt][mt][1];
+      base0[dv_b] = state.o[nt][mt][2];
+      base1[dv_b] = state.o[nt][mt][3];
+    }
+    if (g == 0) {
+      area.max[warp * kHeads + head0] = state.row_max[nt][0];
+      area.max[warp * kHeads + head0 + 1] = state.row_max[nt][1];
+      area.sum[warp * kHeads + head0] = state.row_sum[nt][0];
+      area.sum[warp * kHeads + head0 + 1] = state.row_sum[nt][1];
+    }
+  }
+}
+
+// Merges the four parked warp states and stores, per live head, either the
+// normalised output row (`final_out`, type QT) or an F32 state row
+// (`state_rows` + head * state_head_stride floats).
+template <typename QT, int kD, int kNT>
+__device__ __forceinline__ void combine_and_store(MergeArea<kD, kNT> area, uint32_t live_heads,
+                                                  float value_scale, QT* final_out,
+                                                  uint64_t final_head_stride, float* state_rows,
+                                                  uint64_t state_head_stride) {
+  constexpr int kHeads = 8 * kNT;
+  constexpr int kORow = kD + 4;
+  for (uint32_t index = threadIdx.x; index < live_heads * kD; index += kMmaThreads) {
+    const uint32_t head = index / kD;
+    const uint32_t dv = index % kD;
+    float top = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kMmaWarps; ++w) top = fmaxf(top, area.max[w * kHeads + head]);
+    float acc = 0.0f, total = 0.0f;
+    if (top > -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < kMmaWarps; ++w) {
+        const float factor = fast_exp2(area.max[w * kHeads + head] - top);
+        acc += area.o[((size_t)w * kHeads + head) * kORow + dv] * factor;
+        total += area.sum[w * kHeads + head] * factor;
+      }
+    }
+    acc *= value_scale;
+    if (final_out != nullptr) {
+      const float result = total > 0.0f ? acc / total : 0.0f;
+      QT* out = final_out + (uint64_t)head * final_head_stride;
+      if constexpr (std::is_same<QT, __nv_bfloat16>::value) out[dv] = __float2bfloat16_rn(result);
+      else out[dv] = __float2half_rn(result);
+    } else {
+      float* row = state_rows + (uint64_t)head * state_head_stride;
+      row[dv] = acc;
+      if (dv == 0) {
+        row[kD] = top * kLn2;
+        row[kD + 1] = total;
+      }
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------
+// Fixed-partition kernel: one CTA per (sequence, KV head, partition of
+// `partition_tokens`); used for the workspace-free single pass, for block sizes
+// that are not a multiple of 16, and when the caller fixes the partition length.
+// ----------------------------------------------------------------------------
 template <typename QT, bool kFp8, int kD, int kNT>
 __global__ void __launch_bounds__(kMmaThreads, 2) decode_mma_kernel(const DecodeParams p) {
   using Tile = MmaTile<kFp8, kD>;
-  constexpr bool kBf16Mma = !kFp8 && std::is_same<QT, __nv_bfloat16>::value;
   constexpr int kHeads = 8 * kNT;
-  constexpr int kKSteps = kD / 16;
 
   extern __shared__ __align__(128) uint8_t smem[];
 
@@ -114,56 +414,17 @@ __global__ void __launch_bounds__(kMmaThreads, 2) decode_mma_kernel(const Decode
   const uint32_t n_parts = length == 0 ? 1u : (length + p.partition_tokens - 1) / p.partition_tokens;
   const uint32_t n_chunks = part_end > part_begin ? (part_end - part_begin + 15u) / 16u : 0u;
   const uint32_t my_chunks = n_chunks > warp ? (n_chunks - warp + kMmaWarps - 1) / kMmaWarps : 0u;
+  const uint32_t live_heads = min((uint32_t)kHeads, p.group - first_head);
 
-  // ---- Q^T fragments, resident for the whole CTA -----------------------
-  uint32_t qf[kNT][kKSteps][2];
-  {
-    const QT* query = static_cast<const QT*>(p.query);
-#pragma unroll
-    for (int nt = 0; nt < kNT; ++nt) {
-      const uint32_t head_in_group = first_head + nt * 8 + g;
-      const bool live = head_in_group < p.group;
-      const QT* row = query + (uint64_t)seq * p.q_token +
-                      ((uint64_t)kv_head * p.group + (live ? head_in_group : 0u)) * p.q_head;
-#pragma unroll
-      for (int ks = 0; ks < kKSteps; ++ks) {
-        uint32_t b0 = 0, b1 = 0;
-        if (live) {
-          if constexpr (kFp8) {
-            // reduction index permuted to the byte order ldmatrix delivers
-            const uint2 four = *reinterpret_cast<const uint2*>(row + ks * 16 + t * 4);
-            b0 = four.x;
-            b1 = four.y;
-            if constexpr (std::is_same<QT, __nv_bfloat16>::value) {
-              b0 = bf16x2_to_f16x2(b0);
-              b1 = bf16x2_to_f16x2(b1);
-            }
-          } else {
-            b0 = *reinterpret_cast<const uint32_t*>(row + ks * 16 + t * 2);
-            b1 = *reinterpret_cast<const uint32_t*>(row + ks * 16 + 8 + t * 2);
-          }
-        }
-        qf[nt][ks][0] = b0;
-        qf[nt][ks][1] = b1;
-      }
-    }
-  }
+  WarpState<kD, kNT> state;
+  state.reset();
+  const uint64_t first_query_head = (uint64_t)kv_head * p.group + first_head;
+  load_query<QT, kFp8, kD, kNT>(
+      state, static_cast<const QT*>(p.query) + (uint64_t)seq * p.q_token + first_query_head * p.q_head,
+      p.q_head, live_heads, g, t);
 
   float score_scale = p.scale_log2;
   if constexpr (kFp8) score_scale *= p.key_scales[(uint64_t)kv_head * p.scale_stride];
-
-  // ---- running state ------------------------------------------------------
-  float o[kNT][kKSteps][4];
-  float row_max[kNT][2], row_sum[kNT][2];
-#pragma unroll
-  for (int nt = 0; nt < kNT; ++nt) {
-    row_max[nt][0] = row_max[nt][1] = -INFINITY;
-    row_sum[nt][0] = row_sum[nt][1] = 0.0f;
-#pragma unroll
-    for (int mt = 0; mt < kKSteps; ++mt) {
-      o[nt][mt][0] = o[nt][mt][1] = o[nt][mt][2] = o[nt][mt][3] = 0.0f;
-    }
-  }
 
   // ---- producer side: page-table driven 16-byte copies --------------------
   const uint8_t* key_bytes = static_cast<const uint8_t*>(p.key_cache);
@@ -234,12 +495,6 @@ __global__ void __launch_bounds__(kMmaThreads, 2) decode_mma_kernel(const Decode
     cp_async_commit();
   }
 
-  // ldmatrix lane roles
-  const uint32_t ld_row_a = (lane & 7u) + ((lane >> 3) & 1u) * 8u;  // matrices 0..3 = (r0,c0)(r8,c0)(r0,c1)(r8,c1)
-  const uint32_t ld_col_a = lane >> 4;
-  const uint32_t ld_row_t = (lane & 7u) + (lane >> 4) * 8u;         // matrices 0..3 = (r0,c0)(r0,c1)(r8,c0)(r8,c1)
-  const uint32_t ld_col_t = (lane >> 3) & 1u;
-
   for (uint32_t i = 0; i < my_chunks; ++i) {
     cp_async_wait<Tile::kStages - 2>();
     __syncwarp();
@@ -249,192 +504,37 @@ __global__ void __launch_bounds__(kMmaThreads, 2) decode_mma_kernel(const Decode
       cp_async_commit();
     }
     const uint32_t stage = smem_base + (i % Tile::kStages) * Tile::kStageBytes;
-    const uint32_t k_tile = stage;
-    const uint32_t v_tile = stage + Tile::kTileBytes;
     const uint32_t token0 = part_begin + (warp + i * kMmaWarps) * 16u;
     const uint32_t live_rows = part_end - token0;  // >= 1; rows beyond it are zero filled
 
-    // ---- S^T = K . Q^T ----------------------------------------------------
     float s[kNT][4];
-#pragma unroll
-    for (int nt = 0; nt < kNT; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f;
-
-    if constexpr (!kFp8) {
-#pragma unroll
-      for (int ks = 0; ks < kKSteps; ++ks) {
-        uint32_t a[4];
-        ldmatrix_x4(a, k_tile + swizzled<Tile::kSegs>(ld_row_a, 2 * ks + ld_col_a));
-#pragma unroll
-        for (int nt = 0; nt < kNT; ++nt) {
-          if constexpr (kBf16Mma) mma_16816_bf16(s[nt], a, qf[nt][ks][0], qf[nt][ks][1]);
-          else mma_16816_f16(s[nt], a, qf[nt][ks][0], qf[nt][ks][1]);
-        }
-      }
-    } else {
-#pragma unroll
-      for (int pair = 0; pair < kKSteps / 2; ++pair) {
-        uint32_t r[4];
-        ldmatrix_x4(r, k_tile + swizzled<Tile::kSegs>(ld_row_a, 2 * pair + ld_col_a));
-        uint32_t a[4];
-        e4m3x4_to_f16x2x2(r[0], a[0], a[2]);
-        e4m3x4_to_f16x2x2(r[1], a[1], a[3]);
-#pragma unroll
-        for (int nt = 0; nt < kNT; ++nt) mma_16816_f16(s[nt], a, qf[nt][2 * pair][0], qf[nt][2 * pair][1]);
-        e4m3x4_to_f16x2x2(r[2], a[0], a[2]);
-        e4m3x4_to_f16x2x2(r[3], a[1], a[3]);
-#pragma unroll
-        for (int nt = 0; nt < kNT; ++nt) mma_16816_f16(s[nt], a, qf[nt][2 * pair + 1][0], qf[nt][2 * pair + 1][1]);
-      }
-    }
-
-    // ---- online softmax over this chunk's 16 tokens -----------------------
+    chunk_scores<QT, kFp8, kD, kNT>(s, state, stage, lane);
     uint32_t pb[kNT][2];
-#pragma unroll
-    for (int nt = 0; nt < kNT; ++nt) {
-      const bool low_live = g < live_rows;
-      const bool high_live = (g + 8u) < live_rows;
-      const float s0 = low_live ? s[nt][0] * score_scale : -INFINITY;
-      const float s1 = low_live ? s[nt][1] * score_scale : -INFINITY;
-      const float s2 = high_live ? s[nt][2] * score_scale : -INFINITY;
-      const float s3 = high_live ? s[nt][3] * score_scale : -INFINITY;
-      float max0 = fmaxf(s0, s2), max1 = fmaxf(s1, s3);
-#pragma unroll
-      for (int offset = 4; offset < 32; offset <<= 1) {
-        max0 = fmaxf(max0, __shfl_xor_sync(0xffffffffu, max0, offset));
-        max1 = fmaxf(max1, __shfl_xor_sync(0xffffffffu, max1, offset));
-      }
-      const float new0 = fmaxf(row_max[nt][0], max0);
-      const float new1 = fmaxf(row_max[nt][1], max1);
-      const float alpha0 = fast_exp2(row_max[nt][0] - new0);
-      const float alpha1 = fast_exp2(row_max[nt][1] - new1);
-      row_max[nt][0] = new0;
-      row_max[nt][1] = new1;
-      const float p0 = fast_exp2(s0 - new0), p1 = fast_exp2(s1 - new1);
-      const float p2 = fast_exp2(s2 - new0), p3 = fast_exp2(s3 - new1);
-      row_sum[nt][0] = row_sum[nt][0] * alpha0 + (p0 + p2);
-      row_sum[nt][1] = row_sum[nt][1] * alpha1 + (p1 + p3);
-#pragma unroll
-      for (int mt = 0; mt < kKSteps; ++mt) {
-        o[nt][mt][0] *= alpha0;
-        o[nt][mt][1] *= alpha1;
-        o[nt][mt][2] *= alpha0;
-        o[nt][mt][3] *= alpha1;
-      }
-      if constexpr (kBf16Mma) {
-        pb[nt][0] = movmatrix_trans(pack_bf16x2(p0, p1));
-        pb[nt][1] = movmatrix_trans(pack_bf16x2(p2, p3));
-      } else {
-        pb[nt][0] = movmatrix_trans(pack_f16x2(p0, p1));
-        pb[nt][1] = movmatrix_trans(pack_f16x2(p2, p3));
-      }
-    }
-
-    // ---- O^T += V^T . P^T ---------------------------------------------------
-    if constexpr (!kFp8) {
-#pragma unroll
-      for (int mt = 0; mt < kKSteps; ++mt) {
-        uint32_t a[4];
-        ldmatrix_x4_trans(a, v_tile + swizzled<Tile::kSegs>(ld_row_t, 2 * mt + ld_col_t));
-#pragma unroll
-        for (int nt = 0; nt < kNT; ++nt) {
-          if constexpr (kBf16Mma) mma_16816_bf16(o[nt][mt], a, pb[nt][0], pb[nt][1]);
-          else mma_16816_f16(o[nt][mt], a, pb[nt][0], pb[nt][1]);
-        }
-      }
-    } else {
-#pragma unroll
-      for (int pair = 0; pair < kKSteps / 2; ++pair) {
-        // matrices: (tokens 0-7, col c)(tokens 8-15, col c)(tokens 0-7, col c+1)(tokens 8-15, col c+1)
-        uint32_t r[4];
-        ldmatrix_x4_trans(r, v_tile + swizzled<Tile::kSegs>(ld_row_a, 2 * pair + ld_col_a));
-        uint32_t a[4];
-        e4m3x4_to_f16x2x2(__byte_perm(r[0], 0u, 0x3120u), a[0], a[1]);
-        e4m3x4_to_f16x2x2(__byte_perm(r[1], 0u, 0x3120u), a[2], a[3]);
-#pragma unroll
-        for (int nt = 0; nt < kNT; ++nt) mma_16816_f16(o[nt][2 * pair], a, pb[nt][0], pb[nt][1]);
-        e4m3x4_to_f16x2x2(__byte_perm(r[2], 0u, 0x3120u), a[0], a[1]);
-        e4m3x4_to_f16x2x2(__byte_perm(r[3], 0u, 0x3120u), a[2], a[3]);
-#pragma unroll
-        for (int nt = 0; nt < kNT; ++nt) mma_16816_f16(o[nt][2 * pair + 1], a, pb[nt][0], pb[nt][1]);
-      }
-    }
+    chunk_softmax<QT, kFp8, kD, kNT>(pb, s, state, score_scale, live_rows, g);
+    chunk_values<QT, kFp8, kD, kNT>(state, pb, stage + Tile::kTileBytes, lane);
   }
   cp_async_wait<0>();
 
-  // ---- finish the per-warp sums, then merge the four warps ----------------
-#pragma unroll
-  for (int nt = 0; nt < kNT; ++nt) {
-#pragma unroll
-    for (int offset = 4; offset < 32; offset <<= 1) {
-      row_sum[nt][0] += __shfl_xor_sync(0xffffffffu, row_sum[nt][0], offset);
-      row_sum[nt][1] += __shfl_xor_sync(0xffffffffu, row_sum[nt][1], offset);
-    }
-  }
+  // ---- merge the four warps and store --------------------------------------
   __syncthreads();  // every warp is done with its ring; reuse the memory
-
-  constexpr int kORow = kD + 4;
-  float* merge_o = reinterpret_cast<float*>(smem);                    // [warps][kHeads][kORow]
-  float* merge_max = merge_o + kMmaWarps * kHeads * kORow;            // [warps][kHeads]
-  float* merge_sum = merge_max + kMmaWarps * kHeads;                  // [warps][kHeads]
-#pragma unroll
-  for (int nt = 0; nt < kNT; ++nt) {
-    const uint32_t head0 = nt * 8 + 2 * t;
-    float* base0 = merge_o + ((size_t)warp * kHeads + head0) * kORow;
-    float* base1 = base0 + kORow;
-#pragma unroll
-    for (int mt = 0; mt < kKSteps; ++mt) {
-      const uint32_t dv_a = kFp8 ? mt * 16 + 2 * g : mt * 16 + g;
-      const uint32_t dv_b = kFp8 ? dv_a + 1 : dv_a + 8;
-      base0[dv_a] = o[nt][mt][0];
-      base1[dv_a] = o[nt][mt][1];
-      base0[dv_b] = o[nt][mt][2];
-      base1[dv_b] = o[nt][mt][3];
-    }
-    if (g == 0) {
-      merge_max[warp * kHeads + head0] = row_max[nt][0];
-      merge_max[warp * kHeads + head0 + 1] = row_max[nt][1];
-      merge_sum[warp * kHeads + head0] = row_sum[nt][0];
-      merge_sum[warp * kHeads + head0 + 1] = row_sum[nt][1];
-    }
-  }
+  MergeArea<kD, kNT> area(smem);
+  park_warp_state<kFp8, kD, kNT>(area, state, warp, g, t);
   __syncthreads();
 
   float value_scale = 1.0f;
   if constexpr (kFp8) value_scale = p.value_scales[(uint64_t)kv_head * p.scale_stride];
-  const uint32_t live_heads = min((uint32_t)kHeads, p.group - first_head);
-  const bool final_rows = n_parts == 1;
+  const uint64_t query_row = (uint64_t)seq * p.query_heads + first_query_head;
   const uint32_t stride = state_stride(kD);
-  for (uint32_t index = threadIdx.x; index < live_heads * kD; index += kMmaThreads) {
-    const uint32_t head = index / kD;
-    const uint32_t dv = index % kD;
-    float top = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < kMmaWarps; ++w) top = fmaxf(top, merge_max[w * kHeads + head]);
-    float acc = 0.0f, total = 0.0f;
-    if (top > -INFINITY) {
-#pragma unroll
-      for (int w = 0; w < kMmaWarps; ++w) {
-        const float factor = fast_exp2(merge_max[w * kHeads + head] - top);
-        acc += merge_o[((size_t)w * kHeads + head) * kORow + dv] * factor;
-        total += merge_sum[w * kHeads + head] * factor;
-      }
-    }
-    acc *= value_scale;
-    const uint64_t query_row = (uint64_t)seq * p.query_heads + (uint64_t)kv_head * p.group + first_head + head;
-    if (final_rows && !p.emit_state) {
-      const float result = total > 0.0f ? acc / total : 0.0f;
-      QT* out = static_cast<QT*>(p.output) + query_row * kD;
-      if constexpr (std::is_same<QT, __nv_bfloat16>::value) out[dv] = __float2bfloat16_rn(result);
-      else out[dv] = __float2half_rn(result);
-    } else {
-      float* state = final_rows ? static_cast<float*>(p.output) + query_row * stride
-                                : p.partials + (query_row * p.max_partitions + part) * stride;
-      state[dv] = acc;
-      if (dv == 0) {
-        state[kD] = top * kLn2;
-        state[kD + 1] = total;
-      }
-    }
+  if (n_parts == 1 && !p.emit_state) {
+    combine_and_store<QT, kD, kNT>(area, live_heads, value_scale, static_cast<QT*>(p.output) + query_row * kD,
+                                   kD, nullptr, 0);
+  } else if (n_parts == 1) {
+    combine_and_store<QT, kD, kNT>(area, live_heads, value_scale, nullptr, 0,
+                                   static_cast<float*>(p.output) + query_row * stride, stride);
+  } else {
+    combine_and_store<QT, kD, kNT>(area, live_heads, value_scale, nullptr, 0,
+                                   p.partials + (query_row * p.max_partitions + part) * stride,
+                                   (uint64_t)p.max_partitions * stride);
   }
 }
 

@@ -187,19 +187,15 @@ void paged_decode_attention_split_k(DType call_dtype, Region query, Region key_c
 
 uint32_t decode_partition_tokens(const PagedDecodeAttentionSpec& spec, uint32_t requested) {
   require_decode_abi(spec);
-  if (requested != 0) {
-    if (requested % 16 != 0) throw invalid("paged decode partition length must be a multiple of 16 tokens");
-    return requested;
-  }
-  return loom_cuda_paged_decode_default_partition_tokens(
-      (uint32_t)spec.sequences, (uint32_t)spec.kv_heads, (uint32_t)spec.max_sequence_length);
+  if (requested % 16 != 0) throw invalid("paged decode partition length must be a multiple of 16 tokens");
+  return requested;  // 0 = the library chooses at launch
 }
 
 size_t decode_workspace_elements(const PagedDecodeAttentionSpec& spec, uint32_t partition_tokens) {
   require_decode_abi(spec);
   const uint64_t elements = loom_cuda_paged_decode_workspace_elements(
-      (uint32_t)spec.sequences, (uint32_t)spec.query_heads, (uint32_t)spec.value_head_size,
-      (uint32_t)spec.max_sequence_length, partition_tokens);
+      (uint32_t)spec.sequences, (uint32_t)spec.query_heads, (uint32_t)spec.kv_heads,
+      (uint32_t)spec.value_head_size, (uint32_t)spec.max_sequence_length, partition_tokens);
   if (elements == 0) throw invalid("paged decode workspace size overflows the CUDA ABI");
   return (size_t)elements;
 }

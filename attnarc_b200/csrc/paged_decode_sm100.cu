@@ -12,11 +12,14 @@
 //                          128, 16-byte aligned cache rows: the fast path.
 //   decode_scalar_kernel   everything else (F32, odd head sizes, unaligned
 //                          views): one query head per CTA, CUDA cores.
-//   merge_states_kernel    second, light kernel: combines the partial
-//                          (O, max, sum) states of the KV partitions of a
-//                          sequence, or of several GPUs.
-// A sequence that fits one partition is finished by the first kernel, so the
-// merge kernel only touches the sequences that were actually split.
+//   decode_stream_kernel   (decode_stream.cuh) the same math in persistent CTAs
+//                          that share the batch's tiles evenly: the default
+//                          whenever a workspace is given.
+//   merge_*_kernel         second, light kernel: combines the partial
+//                          (O, max, sum) states of a split sequence, or of
+//                          several GPUs.
+// A work item that one CTA finished alone is written by the first kernel, so
+// the merge kernel only touches the rows that were actually split.
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -32,6 +35,7 @@
 #include "../../include/loom_launch.h"
 #include "decode_common.cuh"
 #include "decode_mma.cuh"
+#include "decode_stream.cuh"
 
 namespace loom_decode {
 
@@ -188,16 +192,61 @@ __global__ void __launch_bounds__(kScalarThreads) decode_scalar_kernel(const Dec
 
 constexpr int kMergeThreads = 128;
 
-__device__ __forceinline__ float block_reduce(float value, bool take_max, float* scratch) {
-  value = take_max ? warp_max(value) : warp_sum(value);
-  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-  __syncthreads();  // scratch may still be read from the previous reduction
-  if (lane == 0) scratch[warp] = value;
-  __syncthreads();
-  float out = scratch[0];
+// Merges `parts` states of one output row. Part i lives at base + i*part_stride
+// and holds O (value_head_size floats), max (natural-log units) and sum. Each
+// thread owns value dims and folds the parts in batches of eight whose loads
+// are all issued before any is used: one round trip to memory per batch, no
+// shared memory, no barrier, no shuffle. max and sum are recomputed by every
+// thread from the same broadcast loads.
+template <typename OT>
+__device__ __forceinline__ void merge_row(const float* __restrict__ base, uint32_t parts,
+                                          uint64_t part_stride, uint32_t value_head_size, uint64_t row,
+                                          void* output, uint32_t emit_state) {
+  constexpr int kBatch = 8;
+  for (uint32_t dv = threadIdx.x; dv < value_head_size; dv += kMergeThreads) {
+    float top = -INFINITY, total = 0.0f, acc = 0.0f;
+    for (uint32_t first = 0; first < parts; first += kBatch) {
+      float part_max[kBatch], part_sum[kBatch], part_o[kBatch];
 #pragma unroll
-  for (int w = 1; w < kMergeThreads / 32; ++w) out = take_max ? fmaxf(out, scratch[w]) : out + scratch[w];
-  return out;
+      for (int j = 0; j < kBatch; ++j) {
+        const bool live = first + j < parts;
+        const float* state = base + (uint64_t)(live ? first + j : first) * part_stride;
+        part_sum[j] = live ? __ldg(state + value_head_size + 1) : 0.0f;
+        part_max[j] = __ldg(state + value_head_size);
+        part_o[j] = __ldg(state + dv);
+      }
+      float batch_top = top;
+#pragma unroll
+      for (int j = 0; j < kBatch; ++j) {
+        if (part_sum[j] > 0.0f) batch_top = fmaxf(batch_top, part_max[j]);
+      }
+      if (batch_top > -INFINITY) {
+        const float rescale = exp2f((top - batch_top) * kLog2e);  // 0 when top is still -inf
+        total *= rescale;
+        acc *= rescale;
+#pragma unroll
+        for (int j = 0; j < kBatch; ++j) {
+          if (part_sum[j] > 0.0f) {
+            const float factor = exp2f((part_max[j] - batch_top) * kLog2e);
+            total += part_sum[j] * factor;
+            acc += part_o[j] * factor;
+          }
+        }
+        top = batch_top;
+      }
+    }
+    if (emit_state) {
+      float* out = static_cast<float*>(output) + row * state_stride(value_head_size);
+      out[dv] = acc;
+      if (dv == 0) {
+        out[value_head_size] = top;
+        out[value_head_size + 1] = total;
+      }
+    } else {
+      narrow_store<OT>(static_cast<OT*>(output) + row * value_head_size + dv,
+                       total > 0.0f ? acc / total : 0.0f);
+    }
+  }
 }
 
 // One CTA per output row. Part `i` of row `r` lives at
@@ -211,7 +260,6 @@ merge_states_kernel(const float* __restrict__ states, uint64_t row_stride, uint6
                     const int32_t* __restrict__ sequence_lengths, uint32_t rows_per_sequence,
                     uint32_t partition_tokens, uint32_t max_sequence_length, void* output,
                     uint32_t emit_state) {
-  __shared__ float scratch[kMergeThreads / 32];
   const uint32_t row = blockIdx.x;
   uint32_t parts = fixed_parts;
   if (sequence_lengths != nullptr) {
@@ -219,47 +267,40 @@ merge_states_kernel(const float* __restrict__ states, uint64_t row_stride, uint6
     parts = (length + partition_tokens - 1) / partition_tokens;
     if (parts <= 1) return;
   }
-  const float* base = states + (uint64_t)row * row_stride;
+  merge_row<OT>(states + (uint64_t)row * row_stride, parts, part_stride, value_head_size, row, output,
+                emit_state);
+}
 
-  float top = -INFINITY;
-  for (uint32_t i = threadIdx.x; i < parts; i += kMergeThreads) {
-    const float* state = base + (uint64_t)i * part_stride;
-    if (state[value_head_size + 1] > 0.0f) top = fmaxf(top, state[value_head_size]);
+// Merge after the balanced kernel: the item table says which CTAs hold parts of
+// this row's work item. Rows finished by a single CTA are skipped; rows of an
+// empty sequence (which no CTA visits) are written as zero.
+template <typename OT>
+__global__ void __launch_bounds__(kMergeThreads)
+merge_stream_kernel(const float* __restrict__ slots, const uint32_t* __restrict__ item_meta,
+                    const int32_t* __restrict__ sequence_lengths, uint32_t query_heads, uint32_t group,
+                    uint32_t heads_per_item, uint32_t value_head_size, uint32_t max_sequence_length,
+                    void* output, uint32_t emit_state) {
+  const uint32_t row = blockIdx.x;
+  const uint32_t seq = row / query_heads;
+  const uint32_t query_head = row % query_heads;
+  const uint32_t kv_head = query_head / group;
+  const uint32_t head_in_group = query_head % group;
+  const uint32_t head_chunks = (group + heads_per_item - 1) / heads_per_item;
+  const uint32_t items_per_sequence = (query_heads / group) * head_chunks;
+  const uint64_t item = (uint64_t)seq * items_per_sequence + (uint64_t)kv_head * head_chunks +
+                        head_in_group / heads_per_item;
+  const uint32_t stride = state_stride(value_head_size);
+  // three independent loads, issued together
+  const int32_t raw_length = __ldg(sequence_lengths + seq);
+  const uint32_t first_cta = item_meta[2 * item];
+  const uint32_t parts = item_meta[2 * item + 1];
+  if (clamp_length(raw_length, max_sequence_length) == 0) {
+    merge_row<OT>(slots, 0, 0, value_head_size, row, output, emit_state);
+    return;
   }
-  top = block_reduce(top, true, scratch);
-
-  float total = 0.0f;
-  if (top > -INFINITY) {
-    for (uint32_t i = threadIdx.x; i < parts; i += kMergeThreads) {
-      const float* state = base + (uint64_t)i * part_stride;
-      const float sum = state[value_head_size + 1];
-      if (sum > 0.0f) total += sum * exp2f((state[value_head_size] - top) * kLog2e);
-    }
-  }
-  total = block_reduce(total, false, scratch);
-
-  for (uint32_t dv = threadIdx.x; dv < value_head_size; dv += kMergeThreads) {
-    float acc = 0.0f;
-    if (top > -INFINITY) {
-      for (uint32_t i = 0; i < parts; ++i) {
-        const float* state = base + (uint64_t)i * part_stride;
-        if (state[value_head_size + 1] > 0.0f) {
-          acc += state[dv] * exp2f((state[value_head_size] - top) * kLog2e);
-        }
-      }
-    }
-    if (emit_state) {
-      float* out = static_cast<float*>(output) + (uint64_t)row * state_stride(value_head_size);
-      out[dv] = acc;
-      if (dv == 0) {
-        out[value_head_size] = top;
-        out[value_head_size + 1] = total;
-      }
-    } else {
-      narrow_store<OT>(static_cast<OT*>(output) + (uint64_t)row * value_head_size + dv,
-                       total > 0.0f ? acc / total : 0.0f);
-    }
-  }
+  if (parts <= 1) return;
+  const float* base = slots + ((item + first_cta) * heads_per_item + head_in_group % heads_per_item) * stride;
+  merge_row<OT>(base, parts, (uint64_t)heads_per_item * stride, value_head_size, row, output, emit_state);
 }
 
 // ================================================================= host
@@ -281,6 +322,36 @@ cudaError_t ensure_smem(Kernel kernel, int bytes, std::atomic<uint64_t>& done_ma
   return status;
 }
 
+// SMs of the current device (148 on a B200); 0 if no device can be queried.
+uint32_t current_sm_count() {
+  static std::atomic<uint32_t> cached[64];
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  if (device >= 0 && device < 64) {
+    const uint32_t known = cached[device].load(std::memory_order_acquire);
+    if (known != 0) return known;
+  }
+  int count = 0;
+  if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || count <= 0) {
+    cudaGetLastError();
+    return 0;
+  }
+  if (device >= 0 && device < 64) cached[device].store((uint32_t)count, std::memory_order_release);
+  return (uint32_t)count;
+}
+
+// CTAs of the balanced kernel: two per SM. Workspaces are sized for at least a
+// 148-SM device so that a size computed before a device is current still fits.
+constexpr uint32_t kStreamCtasPerSm = 2;
+uint32_t stream_ctas_for_launch() { return kStreamCtasPerSm * current_sm_count(); }
+uint32_t stream_ctas_for_sizing() {
+  const uint32_t sms = current_sm_count();
+  return kStreamCtasPerSm * (sms > 148 ? sms : 148);
+}
+
 template <typename QT, bool kFp8, int kD, int kNT>
 int launch_mma(const DecodeParams& p, cudaStream_t stream) {
   static std::atomic<uint64_t> configured{0};
@@ -293,9 +364,27 @@ int launch_mma(const DecodeParams& p, cudaStream_t stream) {
   return cudaGetLastError() == cudaSuccess ? LOOM_CUDA_SUCCESS : LOOM_CUDA_LAUNCH_ERROR;
 }
 
+template <typename QT, bool kFp8, int kD, int kNT>
+int launch_stream(const DecodeParams& p, uint32_t ctas, cudaStream_t stream) {
+  static std::atomic<uint64_t> configured{0};
+  constexpr int kBytes = StreamRing<kFp8, kD, kNT>::kSmemBytes;
+  auto kernel = decode_stream_kernel<QT, kFp8, kD, kNT>;
+  if (ensure_smem(kernel, kBytes, configured) != cudaSuccess) return LOOM_CUDA_LAUNCH_ERROR;
+  kernel<<<ctas, kMmaThreads, kBytes, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? LOOM_CUDA_SUCCESS : LOOM_CUDA_LAUNCH_ERROR;
+}
+
 template <typename QT, bool kFp8>
-int launch_mma_shape(const DecodeParams& p, cudaStream_t stream) {
+int launch_mma_shape(const DecodeParams& p, uint32_t stream_ctas, cudaStream_t stream) {
   const bool wide = p.group > 8;
+  if (stream_ctas != 0) {
+    if (p.head_size == 128) {
+      return wide ? launch_stream<QT, kFp8, 128, 2>(p, stream_ctas, stream)
+                  : launch_stream<QT, kFp8, 128, 1>(p, stream_ctas, stream);
+    }
+    return wide ? launch_stream<QT, kFp8, 64, 2>(p, stream_ctas, stream)
+                : launch_stream<QT, kFp8, 64, 1>(p, stream_ctas, stream);
+  }
   if (p.head_size == 128) {
     return wide ? launch_mma<QT, kFp8, 128, 2>(p, stream) : launch_mma<QT, kFp8, 128, 1>(p, stream);
   }
@@ -331,9 +420,9 @@ bool mma_route_fits(const LoomDecodeArgs& a, bool fp8) {
 
 uint32_t ceil_div(uint32_t a, uint32_t b) { return (a + b - 1) / b; }
 
-// Partition length the library picks when the caller does not: the longest of
-// {2048, ..., 64} that still yields enough CTAs to fill 148 SMs a few times
-// over, assuming every sequence were as long as the maximum.
+// Partition length of the fixed-partition kernels when the caller does not
+// choose: the longest of {2048, ..., 64} that still yields enough CTAs to fill
+// 148 SMs a few times over, assuming every sequence were as long as the maximum.
 uint32_t default_partition_tokens(uint32_t sequences, uint32_t kv_heads, uint32_t max_sequence_length) {
   constexpr uint64_t kWantedCtas = 148ull * 2 * 4;
   const uint64_t heads = (uint64_t)sequences * kv_heads;
@@ -343,17 +432,66 @@ uint32_t default_partition_tokens(uint32_t sequences, uint32_t kv_heads, uint32_
   return 64;
 }
 
-uint64_t workspace_elements(uint32_t sequences, uint32_t query_heads, uint32_t value_head_size,
-                            uint32_t max_sequence_length, uint32_t partition_tokens) {
+bool mul_checked(uint64_t a, uint64_t b, uint64_t* out) { return !__builtin_mul_overflow(a, b, out); }
+
+// F32 elements the fixed-partition path needs; 0 on bad arguments or overflow.
+uint64_t fixed_workspace_elements(uint32_t sequences, uint32_t query_heads, uint32_t value_head_size,
+                                  uint32_t max_sequence_length, uint32_t partition_tokens) {
   if (sequences == 0 || query_heads == 0 || value_head_size == 0 || max_sequence_length == 0 ||
       partition_tokens == 0 || partition_tokens % 16 != 0) {
     return 0;
   }
-  uint64_t total = (uint64_t)sequences * query_heads;  // < 2^64
-  const uint64_t parts = ceil_div(max_sequence_length, partition_tokens);
-  const uint64_t per_row = parts * ((uint64_t)value_head_size + 2);
-  if (per_row != 0 && total > std::numeric_limits<uint64_t>::max() / per_row) return 0;
-  return total * per_row;
+  uint64_t rows = 0, per_row = 0, total = 0;
+  if (!mul_checked(sequences, query_heads, &rows) ||
+      !mul_checked(ceil_div(max_sequence_length, partition_tokens), (uint64_t)value_head_size + 2, &per_row) ||
+      !mul_checked(rows, per_row, &total)) {
+    return 0;
+  }
+  return total;
+}
+
+struct StreamShape {
+  uint32_t heads_per_item;  // 8 or 16 query heads per work item
+  uint64_t items;           // sequences * kv_heads * head chunks
+  uint64_t slot_elements;   // F32 elements of the state slots
+  uint64_t total_elements;  // slots + item table
+};
+
+// Workspace of the balanced kernel: one state slot per (item + CTA), then two
+// 32-bit words per item. Returns false on overflow.
+bool stream_shape(uint32_t sequences, uint32_t query_heads, uint32_t kv_heads, uint32_t value_head_size,
+                  uint32_t ctas, StreamShape* shape) {
+  if (sequences == 0 || query_heads == 0 || kv_heads == 0 || value_head_size == 0 ||
+      query_heads % kv_heads != 0) {
+    return false;
+  }
+  const uint32_t group = query_heads / kv_heads;
+  shape->heads_per_item = group > 8 ? 16 : 8;
+  const uint32_t head_chunks = ceil_div(group, shape->heads_per_item);
+  uint64_t per_sequence = 0, per_slot = 0, meta = 0;
+  if (!mul_checked(kv_heads, head_chunks, &per_sequence) || !mul_checked(sequences, per_sequence, &shape->items) ||
+      !mul_checked(shape->heads_per_item, (uint64_t)value_head_size + 2, &per_slot) ||
+      shape->items > std::numeric_limits<uint64_t>::max() - ctas ||
+      !mul_checked(shape->items + ctas, per_slot, &shape->slot_elements) ||
+      !mul_checked(shape->items, 2, &meta) ||
+      shape->slot_elements > std::numeric_limits<uint64_t>::max() - meta) {
+    return false;
+  }
+  shape->total_elements = shape->slot_elements + meta;
+  return true;
+}
+
+// Size that serves whichever partitioned kernel the launch then picks.
+uint64_t auto_workspace_elements(uint32_t sequences, uint32_t query_heads, uint32_t kv_heads,
+                                 uint32_t value_head_size, uint32_t max_sequence_length) {
+  const uint64_t fixed = fixed_workspace_elements(
+      sequences, query_heads, value_head_size, max_sequence_length,
+      default_partition_tokens(sequences, kv_heads, max_sequence_length));
+  StreamShape shape{};
+  if (fixed == 0 || !stream_shape(sequences, query_heads, kv_heads, value_head_size, stream_ctas_for_sizing(), &shape)) {
+    return 0;
+  }
+  return fixed > shape.total_elements ? fixed : shape.total_elements;
 }
 
 bool product_fits_u64(std::initializer_list<uint64_t> dims) {
@@ -422,20 +560,34 @@ int launch_decode(const LoomDecodeArgs& a) {
   p.q_token = dense_query ? (uint64_t)a.query_heads * a.head_size : a.query_token_stride;
   p.scale_log2 = a.scale * kLog2e;
 
+  const bool use_mma = mma_route_fits(a, fp8);
   const bool partitioned = a.workspace != nullptr || a.workspace_elements != 0;
+  uint32_t stream_ctas = 0;  // non-zero selects the balanced kernel
+  StreamShape shape{};
   if (partitioned) {
-    const uint32_t tokens = a.partition_tokens != 0
-                                ? a.partition_tokens
-                                : default_partition_tokens(a.sequences, a.kv_heads, a.max_sequence_length);
-    const uint64_t needed =
-        workspace_elements(a.sequences, a.query_heads, a.value_head_size, a.max_sequence_length, tokens);
-    if (a.workspace == nullptr || needed == 0 || a.workspace_elements < needed ||
-        (reinterpret_cast<uintptr_t>(a.workspace) & 3u) != 0) {
+    if (a.workspace == nullptr || (reinterpret_cast<uintptr_t>(a.workspace) & 3u) != 0) {
       return LOOM_CUDA_INVALID_ARGUMENT;
     }
     p.partials = a.workspace;
-    p.partition_tokens = tokens;
-    p.max_partitions = ceil_div(a.max_sequence_length, tokens);
+    uint32_t tokens = a.partition_tokens;
+    if (tokens == 0 && use_mma && a.block_size % 16 == 0 && a.sequences <= kStreamMaxSequences) {
+      const uint32_t ctas = stream_ctas_for_launch();
+      if (ctas != 0 && stream_shape(a.sequences, a.query_heads, a.kv_heads, a.value_head_size, ctas, &shape) &&
+          a.workspace_elements >= shape.total_elements) {
+        stream_ctas = ctas;
+        p.item_meta = reinterpret_cast<uint32_t*>(a.workspace + shape.slot_elements);
+        p.partition_tokens = kStreamTileTokens;
+        p.max_partitions = 1;
+      }
+    }
+    if (stream_ctas == 0) {
+      if (tokens == 0) tokens = default_partition_tokens(a.sequences, a.kv_heads, a.max_sequence_length);
+      const uint64_t needed = fixed_workspace_elements(a.sequences, a.query_heads, a.value_head_size,
+                                                       a.max_sequence_length, tokens);
+      if (needed == 0 || a.workspace_elements < needed) return LOOM_CUDA_INVALID_ARGUMENT;
+      p.partition_tokens = tokens;
+      p.max_partitions = ceil_div(a.max_sequence_length, tokens);
+    }
   } else {
     p.partials = nullptr;
     p.partition_tokens = (a.max_sequence_length + 15u) & ~15u;
@@ -445,13 +597,15 @@ int launch_decode(const LoomDecodeArgs& a) {
 
   cudaStream_t stream = static_cast<cudaStream_t>(a.stream);
   int status;
-  if (mma_route_fits(a, fp8)) {
-    g_last_route = fp8 ? "mma16-fp8" : "mma16";
+  if (use_mma) {
+    g_last_route = stream_ctas != 0 ? (fp8 ? "mma16-fp8-balanced" : "mma16-balanced")
+                                    : (fp8 ? "mma16-fp8" : "mma16");
     if (a.dtype == 1) {
-      status = fp8 ? launch_mma_shape<__half, true>(p, stream) : launch_mma_shape<__half, false>(p, stream);
+      status = fp8 ? launch_mma_shape<__half, true>(p, stream_ctas, stream)
+                   : launch_mma_shape<__half, false>(p, stream_ctas, stream);
     } else {
-      status = fp8 ? launch_mma_shape<__nv_bfloat16, true>(p, stream)
-                   : launch_mma_shape<__nv_bfloat16, false>(p, stream);
+      status = fp8 ? launch_mma_shape<__nv_bfloat16, true>(p, stream_ctas, stream)
+                   : launch_mma_shape<__nv_bfloat16, false>(p, stream_ctas, stream);
     }
   } else {
     if (a.value_head_size > 32u * kScalarMaxValueRegs || a.query_heads > 65535u) return LOOM_CUDA_UNSUPPORTED;
@@ -469,22 +623,34 @@ int launch_decode(const LoomDecodeArgs& a) {
         break;
     }
   }
-  if (status != LOOM_CUDA_SUCCESS || !partitioned || p.max_partitions <= 1) return status;
+  if (status != LOOM_CUDA_SUCCESS || !partitioned) return status;
+  if (stream_ctas == 0 && p.max_partitions <= 1) return status;
 
-  // Second kernel: merge the partitions of every sequence that had several.
+  // Second kernel: merge the parts of every row that was split.
   const uint64_t rows = (uint64_t)p.sequences * p.query_heads;
   if (rows > 0x7fffffffull) return LOOM_CUDA_INVALID_ARGUMENT;
-  const uint64_t part_stride = state_stride(p.value_head_size);
-  const uint64_t row_stride = part_stride * p.max_partitions;
   const uint32_t grid = (uint32_t)rows;
+  if (stream_ctas != 0) {
+#define LOOM_MERGE(type)                                                                          \
+  merge_stream_kernel<type><<<grid, kMergeThreads, 0, stream>>>(                                 \
+      p.partials, p.item_meta, p.sequence_lengths, p.query_heads, p.group, shape.heads_per_item, \
+      p.value_head_size, p.max_sequence_length, p.output, p.emit_state)
+    if (p.emit_state || a.dtype == 0) LOOM_MERGE(float);
+    else if (a.dtype == 1) LOOM_MERGE(__half);
+    else LOOM_MERGE(__nv_bfloat16);
+#undef LOOM_MERGE
+  } else {
+    const uint64_t part_stride = state_stride(p.value_head_size);
+    const uint64_t row_stride = part_stride * p.max_partitions;
 #define LOOM_MERGE(type)                                                                        \
   merge_states_kernel<type><<<grid, kMergeThreads, 0, stream>>>(                               \
       p.partials, row_stride, part_stride, p.value_head_size, 0u, p.sequence_lengths,          \
       p.query_heads, p.partition_tokens, p.max_sequence_length, p.output, p.emit_state)
-  if (p.emit_state || a.dtype == 0) LOOM_MERGE(float);
-  else if (a.dtype == 1) LOOM_MERGE(__half);
-  else LOOM_MERGE(__nv_bfloat16);
+    if (p.emit_state || a.dtype == 0) LOOM_MERGE(float);
+    else if (a.dtype == 1) LOOM_MERGE(__half);
+    else LOOM_MERGE(__nv_bfloat16);
 #undef LOOM_MERGE
+  }
   return cudaGetLastError() == cudaSuccess ? LOOM_CUDA_SUCCESS : LOOM_CUDA_LAUNCH_ERROR;
 }
 
@@ -589,9 +755,10 @@ extern "C" uint64_t loom_cuda_paged_decode_attention_split_k_workspace_elements(
       max_sequence_length == 0 || query_heads % kv_heads != 0) {
     return 0;
   }
-  const uint32_t tokens = loom_decode::default_partition_tokens(sequences, kv_heads, max_sequence_length);
-  if (max_sequence_length <= tokens) return 0;  // one partition: use the workspace-free entry point
-  return loom_decode::workspace_elements(sequences, query_heads, value_head_size, max_sequence_length, tokens);
+  // Short contexts are served by one pass per (sequence, KV head).
+  if (max_sequence_length <= 256) return 0;
+  return loom_decode::auto_workspace_elements(sequences, query_heads, kv_heads, value_head_size,
+                                              max_sequence_length);
 }
 
 extern "C" uint32_t loom_cuda_paged_decode_default_partition_tokens(uint32_t sequences, uint32_t kv_heads,
@@ -601,11 +768,16 @@ extern "C" uint32_t loom_cuda_paged_decode_default_partition_tokens(uint32_t seq
 }
 
 extern "C" uint64_t loom_cuda_paged_decode_workspace_elements(uint32_t sequences, uint32_t query_heads,
-                                                              uint32_t value_head_size,
+                                                              uint32_t kv_heads, uint32_t value_head_size,
                                                               uint32_t max_sequence_length,
                                                               uint32_t partition_tokens) {
-  return loom_decode::workspace_elements(sequences, query_heads, value_head_size, max_sequence_length,
-                                         partition_tokens);
+  if (kv_heads == 0 || query_heads % kv_heads != 0) return 0;
+  if (partition_tokens == 0) {
+    return loom_decode::auto_workspace_elements(sequences, query_heads, kv_heads, value_head_size,
+                                                max_sequence_length);
+  }
+  return loom_decode::fixed_workspace_elements(sequences, query_heads, value_head_size, max_sequence_length,
+                                               partition_tokens);
 }
 
 extern "C" int loom_cuda_paged_decode_attention_ex(const LoomDecodeArgs* args) {

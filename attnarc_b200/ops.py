@@ -285,7 +285,7 @@ def paged_decode_attention_ex(
         needed, tokens = decode_workspace_elements_ex(sequences, query_heads, kv_heads, value_head_size,
                                                       int(max_sequence_length), partition_tokens)
         if split is None:
-            split = max_sequence_length > tokens
+            split = max_sequence_length > (tokens if tokens else 256)
         if split:
             if workspace is None or workspace.numel() < needed:
                 workspace = torch.empty(needed, device=query.device, dtype=torch.float32)
@@ -307,7 +307,7 @@ def paged_decode_attention_ex(
             sequences, query_heads, kv_heads, head_size, value_head_size, num_blocks, block_size,
             key_cache.stride(0), key_cache.stride(1), key_cache.stride(2),
             value_cache.stride(0), value_cache.stride(1), value_cache.stride(2),
-            block_tables.shape[1], int(max_sequence_length), tokens if split else 0, float(scale),
+            block_tables.shape[1], int(max_sequence_length), partition_tokens if split else 0, float(scale),
             1 if emit_state else 0,
             0 if query.is_contiguous() else query.stride(0), 0 if query.is_contiguous() else query.stride(1),
             _stream(query.device),

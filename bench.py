@@ -376,18 +376,24 @@ def run_b200(args):
         torch.cuda.synchronize()
     graph_ms = start.elapsed_time(stop)
 
-    # ---- the decode launch on its own, for the roofline ----------------------
-    decode_events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
-                     for _ in range(args.steps)]
+    # ---- the decode operator on its own, for the roofline ---------------------
+    # A second graph with only the K decode calls (partition kernel + merge
+    # kernel each), timed by CUDA events on the stream that launches it.
+    decode_graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        queries = [qkv_views(qkv_steps[index])[0] for index in range(copies)]
+        with torch.cuda.graph(decode_graph, stream=stream):
+            for k in range(args.steps):
+                decode_step(k % copies, queries[k % copies])
     barrier()
-    for k in range(args.steps):
-        index = k % copies
-        q = write_step(index)
-        decode_events[k][0].record()
-        decode_step(index, q)
-        decode_events[k][1].record()
-    torch.cuda.synchronize()
-    decode_ms = statistics.mean(a.elapsed_time(b) for a, b in decode_events)
+    decode_graph.replay()
+    barrier()
+    decode_start, decode_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    decode_start.record()
+    decode_graph.replay()
+    decode_stop.record()
+    barrier()
+    decode_ms = decode_start.elapsed_time(decode_stop) / args.steps
 
     # ---- end to end through the public API with host buffers ----------------
     host_qkv = pristine_qkv.cpu().pin_memory()

@@ -162,7 +162,8 @@ typedef struct LoomDecodeArgs {
   uint64_t workspace_elements;
   uint32_t sequences, query_heads, kv_heads, head_size, value_head_size;
   uint32_t num_blocks, block_size, max_blocks_per_sequence, max_sequence_length;
-  uint32_t partition_tokens; /* 0 = let the library choose; else multiple of 16 */
+  uint32_t partition_tokens; /* 0 = balanced persistent kernel where possible; */
+                             /* else fixed partitions of this multiple of 16   */
   uint64_t key_block_stride, key_page_stride, key_head_stride;
   uint64_t value_block_stride, value_page_stride, value_head_stride;
   /* Element strides of `query` between sequences and between heads; 0 and 0
@@ -175,18 +176,23 @@ typedef struct LoomDecodeArgs {
   void* stream;
 } LoomDecodeArgs;
 
-/* Partition length (tokens) the library would choose for this shape. */
+/* Partition length (tokens) the fixed-partition kernels default to. */
 uint32_t loom_cuda_paged_decode_default_partition_tokens(
     uint32_t sequences, uint32_t kv_heads, uint32_t max_sequence_length);
 
 /*
- * F32 workspace elements for a partitioned decode with the given partition
+ * F32 workspace elements of a partitioned decode. partition_tokens 0 sizes for
+ * the library's own choice (the balanced persistent kernel when the shape
+ * allows it, fixed partitions of the default length otherwise; the size
+ * covers both). A non-zero multiple of 16 sizes for fixed partitions of that
  * length: sequences * query_heads * ceil(max_sequence_length / partition) *
  * (value_head_size + 2). Returns 0 if the arguments are invalid or overflow.
+ * The balanced kernel's share depends on the SM count of the current device.
  */
 uint64_t loom_cuda_paged_decode_workspace_elements(
-    uint32_t sequences, uint32_t query_heads, uint32_t value_head_size,
-    uint32_t max_sequence_length, uint32_t partition_tokens);
+    uint32_t sequences, uint32_t query_heads, uint32_t kv_heads,
+    uint32_t value_head_size, uint32_t max_sequence_length,
+    uint32_t partition_tokens);
 
 /* General decode: any stride order, native or FP8 cache, optional workspace. */
 int loom_cuda_paged_decode_attention_ex(const LoomDecodeArgs* args);

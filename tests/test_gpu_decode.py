@@ -85,11 +85,21 @@ def test_reference_shape_matrix(ops, dtype, shape):
                                           max_sequence_length=max(lengths), scale=scale,
                                           partition_tokens=64, split=True)
     helpers.assert_close(split, expected, dtype, "partitioned path")
+    # and through the library's own choice of partitioned kernel (balanced where it applies)
+    balanced = ops.paged_decode_attention_ex(query, key_cache, value_cache, tables, seq_lens,
+                                             max_sequence_length=max(lengths), scale=scale, split=True)
+    helpers.assert_close(balanced, expected, dtype, "balanced path")
 
 
 def test_expected_kernel_routes(ops):
     query, key_cache, value_cache, tables, seq_lens = make_case(torch.bfloat16, 2, 8, 2, 128, 128, 16, [40, 70], 1)
     ops.paged_decode_attention(query, key_cache, value_cache, tables, seq_lens, max_sequence_length=70)
+    assert ops.last_decode_route() == "mma16"
+    ops.paged_decode_attention_ex(query, key_cache, value_cache, tables, seq_lens, max_sequence_length=70,
+                                  split=True)
+    assert ops.last_decode_route() == "mma16-balanced"
+    ops.paged_decode_attention_ex(query, key_cache, value_cache, tables, seq_lens, max_sequence_length=70,
+                                  split=True, partition_tokens=32)
     assert ops.last_decode_route() == "mma16"
     query, key_cache, value_cache, tables, seq_lens = make_case(torch.float32, 2, 8, 2, 128, 128, 16, [40, 70], 1)
     ops.paged_decode_attention(query, key_cache, value_cache, tables, seq_lens, max_sequence_length=70)
@@ -164,12 +174,12 @@ def test_layouts_groups_and_partitions(ops, layout, dtype, group):
     query = case.query.contiguous()
     expected = helpers.oracle_decode(query, key_cache, value_cache, case.block_tables, case.sequence_lengths,
                                      scale=case.scale, max_sequence_length=case.max_sequence_length)
-    for partition in (0, 128, 256):
+    for partition, split in ((0, False), (0, True), (128, True), (256, True)):
         actual = ops.paged_decode_attention_ex(query, key_cache, value_cache, case.block_tables,
                                                case.sequence_lengths,
                                                max_sequence_length=case.max_sequence_length, scale=case.scale,
-                                               partition_tokens=partition, split=partition != 0)
-        helpers.assert_close(actual, expected, config.torch_dtype, f"{layout} partition={partition}")
+                                               partition_tokens=partition, split=split)
+        helpers.assert_close(actual, expected, config.torch_dtype, f"{layout} partition={partition} split={split}")
 
 
 @pytest.mark.parametrize("granularity", ["tensor", "head"])
@@ -184,13 +194,14 @@ def test_fp8_cache_dequantised_on_load(ops, granularity, dtype, layout):
     expected = helpers.oracle_decode(query, key_cache, value_cache, case.block_tables, case.sequence_lengths,
                                      scale=case.scale, max_sequence_length=case.max_sequence_length,
                                      key_scales=case.key_scales, value_scales=case.value_scales)
-    for partition in (0, 256):
+    for partition, split in ((0, False), (0, True), (256, True)):
         actual = ops.paged_decode_attention_ex(query, key_cache, value_cache, case.block_tables,
                                                case.sequence_lengths,
                                                max_sequence_length=case.max_sequence_length, scale=case.scale,
                                                key_scales=case.key_scales, value_scales=case.value_scales,
-                                               partition_tokens=partition, split=partition != 0)
-        helpers.assert_close(actual, expected, config.torch_dtype, f"fp8 {granularity} partition={partition}")
+                                               partition_tokens=partition, split=split)
+        helpers.assert_close(actual, expected, config.torch_dtype,
+                             f"fp8 {granularity} partition={partition} split={split}")
     expected_route = "scalar-fp8" if dtype == "f32" else "mma16-fp8"
     assert ops.last_decode_route() == expected_route
 
@@ -205,7 +216,8 @@ def test_block_sizes_and_head_sizes(ops, head_size, block_size):
                                      max_sequence_length=max(lengths))
     actual = ops.paged_decode_attention(query, key_cache, value_cache, tables, seq_lens,
                                         max_sequence_length=max(lengths), scale=0.1)
-    assert ops.last_decode_route() == "mma16"
+    # blocks of a multiple of 16 tokens take the balanced kernel, others fixed partitions
+    assert ops.last_decode_route() == ("mma16-balanced" if block_size % 16 == 0 else "mma16")
     helpers.assert_close(actual, expected, torch.bfloat16, f"block_size={block_size}")
 
 
@@ -255,6 +267,11 @@ def test_partial_states_merge_to_the_same_answer(ops):
                                           emit_state=True, split=False)
     merged_one = ops.merge_decode_states(whole.reshape(1, -1, whole.shape[-1]).contiguous(), torch.bfloat16)
     helpers.assert_close(merged_one.reshape(expected.shape), expected, torch.bfloat16, "single state")
+    balanced = ops.paged_decode_attention_ex(query, key_cache, value_cache, tables, lengths,
+                                             max_sequence_length=case.max_sequence_length, scale=case.scale,
+                                             emit_state=True, split=True)
+    merged_two = ops.merge_decode_states(balanced.reshape(1, -1, balanced.shape[-1]).contiguous(), torch.bfloat16)
+    helpers.assert_close(merged_two.reshape(expected.shape), expected, torch.bfloat16, "balanced state")
 
 
 def test_cfg1_f32_oracle_case(ops):
@@ -337,6 +354,10 @@ def test_long_context_properties_at_full_length(ops):
     single = ops.paged_decode_attention_ex(query, key_cache, value_cache, tables, lens, max_sequence_length=length,
                                            split=False)
     helpers.assert_close(split, single, torch.bfloat16, "split vs single pass")
+    balanced = ops.paged_decode_attention_ex(query, key_cache, value_cache, tables, lens,
+                                             max_sequence_length=length, split=True)
+    assert ops.last_decode_route() == "mma16-balanced"
+    helpers.assert_close(balanced, single, torch.bfloat16, "balanced vs single pass")
 
     shuffle = torch.randperm(blocks + 3, device=DEVICE)
     moved_k, moved_v = torch.empty_like(key_cache), torch.empty_like(value_cache)
