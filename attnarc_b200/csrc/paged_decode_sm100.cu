@@ -36,6 +36,7 @@
 #include "decode_common.cuh"
 #include "decode_mma.cuh"
 #include "decode_stream.cuh"
+#include "decode_stream_tma.cuh"
 
 namespace loom_decode {
 
@@ -374,9 +375,111 @@ int launch_stream(const DecodeParams& p, uint32_t ctas, cudaStream_t stream) {
   return cudaGetLastError() == cudaSuccess ? LOOM_CUDA_SUCCESS : LOOM_CUDA_LAUNCH_ERROR;
 }
 
+// ---- tensor maps for the TMA-fed kernel ---------------------------------------
+
+struct CacheMaps {
+  CUtensorMap key, value;
+  TmaAxes axes;
+};
+
+using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// cuTensorMapEncodeTiled, fetched through the runtime so that the library does
+// not link against libcuda. Null if the driver does not offer it.
+EncodeTiled tensor_map_encoder() {
+  static const EncodeTiled encoder = [] {
+    void* symbol = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &symbol, cudaEnableDefault, &result) != cudaSuccess ||
+        result != cudaDriverEntryPointSuccess) {
+      cudaGetLastError();
+      symbol = nullptr;
+    }
+    return reinterpret_cast<EncodeTiled>(symbol);
+  }();
+  return encoder;
+}
+
+// 0 = TMA where possible, 1 = always cp.async (for comparisons and as a guard).
+std::atomic<uint32_t> g_copy_engine{0};
+
+// Describes one cache as a 4-D byte tensor: (row bytes, then head / page / block
+// sorted by stride). Box: up to 128 bytes of a row, 16 pages, one head, one block.
+bool encode_cache_map(CUtensorMap* map, const void* base, uint32_t row_bytes, const uint64_t (&sizes)[3],
+                      const uint64_t (&strides_bytes)[3], const uint32_t (&order)[3]) {
+  const EncodeTiled encode = tensor_map_encoder();
+  if (encode == nullptr) return false;
+  cuuint64_t dims[4] = {row_bytes, 0, 0, 0};
+  cuuint64_t strides[3] = {0, 0, 0};
+  cuuint32_t box[4] = {row_bytes > 128 ? 128u : row_bytes, 1, 1, 1};
+  cuuint32_t element_strides[4] = {1, 1, 1, 1};
+  for (int position = 0; position < 3; ++position) {
+    const uint32_t which = order[position];  // 0 = head, 1 = page, 2 = block
+    dims[position + 1] = sizes[which];
+    strides[position] = strides_bytes[which];
+    if (which == 1) box[position + 1] = 16;
+    if (strides[position] % 16 != 0 || strides[position] >= (1ull << 40)) return false;
+  }
+  const CUtensorMapSwizzle swizzle = row_bytes >= 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+  return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(base), dims, strides, box,
+                element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool build_cache_maps(const LoomDecodeArgs& a, bool fp8, CacheMaps* maps) {
+  const uint64_t elem = fp8 ? 1 : 2;
+  const uint32_t row_bytes = (uint32_t)(a.head_size * elem);
+  if (row_bytes != 64 && row_bytes != 128 && row_bytes != 256) return false;
+  const uint64_t sizes[3] = {a.kv_heads, a.block_size, a.num_blocks};
+  const uint64_t key_strides[3] = {a.key_head_stride * elem, a.key_page_stride * elem, a.key_block_stride * elem};
+  const uint64_t value_strides[3] = {a.value_head_stride * elem, a.value_page_stride * elem,
+                                     a.value_block_stride * elem};
+  // order the outer dimensions by the key cache's strides; the value cache must agree
+  uint32_t order[3] = {0, 1, 2};
+  for (int i = 0; i < 3; ++i) {
+    for (int j = i + 1; j < 3; ++j) {
+      if (key_strides[order[j]] < key_strides[order[i]]) {
+        const uint32_t swap = order[i];
+        order[i] = order[j];
+        order[j] = swap;
+      }
+    }
+  }
+  for (int i = 0; i + 1 < 3; ++i) {
+    if (value_strides[order[i]] > value_strides[order[i + 1]]) return false;
+  }
+  for (uint32_t position = 0; position < 3; ++position) {
+    if (order[position] == 0) maps->axes.head = position + 1;
+    if (order[position] == 1) maps->axes.page = position + 1;
+    if (order[position] == 2) maps->axes.block = position + 1;
+  }
+  return encode_cache_map(&maps->key, a.key_cache, row_bytes, sizes, key_strides, order) &&
+         encode_cache_map(&maps->value, a.value_cache, row_bytes, sizes, value_strides, order);
+}
+
+template <typename QT, bool kFp8, int kD, int kNT>
+int launch_stream_tma(const DecodeParams& p, uint32_t ctas, const CacheMaps& maps, cudaStream_t stream) {
+  static std::atomic<uint64_t> configured{0};
+  constexpr int kBytes = TmaRing<kFp8, kD, kNT>::kSmemBytes;
+  auto kernel = decode_stream_tma_kernel<QT, kFp8, kD, kNT>;
+  if (ensure_smem(kernel, kBytes, configured) != cudaSuccess) return LOOM_CUDA_LAUNCH_ERROR;
+  kernel<<<ctas, kMmaThreads, kBytes, stream>>>(p, maps.key, maps.value, maps.axes);
+  return cudaGetLastError() == cudaSuccess ? LOOM_CUDA_SUCCESS : LOOM_CUDA_LAUNCH_ERROR;
+}
+
 template <typename QT, bool kFp8>
-int launch_mma_shape(const DecodeParams& p, uint32_t stream_ctas, cudaStream_t stream) {
+int launch_mma_shape(const DecodeParams& p, uint32_t stream_ctas, const CacheMaps* maps, cudaStream_t stream) {
   const bool wide = p.group > 8;
+  if (stream_ctas != 0 && maps != nullptr) {
+    if (p.head_size == 128) {
+      return wide ? launch_stream_tma<QT, kFp8, 128, 2>(p, stream_ctas, *maps, stream)
+                  : launch_stream_tma<QT, kFp8, 128, 1>(p, stream_ctas, *maps, stream);
+    }
+    return wide ? launch_stream_tma<QT, kFp8, 64, 2>(p, stream_ctas, *maps, stream)
+                : launch_stream_tma<QT, kFp8, 64, 1>(p, stream_ctas, *maps, stream);
+  }
   if (stream_ctas != 0) {
     if (p.head_size == 128) {
       return wide ? launch_stream<QT, kFp8, 128, 2>(p, stream_ctas, stream)
@@ -598,14 +701,20 @@ int launch_decode(const LoomDecodeArgs& a) {
   cudaStream_t stream = static_cast<cudaStream_t>(a.stream);
   int status;
   if (use_mma) {
-    g_last_route = stream_ctas != 0 ? (fp8 ? "mma16-fp8-balanced" : "mma16-balanced")
-                                    : (fp8 ? "mma16-fp8" : "mma16");
+    CacheMaps maps;
+    const CacheMaps* tma = nullptr;
+    if (stream_ctas != 0 && g_copy_engine.load(std::memory_order_relaxed) == 0 && build_cache_maps(a, fp8, &maps)) {
+      tma = &maps;
+    }
+    if (stream_ctas == 0) g_last_route = fp8 ? "mma16-fp8" : "mma16";
+    else if (tma != nullptr) g_last_route = fp8 ? "mma16-fp8-balanced-tma" : "mma16-balanced-tma";
+    else g_last_route = fp8 ? "mma16-fp8-balanced" : "mma16-balanced";
     if (a.dtype == 1) {
-      status = fp8 ? launch_mma_shape<__half, true>(p, stream_ctas, stream)
-                   : launch_mma_shape<__half, false>(p, stream_ctas, stream);
+      status = fp8 ? launch_mma_shape<__half, true>(p, stream_ctas, tma, stream)
+                   : launch_mma_shape<__half, false>(p, stream_ctas, tma, stream);
     } else {
-      status = fp8 ? launch_mma_shape<__nv_bfloat16, true>(p, stream_ctas, stream)
-                   : launch_mma_shape<__nv_bfloat16, false>(p, stream_ctas, stream);
+      status = fp8 ? launch_mma_shape<__nv_bfloat16, true>(p, stream_ctas, tma, stream)
+                   : launch_mma_shape<__nv_bfloat16, false>(p, stream_ctas, tma, stream);
     }
   } else {
     if (a.value_head_size > 32u * kScalarMaxValueRegs || a.query_heads > 65535u) return LOOM_CUDA_UNSUPPORTED;
@@ -833,3 +942,27 @@ extern "C" int loom_cuda_supports_paged_decode(uint32_t dtype, uint32_t cache_en
 }
 
 extern "C" const char* loom_cuda_last_decode_route(void) { return loom_decode::g_last_route; }
+
+extern "C" int loom_cuda_set_decode_copy_engine(uint32_t engine) {
+  if (engine > 1) return LOOM_CUDA_INVALID_ARGUMENT;
+  loom_decode::g_copy_engine.store(engine, std::memory_order_relaxed);
+  return LOOM_CUDA_SUCCESS;
+}
+
+extern "C" int loom_cuda_decode_timeout_flag(uint32_t* value, uint32_t reset) {
+  if (value == nullptr) return LOOM_CUDA_INVALID_ARGUMENT;
+  unsigned int flag = 0;
+  if (cudaMemcpyFromSymbol(&flag, loom_decode::g_decode_timeout_flag, sizeof(flag)) != cudaSuccess) {
+    cudaGetLastError();
+    return LOOM_CUDA_LAUNCH_ERROR;
+  }
+  *value = flag;
+  if (reset != 0 && flag != 0) {
+    const unsigned int zero = 0;
+    if (cudaMemcpyToSymbol(loom_decode::g_decode_timeout_flag, &zero, sizeof(zero)) != cudaSuccess) {
+      cudaGetLastError();
+      return LOOM_CUDA_LAUNCH_ERROR;
+    }
+  }
+  return LOOM_CUDA_SUCCESS;
+}

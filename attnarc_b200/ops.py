@@ -55,6 +55,23 @@ def last_decode_route() -> str:
     return library().loom_cuda_last_decode_route().decode()
 
 
+def set_decode_copy_engine(engine: str) -> None:
+    """``"tma"`` (default) or ``"cp_async"``: how the balanced kernel fills its rings."""
+    code = {"tma": 0, "cp_async": 1}[engine]
+    if library().loom_cuda_set_decode_copy_engine(code) != 0:
+        raise RuntimeError("could not select the decode copy engine")
+
+
+def decode_timeout_flag(device=None, reset: bool = False) -> int:
+    """Non-zero if a bounded wait inside the TMA-fed kernel ever expired on the device."""
+    value = _native.u32(0)
+    with torch.cuda.device(device if device is not None else torch.cuda.current_device()):
+        status = library().loom_cuda_decode_timeout_flag(value, 1 if reset else 0)
+    if status != 0:
+        raise RuntimeError("could not read the decode timeout flag")
+    return int(value.value)
+
+
 def _require_inference_tensors(*tensors: torch.Tensor) -> None:
     for tensor in tensors:
         if tensor.requires_grad:

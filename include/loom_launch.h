@@ -229,6 +229,22 @@ int loom_cuda_supports_paged_decode(uint32_t dtype, uint32_t cache_encoding,
  * ("mma16", "scalar", ...); for tests and profiling notes. */
 const char* loom_cuda_last_decode_route(void);
 
+/*
+ * How the balanced decode kernel fills its shared-memory rings: 0 (default)
+ * uses the Tensor Memory Accelerator whenever the cache can be described by a
+ * tensor map, 1 always uses per-lane cp.async copies. Process-wide; meant for
+ * comparisons and as a switch to fall back on.
+ */
+int loom_cuda_set_decode_copy_engine(uint32_t engine);
+
+/*
+ * The TMA-fed kernel bounds every wait on a copy; if one ever expires it sets a
+ * flag on the device instead of hanging. This reads the flag of the current
+ * device into *value (0 = never happened) and optionally clears it. Unlike the
+ * launch functions this call synchronises with the device.
+ */
+int loom_cuda_decode_timeout_flag(uint32_t* value, uint32_t reset);
+
 #ifdef __cplusplus
 }
 #endif

@@ -97,7 +97,7 @@ def test_expected_kernel_routes(ops):
     assert ops.last_decode_route() == "mma16"
     ops.paged_decode_attention_ex(query, key_cache, value_cache, tables, seq_lens, max_sequence_length=70,
                                   split=True)
-    assert ops.last_decode_route() == "mma16-balanced"
+    assert ops.last_decode_route() == "mma16-balanced-tma"
     ops.paged_decode_attention_ex(query, key_cache, value_cache, tables, seq_lens, max_sequence_length=70,
                                   split=True, partition_tokens=32)
     assert ops.last_decode_route() == "mma16"
@@ -217,7 +217,7 @@ def test_block_sizes_and_head_sizes(ops, head_size, block_size):
     actual = ops.paged_decode_attention(query, key_cache, value_cache, tables, seq_lens,
                                         max_sequence_length=max(lengths), scale=0.1)
     # blocks of a multiple of 16 tokens take the balanced kernel, others fixed partitions
-    assert ops.last_decode_route() == ("mma16-balanced" if block_size % 16 == 0 else "mma16")
+    assert ops.last_decode_route() == ("mma16-balanced-tma" if block_size % 16 == 0 else "mma16")
     helpers.assert_close(actual, expected, torch.bfloat16, f"block_size={block_size}")
 
 
@@ -356,7 +356,7 @@ def test_long_context_properties_at_full_length(ops):
     helpers.assert_close(split, single, torch.bfloat16, "split vs single pass")
     balanced = ops.paged_decode_attention_ex(query, key_cache, value_cache, tables, lens,
                                              max_sequence_length=length, split=True)
-    assert ops.last_decode_route() == "mma16-balanced"
+    assert ops.last_decode_route() == "mma16-balanced-tma"
     helpers.assert_close(balanced, single, torch.bfloat16, "balanced vs single pass")
 
     shuffle = torch.randperm(blocks + 3, device=DEVICE)
@@ -383,3 +383,39 @@ def test_launch_counter_and_error_text(ops):
         ops.paged_decode_attention_out(query, key_cache, value_cache, tables, seq_lens, query,
                                        max_sequence_length=200)
     assert ops.launch_count(ops.Operator.PAGED_DECODE_ATTENTION) == 1  # failures are not counted
+
+
+@pytest.mark.parametrize("engine", ["cp_async", "tma"])
+@pytest.mark.parametrize("cache", ["native", "fp8"])
+@pytest.mark.parametrize("layout", ["NHD", "HND"])
+@pytest.mark.parametrize("head_size", [64, 128])
+def test_both_copy_engines_of_the_balanced_kernel(ops, engine, cache, layout, head_size):
+    # ragged lengths: partial last pages, tiles with idle warps, items split over CTAs
+    config = workloads.DecodeConfig("t", 7, 16, 2, head_size=head_size, dtype="bf16", cache=cache, layout=layout,
+                                    lengths=("fixed", [1, 15, 16, 17, 63, 65, 3000]))
+    case = workloads.build_case(config, DEVICE, seed=31)
+    key_cache, value_cache = case.cache_views()
+    query = case.query  # strided view of the packed QKV row
+    scales = dict(key_scales=case.key_scales, value_scales=case.value_scales) if cache == "fp8" else {}
+    expected = helpers.oracle_decode(query, key_cache, value_cache, case.block_tables, case.sequence_lengths,
+                                     scale=case.scale, max_sequence_length=case.max_sequence_length, **scales)
+    # stale contents after the end of each sequence must not matter to either engine
+    poisoned_k, poisoned_v = key_cache.clone(), value_cache.clone()
+    if cache == "native":
+        for s, length in enumerate(case.lengths.tolist()):
+            if length % 16:
+                block = int(case.block_tables[s, (length - 1) // 16])
+                poisoned_k[block, length % 16:] = float("nan")
+                poisoned_v[block, length % 16:] = float("nan")
+    ops.set_decode_copy_engine(engine)
+    try:
+        actual = ops.paged_decode_attention_ex(query, poisoned_k, poisoned_v, case.block_tables,
+                                               case.sequence_lengths,
+                                               max_sequence_length=case.max_sequence_length, scale=case.scale,
+                                               split=True, **scales)
+        route = ops.last_decode_route()
+    finally:
+        ops.set_decode_copy_engine("tma")
+    assert route.endswith("-tma") == (engine == "tma")
+    helpers.assert_close(actual, expected, torch.bfloat16, f"{engine} {cache} {layout} D={head_size}")
+    assert ops.decode_timeout_flag() == 0
