@@ -29,6 +29,7 @@
 #include <atomic>
 #include <cmath>
 #include <cstdint>
+#include <cstdio>
 #include <limits>
 #include <type_traits>
 
@@ -808,6 +809,51 @@ int launch_reference_abi(uint32_t dtype, const void* query, const void* key_cach
   return launch_decode(a);
 }
 
+// ---- scratch that lives inside the library ---------------------------------------
+//
+// Some callers of a partitioned decode cannot hand over a workspace because they
+// have no way to get device memory at that point: an engine that sized and
+// claimed all of its GPU memory at start-up and treats any later allocation as a
+// bug, a request handler that must not risk the device-wide stall an allocation
+// can cause, or a plug-in host that gives extensions input and output buffers
+// and nothing else. For them the library keeps one fixed block of device memory
+// of its own. Every GPU that loads the library pays for it (16 MiB) until the
+// process exits, which is why it is small and why larger shapes are refused.
+constexpr uint64_t kBuiltInScratchFloats = 4ull << 20;  // 4 Mi floats = 16 MiB
+static __device__ __align__(256) float g_built_in_scratch[kBuiltInScratchFloats];
+
+// `g_built_in_scratch` in host code is only a handle for the runtime, not an
+// address a kernel can use. The device address is asked for once per device,
+// with that device current, and remembered.
+float* built_in_scratch_address(cudaError_t* failure) {
+  static std::atomic<float*> known[64];
+  int device = 0;
+  cudaError_t status = cudaGetDevice(&device);
+  if (status != cudaSuccess) {
+    *failure = status;
+    return nullptr;
+  }
+  const bool cacheable = device >= 0 && device < 64;
+  if (cacheable) {
+    float* address = known[device].load(std::memory_order_acquire);
+    if (address != nullptr) return address;
+  }
+  float* address = nullptr;
+  status = cudaGetSymbolAddress(reinterpret_cast<void**>(&address), g_built_in_scratch);
+  if (status != cudaSuccess || address == nullptr) {
+    *failure = status != cudaSuccess ? status : cudaErrorInvalidSymbol;
+    cudaGetLastError();
+    return nullptr;
+  }
+  if (cacheable) known[device].store(address, std::memory_order_release);
+  return address;
+}
+
+void explain(char* text, uint64_t capacity, const char* format, unsigned long long a = 0,
+             unsigned long long b = 0) {
+  if (text != nullptr && capacity != 0) std::snprintf(text, (size_t)capacity, format, a, b);
+}
+
 }  // namespace loom_decode
 
 // ================================================================ C ABI
@@ -965,4 +1011,52 @@ extern "C" int loom_cuda_decode_timeout_flag(uint32_t* value, uint32_t reset) {
     }
   }
   return LOOM_CUDA_SUCCESS;
+}
+
+// Partitioned decode for callers that cannot allocate: identical to
+// loom_cuda_paged_decode_attention_ex, except that the partial states go into
+// the library's own fixed block of device memory instead of a caller workspace
+// (args->workspace and args->workspace_elements are ignored). Nothing is
+// allocated or freed here or anywhere below this call.
+extern "C" int loom_cuda_paged_decode_attention_built_in_scratch(const LoomDecodeArgs* args, char* error_text,
+                                                                  uint64_t error_capacity) {
+  using namespace loom_decode;
+  explain(error_text, error_capacity, "ok");
+  if (args == nullptr || args->struct_size != sizeof(LoomDecodeArgs) || args->partition_tokens % 16 != 0 ||
+      args->kv_heads == 0 || args->query_heads % args->kv_heads != 0) {
+    explain(error_text, error_capacity, "decode arguments are not well formed");
+    return LOOM_CUDA_INVALID_ARGUMENT;
+  }
+  const uint64_t needed =
+      args->partition_tokens == 0
+          ? auto_workspace_elements(args->sequences, args->query_heads, args->kv_heads, args->value_head_size,
+                                    args->max_sequence_length)
+          : fixed_workspace_elements(args->sequences, args->query_heads, args->value_head_size,
+                                     args->max_sequence_length, args->partition_tokens);
+  if (needed == 0) {
+    explain(error_text, error_capacity, "decode shape is empty or its scratch size overflows");
+    return LOOM_CUDA_INVALID_ARGUMENT;
+  }
+  if (needed > kBuiltInScratchFloats) {
+    explain(error_text, error_capacity,
+            "this decode needs %llu F32 elements of scratch but the built-in block holds %llu; "
+            "pass a workspace to loom_cuda_paged_decode_attention_ex instead",
+            (unsigned long long)needed, (unsigned long long)kBuiltInScratchFloats);
+    return LOOM_CUDA_UNSUPPORTED;
+  }
+  cudaError_t failure = cudaSuccess;
+  float* scratch = built_in_scratch_address(&failure);
+  if (scratch == nullptr) {
+    explain(error_text, error_capacity, "the address of the built-in scratch block is unavailable (CUDA error %llu)",
+            (unsigned long long)failure);
+    return LOOM_CUDA_UNAVAILABLE;
+  }
+  // Every word of the block that the merge kernel reads is written by the decode
+  // kernel of this same call, so nothing has to be cleared between calls.
+  LoomDecodeArgs with_scratch = *args;
+  with_scratch.workspace = scratch;
+  with_scratch.workspace_elements = kBuiltInScratchFloats;
+  const int status = launch_decode(with_scratch);
+  if (status != LOOM_CUDA_SUCCESS) explain(error_text, error_capacity, loom_cuda_status_string(status));
+  return status;
 }

@@ -245,6 +245,43 @@ int loom_cuda_set_decode_copy_engine(uint32_t engine);
  */
 int loom_cuda_decode_timeout_flag(uint32_t* value, uint32_t reset);
 
+/*
+ * Partitioned decode without a caller workspace. This entry point has no
+ * counterpart in the reference.
+ *
+ * Who it is for: code that must run a split decode but has no means of getting
+ * device memory when it does so. Typical cases are a serving engine that
+ * claims its whole GPU budget at start-up and forbids allocation afterwards, a
+ * latency-critical handler that will not risk the device-wide pause an
+ * allocation may cause, and a host application that passes its plug-ins input
+ * and output buffers only.
+ *
+ * What it does: the same as loom_cuda_paged_decode_attention_ex, with the
+ * partial (O, max, sum) states kept in a block of device memory that is part of
+ * the library itself. args->workspace and args->workspace_elements are
+ * ignored; inputs and outputs are still the caller's. Neither this call nor
+ * anything it reaches allocates or frees memory.
+ *
+ * Limits and rules:
+ *  - the block holds 4,194,304 F32 elements (16 MiB) and exists once per GPU
+ *    that loads the library, for the life of the process. A shape whose
+ *    scratch need (loom_cuda_paged_decode_workspace_elements) is larger is
+ *    refused with LOOM_CUDA_UNSUPPORTED and a message saying how much it
+ *    needs;
+ *  - the first call on each device looks up the block's device address (one
+ *    runtime query, no allocation). Make that first call outside any stream
+ *    capture;
+ *  - all calls on a device share the one block, and it keeps whatever the last
+ *    call left there. No clearing is needed, because a call writes every word
+ *    it later reads. Two such calls that can overlap on the GPU (different
+ *    streams without an ordering between them) race on the block: serialise
+ *    them.
+ * error_text, if non-null, receives a NUL-terminated explanation of a failure
+ * (up to error_capacity bytes). Returns a LoomCudaStatus.
+ */
+int loom_cuda_paged_decode_attention_built_in_scratch(
+    const LoomDecodeArgs* args, char* error_text, uint64_t error_capacity);
+
 #ifdef __cplusplus
 }
 #endif
