@@ -39,6 +39,7 @@ struct DecodeParams {
   uint32_t partition_tokens;  // tokens per partition (whole context when partials == null)
   uint32_t max_partitions;
   uint32_t scale_stride;
+  uint32_t block_shift;  // log2(block_size), or 32 if it is not a power of two
   uint32_t emit_state;  // final rows are F32 states instead of normalised output
   uint64_t k_block, k_page, k_head, v_block, v_page, v_head;  // element strides
   uint64_t q_token, q_head;                                   // element strides of the query
@@ -101,6 +102,22 @@ __device__ __forceinline__ void mma_16816_f16(float (&d)[4], const uint32_t (&a)
       "{%0,%1,%2,%3};\n"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// Four E4M3 bytes [b3 b2 b1 b0] -> F16 pairs (b0, b2) and (b1, b3), each value
+// 2^-8 times the E4M3 value, using integer operations only. An E4M3 byte
+// s eeee mmm placed as s 0eeee mmm0000000 is an F16 with the same sign and
+// mantissa whose exponent field is read with bias 15 instead of 7, i.e. the
+// value divided by 2^8; subnormals map to subnormals under the same factor, so
+// the map is exact for every finite code. The conversion instruction
+// (cvt.rn.f16x2.e4m3x2) shares a quarter-rate pipe with ex2; this form keeps
+// that pipe free.
+__device__ __forceinline__ uint32_t e4m3_high_bytes_to_f16x2(uint32_t x) {
+  return ((x >> 1) & 0x3f803f80u) | (x & 0x80008000u);
+}
+__device__ __forceinline__ void e4m3x4_to_f16_by_alu(uint32_t packed, uint32_t& even, uint32_t& odd) {
+  odd = e4m3_high_bytes_to_f16x2(packed);        // bytes 1 and 3
+  even = e4m3_high_bytes_to_f16x2(packed << 8);  // bytes 0 and 2
 }
 
 __device__ __forceinline__ float fast_exp2(float x) {

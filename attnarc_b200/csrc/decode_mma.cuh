@@ -103,10 +103,16 @@ __device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t packed) {
 template <int kD, int kNT>
 struct WarpState {
   static constexpr int kKSteps = kD / 16;
+  // Q^T as 16-bit MMA B fragments, one register pair per 16 head dims (F16 with
+  // a permuted pairing for an FP8 cache, see load_query).
   uint32_t qf[kNT][kKSteps][2];
   float o[kNT][kKSteps][4];
   float row_max[kNT][2];
   float row_sum[kNT][2];
+  // Factor that turns a raw QK^T accumulator of heads (2t, 2t+1) into a score
+  // in base-2 units: softmax scale * log2(e), times the K scale and 2^8 for an
+  // FP8 cache.
+  float head_scale[kNT][2];
 
   __device__ __forceinline__ void reset() {
 #pragma unroll
@@ -122,36 +128,57 @@ struct WarpState {
 // Loads the Q^T fragments of up to 8*kNT heads starting at `first_row` (a
 // pointer to the first head's row; rows are `head_stride` elements apart).
 // Heads at or beyond `live_heads` read as zero.
+//
+// FP8 cache: K bytes are turned into F16 by integer operations (see
+// e4m3x4_to_f16_by_alu) that pair byte 0 with byte 2 and byte 1 with byte 3 of
+// every 4-byte group and leave the values 2^-8 too small. Q is therefore loaded
+// as F16 with the same pairing, and 2^8 goes into the score scale.
+template <typename QT>
+__device__ __forceinline__ float2 widen_pair(uint32_t packed) {
+  if constexpr (std::is_same<QT, __nv_bfloat16>::value) {
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&packed));
+  } else {
+    return __half22float2(*reinterpret_cast<const __half2*>(&packed));
+  }
+}
+
 template <typename QT, bool kFp8, int kD, int kNT>
 __device__ __forceinline__ void load_query(WarpState<kD, kNT>& state, const QT* first_row,
-                                           uint64_t head_stride, uint32_t live_heads, uint32_t g,
-                                           uint32_t t) {
+                                           uint64_t head_stride, uint32_t live_heads, float base_scale,
+                                           uint32_t g, uint32_t t) {
   constexpr int kKSteps = kD / 16;
 #pragma unroll
   for (int nt = 0; nt < kNT; ++nt) {
     const uint32_t head = nt * 8 + g;
     const bool live = head < live_heads;
     const QT* row = first_row + (uint64_t)(live ? head : 0u) * head_stride;
+    if constexpr (kFp8) {
 #pragma unroll
-    for (int ks = 0; ks < kKSteps; ++ks) {
-      uint32_t b0 = 0, b1 = 0;
-      if (live) {
-        if constexpr (kFp8) {
-          // reduction index permuted to the byte order ldmatrix delivers
+      for (int ks = 0; ks < kKSteps; ++ks) {
+        // this lane's reduction indices of step ks are dims 16 ks + 4 t + {0, 2} (b0) and {1, 3} (b1)
+        uint32_t b0 = 0, b1 = 0;
+        if (live) {
           const uint2 four = *reinterpret_cast<const uint2*>(row + ks * 16 + t * 4);
-          b0 = four.x;
-          b1 = four.y;
-          if constexpr (std::is_same<QT, __nv_bfloat16>::value) {
-            b0 = bf16x2_to_f16x2(b0);
-            b1 = bf16x2_to_f16x2(b1);
-          }
-        } else {
+          const float2 low = widen_pair<QT>(four.x), high = widen_pair<QT>(four.y);
+          b0 = pack_f16x2(low.x, high.x);
+          b1 = pack_f16x2(low.y, high.y);
+        }
+        state.qf[nt][ks][0] = b0;
+        state.qf[nt][ks][1] = b1;
+      }
+      state.head_scale[nt][0] = state.head_scale[nt][1] = base_scale * 256.0f;
+    } else {
+#pragma unroll
+      for (int ks = 0; ks < kKSteps; ++ks) {
+        uint32_t b0 = 0, b1 = 0;
+        if (live) {
           b0 = *reinterpret_cast<const uint32_t*>(row + ks * 16 + t * 2);
           b1 = *reinterpret_cast<const uint32_t*>(row + ks * 16 + 8 + t * 2);
         }
+        state.qf[nt][ks][0] = b0;
+        state.qf[nt][ks][1] = b1;
       }
-      state.qf[nt][ks][0] = b0;
-      state.qf[nt][ks][1] = b1;
+      state.head_scale[nt][0] = state.head_scale[nt][1] = base_scale;
     }
   }
 }
@@ -184,13 +211,14 @@ __device__ __forceinline__ void chunk_scores(float (&s)[kNT][4], const WarpState
     for (int pair = 0; pair < kKSteps / 2; ++pair) {
       uint32_t r[4];
       ldmatrix_x4(r, k_tile + tile_offset<Tile::kSegs, kTmaLayout>(ld_row, 2 * pair + ld_col));
+      // rows 0-7 / 8-15 of byte column c (r[0], r[1]) and of column c+1 (r[2], r[3])
       uint32_t a[4];
-      e4m3x4_to_f16x2x2(r[0], a[0], a[2]);
-      e4m3x4_to_f16x2x2(r[1], a[1], a[3]);
+      e4m3x4_to_f16_by_alu(r[0], a[0], a[2]);
+      e4m3x4_to_f16_by_alu(r[1], a[1], a[3]);
 #pragma unroll
       for (int nt = 0; nt < kNT; ++nt) mma_16816_f16(s[nt], a, state.qf[nt][2 * pair][0], state.qf[nt][2 * pair][1]);
-      e4m3x4_to_f16x2x2(r[2], a[0], a[2]);
-      e4m3x4_to_f16x2x2(r[3], a[1], a[3]);
+      e4m3x4_to_f16_by_alu(r[2], a[0], a[2]);
+      e4m3x4_to_f16_by_alu(r[3], a[1], a[3]);
 #pragma unroll
       for (int nt = 0; nt < kNT; ++nt) {
         mma_16816_f16(s[nt], a, state.qf[nt][2 * pair + 1][0], state.qf[nt][2 * pair + 1][1]);
@@ -199,45 +227,91 @@ __device__ __forceinline__ void chunk_scores(float (&s)[kNT][4], const WarpState
   }
 }
 
-// Online softmax over the chunk's 16 tokens: updates max/sum, rescales O, and
-// returns P^T as MMA B fragments. Rows at or beyond `live_rows` are masked.
+// Online softmax over the chunk's 16 tokens: updates the running exponent
+// reference and sum, rescales O when the reference moves, and returns P^T as MMA
+// B fragments. Rows at or beyond `live_rows` are masked.
+//
+// The reference exponent (state.row_max) is not the exact running maximum: it
+// only moves when some score of the chunk exceeds it by more than kSoftmaxSlack
+// (base-2 units), and then rises to the largest score of that chunk. So every
+// p = 2^(score - reference) is at most 2^kSoftmaxSlack, well inside the
+// range of the 16-bit P operand and of the F32 sums, and softmax is invariant
+// to the choice of reference. In the common case this removes the cross-lane
+// maximum (six shuffles per head pair), the correction factors and the rescale
+// of the O accumulators from the chunk; one warp vote decides.
+constexpr float kSoftmaxSlack = 8.0f;
+
 template <typename QT, bool kFp8, int kD, int kNT>
 __device__ __forceinline__ void chunk_softmax(uint32_t (&pb)[kNT][2], const float (&s)[kNT][4],
-                                              WarpState<kD, kNT>& state, float score_scale,
-                                              uint32_t live_rows, uint32_t g) {
+                                              WarpState<kD, kNT>& state, uint32_t live_rows,
+                                              uint32_t g) {
   constexpr bool kBf16Mma = !kFp8 && std::is_same<QT, __nv_bfloat16>::value;
   constexpr int kKSteps = kD / 16;
-  const bool low_live = g < live_rows;
-  const bool high_live = (g + 8u) < live_rows;
+  // exponents relative to the current reference
+  float d[kNT][4];
+  bool over = false;
 #pragma unroll
   for (int nt = 0; nt < kNT; ++nt) {
-    const float s0 = low_live ? s[nt][0] * score_scale : -INFINITY;
-    const float s1 = low_live ? s[nt][1] * score_scale : -INFINITY;
-    const float s2 = high_live ? s[nt][2] * score_scale : -INFINITY;
-    const float s3 = high_live ? s[nt][3] * score_scale : -INFINITY;
-    float max0 = fmaxf(s0, s2), max1 = fmaxf(s1, s3);
+    d[nt][0] = fmaf(s[nt][0], state.head_scale[nt][0], -state.row_max[nt][0]);
+    d[nt][1] = fmaf(s[nt][1], state.head_scale[nt][1], -state.row_max[nt][1]);
+    d[nt][2] = fmaf(s[nt][2], state.head_scale[nt][0], -state.row_max[nt][0]);
+    d[nt][3] = fmaf(s[nt][3], state.head_scale[nt][1], -state.row_max[nt][1]);
+  }
+  if (live_rows < 16u) {  // warp-uniform
+    const bool low_live = g < live_rows;
+    const bool high_live = (g + 8u) < live_rows;
 #pragma unroll
-    for (int offset = 4; offset < 32; offset <<= 1) {
-      max0 = fmaxf(max0, __shfl_xor_sync(0xffffffffu, max0, offset));
-      max1 = fmaxf(max1, __shfl_xor_sync(0xffffffffu, max1, offset));
+    for (int nt = 0; nt < kNT; ++nt) {
+      if (!low_live) d[nt][0] = d[nt][1] = -INFINITY;
+      if (!high_live) d[nt][2] = d[nt][3] = -INFINITY;
     }
-    const float new0 = fmaxf(state.row_max[nt][0], max0);
-    const float new1 = fmaxf(state.row_max[nt][1], max1);
-    const float alpha0 = fast_exp2(state.row_max[nt][0] - new0);
-    const float alpha1 = fast_exp2(state.row_max[nt][1] - new1);
-    state.row_max[nt][0] = new0;
-    state.row_max[nt][1] = new1;
-    const float p0 = fast_exp2(s0 - new0), p1 = fast_exp2(s1 - new1);
-    const float p2 = fast_exp2(s2 - new0), p3 = fast_exp2(s3 - new1);
-    state.row_sum[nt][0] = state.row_sum[nt][0] * alpha0 + (p0 + p2);
-    state.row_sum[nt][1] = state.row_sum[nt][1] * alpha1 + (p1 + p3);
+  }
 #pragma unroll
-    for (int mt = 0; mt < kKSteps; ++mt) {
-      state.o[nt][mt][0] *= alpha0;
-      state.o[nt][mt][1] *= alpha1;
-      state.o[nt][mt][2] *= alpha0;
-      state.o[nt][mt][3] *= alpha1;
+  for (int nt = 0; nt < kNT; ++nt) {
+    over |= fmaxf(fmaxf(d[nt][0], d[nt][1]), fmaxf(d[nt][2], d[nt][3])) > kSoftmaxSlack;
+  }
+  if (__any_sync(0xffffffffu, over)) {
+    // rare: move every head's reference up to the largest score of this chunk
+#pragma unroll
+    for (int nt = 0; nt < kNT; ++nt) {
+      const bool low_dead = d[nt][0] == -INFINITY, high_dead = d[nt][2] == -INFINITY;
+      const float v0 = low_dead ? -INFINITY : s[nt][0] * state.head_scale[nt][0];
+      const float v1 = low_dead ? -INFINITY : s[nt][1] * state.head_scale[nt][1];
+      const float v2 = high_dead ? -INFINITY : s[nt][2] * state.head_scale[nt][0];
+      const float v3 = high_dead ? -INFINITY : s[nt][3] * state.head_scale[nt][1];
+      float max0 = fmaxf(v0, v2), max1 = fmaxf(v1, v3);
+#pragma unroll
+      for (int offset = 4; offset < 32; offset <<= 1) {
+        max0 = fmaxf(max0, __shfl_xor_sync(0xffffffffu, max0, offset));
+        max1 = fmaxf(max1, __shfl_xor_sync(0xffffffffu, max1, offset));
+      }
+      const float old0 = state.row_max[nt][0], old1 = state.row_max[nt][1];
+      const float new0 = fmaxf(old0, max0), new1 = fmaxf(old1, max1);
+      const float alpha0 = old0 == -INFINITY ? 0.0f : fast_exp2(old0 - new0);
+      const float alpha1 = old1 == -INFINITY ? 0.0f : fast_exp2(old1 - new1);
+      state.row_max[nt][0] = new0;
+      state.row_max[nt][1] = new1;
+      d[nt][0] = v0 - new0;
+      d[nt][1] = v1 - new1;
+      d[nt][2] = v2 - new0;
+      d[nt][3] = v3 - new1;
+      state.row_sum[nt][0] *= alpha0;
+      state.row_sum[nt][1] *= alpha1;
+#pragma unroll
+      for (int mt = 0; mt < kKSteps; ++mt) {
+        state.o[nt][mt][0] *= alpha0;
+        state.o[nt][mt][1] *= alpha1;
+        state.o[nt][mt][2] *= alpha0;
+        state.o[nt][mt][3] *= alpha1;
+      }
     }
+  }
+#pragma unroll
+  for (int nt = 0; nt < kNT; ++nt) {
+    const float p0 = fast_exp2(d[nt][0]), p1 = fast_exp2(d[nt][1]);
+    const float p2 = fast_exp2(d[nt][2]), p3 = fast_exp2(d[nt][3]);
+    state.row_sum[nt][0] += p0 + p2;
+    state.row_sum[nt][1] += p1 + p3;
     if constexpr (kBf16Mma) {
       pb[nt][0] = movmatrix_trans(pack_bf16x2(p0, p1));
       pb[nt][1] = movmatrix_trans(pack_bf16x2(p2, p3));
@@ -419,12 +493,11 @@ __global__ void __launch_bounds__(kMmaThreads, 2) decode_mma_kernel(const Decode
   WarpState<kD, kNT> state;
   state.reset();
   const uint64_t first_query_head = (uint64_t)kv_head * p.group + first_head;
-  load_query<QT, kFp8, kD, kNT>(
-      state, static_cast<const QT*>(p.query) + (uint64_t)seq * p.q_token + first_query_head * p.q_head,
-      p.q_head, live_heads, g, t);
-
   float score_scale = p.scale_log2;
   if constexpr (kFp8) score_scale *= p.key_scales[(uint64_t)kv_head * p.scale_stride];
+  load_query<QT, kFp8, kD, kNT>(
+      state, static_cast<const QT*>(p.query) + (uint64_t)seq * p.q_token + first_query_head * p.q_head,
+      p.q_head, live_heads, score_scale, g, t);
 
   // ---- producer side: page-table driven 16-byte copies --------------------
   const uint8_t* key_bytes = static_cast<const uint8_t*>(p.key_cache);
@@ -510,7 +583,7 @@ __global__ void __launch_bounds__(kMmaThreads, 2) decode_mma_kernel(const Decode
     float s[kNT][4];
     chunk_scores<QT, kFp8, kD, kNT>(s, state, stage, lane);
     uint32_t pb[kNT][2];
-    chunk_softmax<QT, kFp8, kD, kNT>(pb, s, state, score_scale, live_rows, g);
+    chunk_softmax<QT, kFp8, kD, kNT>(pb, s, state, live_rows, g);
     chunk_values<QT, kFp8, kD, kNT>(state, pb, stage + Tile::kTileBytes, lane);
   }
   cp_async_wait<0>();

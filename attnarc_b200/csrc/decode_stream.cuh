@@ -210,7 +210,6 @@ __global__ void __launch_bounds__(kMmaThreads, 2) decode_stream_kernel(const Dec
 
   // current work item
   uint32_t item_seq = 0, item_head = 0, item_tiles = 0;
-  float score_scale = 0.0f;
 
   auto begin_item = [&]() {
     item_seq = consumer.seq;
@@ -220,13 +219,13 @@ __global__ void __launch_bounds__(kMmaThreads, 2) decode_stream_kernel(const Dec
     const uint32_t first_head = (item_head % head_chunks) * kHeads;
     const uint32_t live_heads = min((uint32_t)kHeads, p.group - first_head);
     state.reset();
+    float score_scale = p.scale_log2;
+    if constexpr (kFp8) score_scale *= __ldg(p.key_scales + (uint64_t)kv_head * p.scale_stride);
     load_query<QT, kFp8, kD, kNT>(
         state,
         static_cast<const QT*>(p.query) + (uint64_t)item_seq * p.q_token +
             ((uint64_t)kv_head * p.group + first_head) * p.q_head,
-        p.q_head, live_heads, g, t);
-    score_scale = p.scale_log2;
-    if constexpr (kFp8) score_scale *= __ldg(p.key_scales + (uint64_t)kv_head * p.scale_stride);
+        p.q_head, live_heads, score_scale, g, t);
   };
 
   auto finish_item = [&]() {
@@ -277,7 +276,7 @@ __global__ void __launch_bounds__(kMmaThreads, 2) decode_stream_kernel(const Dec
       const uint32_t k_tile = ring_base + ((2 * chunk) % Ring::kSlots) * Tile::kTileBytes;
       float s[kNT][4];
       chunk_scores<QT, kFp8, kD, kNT>(s, state, k_tile, lane);
-      chunk_softmax<QT, kFp8, kD, kNT>(pb, s, state, score_scale, consumer.length - token0, g);
+      chunk_softmax<QT, kFp8, kD, kNT>(pb, s, state, consumer.length - token0, g);
     }
     // ---- V tile ------------------------------------------------------------
     cp_async_wait<Ring::kAhead - 1>();

@@ -80,24 +80,31 @@ __device__ __forceinline__ void tma_load_4d(uint32_t smem, const CUtensorMap* ma
       : "memory");
 }
 
+// Sequences per launch of this kernel (its prefix table lives in shared memory).
+constexpr uint32_t kTmaMaxSequences = 1024;
+
 template <bool kFp8, int kD, int kNT>
 struct TmaRing {
   using Tile = MmaTile<kFp8, kD>;
   static constexpr int kBoxBytes = Tile::kRowBytes > 128 ? 128 : Tile::kRowBytes;  // swizzle span
   static constexpr int kBoxes = Tile::kRowBytes / kBoxBytes;                       // per tile
-  static constexpr int kWantedBytes = kNT == 1 ? 20 * 1024 : 16 * 1024;
+  // One 8-head item per warp needs about 170 registers a thread, so three CTAs
+  // fit an SM; twelve warps hide the latency of the dependent MMA and softmax
+  // steps better than eight. Sixteen heads need about 240 registers: two CTAs.
+  static constexpr int kCtasPerSm = kNT == 1 ? 3 : 2;
+  static constexpr int kWantedBytes = kNT == 1 ? 12 * 1024 : 16 * 1024;
   static constexpr int kRaw = kWantedBytes / Tile::kTileBytes;
   static constexpr int kSlots = kRaw < 3 ? 3 : (kRaw > 9 ? 9 : kRaw);
   static constexpr int kAhead = kSlots - 1;
   static constexpr int kRingBytes = kMmaWarps * kSlots * Tile::kTileBytes;  // 1024-byte aligned pieces
   static constexpr int kMergeBytes = mma_merge_bytes<kNT, kD>();
-  static constexpr int kPrefixBytes = (kStreamMaxSequences + 1) * 4;
+  static constexpr int kPrefixBytes = (kTmaMaxSequences + 1) * 4;
   static constexpr int kBarrierBytes = kMmaWarps * kSlots * 8;
   static constexpr int kSmemBytes = kRingBytes + kMergeBytes + kPrefixBytes + 4 + kBarrierBytes + 1024;
 };
 
 template <typename QT, bool kFp8, int kD, int kNT>
-__global__ void __launch_bounds__(kMmaThreads, 2)
+__global__ void __launch_bounds__(kMmaThreads, (TmaRing<kFp8, kD, kNT>::kCtasPerSm))
 decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap key_map,
                          const __grid_constant__ CUtensorMap value_map, const TmaAxes axes) {
   using Tile = MmaTile<kFp8, kD>;
@@ -111,7 +118,7 @@ decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorM
   uint8_t* merge_base = smem + Ring::kRingBytes;
   uint32_t* prefix = reinterpret_cast<uint32_t*>(merge_base + Ring::kMergeBytes);  // [sequences + 1]
   uint8_t* barrier_base = reinterpret_cast<uint8_t*>(
-      (reinterpret_cast<uintptr_t>(prefix + kStreamMaxSequences + 1) + 7u) & ~uintptr_t(7));
+      (reinterpret_cast<uintptr_t>(prefix + kTmaMaxSequences + 1) + 7u) & ~uintptr_t(7));
   __shared__ uint32_t warp_totals[kMmaWarps];
 
   const uint32_t warp = threadIdx.x >> 5;
@@ -203,56 +210,61 @@ decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorM
   }
 
   // ---- producer: lane 0 of each warp feeds that warp's ring ------------------
+  // All bookkeeping below is incremental (no division or modulo per tile): the
+  // instruction stream of the eight..twelve resident warps is what limits this
+  // kernel once HBM is kept busy.
   const uint32_t warp_token = warp * 16u;
-  const uint32_t pages_per_block = p.block_size;  // a multiple of 16 on this route
+  const bool head_inner = axes.head < axes.page;  // NHD-like: the head stride is the smaller one
   StreamCursor producer = start;
-  uint32_t producer_block = 0, producer_page = 0;
+  uint32_t producer_block = 0, producer_page = 0, producer_head = 0;
   auto fetch_block = [&]() {
     const uint32_t token0 = producer.tile * kStreamTileTokens + warp_token;
     producer_block = 0;
     producer_page = 0;
+    producer_head = head_chunks == 1 ? producer.head : producer.head / head_chunks;
     if (token0 < producer.length) {
-      const uint32_t logical = token0 / pages_per_block;
-      producer_page = token0 - logical * pages_per_block;
+      // block_size is a multiple of 16 on this route, so a 16-token tile never straddles blocks
+      const uint32_t logical = p.block_shift < 32u ? token0 >> p.block_shift : token0 / p.block_size;
+      producer_page = token0 - logical * p.block_size;
       producer_block = clamp_block(
           __ldg(p.block_tables + (uint64_t)producer.seq * p.max_blocks_per_sequence + logical), p.num_blocks);
     }
   };
   fetch_block();
 
-  // Issues ring tile `index` (even = K, odd = V of chunk index/2).
-  auto issue_tile = [&](uint32_t index) {
-    if ((index >> 1) >= my_tiles) return;
-    const bool is_value = index & 1u;
+  uint32_t issue_left = 2 * my_tiles;  // ring tiles not yet issued (even = K, odd = V of a chunk)
+  uint32_t issue_slot = 0;
+  bool issue_value = false;
+  auto issue_tile = [&]() {
+    if (issue_left == 0) return;
+    --issue_left;
     const uint32_t token0 = producer.tile * kStreamTileTokens + warp_token;
     if (token0 < producer.length && lane == 0) {
-      const uint32_t slot = index % Ring::kSlots;
-      const uint32_t destination = ring_base + slot * Tile::kTileBytes;
-      const uint32_t barrier = barriers + slot * 8;
-      const int32_t head_coord = (int32_t)(producer.head / head_chunks);
-      const int32_t page_coord = (int32_t)producer_page, block_coord = (int32_t)producer_block;
-      const auto pick = [&](uint32_t axis) {
-        return axes.head == axis ? head_coord : (axes.page == axis ? page_coord : block_coord);
-      };
-      const int32_t c1 = pick(1), c2 = pick(2), c3 = pick(3);
+      const uint32_t destination = ring_base + issue_slot * Tile::kTileBytes;
+      const uint32_t barrier = barriers + issue_slot * 8;
+      const int32_t c1 = (int32_t)(head_inner ? producer_head : producer_page);
+      const int32_t c2 = (int32_t)(head_inner ? producer_page : producer_head);
       // generic-proxy reads of this slot (ldmatrix of its previous tile) come
       // before the async-proxy write that refills it
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
       mbarrier_expect_tx(barrier, Tile::kTileBytes);
-      const CUtensorMap* map = is_value ? &value_map : &key_map;
+      const CUtensorMap* map = issue_value ? &value_map : &key_map;
 #pragma unroll
       for (int box = 0; box < Ring::kBoxes; ++box) {
-        tma_load_4d(destination + box * (16 * Ring::kBoxBytes), map, barrier, box * Ring::kBoxBytes, c1, c2, c3);
+        tma_load_4d(destination + box * (16 * Ring::kBoxBytes), map, barrier, box * Ring::kBoxBytes, c1, c2,
+                    (int32_t)producer_block);
       }
     }
-    if (is_value && (index >> 1) + 1 < my_tiles) {
+    issue_slot = issue_slot + 1 == (uint32_t)Ring::kSlots ? 0u : issue_slot + 1;
+    if (issue_value && issue_left != 0) {
       advance(producer);
       fetch_block();
     }
+    issue_value = !issue_value;
   };
 
 #pragma unroll
-  for (int index = 0; index < Ring::kAhead; ++index) issue_tile(index);
+  for (int index = 0; index < Ring::kAhead; ++index) issue_tile();
 
   // ---- consumer -----------------------------------------------------------------
   WarpState<kD, kNT> state;
@@ -260,9 +272,9 @@ decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorM
   StreamCursor consumer = start;
   const uint32_t stride = state_stride(kD);
   uint32_t phases = 0;  // bit s = parity the next use of slot s completes
+  uint32_t consume_slot = 0;
 
   uint32_t item_seq = 0, item_head = 0, item_tiles = 0;
-  float score_scale = 0.0f;
 
   auto begin_item = [&]() {
     item_seq = consumer.seq;
@@ -272,13 +284,13 @@ decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorM
     const uint32_t first_head = (item_head % head_chunks) * kHeads;
     const uint32_t live_heads = min((uint32_t)kHeads, p.group - first_head);
     state.reset();
+    float score_scale = p.scale_log2;
+    if constexpr (kFp8) score_scale *= __ldg(p.key_scales + (uint64_t)kv_head * p.scale_stride);
     load_query<QT, kFp8, kD, kNT>(
         state,
         static_cast<const QT*>(p.query) + (uint64_t)item_seq * p.q_token +
             ((uint64_t)kv_head * p.group + first_head) * p.q_head,
-        p.q_head, live_heads, g, t);
-    score_scale = p.scale_log2;
-    if constexpr (kFp8) score_scale *= __ldg(p.key_scales + (uint64_t)kv_head * p.scale_stride);
+        p.q_head, live_heads, score_scale, g, t);
   };
 
   auto finish_item = [&]() {
@@ -320,7 +332,7 @@ decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorM
 
   for (uint32_t chunk = 0; chunk < my_tiles; ++chunk) {
     // refills the slot of the V tile consumed at the end of the previous round
-    issue_tile(2 * chunk + Ring::kAhead);
+    issue_tile();
     if (chunk == 0 || consumer.tile == 0) {
       if (chunk != 0) finish_item();
       begin_item();
@@ -328,8 +340,9 @@ decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorM
     const uint32_t token0 = consumer.tile * kStreamTileTokens + warp_token;
     const bool has_rows = token0 < consumer.length;  // warp-uniform
     const uint32_t live_rows = has_rows ? min(16u, consumer.length - token0) : 0u;
-    const uint32_t k_slot = (2 * chunk) % Ring::kSlots;
-    const uint32_t v_slot = (2 * chunk + 1) % Ring::kSlots;
+    const uint32_t k_slot = consume_slot;
+    const uint32_t v_slot = k_slot + 1 == (uint32_t)Ring::kSlots ? 0u : k_slot + 1;
+    consume_slot = v_slot + 1 == (uint32_t)Ring::kSlots ? 0u : v_slot + 1;
 
     // ---- K tile ------------------------------------------------------------
     uint32_t pb[kNT][2];
@@ -337,10 +350,10 @@ decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorM
       wait_slot(k_slot);
       float s[kNT][4];
       chunk_scores<QT, kFp8, kD, kNT, true>(s, state, ring_base + k_slot * Tile::kTileBytes, lane);
-      chunk_softmax<QT, kFp8, kD, kNT>(pb, s, state, score_scale, live_rows, g);
+      chunk_softmax<QT, kFp8, kD, kNT>(pb, s, state, live_rows, g);
     }
     __syncwarp();
-    issue_tile(2 * chunk + 1 + Ring::kAhead);  // refills the slot of the K tile just consumed
+    issue_tile();  // refills the slot of the K tile just consumed
 
     // ---- V tile ------------------------------------------------------------
     if (has_rows) {

@@ -345,13 +345,16 @@ uint32_t current_sm_count() {
   return (uint32_t)count;
 }
 
-// CTAs of the balanced kernel: two per SM. Workspaces are sized for at least a
-// 148-SM device so that a size computed before a device is current still fits.
+// CTAs of the balanced kernels: two per SM, three for the TMA-fed kernel with
+// eight heads per item. Workspaces are sized for the larger count and for at
+// least a 148-SM device, so that a size computed before a device is current,
+// or before the kernel is chosen, still fits.
 constexpr uint32_t kStreamCtasPerSm = 2;
-uint32_t stream_ctas_for_launch() { return kStreamCtasPerSm * current_sm_count(); }
+constexpr uint32_t kStreamMaxCtasPerSm = 3;
+uint32_t stream_ctas_for_launch(uint32_t per_sm) { return per_sm * current_sm_count(); }
 uint32_t stream_ctas_for_sizing() {
   const uint32_t sms = current_sm_count();
-  return kStreamCtasPerSm * (sms > 148 ? sms : 148);
+  return kStreamMaxCtasPerSm * (sms > 148 ? sms : 148);
 }
 
 template <typename QT, bool kFp8, int kD, int kNT>
@@ -424,8 +427,16 @@ bool encode_cache_map(CUtensorMap* map, const void* base, uint32_t row_bytes, co
     if (strides[position] % 16 != 0 || strides[position] >= (1ull << 40)) return false;
   }
   const CUtensorMapSwizzle swizzle = row_bytes >= 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+  // L2 fetch granule no wider than a row: in an NHD cache the bytes after a
+  // 128-byte row belong to another KV head, which another CTA reads at another
+  // time. A 256-byte granule there cost 42 % extra DRAM reads on an FP8 cache.
+  // (Rows of consecutive pages that touch, as in an HND cache, keep the wide granule.)
+  const bool rows_touch = strides_bytes[1] == row_bytes;
+  const CUtensorMapL2promotion promotion = (row_bytes >= 256 || rows_touch) ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B
+                                           : row_bytes >= 128               ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B
+                                                                            : CU_TENSOR_MAP_L2_PROMOTION_L2_64B;
   return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(base), dims, strides, box,
-                element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, promotion,
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -451,6 +462,7 @@ bool build_cache_maps(const LoomDecodeArgs& a, bool fp8, CacheMaps* maps) {
   for (int i = 0; i + 1 < 3; ++i) {
     if (value_strides[order[i]] > value_strides[order[i + 1]]) return false;
   }
+  if (order[2] != 2) return false;  // the kernel expects the block to be the outermost coordinate
   for (uint32_t position = 0; position < 3; ++position) {
     if (order[position] == 0) maps->axes.head = position + 1;
     if (order[position] == 1) maps->axes.page = position + 1;
@@ -652,6 +664,8 @@ int launch_decode(const LoomDecodeArgs& a) {
   p.max_blocks_per_sequence = a.max_blocks_per_sequence;
   p.max_sequence_length = a.max_sequence_length;
   p.scale_stride = fp8 ? a.scale_stride : 0;
+  p.block_shift = 32;
+  if ((a.block_size & (a.block_size - 1)) == 0) p.block_shift = (uint32_t)__builtin_ctz(a.block_size);
   p.emit_state = a.emit_state ? 1 : 0;
   p.k_block = a.key_block_stride;
   p.k_page = a.key_page_stride;
@@ -668,6 +682,8 @@ int launch_decode(const LoomDecodeArgs& a) {
   const bool partitioned = a.workspace != nullptr || a.workspace_elements != 0;
   uint32_t stream_ctas = 0;  // non-zero selects the balanced kernel
   StreamShape shape{};
+  CacheMaps maps;
+  const CacheMaps* tma = nullptr;
   if (partitioned) {
     if (a.workspace == nullptr || (reinterpret_cast<uintptr_t>(a.workspace) & 3u) != 0) {
       return LOOM_CUDA_INVALID_ARGUMENT;
@@ -675,7 +691,12 @@ int launch_decode(const LoomDecodeArgs& a) {
     p.partials = a.workspace;
     uint32_t tokens = a.partition_tokens;
     if (tokens == 0 && use_mma && a.block_size % 16 == 0 && a.sequences <= kStreamMaxSequences) {
-      const uint32_t ctas = stream_ctas_for_launch();
+      if (a.sequences <= kTmaMaxSequences && g_copy_engine.load(std::memory_order_relaxed) == 0 &&
+          build_cache_maps(a, fp8, &maps)) {
+        tma = &maps;
+      }
+      const uint32_t ctas =
+          stream_ctas_for_launch(tma != nullptr && p.group <= 8 ? kStreamMaxCtasPerSm : kStreamCtasPerSm);
       if (ctas != 0 && stream_shape(a.sequences, a.query_heads, a.kv_heads, a.value_head_size, ctas, &shape) &&
           a.workspace_elements >= shape.total_elements) {
         stream_ctas = ctas;
@@ -702,11 +723,7 @@ int launch_decode(const LoomDecodeArgs& a) {
   cudaStream_t stream = static_cast<cudaStream_t>(a.stream);
   int status;
   if (use_mma) {
-    CacheMaps maps;
-    const CacheMaps* tma = nullptr;
-    if (stream_ctas != 0 && g_copy_engine.load(std::memory_order_relaxed) == 0 && build_cache_maps(a, fp8, &maps)) {
-      tma = &maps;
-    }
+    if (stream_ctas == 0) tma = nullptr;
     if (stream_ctas == 0) g_last_route = fp8 ? "mma16-fp8" : "mma16";
     else if (tma != nullptr) g_last_route = fp8 ? "mma16-fp8-balanced-tma" : "mma16-balanced-tma";
     else g_last_route = fp8 ? "mma16-fp8-balanced" : "mma16-balanced";

@@ -52,6 +52,8 @@ def parse_args():
     parser.add_argument("--impl", choices=["b200", "reference"], default="b200")
     parser.add_argument("--workload", default="cfg2", help="cfg2 (default), cfg3, cfg4, cfg5, cfg1")
     parser.add_argument("--seed", type=int, default=0)
+    parser.add_argument("--batch", type=int, default=0,
+                        help="override the workload's batch size (smaller cases for profiler captures)")
     parser.add_argument("--copies", type=int, default=0, help="cache copies rotated between steps (0 = auto)")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--cpu-seconds", type=float, default=15.0, help="CPU work per baseline sample")
@@ -234,6 +236,8 @@ def run_reference(args):
     from oracle import binding as ob
 
     config = workloads.CONFIGS[args.workload]
+    if args.batch:
+        config = workloads.scaled(config, batch=args.batch, name=f"{config.name}-batch{args.batch}")
     case = workloads.build_case(config, "cpu", seed=args.seed)
     threads = ob.max_threads()
     steps_total = max(1, args.steps + args.warmup)
@@ -287,6 +291,8 @@ def run_b200(args):
         dist.init_process_group("nccl", device_id=device)
 
     config = workloads.CONFIGS[args.workload]
+    if args.batch:
+        config = workloads.scaled(config, batch=args.batch, name=f"{config.name}-batch{args.batch}")
     # Weak scaling: every rank serves its own batch of the named shape. The
     # path needs no exchange between ranks (sequences are independent).
     case = workloads.build_case(config, device, seed=args.seed + rank, fast_device_fill=True)
