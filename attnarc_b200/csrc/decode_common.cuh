@@ -104,6 +104,13 @@ __device__ __forceinline__ void mma_16816_f16(float (&d)[4], const uint32_t (&a)
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// How the K bytes of an FP8 cache become F16 MMA operands: by integer
+// operations (true) or by the conversion instruction (false). Both are exact.
+#ifndef LOOM_FP8_KEY_BY_ALU
+#define LOOM_FP8_KEY_BY_ALU 0
+#endif
+constexpr bool kFp8KeyByAlu = LOOM_FP8_KEY_BY_ALU != 0;
+
 // Four E4M3 bytes [b3 b2 b1 b0] -> F16 pairs (b0, b2) and (b1, b3), each value
 // 2^-8 times the E4M3 value, using integer operations only. An E4M3 byte
 // s eeee mmm placed as s 0eeee mmm0000000 is an F16 with the same sign and

@@ -160,13 +160,18 @@ __device__ __forceinline__ void load_query(WarpState<kD, kNT>& state, const QT* 
         if (live) {
           const uint2 four = *reinterpret_cast<const uint2*>(row + ks * 16 + t * 4);
           const float2 low = widen_pair<QT>(four.x), high = widen_pair<QT>(four.y);
-          b0 = pack_f16x2(low.x, high.x);
-          b1 = pack_f16x2(low.y, high.y);
+          if constexpr (kFp8KeyByAlu) {
+            b0 = pack_f16x2(low.x, high.x);
+            b1 = pack_f16x2(low.y, high.y);
+          } else {
+            b0 = pack_f16x2(low.x, low.y);
+            b1 = pack_f16x2(high.x, high.y);
+          }
         }
         state.qf[nt][ks][0] = b0;
         state.qf[nt][ks][1] = b1;
       }
-      state.head_scale[nt][0] = state.head_scale[nt][1] = base_scale * 256.0f;
+      state.head_scale[nt][0] = state.head_scale[nt][1] = kFp8KeyByAlu ? base_scale * 256.0f : base_scale;
     } else {
 #pragma unroll
       for (int ks = 0; ks < kKSteps; ++ks) {
@@ -213,12 +218,22 @@ __device__ __forceinline__ void chunk_scores(float (&s)[kNT][4], const WarpState
       ldmatrix_x4(r, k_tile + tile_offset<Tile::kSegs, kTmaLayout>(ld_row, 2 * pair + ld_col));
       // rows 0-7 / 8-15 of byte column c (r[0], r[1]) and of column c+1 (r[2], r[3])
       uint32_t a[4];
-      e4m3x4_to_f16_by_alu(r[0], a[0], a[2]);
-      e4m3x4_to_f16_by_alu(r[1], a[1], a[3]);
+      if constexpr (kFp8KeyByAlu) {
+        e4m3x4_to_f16_by_alu(r[0], a[0], a[2]);
+        e4m3x4_to_f16_by_alu(r[1], a[1], a[3]);
+      } else {
+        e4m3x4_to_f16x2x2(r[0], a[0], a[2]);
+        e4m3x4_to_f16x2x2(r[1], a[1], a[3]);
+      }
 #pragma unroll
       for (int nt = 0; nt < kNT; ++nt) mma_16816_f16(s[nt], a, state.qf[nt][2 * pair][0], state.qf[nt][2 * pair][1]);
-      e4m3x4_to_f16_by_alu(r[2], a[0], a[2]);
-      e4m3x4_to_f16_by_alu(r[3], a[1], a[3]);
+      if constexpr (kFp8KeyByAlu) {
+        e4m3x4_to_f16_by_alu(r[2], a[0], a[2]);
+        e4m3x4_to_f16_by_alu(r[3], a[1], a[3]);
+      } else {
+        e4m3x4_to_f16x2x2(r[2], a[0], a[2]);
+        e4m3x4_to_f16x2x2(r[3], a[1], a[3]);
+      }
 #pragma unroll
       for (int nt = 0; nt < kNT; ++nt) {
         mma_16816_f16(s[nt], a, state.qf[nt][2 * pair + 1][0], state.qf[nt][2 * pair + 1][1]);
