@@ -65,6 +65,7 @@ def _declare(lib):
     lib.loom_cuda_last_decode_route.restype = ctypes.c_char_p
     lib.loom_cuda_last_decode_route.argtypes = []
     lib.loom_cuda_set_decode_copy_engine.argtypes = [u32]
+    lib.loom_cuda_set_programmatic_launch.argtypes = [u32]
     lib.loom_cuda_decode_timeout_flag.argtypes = [ctypes.POINTER(u32), u32]
     lib.loom_cuda_status_string.restype = ctypes.c_char_p
     lib.loom_cuda_status_string.argtypes = [ctypes.c_int]

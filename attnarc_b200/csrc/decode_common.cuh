@@ -8,6 +8,8 @@
 
 #include <cstdint>
 
+#include "launch_util.cuh"
+
 namespace loom_decode {
 
 // log2(e): scores are kept in base-2 units so the softmax uses ex2.

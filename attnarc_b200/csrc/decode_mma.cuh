@@ -484,6 +484,7 @@ __global__ void __launch_bounds__(kMmaThreads, 2) decode_mma_kernel(const Decode
   constexpr int kHeads = 8 * kNT;
 
   extern __shared__ __align__(128) uint8_t smem[];
+  loom_launch::grid_dependency_wait();
 
   const uint32_t warp = threadIdx.x >> 5;
   const uint32_t lane = threadIdx.x & 31u;

@@ -58,6 +58,7 @@ __global__ void __launch_bounds__(kMmaThreads, 2) decode_stream_kernel(const Dec
   constexpr uint32_t kElem = kFp8 ? 1 : 2;
 
   extern __shared__ __align__(128) uint8_t smem[];
+  loom_launch::grid_dependency_wait();
   uint32_t* prefix = reinterpret_cast<uint32_t*>(smem + Ring::kRingBytes + Ring::kMergeBytes);  // [sequences + 1]
   __shared__ uint32_t warp_totals[kMmaWarps];
 

@@ -134,6 +134,7 @@ decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorM
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   }
+  loom_launch::grid_dependency_wait();
 
   // ---- tiles per sequence, exclusive prefix sum -----------------------------
   {

@@ -1,0 +1,58 @@
+// Kernel launch helper shared by the decode and RoPE translation units, and the
+// device side of programmatic dependent launch.
+//
+// With programmatic launch on (the default), every kernel of this library is
+// launched with cudaLaunchAttributeProgrammaticStreamSerialization: its CTAs
+// may become resident while the kernel before it in the stream drains (that
+// kernel's CTAs release their dependents when they exit), which hides launch
+// latency and CTA set-up. Each kernel executes griddepcontrol.wait before its
+// first access to global memory, and that instruction returns only when the
+// earlier kernel has completed and its writes are visible, so results do not
+// depend on the mode. A kernel launched without the attribute, or after
+// something that is not a kernel, passes the wait at once.
+//
+// No kernel here signals its dependents early (griddepcontrol.launch_dependents
+// at the top): measured on the RoPE -> decode -> merge chain, early signals let
+// the next step's persistent decode CTAs occupy SMs while this step's merge
+// still needed them, and a 39 us step became 46 us. Without early signals the
+// same chain runs in 37.9 us.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <utility>
+
+namespace loom_launch {
+
+// 0 = plain launches; 1 = programmatic launch.
+inline std::atomic<uint32_t>& programmatic_mode() {
+  static std::atomic<uint32_t> mode{1};
+  return mode;
+}
+
+template <typename... Params, typename... Args>
+cudaError_t launch(void (*kernel)(Params...), dim3 grid, dim3 block, size_t shared_bytes,
+                   cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t config{};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = shared_bytes;
+  config.stream = stream;
+  cudaLaunchAttribute attribute{};
+  if (programmatic_mode().load(std::memory_order_relaxed) != 0) {
+    attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute.val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+  }
+  return cudaLaunchKernelEx(&config, kernel, std::forward<Args>(args)...);
+}
+
+#ifdef __CUDACC__
+// Blocks until every kernel this one depends on has completed and flushed.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+
+#endif
+
+}  // namespace loom_launch

@@ -91,6 +91,7 @@ template <typename QT, typename CT>
 __global__ void __launch_bounds__(kScalarThreads) decode_scalar_kernel(const DecodeParams p) {
   constexpr bool kFp8 = std::is_same<CT, uint8_t>::value;
   extern __shared__ __align__(16) float scalar_smem[];
+  loom_launch::grid_dependency_wait();
   float* q_shared = scalar_smem;                                 // [head_size]
   float* merge_o = q_shared + p.head_size;                       // [warps][value_head_size]
   float* merge_max = merge_o + kScalarWarps * p.value_head_size; // [warps]
@@ -262,6 +263,7 @@ merge_states_kernel(const float* __restrict__ states, uint64_t row_stride, uint6
                     const int32_t* __restrict__ sequence_lengths, uint32_t rows_per_sequence,
                     uint32_t partition_tokens, uint32_t max_sequence_length, void* output,
                     uint32_t emit_state) {
+  loom_launch::grid_dependency_wait();
   const uint32_t row = blockIdx.x;
   uint32_t parts = fixed_parts;
   if (sequence_lengths != nullptr) {
@@ -282,6 +284,7 @@ merge_stream_kernel(const float* __restrict__ slots, const uint32_t* __restrict_
                     const int32_t* __restrict__ sequence_lengths, uint32_t query_heads, uint32_t group,
                     uint32_t heads_per_item, uint32_t value_head_size, uint32_t max_sequence_length,
                     void* output, uint32_t emit_state) {
+  loom_launch::grid_dependency_wait();
   const uint32_t row = blockIdx.x;
   const uint32_t seq = row / query_heads;
   const uint32_t query_head = row % query_heads;
@@ -308,6 +311,13 @@ merge_stream_kernel(const float* __restrict__ slots, const uint32_t* __restrict_
 // ================================================================= host
 
 thread_local const char* g_last_route = "none";
+
+// Launch status of this library from a runtime status (clears a sticky error).
+int launched(cudaError_t status) {
+  if (status == cudaSuccess) return LOOM_CUDA_SUCCESS;
+  cudaGetLastError();
+  return LOOM_CUDA_LAUNCH_ERROR;
+}
 
 bool aligned16(const void* pointer) { return (reinterpret_cast<uintptr_t>(pointer) & 15u) == 0; }
 
@@ -365,8 +375,7 @@ int launch_mma(const DecodeParams& p, cudaStream_t stream) {
   if (ensure_smem(kernel, kBytes, configured) != cudaSuccess) return LOOM_CUDA_LAUNCH_ERROR;
   const uint32_t head_chunks = (p.group + 8 * kNT - 1) / (8 * kNT);
   const dim3 grid(p.sequences * p.max_partitions, p.kv_heads * head_chunks, 1);
-  kernel<<<grid, kMmaThreads, kBytes, stream>>>(p);
-  return cudaGetLastError() == cudaSuccess ? LOOM_CUDA_SUCCESS : LOOM_CUDA_LAUNCH_ERROR;
+  return launched(loom_launch::launch(kernel, grid, dim3(kMmaThreads), kBytes, stream, p));
 }
 
 template <typename QT, bool kFp8, int kD, int kNT>
@@ -375,8 +384,7 @@ int launch_stream(const DecodeParams& p, uint32_t ctas, cudaStream_t stream) {
   constexpr int kBytes = StreamRing<kFp8, kD, kNT>::kSmemBytes;
   auto kernel = decode_stream_kernel<QT, kFp8, kD, kNT>;
   if (ensure_smem(kernel, kBytes, configured) != cudaSuccess) return LOOM_CUDA_LAUNCH_ERROR;
-  kernel<<<ctas, kMmaThreads, kBytes, stream>>>(p);
-  return cudaGetLastError() == cudaSuccess ? LOOM_CUDA_SUCCESS : LOOM_CUDA_LAUNCH_ERROR;
+  return launched(loom_launch::launch(kernel, dim3(ctas), dim3(kMmaThreads), kBytes, stream, p));
 }
 
 // ---- tensor maps for the TMA-fed kernel ---------------------------------------
@@ -478,8 +486,8 @@ int launch_stream_tma(const DecodeParams& p, uint32_t ctas, const CacheMaps& map
   constexpr int kBytes = TmaRing<kFp8, kD, kNT>::kSmemBytes;
   auto kernel = decode_stream_tma_kernel<QT, kFp8, kD, kNT>;
   if (ensure_smem(kernel, kBytes, configured) != cudaSuccess) return LOOM_CUDA_LAUNCH_ERROR;
-  kernel<<<ctas, kMmaThreads, kBytes, stream>>>(p, maps.key, maps.value, maps.axes);
-  return cudaGetLastError() == cudaSuccess ? LOOM_CUDA_SUCCESS : LOOM_CUDA_LAUNCH_ERROR;
+  return launched(loom_launch::launch(kernel, dim3(ctas), dim3(kMmaThreads), kBytes, stream, p, maps.key, maps.value,
+                                      maps.axes));
 }
 
 template <typename QT, bool kFp8>
@@ -513,8 +521,7 @@ int launch_scalar(const DecodeParams& p, cudaStream_t stream) {
       ((size_t)p.head_size + (size_t)kScalarWarps * p.value_head_size + 2 * kScalarWarps) * sizeof(float);
   if (bytes > 48 * 1024) return LOOM_CUDA_UNSUPPORTED;
   const dim3 grid(p.sequences * p.max_partitions, p.query_heads, 1);
-  decode_scalar_kernel<QT, CT><<<grid, kScalarThreads, bytes, stream>>>(p);
-  return cudaGetLastError() == cudaSuccess ? LOOM_CUDA_SUCCESS : LOOM_CUDA_LAUNCH_ERROR;
+  return launched(loom_launch::launch(decode_scalar_kernel<QT, CT>, grid, dim3(kScalarThreads), bytes, stream, p));
 }
 
 bool mma_route_fits(const LoomDecodeArgs& a, bool fp8) {
@@ -757,10 +764,13 @@ int launch_decode(const LoomDecodeArgs& a) {
   const uint64_t rows = (uint64_t)p.sequences * p.query_heads;
   if (rows > 0x7fffffffull) return LOOM_CUDA_INVALID_ARGUMENT;
   const uint32_t grid = (uint32_t)rows;
+  cudaError_t merge_status = cudaSuccess;
   if (stream_ctas != 0) {
-#define LOOM_MERGE(type)                                                                          \
-  merge_stream_kernel<type><<<grid, kMergeThreads, 0, stream>>>(                                 \
-      p.partials, p.item_meta, p.sequence_lengths, p.query_heads, p.group, shape.heads_per_item, \
+#define LOOM_MERGE(type)                                                                              \
+  merge_status = loom_launch::launch(                                                                 \
+      merge_stream_kernel<type>, dim3(grid), dim3(kMergeThreads), 0, stream,                          \
+      static_cast<const float*>(p.partials), static_cast<const uint32_t*>(p.item_meta),               \
+      static_cast<const int32_t*>(p.sequence_lengths), p.query_heads, p.group, shape.heads_per_item, \
       p.value_head_size, p.max_sequence_length, p.output, p.emit_state)
     if (p.emit_state || a.dtype == 0) LOOM_MERGE(float);
     else if (a.dtype == 1) LOOM_MERGE(__half);
@@ -769,16 +779,18 @@ int launch_decode(const LoomDecodeArgs& a) {
   } else {
     const uint64_t part_stride = state_stride(p.value_head_size);
     const uint64_t row_stride = part_stride * p.max_partitions;
-#define LOOM_MERGE(type)                                                                        \
-  merge_states_kernel<type><<<grid, kMergeThreads, 0, stream>>>(                               \
-      p.partials, row_stride, part_stride, p.value_head_size, 0u, p.sequence_lengths,          \
-      p.query_heads, p.partition_tokens, p.max_sequence_length, p.output, p.emit_state)
+#define LOOM_MERGE(type)                                                                          \
+  merge_status = loom_launch::launch(                                                             \
+      merge_states_kernel<type>, dim3(grid), dim3(kMergeThreads), 0, stream,                      \
+      static_cast<const float*>(p.partials), row_stride, part_stride, p.value_head_size, 0u,      \
+      static_cast<const int32_t*>(p.sequence_lengths), p.query_heads, p.partition_tokens,         \
+      p.max_sequence_length, p.output, p.emit_state)
     if (p.emit_state || a.dtype == 0) LOOM_MERGE(float);
     else if (a.dtype == 1) LOOM_MERGE(__half);
     else LOOM_MERGE(__nv_bfloat16);
 #undef LOOM_MERGE
   }
-  return cudaGetLastError() == cudaSuccess ? LOOM_CUDA_SUCCESS : LOOM_CUDA_LAUNCH_ERROR;
+  return launched(merge_status);
 }
 
 // The reference ABI: dense-inner NHD caches, block stride free.
@@ -969,14 +981,16 @@ extern "C" int loom_cuda_merge_decode_states(const float* states, uint32_t parts
   const uint64_t row_stride = state_stride(value_head_size);
   const uint64_t part_stride = row_stride * rows;
   cudaStream_t cuda_stream = static_cast<cudaStream_t>(stream);
-#define LOOM_MERGE(type)                                                                      \
-  merge_states_kernel<type><<<rows, kMergeThreads, 0, cuda_stream>>>(                        \
-      states, row_stride, part_stride, value_head_size, parts, nullptr, 1u, 1u, 0u, output, 0u)
+  cudaError_t status = cudaSuccess;
+#define LOOM_MERGE(type)                                                                               \
+  status = loom_launch::launch(merge_states_kernel<type>, dim3(rows), dim3(kMergeThreads), 0,          \
+                               cuda_stream, states, row_stride, part_stride, value_head_size, parts,   \
+                               static_cast<const int32_t*>(nullptr), 1u, 1u, 0u, output, 0u)
   if (out_dtype == 0) LOOM_MERGE(float);
   else if (out_dtype == 1) LOOM_MERGE(__half);
   else LOOM_MERGE(__nv_bfloat16);
 #undef LOOM_MERGE
-  return cudaGetLastError() == cudaSuccess ? LOOM_CUDA_SUCCESS : LOOM_CUDA_LAUNCH_ERROR;
+  return launched(status);
 }
 
 extern "C" int loom_cuda_supports_paged_decode(uint32_t dtype, uint32_t cache_encoding, uint32_t sequences,
@@ -1009,6 +1023,12 @@ extern "C" const char* loom_cuda_last_decode_route(void) { return loom_decode::g
 extern "C" int loom_cuda_set_decode_copy_engine(uint32_t engine) {
   if (engine > 1) return LOOM_CUDA_INVALID_ARGUMENT;
   loom_decode::g_copy_engine.store(engine, std::memory_order_relaxed);
+  return LOOM_CUDA_SUCCESS;
+}
+
+extern "C" int loom_cuda_set_programmatic_launch(uint32_t mode) {
+  if (mode > 1) return LOOM_CUDA_INVALID_ARGUMENT;
+  loom_launch::programmatic_mode().store(mode, std::memory_order_relaxed);
   return LOOM_CUDA_SUCCESS;
 }
 

@@ -35,6 +35,7 @@
 #include <type_traits>
 
 #include "../../include/loom_launch.h"
+#include "launch_util.cuh"
 
 namespace {
 
@@ -170,6 +171,9 @@ rope_paged_kv_vector_kernel(const RopeParams p, uint32_t rotary_units_per_head,
                             uint32_t value_units_per_head,
                             uint32_t units_per_token) {
   constexpr int kVec = Vec16<T>::kCount;
+  // launched early by programmatic dependent launch: global memory is touched
+  // only after the kernels before this one have completed
+  loom_launch::grid_dependency_wait();
   const uint64_t flat = (uint64_t)blockIdx.x * kThreads + threadIdx.x;
   const uint64_t total = (uint64_t)p.tokens * units_per_token;
   if (flat >= total) return;
@@ -283,6 +287,7 @@ __device__ __forceinline__ void store_cache_scalar(void* cache, uint64_t offset,
 template <typename T, bool kFp8>
 __global__ void __launch_bounds__(kThreads)
 rope_paged_kv_scalar_kernel(const RopeParams p, uint32_t units_per_token) {
+  loom_launch::grid_dependency_wait();
   const uint64_t flat = (uint64_t)blockIdx.x * kThreads + threadIdx.x;
   const uint64_t total = (uint64_t)p.tokens * units_per_token;
   if (flat >= total) return;
@@ -389,16 +394,22 @@ int launch_typed(const RopeParams& p, cudaStream_t stream) {
                                (uint64_t)p.kv_heads * (tail_units + value_units);
     const uint64_t blocks = ((uint64_t)p.tokens * per_token + kThreads - 1) / kThreads;
     if (per_token > 0xffffffffull || blocks > 0x7fffffffull) return LOOM_CUDA_INVALID_ARGUMENT;
-    rope_paged_kv_vector_kernel<T, kFp8><<<(uint32_t)blocks, kThreads, 0, stream>>>(
-        p, rotary_units, tail_units, value_units, (uint32_t)per_token);
+    if (loom_launch::launch(rope_paged_kv_vector_kernel<T, kFp8>, dim3((uint32_t)blocks), dim3(kThreads), 0,
+                            stream, p, rotary_units, tail_units, value_units, (uint32_t)per_token) != cudaSuccess) {
+      cudaGetLastError();
+      return LOOM_CUDA_LAUNCH_ERROR;
+    }
   } else {
     const uint64_t per_token =
         (uint64_t)heads * (p.rotary_dim / 2) +
         (uint64_t)p.kv_heads * ((p.head_size - p.rotary_dim) + p.value_head_size);
     const uint64_t blocks = ((uint64_t)p.tokens * per_token + kThreads - 1) / kThreads;
     if (per_token > 0xffffffffull || blocks > 0x7fffffffull) return LOOM_CUDA_INVALID_ARGUMENT;
-    rope_paged_kv_scalar_kernel<T, kFp8><<<(uint32_t)blocks, kThreads, 0, stream>>>(
-        p, (uint32_t)per_token);
+    if (loom_launch::launch(rope_paged_kv_scalar_kernel<T, kFp8>, dim3((uint32_t)blocks), dim3(kThreads), 0,
+                            stream, p, (uint32_t)per_token) != cudaSuccess) {
+      cudaGetLastError();
+      return LOOM_CUDA_LAUNCH_ERROR;
+    }
   }
   return cudaGetLastError() == cudaSuccess ? LOOM_CUDA_SUCCESS : LOOM_CUDA_LAUNCH_ERROR;
 }

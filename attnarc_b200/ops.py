@@ -55,6 +55,12 @@ def last_decode_route() -> str:
     return library().loom_cuda_last_decode_route().decode()
 
 
+def set_programmatic_launch(mode: int) -> None:
+    """0: plain launches; 1 (default): programmatic dependent launch of the library's kernels."""
+    if library().loom_cuda_set_programmatic_launch(int(mode)) != 0:
+        raise ValueError(f"unknown programmatic launch mode {mode!r}")
+
+
 def set_decode_copy_engine(engine: str) -> None:
     """``"tma"`` (default) or ``"cp_async"``: how the balanced kernel fills its rings."""
     code = {"tma": 0, "cp_async": 1}[engine]

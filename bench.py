@@ -56,6 +56,8 @@ def parse_args():
                         help="override the workload's batch size (smaller cases for profiler captures)")
     parser.add_argument("--copies", type=int, default=0, help="cache copies rotated between steps (0 = auto)")
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--programmatic-launch", type=int, choices=[0, 1], default=None,
+                        help="programmatic dependent launch mode of the library (default: the library's, 1)")
     parser.add_argument("--cpu-seconds", type=float, default=15.0, help="CPU work per baseline sample")
     return parser.parse_args()
 
@@ -280,6 +282,9 @@ def run_b200(args):
 
     from attnarc_b200 import ops, workloads
 
+    if args.programmatic_launch is not None:
+        ops.set_programmatic_launch(args.programmatic_launch)
+
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -467,6 +472,7 @@ def run_b200(args):
                 "context_tokens_rank0": int(case.lengths.sum()), "partition_tokens": partition if split else 0,
                 "kv_bytes_per_step_rank0": kv_bytes, "parallelism": f"sequence-sharded x{world}, no collective",
                 "launch": "cuda_graph of K steps (value); eager public API (e2e)",
+                "programmatic_launch": 1 if args.programmatic_launch is None else args.programmatic_launch,
                 "l2": f"inputs rotate over {copies} cache copies of {cache_bytes / 1e6:.0f} MB (> 126 MB L2 in total)",
             },
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,

@@ -238,6 +238,17 @@ const char* loom_cuda_last_decode_route(void);
 int loom_cuda_set_decode_copy_engine(uint32_t engine);
 
 /*
+ * Programmatic dependent launch of every kernel of this library (no
+ * counterpart in the reference). Process-wide.
+ *   0  plain launches.
+ *   1  (default) kernels carry the programmatic-serialisation launch attribute:
+ *      their CTAs may become resident while the preceding kernel of the stream
+ *      drains. Each kernel waits for that kernel to complete before its first
+ *      access to global memory, so results never depend on the mode.
+ */
+int loom_cuda_set_programmatic_launch(uint32_t mode);
+
+/*
  * The TMA-fed kernel bounds every wait on a copy; if one ever expires it sets a
  * flag on the device instead of hanging. This reads the flag of the current
  * device into *value (0 = never happened) and optionally clears it. Unlike the
