@@ -91,8 +91,8 @@ struct TmaRing {
   // One 8-head item per warp needs about 170 registers a thread, so three CTAs
   // fit an SM; twelve warps hide the latency of the dependent MMA and softmax
   // steps better than eight. Sixteen heads need about 240 registers: two CTAs.
-  static constexpr int kCtasPerSm = kNT == 1 ? 3 : 2;
-  static constexpr int kWantedBytes = kNT == 1 ? 12 * 1024 : 16 * 1024;
+  static constexpr int kCtasPerSm = kNT == 1 ? (kFp8 ? 4 : 3) : 2;
+  static constexpr int kWantedBytes = kNT == 1 ? (kFp8 ? 8 * 1024 : 12 * 1024) : 16 * 1024;
   static constexpr int kRaw = kWantedBytes / Tile::kTileBytes;
   static constexpr int kSlots = kRaw < 3 ? 3 : (kRaw > 9 ? 9 : kRaw);
   static constexpr int kAhead = kSlots - 1;

@@ -360,7 +360,7 @@ uint32_t current_sm_count() {
 // least a 148-SM device, so that a size computed before a device is current,
 // or before the kernel is chosen, still fits.
 constexpr uint32_t kStreamCtasPerSm = 2;
-constexpr uint32_t kStreamMaxCtasPerSm = 3;
+constexpr uint32_t kStreamMaxCtasPerSm = 4;
 uint32_t stream_ctas_for_launch(uint32_t per_sm) { return per_sm * current_sm_count(); }
 uint32_t stream_ctas_for_sizing() {
   const uint32_t sms = current_sm_count();
@@ -703,7 +703,7 @@ int launch_decode(const LoomDecodeArgs& a) {
         tma = &maps;
       }
       const uint32_t ctas =
-          stream_ctas_for_launch(tma != nullptr && p.group <= 8 ? kStreamMaxCtasPerSm : kStreamCtasPerSm);
+          stream_ctas_for_launch(tma != nullptr && p.group <= 8 ? (fp8 ? 4u : 3u) : kStreamCtasPerSm);
       if (ctas != 0 && stream_shape(a.sequences, a.query_heads, a.kv_heads, a.value_head_size, ctas, &shape) &&
           a.workspace_elements >= shape.total_elements) {
         stream_ctas = ctas;
