@@ -1,0 +1,648 @@
+// Balanced persistent paged decode over an FP8 E4M3 cache on the fifth
+// generation tensor cores (tcgen05.mma with the accumulators in tensor memory).
+//
+// Why a second compute path for FP8. With mma.sync the E4M3 bytes must be
+// turned into F16 in registers first (ldmatrix, byte permute, conversion): 445
+// warp instructions per 4 KB of cache, and the instruction stream, not HBM,
+// bounds the kernel. tcgen05.mma of kind f8f6f4 reads E4M3 operands straight
+// from the shared-memory tiles that TMA wrote, so the K and V bytes are never
+// touched by a thread at all; what is left per token is the softmax.
+//
+// Shape of the computation, per 128-token tile of one (sequence, KV head):
+//     S[128 tokens x 16] = K[128 x 128] . Qs^T          (4 MMAs, M=128 N=16 K=32)
+//     O[128 dims   x 16] += V^T[128 x 128 tokens] . Ps^T (4 MMAs, A is MN-major)
+// K is the K-major A operand exactly as TMA's 128-byte swizzle lays it out;
+// the same kind of V tile is the MN-major A operand of the second product
+// (value dims on M). The B operands must be E4M3 as well, so the 16-bit query
+// and the probabilities are each split into two E4M3 planes, x = hi + lo with
+// hi = e4m3(x), lo = e4m3(x - hi): columns 0-7 of S and O hold the hi plane of
+// the 8 query heads, columns 8-15 the lo plane, and the two are added when the
+// accumulators are read. Two planes carry 7-8 significant bits, what the BF16
+// operands of the other path carry; Q is pre-scaled per head by a power of two
+// so that its largest element sits near 2^8, P by 2^4.
+//
+// One thread per token row: thread r reads row r of S from tensor memory
+// (tcgen05.ld, lane = row), applies scale and mask, exponentiates against the
+// per-head reference exponent (see chunk_softmax in decode_mma.cuh; here the
+// reference is shared by the CTA and a CTA-wide vote decides when it moves),
+// and writes its 16 probability bytes into the P tile. O stays in tensor memory
+// for the whole work item; thread d reads row d (a value dim) at the end.
+//
+// Pipeline per CTA: thread 0 issues the TMA loads two tiles ahead, the MMAs
+// and their commits; QK of tile i+1 is issued right after PV of tile i, so the
+// tensor pipe works on the next scores while the threads are still busy with
+// this tile's epilogue. Three CTAs per SM overlap each other's bubbles.
+//
+// Every wait is bounded (see mbarrier_wait); tensor memory is freed on every
+// path out of the kernel.
+#pragma once
+
+#include <cuda_fp8.h>
+
+#include "decode_stream_tma.cuh"
+
+namespace loom_decode {
+
+constexpr uint32_t kUmmaTileTokens = 128;
+constexpr int kUmmaThreads = 128;
+constexpr int kUmmaStages = 2;               // K+V tile pairs in flight per CTA
+constexpr uint32_t kUmmaTileBytes = 16384;   // 128 tokens x 128 bytes
+constexpr uint32_t kUmmaTmemColumns = 32;    // S: columns 0-15, O: columns 16-31
+constexpr float kUmmaSlack = 2.0f;           // p <= 2^2 before the reference moves
+constexpr float kUmmaProbabilityScale = 64.0f;
+constexpr int kUmmaCtasPerSm = 3;
+
+struct UmmaSmem {
+  static constexpr uint32_t kStages = 0;                                    // kUmmaStages x (K, V)
+  static constexpr uint32_t kQuery = kUmmaStages * 2 * kUmmaTileBytes;      // 16 rows x 128 B
+  static constexpr uint32_t kProbabilities = kQuery + 2048;                 // 16 rows x 128 B
+  static constexpr uint32_t kPrefix = kProbabilities + 2048;                // [sequences + 1]
+  static constexpr uint32_t kBarriers = kPrefix + ((kTmaMaxSequences + 1) * 4 + 7) / 8 * 8;
+  static constexpr uint32_t kTmemSlot = kBarriers + (kUmmaStages + 2) * 8;  // full[], scores, output
+  static constexpr uint32_t kHeadScale = kTmemSlot + 8;                     // [8]
+  static constexpr uint32_t kReduce = kHeadScale + 32;                      // [4 warps][8]
+  static constexpr uint32_t kWarpTotals = kReduce + 128;                    // [4]
+  static constexpr uint32_t kAborted = kWarpTotals + 16;                    // set when a wait expired
+  static constexpr uint32_t kBytes = kAborted + 16 + 1024;                  // + alignment slack
+};
+
+// ---- tcgen05 wrappers ---------------------------------------------------------
+
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_slot, uint32_t columns) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_slot), "r"(columns)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_free(uint32_t address, uint32_t columns) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(address), "r"(columns) : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_fence_before_sync() {
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+}
+
+__device__ __forceinline__ void tcgen05_fence_after_sync() {
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+}
+
+// D[tmem] (+)= A[smem desc] . B[smem desc]^T, E4M3 operands, F32 accumulate.
+__device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                        uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// Makes `barrier` complete one arrival when every MMA issued so far by this
+// thread has finished.
+__device__ __forceinline__ void umma_commit(uint32_t barrier) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(barrier)
+               : "memory");
+}
+
+// 16 consecutive 32-bit columns of this thread's lane.
+__device__ __forceinline__ void tmem_load16(float (&v)[16], uint32_t address) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(address)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ void tmem_store16(uint32_t address, const float (&v)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};\n" ::"r"(
+          address),
+      "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+      "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+      "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+      "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
+      "r"(__float_as_uint(v[15]))
+      : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a tile whose rows are 128 bytes apart and
+// which was written with the 128-byte swizzle (TMA's, or the same function by
+// hand): 8-row groups 1024 bytes apart. Serves a K-major operand (rows = M or
+// N index) and an MN-major operand (rows = K index) alike; the instruction
+// descriptor says which it is.
+__device__ __forceinline__ uint64_t umma_tile_descriptor(uint32_t smem_byte_address) {
+  uint64_t descriptor = 0;
+  descriptor |= (uint64_t)((smem_byte_address >> 4) & 0x3fffu);  // start address
+  descriptor |= (uint64_t)1 << 16;                               // leading byte offset (unused with swizzle)
+  descriptor |= (uint64_t)(1024 >> 4) << 32;                     // stride byte offset: next 8-row group
+  descriptor |= (uint64_t)1 << 46;                               // descriptor version of this architecture
+  descriptor |= (uint64_t)2 << 61;                               // 128-byte swizzle
+  return descriptor;
+}
+
+// Instruction descriptor: E4M3 x E4M3 -> F32, M = 128, N = 16.
+constexpr uint32_t kUmmaIdescBase = (1u << 4) | ((16u >> 3) << 17) | ((128u >> 4) << 24);
+constexpr uint32_t kUmmaIdescScores = kUmmaIdescBase;               // A (keys) K-major
+constexpr uint32_t kUmmaIdescValues = kUmmaIdescBase | (1u << 15);  // A (values) MN-major
+
+// Two floats -> two E4M3 bytes (round to nearest even, saturating), low byte first.
+__device__ __forceinline__ uint32_t e4m3_pair(float low, float high) {
+  return (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(low, high), __NV_SATFINITE, __NV_E4M3);
+}
+
+__device__ __forceinline__ float2 e4m3_pair_to_float(uint32_t pair) {
+  const __half2_raw raw = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)pair, __NV_E4M3);
+  return __half22float2(*reinterpret_cast<const __half2*>(&raw));
+}
+
+// x = hi + lo in E4M3 for two values: returns the hi pair and the lo pair.
+__device__ __forceinline__ void e4m3_split_pair(float a, float b, uint32_t& hi, uint32_t& lo) {
+  hi = e4m3_pair(a, b);
+  const float2 back = e4m3_pair_to_float(hi);
+  lo = e4m3_pair(a - back.x, b - back.y);
+}
+
+// Byte offset of (row, byte column) inside a 128-byte-swizzled tile.
+__device__ __forceinline__ uint32_t swizzled_byte(uint32_t row, uint32_t column) {
+  return row * 128u + ((((column >> 4) ^ (row & 7u)) << 4) | (column & 15u));
+}
+
+
+template <typename QT>
+__global__ void __launch_bounds__(kUmmaThreads, kUmmaCtasPerSm)
+decode_umma_fp8_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap key_map,
+                       const __grid_constant__ CUtensorMap value_map, const TmaAxes axes) {
+  constexpr uint32_t kD = 128;
+  constexpr uint32_t kHeads = 8;
+
+  extern __shared__ uint8_t raw_smem[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023u) & ~uintptr_t(1023));
+  const uint32_t smem_base = smem_address(smem);
+  const uint32_t query_tile = smem_base + UmmaSmem::kQuery;
+  const uint32_t probability_tile = smem_base + UmmaSmem::kProbabilities;
+  uint32_t* prefix = reinterpret_cast<uint32_t*>(smem + UmmaSmem::kPrefix);
+  const uint32_t barriers = smem_base + UmmaSmem::kBarriers;  // full[kUmmaStages], scores, output
+  const uint32_t scores_barrier = barriers + kUmmaStages * 8;
+  const uint32_t output_barrier = scores_barrier + 8;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + UmmaSmem::kTmemSlot);
+  float* head_scale = reinterpret_cast<float*>(smem + UmmaSmem::kHeadScale);
+  float* reduce = reinterpret_cast<float*>(smem + UmmaSmem::kReduce);
+  uint32_t* warp_totals = reinterpret_cast<uint32_t*>(smem + UmmaSmem::kWarpTotals);
+  volatile uint32_t* aborted = reinterpret_cast<volatile uint32_t*>(smem + UmmaSmem::kAborted);
+
+  const uint32_t tid = threadIdx.x;
+  const uint32_t warp = tid >> 5;
+  const uint32_t lane = tid & 31u;
+
+  if (tid == 0) {
+    *aborted = 0;
+#pragma unroll
+    for (int i = 0; i < kUmmaStages + 2; ++i) mbarrier_init(barriers + i * 8, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+  }
+  loom_launch::grid_dependency_wait();
+
+  // ---- 128-token tiles per sequence, exclusive prefix sum ----------------------
+  {
+    const uint32_t per_thread = (p.sequences + kUmmaThreads - 1) / kUmmaThreads;
+    const uint32_t begin = min(tid * per_thread, p.sequences);
+    const uint32_t end = min(begin + per_thread, p.sequences);
+    uint32_t local = 0;
+    for (uint32_t s = begin; s < end; ++s) {
+      const uint32_t length = clamp_length(__ldg(p.sequence_lengths + s), p.max_sequence_length);
+      local += (length + kUmmaTileTokens - 1) / kUmmaTileTokens;
+    }
+    uint32_t inclusive = local;
+#pragma unroll
+    for (int offset = 1; offset < 32; offset <<= 1) {
+      const uint32_t other = __shfl_up_sync(0xffffffffu, inclusive, offset);
+      if (lane >= (uint32_t)offset) inclusive += other;
+    }
+    if (lane == 31) warp_totals[warp] = inclusive;
+    __syncthreads();
+    uint32_t running = inclusive - local;
+    for (uint32_t w = 0; w < warp; ++w) running += warp_totals[w];
+    for (uint32_t s = begin; s < end; ++s) {
+      prefix[s] = running;
+      const uint32_t length = clamp_length(__ldg(p.sequence_lengths + s), p.max_sequence_length);
+      running += (length + kUmmaTileTokens - 1) / kUmmaTileTokens;
+    }
+    if (tid == kUmmaThreads - 1) prefix[p.sequences] = running;
+    __syncthreads();
+  }
+
+  const uint32_t heads = p.kv_heads;  // work items per sequence (one item = one KV head, up to 8 query heads)
+  const uint64_t total_tiles = (uint64_t)heads * prefix[p.sequences];
+  const uint64_t ctas = gridDim.x;
+  const uint64_t share = total_tiles / ctas;
+  const uint64_t extra = total_tiles % ctas;
+  const uint64_t range_begin = blockIdx.x * share + min((uint64_t)blockIdx.x, extra);
+  const uint64_t range_end = range_begin + share + (blockIdx.x < extra ? 1u : 0u);
+  if (range_begin >= range_end) return;  // nothing allocated yet
+  auto cta_of = [&](uint64_t tile) -> uint32_t {
+    const uint64_t boundary = extra * (share + 1);
+    return tile < boundary ? (uint32_t)(tile / (share + 1)) : (uint32_t)(extra + (tile - boundary) / share);
+  };
+  const uint32_t my_tiles = (uint32_t)(range_end - range_begin);
+
+  // ---- tensor memory -------------------------------------------------------------
+  if (warp == 0) tmem_alloc(smem_base + UmmaSmem::kTmemSlot, kUmmaTmemColumns);
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  tcgen05_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_scores = tmem_base;        // columns 0-15
+  const uint32_t tmem_output = tmem_base + 16u;  // columns 16-31
+  const uint32_t lane_offset = (warp * 32u) << 16;  // this warp's quarter of the 128 lanes
+
+  auto load_sequence = [&](StreamCursor& c) {
+    c.tiles = prefix[c.seq + 1] - prefix[c.seq];
+    c.length = clamp_length(__ldg(p.sequence_lengths + c.seq), p.max_sequence_length);
+  };
+  auto advance = [&](StreamCursor& c) {
+    if (++c.tile < c.tiles) return;
+    c.tile = 0;
+    if (++c.head < heads) return;
+    c.head = 0;
+    do {
+      ++c.seq;
+    } while (c.seq < p.sequences && prefix[c.seq + 1] == prefix[c.seq]);
+    if (c.seq < p.sequences) load_sequence(c);
+  };
+
+  StreamCursor start;
+  {
+    uint32_t low = 0, high = p.sequences;
+    while (high - low > 1) {
+      const uint32_t middle = (low + high) >> 1;
+      if ((uint64_t)heads * prefix[middle] <= range_begin) low = middle;
+      else high = middle;
+    }
+    start.seq = low;
+    load_sequence(start);
+    const uint64_t inside = range_begin - (uint64_t)heads * prefix[low];
+    start.head = (uint32_t)(inside / start.tiles);
+    start.tile = (uint32_t)(inside % start.tiles);
+  }
+
+  // ---- producer (thread 0): TMA loads of whole tiles, kUmmaStages ahead ---------
+  const bool head_inner = axes.head < axes.page;
+  StreamCursor producer = start;
+  uint32_t issued = 0;
+  auto issue_loads = [&]() {  // thread 0 only
+    if (issued >= my_tiles) return;
+    const uint32_t stage = issued % kUmmaStages;
+    const uint32_t token0 = producer.tile * kUmmaTileTokens;
+    const uint32_t live = min(kUmmaTileTokens, producer.length - token0);
+    const uint32_t boxes = (live + 15u) >> 4;
+    const uint32_t barrier = barriers + stage * 8;
+    const uint32_t key_tile = smem_base + stage * (2 * kUmmaTileBytes);
+    const uint32_t value_tile = key_tile + kUmmaTileBytes;
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    mbarrier_expect_tx(barrier, boxes * 2u * 2048u);
+    const int32_t* table = p.block_tables + (uint64_t)producer.seq * p.max_blocks_per_sequence;
+    // all block ids first (independent loads), then the copies
+    int32_t pages[8], blocks[8];
+#pragma unroll
+    for (uint32_t box = 0; box < 8; ++box) {
+      const uint32_t token = token0 + box * 16u;
+      const uint32_t logical = p.block_shift < 32u ? token >> p.block_shift : token / p.block_size;
+      pages[box] = (int32_t)(token - logical * p.block_size);
+      blocks[box] = box < boxes ? __ldg(table + logical) : 0;
+    }
+    const int32_t head = (int32_t)producer.head;
+#pragma unroll
+    for (uint32_t box = 0; box < 8; ++box) {
+      if (box < boxes) {
+        const int32_t block = (int32_t)clamp_block(blocks[box], p.num_blocks);
+        const int32_t c1 = head_inner ? head : pages[box], c2 = head_inner ? pages[box] : head;
+        tma_load_4d(key_tile + box * 2048u, &key_map, barrier, 0, c1, c2, block);
+        tma_load_4d(value_tile + box * 2048u, &value_map, barrier, 0, c1, c2, block);
+      }
+    }
+    ++issued;
+    if (issued < my_tiles) advance(producer);
+  };
+  if (tid == 0) {
+#pragma unroll
+    for (int i = 0; i < kUmmaStages; ++i) issue_loads();
+  }
+
+  // ---- per-item state ----------------------------------------------------------------
+  StreamCursor consumer = start;
+  float reference[kHeads];  // exponent reference per head (base-2 units), the same in every thread
+  float row_sum[kHeads];    // this thread's share of sum_i p_i
+  uint32_t item_first_tile = 0;  // local index of the current item's first tile in this CTA
+  bool output_pending = false;   // a PV product whose completion has not been waited for
+
+  // After one wait has expired (the device-wide flag is set by mbarrier_wait) the
+  // CTA stops waiting altogether and runs to its end on whatever it has.
+  auto wait_phase = [&](uint32_t barrier, uint32_t completions) {
+    if (*aborted) return;
+    if (!mbarrier_wait(barrier, completions & 1u)) *aborted = 1;
+  };
+
+  // Writes the two E4M3 planes of the item's queries and the per-head score scales.
+  auto begin_item = [&]() {
+#pragma unroll
+    for (int h = 0; h < (int)kHeads; ++h) {
+      reference[h] = -INFINITY;
+      row_sum[h] = 0.0f;
+    }
+    const uint32_t kv_head = consumer.head;
+    const uint32_t live_heads = min(kHeads, p.group);
+    const uint32_t head = tid >> 4, piece = tid & 15u;  // 16 threads per head, 8 dims each
+    float q[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) q[j] = 0.0f;
+    if (head < live_heads) {
+      const QT* row = static_cast<const QT*>(p.query) + (uint64_t)consumer.seq * p.q_token +
+                      ((uint64_t)kv_head * p.group + head) * p.q_head + piece * 8u;
+      const uint4 packed = *reinterpret_cast<const uint4*>(row);
+      const uint32_t words[4] = {packed.x, packed.y, packed.z, packed.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 pair = widen_pair<QT>(words[j]);
+        q[2 * j] = pair.x;
+        q[2 * j + 1] = pair.y;
+      }
+    }
+    float largest = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) largest = fmaxf(largest, fabsf(q[j]));
+#pragma unroll
+    for (int offset = 1; offset < 16; offset <<= 1) {
+      largest = fmaxf(largest, __shfl_xor_sync(0xffffffffu, largest, offset));
+    }
+    // power of two that brings the largest element into [128, 256)
+    int exponent = 0;
+    float prescale = 1.0f;
+    if (largest > 0.0f && largest < INFINITY) {
+      frexpf(largest, &exponent);
+      prescale = ldexpf(1.0f, 8 - exponent);
+    }
+    uint32_t hi[4], lo[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) e4m3_split_pair(q[2 * j] * prescale, q[2 * j + 1] * prescale, hi[j], lo[j]);
+    const uint32_t hi_low = hi[0] | (hi[1] << 16), hi_high = hi[2] | (hi[3] << 16);
+    const uint32_t lo_low = lo[0] | (lo[1] << 16), lo_high = lo[2] | (lo[3] << 16);
+    asm volatile("st.shared.v2.u32 [%0], {%1, %2};\n" ::"r"(query_tile + swizzled_byte(head, piece * 8u)), "r"(hi_low),
+                 "r"(hi_high)
+                 : "memory");
+    asm volatile("st.shared.v2.u32 [%0], {%1, %2};\n" ::"r"(query_tile + swizzled_byte(8u + head, piece * 8u)),
+                 "r"(lo_low), "r"(lo_high)
+                 : "memory");
+    if (piece == 0) {
+      const float key_scale = __ldg(p.key_scales + (uint64_t)kv_head * p.scale_stride);
+      head_scale[head] = p.scale_log2 * key_scale / prescale;
+    }
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    __syncthreads();
+  };
+
+  // Stores the item's result: final rows if this CTA covered the whole item,
+  // else a partial state.
+  auto finish_item = [&](uint32_t item_seq, uint32_t item_head, uint32_t item_tiles) {
+    // the last PV product of the item has completed (caller waited)
+    tcgen05_fence_after_sync();
+    float o[16];
+    tmem_load16(o, tmem_output + lane_offset);
+    tcgen05_fence_before_sync();
+#pragma unroll
+    for (int h = 0; h < (int)kHeads; ++h) {
+      float total = row_sum[h];
+#pragma unroll
+      for (int offset = 16; offset > 0; offset >>= 1) total += __shfl_xor_sync(0xffffffffu, total, offset);
+      if (lane == 0) reduce[warp * kHeads + h] = total;
+    }
+    __syncthreads();
+    const uint32_t kv_head = item_head;
+    const uint32_t live_heads = min(kHeads, p.group);
+    const uint64_t item = (uint64_t)item_seq * heads + item_head;
+    const uint64_t item_begin = (uint64_t)heads * prefix[item_seq] + (uint64_t)item_head * item_tiles;
+    const uint32_t first_cta = cta_of(item_begin);
+    const uint32_t last_cta = cta_of(item_begin + item_tiles - 1);
+    const uint32_t parts = last_cta - first_cta + 1;
+    const float value_scale =
+        __ldg(p.value_scales + (uint64_t)kv_head * p.scale_stride) * (1.0f / kUmmaProbabilityScale);
+    const uint32_t stride = state_stride(kD);
+    const uint64_t query_row = (uint64_t)item_seq * p.query_heads + (uint64_t)kv_head * p.group;
+    const uint32_t dv = tid;
+#pragma unroll
+    for (int h = 0; h < (int)kHeads; ++h) {
+      if ((uint32_t)h >= live_heads) break;
+      const float total = reduce[h] + reduce[kHeads + h] + reduce[2 * kHeads + h] + reduce[3 * kHeads + h];
+      const float acc = (o[h] + o[8 + h]) * value_scale;
+      if (parts == 1 && !p.emit_state) {
+        const float result = total > 0.0f ? acc / total : 0.0f;
+        QT* out = static_cast<QT*>(p.output) + (query_row + h) * kD;
+        if constexpr (std::is_same<QT, __nv_bfloat16>::value) out[dv] = __float2bfloat16_rn(result);
+        else out[dv] = __float2half_rn(result);
+      } else {
+        float* row = parts == 1 ? static_cast<float*>(p.output) + (query_row + h) * stride
+                                : p.partials + ((item + blockIdx.x) * kHeads + h) * stride;
+        row[dv] = acc;
+        if (dv == 0) {
+          row[kD] = reference[h] * kLn2;
+          row[kD + 1] = total;
+        }
+      }
+    }
+    if (tid == 0 && blockIdx.x == first_cta) {
+      p.item_meta[2 * item] = first_cta;
+      p.item_meta[2 * item + 1] = parts;
+    }
+    __syncthreads();  // `reduce` and the Q tile are reused by the next item
+  };
+
+  begin_item();
+  if (tid == 0) {
+    // scores of the first tile
+    wait_phase(barriers + 0, 0);
+    tcgen05_fence_after_sync();
+    const uint64_t key_desc = umma_tile_descriptor(smem_base);
+    const uint64_t query_desc = umma_tile_descriptor(query_tile);
+#pragma unroll
+    for (uint32_t k = 0; k < 4; ++k) umma_f8(tmem_scores, key_desc + 2u * k, query_desc + 2u * k, kUmmaIdescScores, k);
+    umma_commit(scores_barrier);
+  }
+
+  for (uint32_t i = 0; i < my_tiles; ++i) {
+    const uint32_t stage = i % kUmmaStages;
+    const uint32_t token0 = consumer.tile * kUmmaTileTokens;
+    const uint32_t live = min(kUmmaTileTokens, consumer.length - token0);
+    const bool row_live = tid < live;
+    const bool last_of_item = consumer.tile + 1 == consumer.tiles;
+    const bool last_of_range = i + 1 == my_tiles;
+
+    // ---- scores of this tile -------------------------------------------------------
+    wait_phase(scores_barrier, i);
+    tcgen05_fence_after_sync();
+    float s[16];
+    tmem_load16(s, tmem_scores + lane_offset);
+    tcgen05_fence_before_sync();
+    float d[kHeads];
+    bool over = false;
+#pragma unroll
+    for (int h = 0; h < (int)kHeads; ++h) {
+      s[h] = (s[h] + s[8 + h]) * head_scale[h];  // base-2 score
+      d[h] = row_live ? s[h] - reference[h] : -INFINITY;
+      over |= d[h] > kUmmaSlack;
+    }
+
+    // ---- the previous tile's PV product must be done before P is overwritten ---------
+    if (output_pending) {
+      wait_phase(output_barrier, i - 1);
+      output_pending = false;
+      if (tid == 0) issue_loads();  // its stage is free again
+    }
+
+    if (live < kUmmaTileTokens) {
+      // rows past the end of the sequence hold whatever the page (or an older
+      // tile) held: clear them in V so that 0 * garbage cannot become NaN
+      wait_phase(barriers + stage * 8, i / kUmmaStages);
+      if (!row_live) {
+        const uint32_t row = smem_base + stage * (2 * kUmmaTileBytes) + kUmmaTileBytes + tid * 128u;
+#pragma unroll
+        for (int piece = 0; piece < 8; ++piece) {
+          asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};\n" ::"r"(row + piece * 16), "r"(0u) : "memory");
+        }
+      }
+    }
+
+    // ---- probabilities ---------------------------------------------------------------
+    auto write_probabilities = [&]() {
+      uint32_t hi[4], lo[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float p0 = fast_exp2(d[2 * j]), p1 = fast_exp2(d[2 * j + 1]);
+        row_sum[2 * j] += p0;
+        row_sum[2 * j + 1] += p1;
+        e4m3_split_pair(p0 * kUmmaProbabilityScale, p1 * kUmmaProbabilityScale, hi[j], lo[j]);
+      }
+#pragma unroll
+      for (int h = 0; h < (int)kHeads; ++h) {
+        const uint32_t hi_byte = (hi[h >> 1] >> ((h & 1) * 8)) & 0xffu;
+        const uint32_t lo_byte = (lo[h >> 1] >> ((h & 1) * 8)) & 0xffu;
+        asm volatile("st.shared.u8 [%0], %1;\n" ::"r"(probability_tile + swizzled_byte(h, tid)), "r"(hi_byte)
+                     : "memory");
+        asm volatile("st.shared.u8 [%0], %1;\n" ::"r"(probability_tile + swizzled_byte(8 + h, tid)), "r"(lo_byte)
+                     : "memory");
+      }
+    };
+
+    const bool first_of_item = i == item_first_tile;
+    float saved_sum[kHeads];
+#pragma unroll
+    for (int h = 0; h < (int)kHeads; ++h) saved_sum[h] = row_sum[h];
+    write_probabilities();
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    if (__syncthreads_or(over ? 1 : 0)) {
+      // Rare: some score left the slack. Raise every head's reference to the
+      // largest score of this tile, rescale what was accumulated, and redo P.
+#pragma unroll
+      for (int h = 0; h < (int)kHeads; ++h) {
+        float top = row_live ? s[h] : -INFINITY;
+#pragma unroll
+        for (int offset = 16; offset > 0; offset >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, offset));
+        if (lane == 0) reduce[warp * kHeads + h] = top;
+      }
+      __syncthreads();
+      float alpha[kHeads];
+#pragma unroll
+      for (int h = 0; h < (int)kHeads; ++h) {
+        const float top = fmaxf(fmaxf(reduce[h], reduce[kHeads + h]), fmaxf(reduce[2 * kHeads + h], reduce[3 * kHeads + h]));
+        const float raised = fmaxf(reference[h], top);
+        alpha[h] = reference[h] == -INFINITY ? 0.0f : fast_exp2(reference[h] - raised);
+        reference[h] = raised;
+        row_sum[h] = saved_sum[h] * alpha[h];
+        d[h] = row_live ? s[h] - raised : -INFINITY;
+      }
+      if (!first_of_item) {
+        // O lives in tensor memory: thread = value dim
+        float o[16];
+        tcgen05_fence_after_sync();
+        tmem_load16(o, tmem_output + lane_offset);
+#pragma unroll
+        for (int h = 0; h < (int)kHeads; ++h) {
+          o[h] *= alpha[h];
+          o[8 + h] *= alpha[h];
+        }
+        tmem_store16(tmem_output + lane_offset, o);
+        tcgen05_fence_before_sync();
+      }
+      write_probabilities();
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+      __syncthreads();
+    }
+
+    // ---- O += V^T . P^T, then the next tile's scores ----------------------------------
+    if (tid == 0) {
+      tcgen05_fence_after_sync();
+      wait_phase(barriers + stage * 8, i / kUmmaStages);  // the V tile has landed (as K did)
+      const uint64_t value_desc = umma_tile_descriptor(smem_base + stage * (2 * kUmmaTileBytes) + kUmmaTileBytes);
+      const uint64_t probability_desc = umma_tile_descriptor(probability_tile);
+#pragma unroll
+      for (uint32_t k = 0; k < 4; ++k) {
+        // 32 tokens per MMA: 32 rows of V (4096 bytes) and 32 bytes of each P row
+        umma_f8(tmem_output, value_desc + 256u * k, probability_desc + 2u * k, kUmmaIdescValues,
+                (first_of_item && k == 0) ? 0u : 1u);
+      }
+      umma_commit(output_barrier);
+      if (!last_of_range && !last_of_item) {
+        const uint32_t next_stage = (i + 1) % kUmmaStages;
+        wait_phase(barriers + next_stage * 8, (i + 1) / kUmmaStages);
+        const uint64_t key_desc = umma_tile_descriptor(smem_base + next_stage * (2 * kUmmaTileBytes));
+        const uint64_t query_desc = umma_tile_descriptor(query_tile);
+#pragma unroll
+        for (uint32_t k = 0; k < 4; ++k) {
+          umma_f8(tmem_scores, key_desc + 2u * k, query_desc + 2u * k, kUmmaIdescScores, k);
+        }
+        umma_commit(scores_barrier);
+      }
+    }
+    output_pending = true;
+
+    if (last_of_item || last_of_range) {
+      wait_phase(output_barrier, i);
+      output_pending = false;
+      if (tid == 0) issue_loads();
+      finish_item(consumer.seq, consumer.head, consumer.tiles);
+      if (!last_of_range) {
+        advance(consumer);
+        item_first_tile = i + 1;
+        begin_item();
+        if (tid == 0) {
+          const uint32_t next_stage = (i + 1) % kUmmaStages;
+          wait_phase(barriers + next_stage * 8, (i + 1) / kUmmaStages);
+          tcgen05_fence_after_sync();
+          const uint64_t key_desc = umma_tile_descriptor(smem_base + next_stage * (2 * kUmmaTileBytes));
+          const uint64_t query_desc = umma_tile_descriptor(query_tile);
+#pragma unroll
+          for (uint32_t k = 0; k < 4; ++k) {
+            umma_f8(tmem_scores, key_desc + 2u * k, query_desc + 2u * k, kUmmaIdescScores, k);
+          }
+          umma_commit(scores_barrier);
+        }
+      }
+    } else {
+      advance(consumer);
+    }
+  }
+
+  // ---- release tensor memory -----------------------------------------------------------
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_free(tmem_base, kUmmaTmemColumns);
+}
+
+}  // namespace loom_decode

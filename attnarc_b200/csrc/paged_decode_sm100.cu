@@ -38,6 +38,7 @@
 #include "decode_mma.cuh"
 #include "decode_stream.cuh"
 #include "decode_stream_tma.cuh"
+#include "decode_umma.cuh"
 
 namespace loom_decode {
 
@@ -490,6 +491,16 @@ int launch_stream_tma(const DecodeParams& p, uint32_t ctas, const CacheMaps& map
                                       maps.axes));
 }
 
+template <typename QT>
+int launch_umma_fp8(const DecodeParams& p, uint32_t ctas, const CacheMaps& maps, cudaStream_t stream) {
+  static std::atomic<uint64_t> configured{0};
+  constexpr int kBytes = UmmaSmem::kBytes;
+  auto kernel = decode_umma_fp8_kernel<QT>;
+  if (ensure_smem(kernel, kBytes, configured) != cudaSuccess) return LOOM_CUDA_LAUNCH_ERROR;
+  return launched(loom_launch::launch(kernel, dim3(ctas), dim3(kUmmaThreads), kBytes, stream, p, maps.key, maps.value,
+                                      maps.axes));
+}
+
 template <typename QT, bool kFp8>
 int launch_mma_shape(const DecodeParams& p, uint32_t stream_ctas, const CacheMaps* maps, cudaStream_t stream) {
   const bool wide = p.group > 8;
@@ -691,6 +702,7 @@ int launch_decode(const LoomDecodeArgs& a) {
   StreamShape shape{};
   CacheMaps maps;
   const CacheMaps* tma = nullptr;
+  bool umma = false;
   if (partitioned) {
     if (a.workspace == nullptr || (reinterpret_cast<uintptr_t>(a.workspace) & 3u) != 0) {
       return LOOM_CUDA_INVALID_ARGUMENT;
@@ -698,12 +710,15 @@ int launch_decode(const LoomDecodeArgs& a) {
     p.partials = a.workspace;
     uint32_t tokens = a.partition_tokens;
     if (tokens == 0 && use_mma && a.block_size % 16 == 0 && a.sequences <= kStreamMaxSequences) {
-      if (a.sequences <= kTmaMaxSequences && g_copy_engine.load(std::memory_order_relaxed) == 0 &&
+      if (a.sequences <= kTmaMaxSequences && g_copy_engine.load(std::memory_order_relaxed) != 1 &&
           build_cache_maps(a, fp8, &maps)) {
         tma = &maps;
       }
-      const uint32_t ctas =
-          stream_ctas_for_launch(tma != nullptr && p.group <= 8 ? (fp8 ? 4u : 3u) : kStreamCtasPerSm);
+      // FP8 cache, head size 128, up to 8 query heads per KV head: tcgen05 path
+      umma = tma != nullptr && fp8 && p.group <= 8 && a.head_size == 128 && a.value_head_size == 128 &&
+             g_copy_engine.load(std::memory_order_relaxed) == 0;
+      const uint32_t ctas = stream_ctas_for_launch(
+          umma ? (uint32_t)kUmmaCtasPerSm : (tma != nullptr && p.group <= 8 ? (fp8 ? 4u : 3u) : kStreamCtasPerSm));
       if (ctas != 0 && stream_shape(a.sequences, a.query_heads, a.kv_heads, a.value_head_size, ctas, &shape) &&
           a.workspace_elements >= shape.total_elements) {
         stream_ctas = ctas;
@@ -730,7 +745,15 @@ int launch_decode(const LoomDecodeArgs& a) {
   cudaStream_t stream = static_cast<cudaStream_t>(a.stream);
   int status;
   if (use_mma) {
-    if (stream_ctas == 0) tma = nullptr;
+    if (stream_ctas == 0) {
+      tma = nullptr;
+      umma = false;
+    }
+    if (umma) {
+      g_last_route = "umma-fp8-balanced-tma";
+      status = a.dtype == 1 ? launch_umma_fp8<__half>(p, stream_ctas, maps, stream)
+                            : launch_umma_fp8<__nv_bfloat16>(p, stream_ctas, maps, stream);
+    } else {
     if (stream_ctas == 0) g_last_route = fp8 ? "mma16-fp8" : "mma16";
     else if (tma != nullptr) g_last_route = fp8 ? "mma16-fp8-balanced-tma" : "mma16-balanced-tma";
     else g_last_route = fp8 ? "mma16-fp8-balanced" : "mma16-balanced";
@@ -740,6 +763,7 @@ int launch_decode(const LoomDecodeArgs& a) {
     } else {
       status = fp8 ? launch_mma_shape<__nv_bfloat16, true>(p, stream_ctas, tma, stream)
                    : launch_mma_shape<__nv_bfloat16, false>(p, stream_ctas, tma, stream);
+    }
     }
   } else {
     if (a.value_head_size > 32u * kScalarMaxValueRegs || a.query_heads > 65535u) return LOOM_CUDA_UNSUPPORTED;
@@ -1021,7 +1045,7 @@ extern "C" int loom_cuda_supports_paged_decode(uint32_t dtype, uint32_t cache_en
 extern "C" const char* loom_cuda_last_decode_route(void) { return loom_decode::g_last_route; }
 
 extern "C" int loom_cuda_set_decode_copy_engine(uint32_t engine) {
-  if (engine > 1) return LOOM_CUDA_INVALID_ARGUMENT;
+  if (engine > 2) return LOOM_CUDA_INVALID_ARGUMENT;
   loom_decode::g_copy_engine.store(engine, std::memory_order_relaxed);
   return LOOM_CUDA_SUCCESS;
 }

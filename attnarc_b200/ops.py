@@ -62,8 +62,10 @@ def set_programmatic_launch(mode: int) -> None:
 
 
 def set_decode_copy_engine(engine: str) -> None:
-    """``"tma"`` (default) or ``"cp_async"``: how the balanced kernel fills its rings."""
-    code = {"tma": 0, "cp_async": 1}[engine]
+    """How the balanced kernel is fed: ``"tma"`` (default: TMA, and the tcgen05
+    kernel where it applies), ``"cp_async"`` (per-lane copies) or ``"tma-mma"``
+    (TMA, but the mma.sync kernel even where the tcgen05 kernel applies)."""
+    code = {"tma": 0, "cp_async": 1, "tma-mma": 2}[engine]
     if library().loom_cuda_set_decode_copy_engine(code) != 0:
         raise RuntimeError("could not select the decode copy engine")
 
