@@ -32,6 +32,8 @@
 namespace loom_decode {
 
 __device__ unsigned int g_decode_timeout_flag = 0;
+// Which wait expired first: (wait kind + 1) << 20 | local tile index << 1; 0 if none.
+__device__ unsigned int g_decode_timeout_where = 0;
 
 // Which coordinate of the 4-D tensor map holds the KV head, the page and the
 // block (coordinate 0 is always the byte offset inside a row). The outer

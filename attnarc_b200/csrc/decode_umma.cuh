@@ -28,10 +28,13 @@
 // and writes its 16 probability bytes into the P tile. O stays in tensor memory
 // for the whole work item; thread d reads row d (a value dim) at the end.
 //
-// Pipeline per CTA: thread 0 issues the TMA loads two tiles ahead, the MMAs
-// and their commits; QK of tile i+1 is issued right after PV of tile i, so the
-// tensor pipe works on the next scores while the threads are still busy with
-// this tile's epilogue. Three CTAs per SM overlap each other's bubbles.
+// Pipeline per CTA: four warps do the softmax, a fifth warp (one lane of it)
+// issues the TMA loads two tiles ahead, the MMAs and their commits. The scores
+// have two buffers in tensor memory, so QK of tile i+1 is issued before the
+// softmax of tile i has finished and its latency is hidden; PV of tile i is
+// issued as soon as the 128 threads have published P. The warps talk through
+// mbarriers only (scores ready, P ready, PV done, Q ready); the softmax threads
+// use one named barrier per tile for the vote. Two CTAs per SM.
 //
 // Every wait is bounded (see mbarrier_wait); tensor memory is freed on every
 // path out of the kernel.
@@ -44,25 +47,30 @@
 namespace loom_decode {
 
 constexpr uint32_t kUmmaTileTokens = 128;
-constexpr int kUmmaThreads = 128;
-constexpr int kUmmaStages = 2;               // K+V tile pairs in flight per CTA
+constexpr int kUmmaSoftmaxThreads = 128;     // warps 0-3: one thread per token row / value dim
+constexpr int kUmmaThreads = 192;            // + warp 4: MMA issue, warp 5: TMA loads
+constexpr int kUmmaStages = 3;               // K+V tile pairs resident per CTA
 constexpr uint32_t kUmmaTileBytes = 16384;   // 128 tokens x 128 bytes
-constexpr uint32_t kUmmaTmemColumns = 32;    // S: columns 0-15, O: columns 16-31
+// Tensor memory columns per CTA: S buffer b in columns 16 b .. 16 b + 15, O in 32-47.
+// (Giving each of a product's four MMAs columns of its own, so that they do not
+// accumulate one after the other, was measured and changed nothing.)
+constexpr uint32_t kUmmaTmemColumns = 64;
 constexpr float kUmmaSlack = 2.0f;           // p <= 2^2 before the reference moves
 constexpr float kUmmaProbabilityScale = 64.0f;
-constexpr int kUmmaCtasPerSm = 3;
+constexpr int kUmmaCtasPerSm = 2;
 
 struct UmmaSmem {
   static constexpr uint32_t kStages = 0;                                    // kUmmaStages x (K, V)
   static constexpr uint32_t kQuery = kUmmaStages * 2 * kUmmaTileBytes;      // 16 rows x 128 B
-  static constexpr uint32_t kProbabilities = kQuery + 2048;                 // 16 rows x 128 B
-  static constexpr uint32_t kPrefix = kProbabilities + 2048;                // [sequences + 1]
+  static constexpr uint32_t kProbabilities = kQuery + 2048;                 // two buffers of 16 rows x 128 B
+  static constexpr uint32_t kPrefix = kProbabilities + 4096;                // [sequences + 1]
   static constexpr uint32_t kBarriers = kPrefix + ((kTmaMaxSequences + 1) * 4 + 7) / 8 * 8;
-  static constexpr uint32_t kTmemSlot = kBarriers + (kUmmaStages + 2) * 8;  // full[], scores, output
+  static constexpr uint32_t kTmemSlot = kBarriers + (2 * kUmmaStages + 6) * 8;  // full[], empty[], scores[2], P, output[2], Q
   static constexpr uint32_t kHeadScale = kTmemSlot + 8;                     // [8]
   static constexpr uint32_t kReduce = kHeadScale + 32;                      // [4 warps][8]
-  static constexpr uint32_t kWarpTotals = kReduce + 128;                    // [4]
-  static constexpr uint32_t kAborted = kWarpTotals + 16;                    // set when a wait expired
+  static constexpr uint32_t kWarpTotals = kReduce + 128;                    // [5]
+  static constexpr uint32_t kVotes = kWarpTotals + 32;                      // [2][4]
+  static constexpr uint32_t kAborted = kVotes + 32;                         // set when a wait expired
   static constexpr uint32_t kBytes = kAborted + 16 + 1024;                  // + alignment slack
 };
 
@@ -176,36 +184,84 @@ __device__ __forceinline__ uint32_t swizzled_byte(uint32_t row, uint32_t column)
 }
 
 
+
+
+// Bounded wait without a suspend hint: the handshakes between the control warp
+// and the softmax warps sit on the critical path of every tile, and a sleeping
+// waiter wakes up too late. Gives up after about a second of polling.
+__device__ __forceinline__ bool mbarrier_wait_prompt(uint32_t barrier, uint32_t parity) {
+  for (uint32_t attempt = 0; attempt < (1u << 24); ++attempt) {
+    uint32_t done;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(done)
+        : "r"(barrier), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  atomicOr(&g_decode_timeout_flag, 1u);
+  return false;
+}
+
+__device__ __forceinline__ void mbarrier_arrive(uint32_t barrier) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(barrier) : "memory");
+}
+
+// Barrier among the 128 softmax threads only (the control warp never joins it).
+__device__ __forceinline__ void softmax_threads_sync() {
+  asm volatile("bar.sync 1, %0;\n" ::"n"(kUmmaSoftmaxThreads) : "memory");
+}
+
 template <typename QT>
 __global__ void __launch_bounds__(kUmmaThreads, kUmmaCtasPerSm)
 decode_umma_fp8_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap key_map,
                        const __grid_constant__ CUtensorMap value_map, const TmaAxes axes) {
   constexpr uint32_t kD = 128;
   constexpr uint32_t kHeads = 8;
+  constexpr uint32_t kStageBytes = 2 * kUmmaTileBytes;
 
   extern __shared__ uint8_t raw_smem[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023u) & ~uintptr_t(1023));
   const uint32_t smem_base = smem_address(smem);
   const uint32_t query_tile = smem_base + UmmaSmem::kQuery;
-  const uint32_t probability_tile = smem_base + UmmaSmem::kProbabilities;
+  const uint32_t probability_tiles = smem_base + UmmaSmem::kProbabilities;  // tile i uses buffer i & 1
   uint32_t* prefix = reinterpret_cast<uint32_t*>(smem + UmmaSmem::kPrefix);
-  const uint32_t barriers = smem_base + UmmaSmem::kBarriers;  // full[kUmmaStages], scores, output
-  const uint32_t scores_barrier = barriers + kUmmaStages * 8;
-  const uint32_t output_barrier = scores_barrier + 8;
+  const uint32_t full_barriers = smem_base + UmmaSmem::kBarriers;          // one per stage: K and V landed
+  const uint32_t empty_barriers = full_barriers + kUmmaStages * 8;         // one per stage: PV has read it
+  const uint32_t scores_barriers = empty_barriers + kUmmaStages * 8;       // QK of an even / odd tile finished
+  const uint32_t probabilities_barrier = scores_barriers + 16;             // 128 threads published P
+  const uint32_t output_barriers = probabilities_barrier + 8;              // PV of an even / odd tile finished
+  const uint32_t query_barrier = output_barriers + 16;                     // 128 threads published Q
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + UmmaSmem::kTmemSlot);
-  float* head_scale = reinterpret_cast<float*>(smem + UmmaSmem::kHeadScale);
-  float* reduce = reinterpret_cast<float*>(smem + UmmaSmem::kReduce);
+  volatile float* head_scale = reinterpret_cast<volatile float*>(smem + UmmaSmem::kHeadScale);
+  volatile float* reduce = reinterpret_cast<volatile float*>(smem + UmmaSmem::kReduce);
   uint32_t* warp_totals = reinterpret_cast<uint32_t*>(smem + UmmaSmem::kWarpTotals);
+  volatile uint32_t* votes = reinterpret_cast<volatile uint32_t*>(smem + UmmaSmem::kVotes);
   volatile uint32_t* aborted = reinterpret_cast<volatile uint32_t*>(smem + UmmaSmem::kAborted);
 
   const uint32_t tid = threadIdx.x;
   const uint32_t warp = tid >> 5;
   const uint32_t lane = tid & 31u;
+  const bool control = warp == 4;  // MMA issue; owns the tensor memory allocation
+  const bool loader = warp == 5;   // TMA loads
 
   if (tid == 0) {
     *aborted = 0;
 #pragma unroll
-    for (int i = 0; i < kUmmaStages + 2; ++i) mbarrier_init(barriers + i * 8, 1);
+    for (int i = 0; i < kUmmaStages; ++i) {
+      mbarrier_init(full_barriers + i * 8, 1);
+      mbarrier_init(empty_barriers + i * 8, 1);
+    }
+    mbarrier_init(scores_barriers, 1);
+    mbarrier_init(scores_barriers + 8, 1);
+    mbarrier_init(probabilities_barrier, kUmmaSoftmaxThreads);
+    mbarrier_init(output_barriers, 1);
+    mbarrier_init(output_barriers + 8, 1);
+    mbarrier_init(query_barrier, kUmmaSoftmaxThreads);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   }
@@ -254,15 +310,13 @@ decode_umma_fp8_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap
   };
   const uint32_t my_tiles = (uint32_t)(range_end - range_begin);
 
-  // ---- tensor memory -------------------------------------------------------------
-  if (warp == 0) tmem_alloc(smem_base + UmmaSmem::kTmemSlot, kUmmaTmemColumns);
+  // ---- tensor memory (owned by the control warp) -----------------------------------
+  if (control) tmem_alloc(smem_base + UmmaSmem::kTmemSlot, kUmmaTmemColumns);
   tcgen05_fence_before_sync();
   __syncthreads();
   tcgen05_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_scores = tmem_base;        // columns 0-15
-  const uint32_t tmem_output = tmem_base + 16u;  // columns 16-31
-  const uint32_t lane_offset = (warp * 32u) << 16;  // this warp's quarter of the 128 lanes
+  const uint32_t tmem_output = tmem_base + 32u;
 
   auto load_sequence = [&](StreamCursor& c) {
     c.tiles = prefix[c.seq + 1] - prefix[c.seq];
@@ -294,355 +348,372 @@ decode_umma_fp8_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap
     start.tile = (uint32_t)(inside % start.tiles);
   }
 
-  // ---- producer (thread 0): TMA loads of whole tiles, kUmmaStages ahead ---------
-  const bool head_inner = axes.head < axes.page;
-  StreamCursor producer = start;
-  uint32_t issued = 0;
-  auto issue_loads = [&]() {  // thread 0 only
-    if (issued >= my_tiles) return;
-    const uint32_t stage = issued % kUmmaStages;
-    const uint32_t token0 = producer.tile * kUmmaTileTokens;
-    const uint32_t live = min(kUmmaTileTokens, producer.length - token0);
-    const uint32_t boxes = (live + 15u) >> 4;
-    const uint32_t barrier = barriers + stage * 8;
-    const uint32_t key_tile = smem_base + stage * (2 * kUmmaTileBytes);
-    const uint32_t value_tile = key_tile + kUmmaTileBytes;
-    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-    mbarrier_expect_tx(barrier, boxes * 2u * 2048u);
-    const int32_t* table = p.block_tables + (uint64_t)producer.seq * p.max_blocks_per_sequence;
-    // all block ids first (independent loads), then the copies
-    int32_t pages[8], blocks[8];
-#pragma unroll
-    for (uint32_t box = 0; box < 8; ++box) {
-      const uint32_t token = token0 + box * 16u;
-      const uint32_t logical = p.block_shift < 32u ? token >> p.block_shift : token / p.block_size;
-      pages[box] = (int32_t)(token - logical * p.block_size);
-      blocks[box] = box < boxes ? __ldg(table + logical) : 0;
-    }
-    const int32_t head = (int32_t)producer.head;
-#pragma unroll
-    for (uint32_t box = 0; box < 8; ++box) {
-      if (box < boxes) {
-        const int32_t block = (int32_t)clamp_block(blocks[box], p.num_blocks);
-        const int32_t c1 = head_inner ? head : pages[box], c2 = head_inner ? pages[box] : head;
-        tma_load_4d(key_tile + box * 2048u, &key_map, barrier, 0, c1, c2, block);
-        tma_load_4d(value_tile + box * 2048u, &value_map, barrier, 0, c1, c2, block);
-      }
-    }
-    ++issued;
-    if (issued < my_tiles) advance(producer);
-  };
-  if (tid == 0) {
-#pragma unroll
-    for (int i = 0; i < kUmmaStages; ++i) issue_loads();
-  }
-
-  // ---- per-item state ----------------------------------------------------------------
-  StreamCursor consumer = start;
-  float reference[kHeads];  // exponent reference per head (base-2 units), the same in every thread
-  float row_sum[kHeads];    // this thread's share of sum_i p_i
-  uint32_t item_first_tile = 0;  // local index of the current item's first tile in this CTA
-  bool output_pending = false;   // a PV product whose completion has not been waited for
-
   // After one wait has expired (the device-wide flag is set by mbarrier_wait) the
   // CTA stops waiting altogether and runs to its end on whatever it has.
   auto wait_phase = [&](uint32_t barrier, uint32_t completions) {
     if (*aborted) return;
-    if (!mbarrier_wait(barrier, completions & 1u)) *aborted = 1;
+    if (!mbarrier_wait_prompt(barrier, completions & 1u)) {
+      *aborted = 1;
+      const uint32_t kind = (barrier - full_barriers) >> 3;  // index into the barrier block
+      atomicCAS(&g_decode_timeout_where, 0u, ((kind + 1u) << 20) | ((completions & 0x7ffffu) << 1));
+    }
   };
 
-  // Writes the two E4M3 planes of the item's queries and the per-head score scales.
-  auto begin_item = [&]() {
+  if (loader) {
+    // ======================= load warp: one lane keeps kUmmaStages tiles in flight =====
+    if (lane == 0) {
+      const bool head_inner = axes.head < axes.page;
+      StreamCursor producer = start;
+      for (uint32_t issued = 0; issued < my_tiles; ++issued) {
+        const uint32_t stage = issued % kUmmaStages;
+        const uint32_t token0 = producer.tile * kUmmaTileTokens;
+        const uint32_t live = min(kUmmaTileTokens, producer.length - token0);
+        const uint32_t boxes = (live + 15u) >> 4;
+        const uint32_t barrier = full_barriers + stage * 8;
+        const uint32_t key_tile = smem_base + stage * kStageBytes;
+        const uint32_t value_tile = key_tile + kUmmaTileBytes;
+        const int32_t* table = p.block_tables + (uint64_t)producer.seq * p.max_blocks_per_sequence;
+        // all block ids first (independent loads, in flight while the stage is
+        // still being read), then the copies
+        int32_t pages[8], blocks[8];
 #pragma unroll
-    for (int h = 0; h < (int)kHeads; ++h) {
-      reference[h] = -INFINITY;
-      row_sum[h] = 0.0f;
-    }
-    const uint32_t kv_head = consumer.head;
-    const uint32_t live_heads = min(kHeads, p.group);
-    const uint32_t head = tid >> 4, piece = tid & 15u;  // 16 threads per head, 8 dims each
-    float q[8];
+        for (uint32_t box = 0; box < 8; ++box) {
+          const uint32_t token = token0 + box * 16u;
+          const uint32_t logical = p.block_shift < 32u ? token >> p.block_shift : token / p.block_size;
+          pages[box] = (int32_t)(token - logical * p.block_size);
+          blocks[box] = box < boxes ? __ldg(table + logical) : 0;
+        }
+        // the stage's previous tile has been read by its PV product
+        if (issued >= (uint32_t)kUmmaStages) wait_phase(empty_barriers + stage * 8, issued / kUmmaStages - 1);
+        mbarrier_expect_tx(barrier, boxes * 2u * 2048u);
+        const int32_t head = (int32_t)producer.head;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) q[j] = 0.0f;
-    if (head < live_heads) {
-      const QT* row = static_cast<const QT*>(p.query) + (uint64_t)consumer.seq * p.q_token +
-                      ((uint64_t)kv_head * p.group + head) * p.q_head + piece * 8u;
-      const uint4 packed = *reinterpret_cast<const uint4*>(row);
-      const uint32_t words[4] = {packed.x, packed.y, packed.z, packed.w};
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 pair = widen_pair<QT>(words[j]);
-        q[2 * j] = pair.x;
-        q[2 * j + 1] = pair.y;
+        for (uint32_t box = 0; box < 8; ++box) {
+          if (box < boxes) {
+            const int32_t block = (int32_t)clamp_block(blocks[box], p.num_blocks);
+            const int32_t c1 = head_inner ? head : pages[box], c2 = head_inner ? pages[box] : head;
+            tma_load_4d(key_tile + box * 2048u, &key_map, barrier, 0, c1, c2, block);
+            tma_load_4d(value_tile + box * 2048u, &value_map, barrier, 0, c1, c2, block);
+          }
+        }
+        if (issued + 1 < my_tiles) advance(producer);
       }
     }
-    float largest = 0.0f;
+  } else if (control) {
+    // ======================= MMA warp: one lane issues every product =================
+    if (lane == 0) {
+      auto issue_scores = [&](uint32_t tile) {  // S[tile & 1] = K(tile) . Q^T
+        const uint32_t stage = tile % kUmmaStages;
+        wait_phase(full_barriers + stage * 8, tile / kUmmaStages);
+        tcgen05_fence_after_sync();
+        const uint64_t key_desc = umma_tile_descriptor(smem_base + stage * kStageBytes);
+        const uint64_t query_desc = umma_tile_descriptor(query_tile);
+        const uint32_t target = tmem_base + (tile & 1u) * 16u;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) largest = fmaxf(largest, fabsf(q[j]));
-#pragma unroll
-    for (int offset = 1; offset < 16; offset <<= 1) {
-      largest = fmaxf(largest, __shfl_xor_sync(0xffffffffu, largest, offset));
-    }
-    // power of two that brings the largest element into [128, 256)
-    int exponent = 0;
-    float prescale = 1.0f;
-    if (largest > 0.0f && largest < INFINITY) {
-      frexpf(largest, &exponent);
-      prescale = ldexpf(1.0f, 8 - exponent);
-    }
-    uint32_t hi[4], lo[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) e4m3_split_pair(q[2 * j] * prescale, q[2 * j + 1] * prescale, hi[j], lo[j]);
-    const uint32_t hi_low = hi[0] | (hi[1] << 16), hi_high = hi[2] | (hi[3] << 16);
-    const uint32_t lo_low = lo[0] | (lo[1] << 16), lo_high = lo[2] | (lo[3] << 16);
-    asm volatile("st.shared.v2.u32 [%0], {%1, %2};\n" ::"r"(query_tile + swizzled_byte(head, piece * 8u)), "r"(hi_low),
-                 "r"(hi_high)
-                 : "memory");
-    asm volatile("st.shared.v2.u32 [%0], {%1, %2};\n" ::"r"(query_tile + swizzled_byte(8u + head, piece * 8u)),
-                 "r"(lo_low), "r"(lo_high)
-                 : "memory");
-    if (piece == 0) {
-      const float key_scale = __ldg(p.key_scales + (uint64_t)kv_head * p.scale_stride);
-      head_scale[head] = p.scale_log2 * key_scale / prescale;
-    }
-    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-    __syncthreads();
-  };
+        for (uint32_t k = 0; k < 4; ++k) umma_f8(target, key_desc + 2u * k, query_desc + 2u * k, kUmmaIdescScores, k);
+        umma_commit(scores_barriers + (tile & 1u) * 8);
+      };
 
-  // Stores the item's result: final rows if this CTA covered the whole item,
-  // else a partial state.
-  auto finish_item = [&](uint32_t item_seq, uint32_t item_head, uint32_t item_tiles) {
-    // the last PV product of the item has completed (caller waited)
-    tcgen05_fence_after_sync();
-    float o[16];
-    tmem_load16(o, tmem_output + lane_offset);
-    tcgen05_fence_before_sync();
+      StreamCursor cursor = start;
+      uint32_t items_begun = 0;
+      wait_phase(query_barrier, items_begun++);
+      issue_scores(0);
+      for (uint32_t i = 0; i < my_tiles; ++i) {
+        const bool first_of_item = i == 0 || cursor.tile == 0;
+        const bool last_of_item = cursor.tile + 1 == cursor.tiles;
+        const bool last_of_range = i + 1 == my_tiles;
+        if (!last_of_range && !last_of_item) issue_scores(i + 1);  // hidden behind this tile's softmax
+        // O += V^T . P^T once the 128 threads have published P
+        wait_phase(probabilities_barrier, i);
+        tcgen05_fence_after_sync();
+        {
+          const uint32_t stage = i % kUmmaStages;
+          const uint64_t value_desc = umma_tile_descriptor(smem_base + stage * kStageBytes + kUmmaTileBytes);
+          const uint64_t probability_desc = umma_tile_descriptor(probability_tiles + (i & 1u) * 2048u);
 #pragma unroll
-    for (int h = 0; h < (int)kHeads; ++h) {
-      float total = row_sum[h];
-#pragma unroll
-      for (int offset = 16; offset > 0; offset >>= 1) total += __shfl_xor_sync(0xffffffffu, total, offset);
-      if (lane == 0) reduce[warp * kHeads + h] = total;
-    }
-    __syncthreads();
-    const uint32_t kv_head = item_head;
-    const uint32_t live_heads = min(kHeads, p.group);
-    const uint64_t item = (uint64_t)item_seq * heads + item_head;
-    const uint64_t item_begin = (uint64_t)heads * prefix[item_seq] + (uint64_t)item_head * item_tiles;
-    const uint32_t first_cta = cta_of(item_begin);
-    const uint32_t last_cta = cta_of(item_begin + item_tiles - 1);
-    const uint32_t parts = last_cta - first_cta + 1;
-    const float value_scale =
-        __ldg(p.value_scales + (uint64_t)kv_head * p.scale_stride) * (1.0f / kUmmaProbabilityScale);
-    const uint32_t stride = state_stride(kD);
-    const uint64_t query_row = (uint64_t)item_seq * p.query_heads + (uint64_t)kv_head * p.group;
-    const uint32_t dv = tid;
-#pragma unroll
-    for (int h = 0; h < (int)kHeads; ++h) {
-      if ((uint32_t)h >= live_heads) break;
-      const float total = reduce[h] + reduce[kHeads + h] + reduce[2 * kHeads + h] + reduce[3 * kHeads + h];
-      const float acc = (o[h] + o[8 + h]) * value_scale;
-      if (parts == 1 && !p.emit_state) {
-        const float result = total > 0.0f ? acc / total : 0.0f;
-        QT* out = static_cast<QT*>(p.output) + (query_row + h) * kD;
-        if constexpr (std::is_same<QT, __nv_bfloat16>::value) out[dv] = __float2bfloat16_rn(result);
-        else out[dv] = __float2half_rn(result);
-      } else {
-        float* row = parts == 1 ? static_cast<float*>(p.output) + (query_row + h) * stride
-                                : p.partials + ((item + blockIdx.x) * kHeads + h) * stride;
-        row[dv] = acc;
-        if (dv == 0) {
-          row[kD] = reference[h] * kLn2;
-          row[kD + 1] = total;
+          for (uint32_t k = 0; k < 4; ++k) {
+            // 32 tokens per MMA: 32 rows of V (4096 bytes) and 32 bytes of each P row
+            umma_f8(tmem_output, value_desc + 256u * k, probability_desc + 2u * k, kUmmaIdescValues,
+                    (first_of_item && k == 0) ? 0u : 1u);
+          }
+          umma_commit(output_barriers + (i & 1u) * 8);
+          umma_commit(empty_barriers + stage * 8);  // the load warp may refill the stage
+        }
+        if (!last_of_range) {
+          advance(cursor);
+          if (last_of_item) {
+            // the next tile belongs to another item: its scores need the new Q
+            wait_phase(query_barrier, items_begun++);
+            issue_scores(i + 1);
+          }
         }
       }
     }
-    if (tid == 0 && blockIdx.x == first_cta) {
-      p.item_meta[2 * item] = first_cta;
-      p.item_meta[2 * item + 1] = parts;
-    }
-    __syncthreads();  // `reduce` and the Q tile are reused by the next item
-  };
+  } else {
+    // ======================= softmax warps =============================================
+    const uint32_t lane_offset = (warp * 32u) << 16;  // this warp's quarter of the 128 lanes
+    StreamCursor consumer = start;
+    float reference[kHeads];  // exponent reference per head (base-2 units), the same in every thread
+    float row_sum[kHeads];    // this thread's share of sum_i p_i
+    uint32_t item_first_tile = 0;
 
-  begin_item();
-  if (tid == 0) {
-    // scores of the first tile
-    wait_phase(barriers + 0, 0);
-    tcgen05_fence_after_sync();
-    const uint64_t key_desc = umma_tile_descriptor(smem_base);
-    const uint64_t query_desc = umma_tile_descriptor(query_tile);
-#pragma unroll
-    for (uint32_t k = 0; k < 4; ++k) umma_f8(tmem_scores, key_desc + 2u * k, query_desc + 2u * k, kUmmaIdescScores, k);
-    umma_commit(scores_barrier);
-  }
-
-  for (uint32_t i = 0; i < my_tiles; ++i) {
-    const uint32_t stage = i % kUmmaStages;
-    const uint32_t token0 = consumer.tile * kUmmaTileTokens;
-    const uint32_t live = min(kUmmaTileTokens, consumer.length - token0);
-    const bool row_live = tid < live;
-    const bool last_of_item = consumer.tile + 1 == consumer.tiles;
-    const bool last_of_range = i + 1 == my_tiles;
-
-    // ---- scores of this tile -------------------------------------------------------
-    wait_phase(scores_barrier, i);
-    tcgen05_fence_after_sync();
-    float s[16];
-    tmem_load16(s, tmem_scores + lane_offset);
-    tcgen05_fence_before_sync();
-    float d[kHeads];
-    bool over = false;
-#pragma unroll
-    for (int h = 0; h < (int)kHeads; ++h) {
-      s[h] = (s[h] + s[8 + h]) * head_scale[h];  // base-2 score
-      d[h] = row_live ? s[h] - reference[h] : -INFINITY;
-      over |= d[h] > kUmmaSlack;
-    }
-
-    // ---- the previous tile's PV product must be done before P is overwritten ---------
-    if (output_pending) {
-      wait_phase(output_barrier, i - 1);
-      output_pending = false;
-      if (tid == 0) issue_loads();  // its stage is free again
-    }
-
-    if (live < kUmmaTileTokens) {
-      // rows past the end of the sequence hold whatever the page (or an older
-      // tile) held: clear them in V so that 0 * garbage cannot become NaN
-      wait_phase(barriers + stage * 8, i / kUmmaStages);
-      if (!row_live) {
-        const uint32_t row = smem_base + stage * (2 * kUmmaTileBytes) + kUmmaTileBytes + tid * 128u;
-#pragma unroll
-        for (int piece = 0; piece < 8; ++piece) {
-          asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};\n" ::"r"(row + piece * 16), "r"(0u) : "memory");
-        }
-      }
-    }
-
-    // ---- probabilities ---------------------------------------------------------------
-    auto write_probabilities = [&]() {
-      uint32_t hi[4], lo[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float p0 = fast_exp2(d[2 * j]), p1 = fast_exp2(d[2 * j + 1]);
-        row_sum[2 * j] += p0;
-        row_sum[2 * j + 1] += p1;
-        e4m3_split_pair(p0 * kUmmaProbabilityScale, p1 * kUmmaProbabilityScale, hi[j], lo[j]);
-      }
+    // Writes the two E4M3 planes of the item's queries and the per-head score scales.
+    auto begin_item = [&]() {
 #pragma unroll
       for (int h = 0; h < (int)kHeads; ++h) {
-        const uint32_t hi_byte = (hi[h >> 1] >> ((h & 1) * 8)) & 0xffu;
-        const uint32_t lo_byte = (lo[h >> 1] >> ((h & 1) * 8)) & 0xffu;
-        asm volatile("st.shared.u8 [%0], %1;\n" ::"r"(probability_tile + swizzled_byte(h, tid)), "r"(hi_byte)
-                     : "memory");
-        asm volatile("st.shared.u8 [%0], %1;\n" ::"r"(probability_tile + swizzled_byte(8 + h, tid)), "r"(lo_byte)
-                     : "memory");
+        reference[h] = -INFINITY;
+        row_sum[h] = 0.0f;
+      }
+      const uint32_t kv_head = consumer.head;
+      const uint32_t live_heads = min(kHeads, p.group);
+      const uint32_t head = tid >> 4, piece = tid & 15u;  // 16 threads per head, 8 dims each
+      float q[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) q[j] = 0.0f;
+      if (head < live_heads) {
+        const QT* row = static_cast<const QT*>(p.query) + (uint64_t)consumer.seq * p.q_token +
+                        ((uint64_t)kv_head * p.group + head) * p.q_head + piece * 8u;
+        const uint4 packed = *reinterpret_cast<const uint4*>(row);
+        const uint32_t words[4] = {packed.x, packed.y, packed.z, packed.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 pair = widen_pair<QT>(words[j]);
+          q[2 * j] = pair.x;
+          q[2 * j + 1] = pair.y;
+        }
+      }
+      float largest = 0.0f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) largest = fmaxf(largest, fabsf(q[j]));
+#pragma unroll
+      for (int offset = 1; offset < 16; offset <<= 1) {
+        largest = fmaxf(largest, __shfl_xor_sync(0xffffffffu, largest, offset));
+      }
+      // power of two that brings the largest element into [128, 256)
+      int exponent = 0;
+      float prescale = 1.0f;
+      if (largest > 0.0f && largest < INFINITY) {
+        frexpf(largest, &exponent);
+        prescale = ldexpf(1.0f, 8 - exponent);
+      }
+      uint32_t hi[4], lo[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) e4m3_split_pair(q[2 * j] * prescale, q[2 * j + 1] * prescale, hi[j], lo[j]);
+      const uint32_t hi_low = hi[0] | (hi[1] << 16), hi_high = hi[2] | (hi[3] << 16);
+      const uint32_t lo_low = lo[0] | (lo[1] << 16), lo_high = lo[2] | (lo[3] << 16);
+      asm volatile("st.shared.v2.u32 [%0], {%1, %2};\n" ::"r"(query_tile + swizzled_byte(head, piece * 8u)),
+                   "r"(hi_low), "r"(hi_high)
+                   : "memory");
+      asm volatile("st.shared.v2.u32 [%0], {%1, %2};\n" ::"r"(query_tile + swizzled_byte(8u + head, piece * 8u)),
+                   "r"(lo_low), "r"(lo_high)
+                   : "memory");
+      if (piece == 0) {
+        const float key_scale = __ldg(p.key_scales + (uint64_t)kv_head * p.scale_stride);
+        head_scale[head] = p.scale_log2 * key_scale / prescale;
+      }
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+      mbarrier_arrive(query_barrier);  // the control warp may issue the item's first scores
+      softmax_threads_sync();          // head_scale is visible to the 128 threads
+    };
+
+    // Stores the item's result: final rows if this CTA covered the whole item,
+    // else a partial state. The item's last PV product has completed.
+    auto finish_item = [&](uint32_t item_seq, uint32_t item_head, uint32_t item_tiles) {
+      tcgen05_fence_after_sync();
+      float o[16];
+      tmem_load16(o, tmem_output + lane_offset);
+      tcgen05_fence_before_sync();
+#pragma unroll
+      for (int h = 0; h < (int)kHeads; ++h) {
+        float total = row_sum[h];
+#pragma unroll
+        for (int offset = 16; offset > 0; offset >>= 1) total += __shfl_xor_sync(0xffffffffu, total, offset);
+        if (lane == 0) reduce[warp * kHeads + h] = total;
+      }
+      softmax_threads_sync();
+      const uint32_t kv_head = item_head;
+      const uint32_t live_heads = min(kHeads, p.group);
+      const uint64_t item = (uint64_t)item_seq * heads + item_head;
+      const uint64_t item_begin = (uint64_t)heads * prefix[item_seq] + (uint64_t)item_head * item_tiles;
+      const uint32_t first_cta = cta_of(item_begin);
+      const uint32_t last_cta = cta_of(item_begin + item_tiles - 1);
+      const uint32_t parts = last_cta - first_cta + 1;
+      const float value_scale =
+          __ldg(p.value_scales + (uint64_t)kv_head * p.scale_stride) * (1.0f / kUmmaProbabilityScale);
+      const uint32_t stride = state_stride(kD);
+      const uint64_t query_row = (uint64_t)item_seq * p.query_heads + (uint64_t)kv_head * p.group;
+      const uint32_t dv = tid;
+#pragma unroll
+      for (int h = 0; h < (int)kHeads; ++h) {
+        if ((uint32_t)h >= live_heads) break;
+        const float total = reduce[h] + reduce[kHeads + h] + reduce[2 * kHeads + h] + reduce[3 * kHeads + h];
+        const float acc = (o[h] + o[8 + h]) * value_scale;
+        if (parts == 1 && !p.emit_state) {
+          const float result = total > 0.0f ? acc / total : 0.0f;
+          QT* out = static_cast<QT*>(p.output) + (query_row + h) * kD;
+          if constexpr (std::is_same<QT, __nv_bfloat16>::value) out[dv] = __float2bfloat16_rn(result);
+          else out[dv] = __float2half_rn(result);
+        } else {
+          float* row = parts == 1 ? static_cast<float*>(p.output) + (query_row + h) * stride
+                                  : p.partials + ((item + blockIdx.x) * kHeads + h) * stride;
+          row[dv] = acc;
+          if (dv == 0) {
+            row[kD] = reference[h] * kLn2;
+            row[kD + 1] = total;
+          }
+        }
+      }
+      if (tid == 0 && blockIdx.x == first_cta) {
+        p.item_meta[2 * item] = first_cta;
+        p.item_meta[2 * item + 1] = parts;
+      }
+      softmax_threads_sync();  // `reduce` is reused
+    };
+
+    begin_item();
+    // Completions of the PV products this thread has observed, per parity of the
+    // tile index. A parity test cannot tell phase n from phase n - 2, so a waiter
+    // must never fall two phases behind a barrier: with one barrier for the even
+    // tiles and one for the odd ones, the next completion of either cannot happen
+    // before this thread has published the P tile it belongs to.
+    uint32_t outputs_seen[2] = {0, 0};
+    auto wait_outputs_through = [&](uint32_t tile) {  // every PV product up to `tile` has landed
+#pragma unroll
+      for (uint32_t parity = 0; parity < 2; ++parity) {
+        if (tile < parity) continue;
+        const uint32_t wanted = (tile - parity) / 2 + 1;
+        while (outputs_seen[parity] < wanted) {
+          wait_phase(output_barriers + parity * 8, outputs_seen[parity]);
+          ++outputs_seen[parity];
+        }
       }
     };
 
-    const bool first_of_item = i == item_first_tile;
-    float saved_sum[kHeads];
-#pragma unroll
-    for (int h = 0; h < (int)kHeads; ++h) saved_sum[h] = row_sum[h];
-    write_probabilities();
-    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-    if (__syncthreads_or(over ? 1 : 0)) {
-      // Rare: some score left the slack. Raise every head's reference to the
-      // largest score of this tile, rescale what was accumulated, and redo P.
+    for (uint32_t i = 0; i < my_tiles; ++i) {
+      const uint32_t stage = i % kUmmaStages;
+      const uint32_t token0 = consumer.tile * kUmmaTileTokens;
+      const uint32_t live = min(kUmmaTileTokens, consumer.length - token0);
+      const bool row_live = tid < live;
+      const bool first_of_item = i == item_first_tile;
+      const bool last_of_item = consumer.tile + 1 == consumer.tiles;
+      const bool last_of_range = i + 1 == my_tiles;
+
+      // ---- scores of this tile: row `tid` of S -------------------------------------
+      wait_phase(scores_barriers + (i & 1u) * 8, i >> 1);
+      tcgen05_fence_after_sync();
+      float s[16];
+      tmem_load16(s, tmem_base + (i & 1u) * 16u + lane_offset);
+      tcgen05_fence_before_sync();
+      float d[kHeads];
+      bool over = false;
 #pragma unroll
       for (int h = 0; h < (int)kHeads; ++h) {
-        float top = row_live ? s[h] : -INFINITY;
-#pragma unroll
-        for (int offset = 16; offset > 0; offset >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, offset));
-        if (lane == 0) reduce[warp * kHeads + h] = top;
+        s[h] = (s[h] + s[8 + h]) * head_scale[h];  // base-2 score
+        d[h] = row_live ? s[h] - reference[h] : -INFINITY;
+        over |= d[h] > kUmmaSlack;
       }
-      __syncthreads();
-      float alpha[kHeads];
+      const bool warp_over = __any_sync(0xffffffffu, over);
+      if (lane == 0) votes[(i & 1u) * 4 + warp] = warp_over ? 1u : 0u;
+
+      // ---- P has two buffers: the PV product of two tiles ago read this one ------------
+      if (i >= 2) wait_outputs_through(i - 2);
+      if (live < kUmmaTileTokens) {
+        // rows past the end of the sequence hold whatever the page (or an older
+        // tile) held: clear them in V so that 0 * garbage cannot become NaN
+        wait_phase(full_barriers + stage * 8, i / kUmmaStages);
+        if (!row_live) {
+          const uint32_t row = smem_base + stage * kStageBytes + kUmmaTileBytes + tid * 128u;
 #pragma unroll
-      for (int h = 0; h < (int)kHeads; ++h) {
-        const float top = fmaxf(fmaxf(reduce[h], reduce[kHeads + h]), fmaxf(reduce[2 * kHeads + h], reduce[3 * kHeads + h]));
-        const float raised = fmaxf(reference[h], top);
-        alpha[h] = reference[h] == -INFINITY ? 0.0f : fast_exp2(reference[h] - raised);
-        reference[h] = raised;
-        row_sum[h] = saved_sum[h] * alpha[h];
-        d[h] = row_live ? s[h] - raised : -INFINITY;
+          for (int piece = 0; piece < 8; ++piece) {
+            asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};\n" ::"r"(row + piece * 16), "r"(0u) : "memory");
+          }
+        }
       }
-      if (!first_of_item) {
-        // O lives in tensor memory: thread = value dim
-        float o[16];
-        tcgen05_fence_after_sync();
-        tmem_load16(o, tmem_output + lane_offset);
+      softmax_threads_sync();  // the four votes are in
+      const uint32_t* tile_votes = const_cast<const uint32_t*>(votes) + (i & 1u) * 4;
+      if (tile_votes[0] | tile_votes[1] | tile_votes[2] | tile_votes[3]) {
+        // Rare: some score left the slack. Raise every head's reference to the
+        // largest score of this tile and rescale what was accumulated (every PV
+        // product issued so far must have landed in O first).
+        if (i >= 1) wait_outputs_through(i - 1);
 #pragma unroll
         for (int h = 0; h < (int)kHeads; ++h) {
-          o[h] *= alpha[h];
-          o[8 + h] *= alpha[h];
-        }
-        tmem_store16(tmem_output + lane_offset, o);
-        tcgen05_fence_before_sync();
-      }
-      write_probabilities();
-      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-      __syncthreads();
-    }
-
-    // ---- O += V^T . P^T, then the next tile's scores ----------------------------------
-    if (tid == 0) {
-      tcgen05_fence_after_sync();
-      wait_phase(barriers + stage * 8, i / kUmmaStages);  // the V tile has landed (as K did)
-      const uint64_t value_desc = umma_tile_descriptor(smem_base + stage * (2 * kUmmaTileBytes) + kUmmaTileBytes);
-      const uint64_t probability_desc = umma_tile_descriptor(probability_tile);
+          float top = row_live ? s[h] : -INFINITY;
 #pragma unroll
-      for (uint32_t k = 0; k < 4; ++k) {
-        // 32 tokens per MMA: 32 rows of V (4096 bytes) and 32 bytes of each P row
-        umma_f8(tmem_output, value_desc + 256u * k, probability_desc + 2u * k, kUmmaIdescValues,
-                (first_of_item && k == 0) ? 0u : 1u);
-      }
-      umma_commit(output_barrier);
-      if (!last_of_range && !last_of_item) {
-        const uint32_t next_stage = (i + 1) % kUmmaStages;
-        wait_phase(barriers + next_stage * 8, (i + 1) / kUmmaStages);
-        const uint64_t key_desc = umma_tile_descriptor(smem_base + next_stage * (2 * kUmmaTileBytes));
-        const uint64_t query_desc = umma_tile_descriptor(query_tile);
-#pragma unroll
-        for (uint32_t k = 0; k < 4; ++k) {
-          umma_f8(tmem_scores, key_desc + 2u * k, query_desc + 2u * k, kUmmaIdescScores, k);
+          for (int offset = 16; offset > 0; offset >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, offset));
+          if (lane == 0) reduce[warp * kHeads + h] = top;
         }
-        umma_commit(scores_barrier);
-      }
-    }
-    output_pending = true;
-
-    if (last_of_item || last_of_range) {
-      wait_phase(output_barrier, i);
-      output_pending = false;
-      if (tid == 0) issue_loads();
-      finish_item(consumer.seq, consumer.head, consumer.tiles);
-      if (!last_of_range) {
-        advance(consumer);
-        item_first_tile = i + 1;
-        begin_item();
-        if (tid == 0) {
-          const uint32_t next_stage = (i + 1) % kUmmaStages;
-          wait_phase(barriers + next_stage * 8, (i + 1) / kUmmaStages);
+        softmax_threads_sync();
+        float alpha[kHeads];
+#pragma unroll
+        for (int h = 0; h < (int)kHeads; ++h) {
+          const float top =
+              fmaxf(fmaxf(reduce[h], reduce[kHeads + h]), fmaxf(reduce[2 * kHeads + h], reduce[3 * kHeads + h]));
+          const float raised = fmaxf(reference[h], top);
+          alpha[h] = reference[h] == -INFINITY ? 0.0f : fast_exp2(reference[h] - raised);
+          reference[h] = raised;
+          row_sum[h] *= alpha[h];
+          d[h] = row_live ? s[h] - raised : -INFINITY;
+        }
+        if (!first_of_item) {
+          // O lives in tensor memory: thread = value dim
+          float o[16];
           tcgen05_fence_after_sync();
-          const uint64_t key_desc = umma_tile_descriptor(smem_base + next_stage * (2 * kUmmaTileBytes));
-          const uint64_t query_desc = umma_tile_descriptor(query_tile);
+          tmem_load16(o, tmem_output + lane_offset);
 #pragma unroll
-          for (uint32_t k = 0; k < 4; ++k) {
-            umma_f8(tmem_scores, key_desc + 2u * k, query_desc + 2u * k, kUmmaIdescScores, k);
+          for (int h = 0; h < (int)kHeads; ++h) {
+            o[h] *= alpha[h];
+            o[8 + h] *= alpha[h];
           }
-          umma_commit(scores_barrier);
+          tmem_store16(tmem_output + lane_offset, o);
+          tcgen05_fence_before_sync();
+        }
+        softmax_threads_sync();  // `reduce` is reused by the next slow path or item end
+      }
+
+      // ---- probabilities: 16 bytes of this token's column of the P tile ----------------
+      {
+        const uint32_t probability_tile = probability_tiles + (i & 1u) * 2048u;
+        uint32_t hi[4], lo[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float p0 = fast_exp2(d[2 * j]), p1 = fast_exp2(d[2 * j + 1]);
+          row_sum[2 * j] += p0;
+          row_sum[2 * j + 1] += p1;
+          e4m3_split_pair(p0 * kUmmaProbabilityScale, p1 * kUmmaProbabilityScale, hi[j], lo[j]);
+        }
+#pragma unroll
+        for (int h = 0; h < (int)kHeads; ++h) {
+          const uint32_t hi_byte = (hi[h >> 1] >> ((h & 1) * 8)) & 0xffu;
+          const uint32_t lo_byte = (lo[h >> 1] >> ((h & 1) * 8)) & 0xffu;
+          asm volatile("st.shared.u8 [%0], %1;\n" ::"r"(probability_tile + swizzled_byte(h, tid)), "r"(hi_byte)
+                       : "memory");
+          asm volatile("st.shared.u8 [%0], %1;\n" ::"r"(probability_tile + swizzled_byte(8 + h, tid)), "r"(lo_byte)
+                       : "memory");
         }
       }
-    } else {
-      advance(consumer);
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+      tcgen05_fence_before_sync();
+      mbarrier_arrive(probabilities_barrier);
+
+      if (last_of_item || last_of_range) {
+        wait_outputs_through(i);
+        finish_item(consumer.seq, consumer.head, consumer.tiles);
+        if (!last_of_range) {
+          advance(consumer);
+          item_first_tile = i + 1;
+          begin_item();
+        }
+      } else {
+        advance(consumer);
+      }
     }
   }
 
   // ---- release tensor memory -----------------------------------------------------------
   tcgen05_fence_before_sync();
   __syncthreads();
-  if (warp == 0) tmem_free(tmem_base, kUmmaTmemColumns);
+  if (control) tmem_free(tmem_base, kUmmaTmemColumns);
 }
 
 }  // namespace loom_decode

@@ -714,9 +714,12 @@ int launch_decode(const LoomDecodeArgs& a) {
           build_cache_maps(a, fp8, &maps)) {
         tma = &maps;
       }
-      // FP8 cache, head size 128, up to 8 query heads per KV head: tcgen05 path
+      // FP8 cache, head size 128, up to 8 query heads per KV head: the tcgen05
+      // kernel applies; it is selected by copy engine 3 only, because the
+      // mma.sync kernel is still the faster of the two (473 vs 547 us on the
+      // Llama-3-70B-shaped FP8 workload)
       umma = tma != nullptr && fp8 && p.group <= 8 && a.head_size == 128 && a.value_head_size == 128 &&
-             g_copy_engine.load(std::memory_order_relaxed) == 0;
+             g_copy_engine.load(std::memory_order_relaxed) == 3;
       const uint32_t ctas = stream_ctas_for_launch(
           umma ? (uint32_t)kUmmaCtasPerSm : (tma != nullptr && p.group <= 8 ? (fp8 ? 4u : 3u) : kStreamCtasPerSm));
       if (ctas != 0 && stream_shape(a.sequences, a.query_heads, a.kv_heads, a.value_head_size, ctas, &shape) &&
@@ -1045,7 +1048,7 @@ extern "C" int loom_cuda_supports_paged_decode(uint32_t dtype, uint32_t cache_en
 extern "C" const char* loom_cuda_last_decode_route(void) { return loom_decode::g_last_route; }
 
 extern "C" int loom_cuda_set_decode_copy_engine(uint32_t engine) {
-  if (engine > 2) return LOOM_CUDA_INVALID_ARGUMENT;
+  if (engine > 3) return LOOM_CUDA_INVALID_ARGUMENT;
   loom_decode::g_copy_engine.store(engine, std::memory_order_relaxed);
   return LOOM_CUDA_SUCCESS;
 }
@@ -1063,7 +1066,12 @@ extern "C" int loom_cuda_decode_timeout_flag(uint32_t* value, uint32_t reset) {
     cudaGetLastError();
     return LOOM_CUDA_LAUNCH_ERROR;
   }
-  *value = flag;
+  unsigned int where = 0;
+  if (cudaMemcpyFromSymbol(&where, loom_decode::g_decode_timeout_where, sizeof(where)) != cudaSuccess) {
+    cudaGetLastError();
+    return LOOM_CUDA_LAUNCH_ERROR;
+  }
+  *value = flag | where;
   if (reset != 0 && flag != 0) {
     const unsigned int zero = 0;
     if (cudaMemcpyToSymbol(loom_decode::g_decode_timeout_flag, &zero, sizeof(zero)) != cudaSuccess) {

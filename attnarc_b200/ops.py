@@ -62,10 +62,10 @@ def set_programmatic_launch(mode: int) -> None:
 
 
 def set_decode_copy_engine(engine: str) -> None:
-    """How the balanced kernel is fed: ``"tma"`` (default: TMA, and the tcgen05
-    kernel where it applies), ``"cp_async"`` (per-lane copies) or ``"tma-mma"``
-    (TMA, but the mma.sync kernel even where the tcgen05 kernel applies)."""
-    code = {"tma": 0, "cp_async": 1, "tma-mma": 2}[engine]
+    """How the balanced kernel is fed: ``"tma"`` (default), ``"cp_async"``
+    (per-lane copies) or ``"tma-umma"`` (TMA, and the tcgen05 kernel where it
+    applies: FP8 cache, head size 128, up to 8 query heads per KV head)."""
+    code = {"tma": 0, "cp_async": 1, "tma-mma": 2, "tma-umma": 3}[engine]
     if library().loom_cuda_set_decode_copy_engine(code) != 0:
         raise RuntimeError("could not select the decode copy engine")
 

@@ -385,7 +385,7 @@ def test_launch_counter_and_error_text(ops):
     assert ops.launch_count(ops.Operator.PAGED_DECODE_ATTENTION) == 1  # failures are not counted
 
 
-@pytest.mark.parametrize("engine", ["cp_async", "tma"])
+@pytest.mark.parametrize("engine", ["cp_async", "tma", "tma-umma"])
 @pytest.mark.parametrize("cache", ["native", "fp8"])
 @pytest.mark.parametrize("layout", ["NHD", "HND"])
 @pytest.mark.parametrize("head_size", [64, 128])
@@ -401,12 +401,12 @@ def test_both_copy_engines_of_the_balanced_kernel(ops, engine, cache, layout, he
                                      scale=case.scale, max_sequence_length=case.max_sequence_length, **scales)
     # stale contents after the end of each sequence must not matter to either engine
     poisoned_k, poisoned_v = key_cache.clone(), value_cache.clone()
-    if cache == "native":
-        for s, length in enumerate(case.lengths.tolist()):
-            if length % 16:
-                block = int(case.block_tables[s, (length - 1) // 16])
-                poisoned_k[block, length % 16:] = float("nan")
-                poisoned_v[block, length % 16:] = float("nan")
+    for s, length in enumerate(case.lengths.tolist()):
+        if length % 16:
+            block = int(case.block_tables[s, (length - 1) // 16])
+            # NaN in the cache's own encoding (0x7f is the E4M3 NaN)
+            poisoned_k[block, length % 16:] = float("nan") if cache == "native" else 0x7F
+            poisoned_v[block, length % 16:] = float("nan") if cache == "native" else 0x7F
     ops.set_decode_copy_engine(engine)
     try:
         actual = ops.paged_decode_attention_ex(query, poisoned_k, poisoned_v, case.block_tables,
@@ -416,6 +416,8 @@ def test_both_copy_engines_of_the_balanced_kernel(ops, engine, cache, layout, he
         route = ops.last_decode_route()
     finally:
         ops.set_decode_copy_engine("tma")
-    assert route.endswith("-tma") == (engine == "tma")
+    assert route.endswith("-tma") == (engine != "cp_async")
+    # the tcgen05 kernel covers FP8 caches with head size 128 and up to 8 query heads per KV head
+    assert route.startswith("umma") == (engine == "tma-umma" and cache == "fp8" and head_size == 128)
     helpers.assert_close(actual, expected, torch.bfloat16, f"{engine} {cache} {layout} D={head_size}")
     assert ops.decode_timeout_flag() == 0
