@@ -28,15 +28,36 @@
 // and writes its 16 probability bytes into the P tile. O stays in tensor memory
 // for the whole work item; thread d reads row d (a value dim) at the end.
 //
-// Pipeline per CTA: four warps do the softmax, a fifth warp (one lane of it)
-// issues the TMA loads two tiles ahead, the MMAs and their commits. The scores
-// have two buffers in tensor memory, so QK of tile i+1 is issued before the
-// softmax of tile i has finished and its latency is hidden; PV of tile i is
-// issued as soon as the 128 threads have published P. The warps talk through
-// mbarriers only (scores ready, P ready, PV done, Q ready); the softmax threads
-// use one named barrier per tile for the vote. Two CTAs per SM.
+// Pipeline per CTA (eight warps, two CTAs per SM):
+//   warps 0-3  softmax, one thread per token row;
+//   warp 4     issues the QK products (and owns the tensor memory allocation);
+//   warp 7     issues the PV products;
+//   warps 5, 6 feed the K ring and the V ring with TMA, eight lanes at a time.
+// The roles talk through mbarriers only: K / V slot landed and released, scores
+// ready, P published, PV done, Q published. Scores and P have two buffers each,
+// so QK of tile i + 1 runs while the softmax of tile i is busy, and PV of tile i
+// runs while the softmax threads are already on tile i + 1. Barriers that are
+// completed once per tile exist once per parity of the tile index: a parity
+// wait cannot tell phase n from phase n - 2, and a role that lags by design
+// (the softmax threads behind PV, the QK warp behind P) would otherwise hang.
 //
-// Every wait is bounded (see mbarrier_wait); tensor memory is freed on every
+// What measurement taught (timestamps per role and tile; 128 sequences of
+// 2k-16k tokens, 8 KV heads): a thread needs about 200 ns per
+// cp.async.bulk.tensor it issues and 60-90 ns per tcgen05.mma or commit, so a
+// single issuing thread for the 16 copies or the 8 MMAs of a tile is the
+// bottleneck (hence eight lanes and two warps); the tensor pipe itself is 3 %
+// busy, and leaving out the MMAs does not change the time. What bounds the
+// kernel now is the softmax threads' own chain per tile, about 1.4 us (tensor
+// memory read, vote barrier, 8 exponentials, 16 byte stores, proxy fence),
+// which two CTAs per SM only half hide: 507 us on that workload against
+// 473 us for the mma.sync kernel, so this kernel is opt-in
+// (loom_cuda_set_decode_copy_engine(3)) until the chain is shorter. A switch
+// of work item costs about 5 us (state out, Q in), negligible at 70 tiles per
+// item.
+//
+// Every wait is bounded (see mbarrier_wait_prompt); after the first expiry the
+// CTA stops waiting and runs to its end, and the first expired wait is
+// recorded (loom_cuda_decode_timeout_flag). Tensor memory is freed on every
 // path out of the kernel.
 #pragma once
 
@@ -48,7 +69,7 @@ namespace loom_decode {
 
 constexpr uint32_t kUmmaTileTokens = 128;
 constexpr int kUmmaSoftmaxThreads = 128;     // warps 0-3: one thread per token row / value dim
-constexpr int kUmmaThreads = 192;            // + warp 4: MMA issue, warp 5: TMA loads
+constexpr int kUmmaThreads = 256;            // + warp 4: QK issue, 5: K loads, 6: V loads, 7: PV issue
 constexpr int kUmmaStages = 3;               // K+V tile pairs resident per CTA
 constexpr uint32_t kUmmaTileBytes = 16384;   // 128 tokens x 128 bytes
 // Tensor memory columns per CTA: S buffer b in columns 16 b .. 16 b + 15, O in 32-47.
@@ -65,7 +86,7 @@ struct UmmaSmem {
   static constexpr uint32_t kProbabilities = kQuery + 2048;                 // two buffers of 16 rows x 128 B
   static constexpr uint32_t kPrefix = kProbabilities + 4096;                // [sequences + 1]
   static constexpr uint32_t kBarriers = kPrefix + ((kTmaMaxSequences + 1) * 4 + 7) / 8 * 8;
-  static constexpr uint32_t kTmemSlot = kBarriers + (2 * kUmmaStages + 6) * 8;  // full[], empty[], scores[2], P, output[2], Q
+  static constexpr uint32_t kTmemSlot = kBarriers + (4 * kUmmaStages + 7) * 8;  // K full/empty, V full/empty, scores[2], P[2], output[2], Q
   static constexpr uint32_t kHeadScale = kTmemSlot + 8;                     // [8]
   static constexpr uint32_t kReduce = kHeadScale + 32;                      // [4 warps][8]
   static constexpr uint32_t kWarpTotals = kReduce + 128;                    // [5]
@@ -211,6 +232,42 @@ __device__ __forceinline__ void mbarrier_arrive(uint32_t barrier) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(barrier) : "memory");
 }
 
+// Barrier among the 128 softmax threads that also ORs a flag over them.
+__device__ __forceinline__ bool softmax_threads_any(bool flag) {
+  uint32_t out;
+  asm volatile(
+      "{\n"
+      ".reg .pred pin, pout;\n"
+      "setp.ne.u32 pin, %1, 0;\n"
+      "bar.red.or.pred pout, 1, %2, pin;\n"
+      "selp.u32 %0, 1, 0, pout;\n"
+      "}\n"
+      : "=r"(out)
+      : "r"((uint32_t)flag), "n"(kUmmaSoftmaxThreads)
+      : "memory");
+  return out != 0;
+}
+
+// 16 columns of this thread's lane, without waiting for the data.
+__device__ __forceinline__ void tmem_load16_start(uint32_t (&r)[16], uint32_t address) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(address)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+
+// x = hi + lo in E4M3 for a pair of F16 values: returns the two hi bytes and the two lo bytes.
+__device__ __forceinline__ void e4m3_split_half2(__half2 value, uint32_t& hi, uint32_t& lo) {
+  const __half2_raw raw = *reinterpret_cast<const __half2_raw*>(&value);
+  hi = (uint32_t)__nv_cvt_halfraw2_to_fp8x2(raw, __NV_SATFINITE, __NV_E4M3);
+  const __half2_raw back = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)hi, __NV_E4M3);
+  const __half2 rest = __hsub2(value, *reinterpret_cast<const __half2*>(&back));
+  lo = (uint32_t)__nv_cvt_halfraw2_to_fp8x2(*reinterpret_cast<const __half2_raw*>(&rest), __NV_SATFINITE, __NV_E4M3);
+}
+
 // Barrier among the 128 softmax threads only (the control warp never joins it).
 __device__ __forceinline__ void softmax_threads_sync() {
   asm volatile("bar.sync 1, %0;\n" ::"n"(kUmmaSoftmaxThreads) : "memory");
@@ -222,7 +279,7 @@ decode_umma_fp8_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap
                        const __grid_constant__ CUtensorMap value_map, const TmaAxes axes) {
   constexpr uint32_t kD = 128;
   constexpr uint32_t kHeads = 8;
-  constexpr uint32_t kStageBytes = 2 * kUmmaTileBytes;
+  constexpr uint32_t kValueRing = kUmmaStages * kUmmaTileBytes;  // byte offset of the V ring
 
   extern __shared__ uint8_t raw_smem[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023u) & ~uintptr_t(1023));
@@ -230,24 +287,31 @@ decode_umma_fp8_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap
   const uint32_t query_tile = smem_base + UmmaSmem::kQuery;
   const uint32_t probability_tiles = smem_base + UmmaSmem::kProbabilities;  // tile i uses buffer i & 1
   uint32_t* prefix = reinterpret_cast<uint32_t*>(smem + UmmaSmem::kPrefix);
-  const uint32_t full_barriers = smem_base + UmmaSmem::kBarriers;          // one per stage: K and V landed
-  const uint32_t empty_barriers = full_barriers + kUmmaStages * 8;         // one per stage: PV has read it
-  const uint32_t scores_barriers = empty_barriers + kUmmaStages * 8;       // QK of an even / odd tile finished
-  const uint32_t probabilities_barrier = scores_barriers + 16;             // 128 threads published P
-  const uint32_t output_barriers = probabilities_barrier + 8;              // PV of an even / odd tile finished
+  // K and V tiles live in two rings of kUmmaStages slots each, fed by a warp
+  // each. A K slot is released by the QK product that read it, a V slot by the
+  // PV product: both loads then run about three tiles ahead of their use, where
+  // a shared slot (released by PV only) left the K load a single tile of lead
+  // and the latency of HBM on the critical path of every tile.
+  const uint32_t full_barriers = smem_base + UmmaSmem::kBarriers;          // K slot s landed
+  const uint32_t empty_barriers = full_barriers + kUmmaStages * 8;         // QK has read K slot s
+  const uint32_t value_full_barriers = empty_barriers + kUmmaStages * 8;   // V slot s landed
+  const uint32_t value_empty_barriers = value_full_barriers + kUmmaStages * 8;  // PV has read V slot s
+  const uint32_t scores_barriers = value_empty_barriers + kUmmaStages * 8; // QK of an even / odd tile finished
+  const uint32_t probabilities_barriers = scores_barriers + 16;            // 128 threads published P of an even / odd tile
+  const uint32_t output_barriers = probabilities_barriers + 16;            // PV of an even / odd tile finished
   const uint32_t query_barrier = output_barriers + 16;                     // 128 threads published Q
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + UmmaSmem::kTmemSlot);
   volatile float* head_scale = reinterpret_cast<volatile float*>(smem + UmmaSmem::kHeadScale);
   volatile float* reduce = reinterpret_cast<volatile float*>(smem + UmmaSmem::kReduce);
   uint32_t* warp_totals = reinterpret_cast<uint32_t*>(smem + UmmaSmem::kWarpTotals);
-  volatile uint32_t* votes = reinterpret_cast<volatile uint32_t*>(smem + UmmaSmem::kVotes);
   volatile uint32_t* aborted = reinterpret_cast<volatile uint32_t*>(smem + UmmaSmem::kAborted);
 
   const uint32_t tid = threadIdx.x;
   const uint32_t warp = tid >> 5;
   const uint32_t lane = tid & 31u;
-  const bool control = warp == 4;  // MMA issue; owns the tensor memory allocation
-  const bool loader = warp == 5;   // TMA loads
+  const bool control = warp == 4;                // issues the QK products; owns the tensor memory allocation
+  const bool loader = warp == 5 || warp == 6;    // TMA loads: warp 5 feeds the K ring, warp 6 the V ring
+  const bool value_issuer = warp == 7;           // issues the PV products
 
   if (tid == 0) {
     *aborted = 0;
@@ -255,10 +319,13 @@ decode_umma_fp8_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap
     for (int i = 0; i < kUmmaStages; ++i) {
       mbarrier_init(full_barriers + i * 8, 1);
       mbarrier_init(empty_barriers + i * 8, 1);
+      mbarrier_init(value_full_barriers + i * 8, 1);
+      mbarrier_init(value_empty_barriers + i * 8, 1);
     }
     mbarrier_init(scores_barriers, 1);
     mbarrier_init(scores_barriers + 8, 1);
-    mbarrier_init(probabilities_barrier, kUmmaSoftmaxThreads);
+    mbarrier_init(probabilities_barriers, kUmmaSoftmaxThreads);
+    mbarrier_init(probabilities_barriers + 8, kUmmaSoftmaxThreads);
     mbarrier_init(output_barriers, 1);
     mbarrier_init(output_barriers + 8, 1);
     mbarrier_init(query_barrier, kUmmaSoftmaxThreads);
@@ -360,93 +427,106 @@ decode_umma_fp8_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap
   };
 
   if (loader) {
-    // ======================= load warp: one lane keeps kUmmaStages tiles in flight =====
-    if (lane == 0) {
+    // ======================= load warps: each keeps one ring full =========================
+    // A single thread needs about 200 ns per cp.async.bulk.tensor it issues (measured:
+    // eight boxes per tile cost the loader 1.6 us, which was the kernel's whole tile
+    // period). So the eight boxes of a tile are issued by eight lanes at once, each
+    // with its own block id.
+    {
+      const bool value = warp == 6;
       const bool head_inner = axes.head < axes.page;
+      const uint32_t full = value ? value_full_barriers : full_barriers;
+      const uint32_t empty = value ? value_empty_barriers : empty_barriers;
+      const uint32_t ring = smem_base + (value ? kValueRing : 0u);
+      const CUtensorMap* map = value ? &value_map : &key_map;
       StreamCursor producer = start;
-      for (uint32_t issued = 0; issued < my_tiles; ++issued) {
-        const uint32_t stage = issued % kUmmaStages;
+      uint32_t described = 0;
+      struct TileLoad {
+        uint32_t boxes;
+        int32_t head, page, block;  // page and block of this lane's box
+      };
+      // Starts the load of this lane's block id of the next tile of the range.
+      auto describe = [&](TileLoad& load) {
         const uint32_t token0 = producer.tile * kUmmaTileTokens;
         const uint32_t live = min(kUmmaTileTokens, producer.length - token0);
-        const uint32_t boxes = (live + 15u) >> 4;
-        const uint32_t barrier = full_barriers + stage * 8;
-        const uint32_t key_tile = smem_base + stage * kStageBytes;
-        const uint32_t value_tile = key_tile + kUmmaTileBytes;
-        const int32_t* table = p.block_tables + (uint64_t)producer.seq * p.max_blocks_per_sequence;
-        // all block ids first (independent loads, in flight while the stage is
-        // still being read), then the copies
-        int32_t pages[8], blocks[8];
-#pragma unroll
-        for (uint32_t box = 0; box < 8; ++box) {
-          const uint32_t token = token0 + box * 16u;
-          const uint32_t logical = p.block_shift < 32u ? token >> p.block_shift : token / p.block_size;
-          pages[box] = (int32_t)(token - logical * p.block_size);
-          blocks[box] = box < boxes ? __ldg(table + logical) : 0;
+        load.boxes = (live + 15u) >> 4;
+        load.head = (int32_t)producer.head;
+        const uint32_t token = token0 + (lane & 7u) * 16u;
+        const uint32_t logical = p.block_shift < 32u ? token >> p.block_shift : token / p.block_size;
+        load.page = (int32_t)(token - logical * p.block_size);
+        load.block = (lane & 7u) < load.boxes
+                         ? __ldg(p.block_tables + (uint64_t)producer.seq * p.max_blocks_per_sequence + logical)
+                         : 0;
+        ++described;
+        if (described < my_tiles) advance(producer);
+      };
+      // The block ids of tile t + 1 are in flight while tile t is copied.
+      TileLoad current, next;
+      describe(current);
+      next = current;
+      for (uint32_t tile = 0; tile < my_tiles; ++tile) {
+        if (tile + 1 < my_tiles) describe(next);
+        const uint32_t slot = tile % kUmmaStages;
+        // the slot's previous tile has been read by its product
+        if (tile >= (uint32_t)kUmmaStages) wait_phase(empty + slot * 8, tile / kUmmaStages - 1);
+        if (lane == 0) mbarrier_expect_tx(full + slot * 8, current.boxes * 2048u);
+        __syncwarp();
+        if (lane < current.boxes) {
+          const int32_t block = (int32_t)clamp_block(current.block, p.num_blocks);
+          const int32_t c1 = head_inner ? current.head : current.page;
+          const int32_t c2 = head_inner ? current.page : current.head;
+          tma_load_4d(ring + slot * kUmmaTileBytes + lane * 2048u, map, full + slot * 8, 0, c1, c2, block);
         }
-        // the stage's previous tile has been read by its PV product
-        if (issued >= (uint32_t)kUmmaStages) wait_phase(empty_barriers + stage * 8, issued / kUmmaStages - 1);
-        mbarrier_expect_tx(barrier, boxes * 2u * 2048u);
-        const int32_t head = (int32_t)producer.head;
-#pragma unroll
-        for (uint32_t box = 0; box < 8; ++box) {
-          if (box < boxes) {
-            const int32_t block = (int32_t)clamp_block(blocks[box], p.num_blocks);
-            const int32_t c1 = head_inner ? head : pages[box], c2 = head_inner ? pages[box] : head;
-            tma_load_4d(key_tile + box * 2048u, &key_map, barrier, 0, c1, c2, block);
-            tma_load_4d(value_tile + box * 2048u, &value_map, barrier, 0, c1, c2, block);
-          }
-        }
-        if (issued + 1 < my_tiles) advance(producer);
+        current = next;
       }
     }
   } else if (control) {
-    // ======================= MMA warp: one lane issues every product =================
+    // ======================= QK warp: one lane issues the score products ================
+    // (A thread needs 60-90 ns per tcgen05.mma or commit it issues; with one thread
+    // for all eight MMAs of a tile that was the tile period. QK and PV products are
+    // independent of each other, so each kind has a thread of its own.)
     if (lane == 0) {
-      auto issue_scores = [&](uint32_t tile) {  // S[tile & 1] = K(tile) . Q^T
+      StreamCursor cursor = start;
+      uint32_t items_begun = 0;
+      for (uint32_t tile = 0; tile < my_tiles; ++tile) {
+        // a new item's scores need its Q; S buffer (tile & 1) was read by the softmax of tile - 2
+        if (tile == 0 || cursor.tile == 0) wait_phase(query_barrier, items_begun++);
+        if (tile >= 2) wait_phase(probabilities_barriers + (tile & 1u) * 8, (tile >> 1) - 1);
         const uint32_t stage = tile % kUmmaStages;
         wait_phase(full_barriers + stage * 8, tile / kUmmaStages);
         tcgen05_fence_after_sync();
-        const uint64_t key_desc = umma_tile_descriptor(smem_base + stage * kStageBytes);
+        const uint64_t key_desc = umma_tile_descriptor(smem_base + stage * kUmmaTileBytes);
         const uint64_t query_desc = umma_tile_descriptor(query_tile);
         const uint32_t target = tmem_base + (tile & 1u) * 16u;
 #pragma unroll
         for (uint32_t k = 0; k < 4; ++k) umma_f8(target, key_desc + 2u * k, query_desc + 2u * k, kUmmaIdescScores, k);
         umma_commit(scores_barriers + (tile & 1u) * 8);
-      };
-
+        umma_commit(empty_barriers + stage * 8);  // the K slot may be refilled
+        if (tile + 1 < my_tiles) advance(cursor);
+      }
+    }
+  } else if (value_issuer) {
+    // ======================= PV warp: one lane issues the output products ===============
+    if (lane == 0) {
       StreamCursor cursor = start;
-      uint32_t items_begun = 0;
-      wait_phase(query_barrier, items_begun++);
-      issue_scores(0);
       for (uint32_t i = 0; i < my_tiles; ++i) {
         const bool first_of_item = i == 0 || cursor.tile == 0;
-        const bool last_of_item = cursor.tile + 1 == cursor.tiles;
-        const bool last_of_range = i + 1 == my_tiles;
-        if (!last_of_range && !last_of_item) issue_scores(i + 1);  // hidden behind this tile's softmax
         // O += V^T . P^T once the 128 threads have published P
-        wait_phase(probabilities_barrier, i);
+        wait_phase(probabilities_barriers + (i & 1u) * 8, i >> 1);
+        const uint32_t stage = i % kUmmaStages;
+        wait_phase(value_full_barriers + stage * 8, i / kUmmaStages);
         tcgen05_fence_after_sync();
-        {
-          const uint32_t stage = i % kUmmaStages;
-          const uint64_t value_desc = umma_tile_descriptor(smem_base + stage * kStageBytes + kUmmaTileBytes);
-          const uint64_t probability_desc = umma_tile_descriptor(probability_tiles + (i & 1u) * 2048u);
+        const uint64_t value_desc = umma_tile_descriptor(smem_base + kValueRing + stage * kUmmaTileBytes);
+        const uint64_t probability_desc = umma_tile_descriptor(probability_tiles + (i & 1u) * 2048u);
 #pragma unroll
-          for (uint32_t k = 0; k < 4; ++k) {
-            // 32 tokens per MMA: 32 rows of V (4096 bytes) and 32 bytes of each P row
-            umma_f8(tmem_output, value_desc + 256u * k, probability_desc + 2u * k, kUmmaIdescValues,
-                    (first_of_item && k == 0) ? 0u : 1u);
-          }
-          umma_commit(output_barriers + (i & 1u) * 8);
-          umma_commit(empty_barriers + stage * 8);  // the load warp may refill the stage
+        for (uint32_t k = 0; k < 4; ++k) {
+          // 32 tokens per MMA: 32 rows of V (4096 bytes) and 32 bytes of each P row
+          umma_f8(tmem_output, value_desc + 256u * k, probability_desc + 2u * k, kUmmaIdescValues,
+                  (first_of_item && k == 0) ? 0u : 1u);
         }
-        if (!last_of_range) {
-          advance(cursor);
-          if (last_of_item) {
-            // the next tile belongs to another item: its scores need the new Q
-            wait_phase(query_barrier, items_begun++);
-            issue_scores(i + 1);
-          }
-        }
+        umma_commit(output_barriers + (i & 1u) * 8);
+        umma_commit(value_empty_barriers + stage * 8);  // the V slot may be refilled
+        if (i + 1 < my_tiles) advance(cursor);
       }
     }
   } else {
@@ -589,6 +669,13 @@ decode_umma_fp8_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap
       }
     };
 
+    // byte offset of this token's column in row h of a P buffer (row 8 + h: + 1024)
+    uint32_t p_offset[kHeads];
+#pragma unroll
+    for (int h = 0; h < (int)kHeads; ++h) p_offset[h] = swizzled_byte((uint32_t)h, tid);
+    uint32_t raw_scores[16];
+    bool scores_started = false;  // the tensor-memory read of this tile's scores is already under way
+
     for (uint32_t i = 0; i < my_tiles; ++i) {
       const uint32_t stage = i % kUmmaStages;
       const uint32_t token0 = consumer.tile * kUmmaTileTokens;
@@ -599,11 +686,17 @@ decode_umma_fp8_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap
       const bool last_of_range = i + 1 == my_tiles;
 
       // ---- scores of this tile: row `tid` of S -------------------------------------
-      wait_phase(scores_barriers + (i & 1u) * 8, i >> 1);
-      tcgen05_fence_after_sync();
-      float s[16];
-      tmem_load16(s, tmem_base + (i & 1u) * 16u + lane_offset);
+      if (!scores_started) {
+        wait_phase(scores_barriers + (i & 1u) * 8, i >> 1);
+        tcgen05_fence_after_sync();
+        tmem_load16_start(raw_scores, tmem_base + (i & 1u) * 16u + lane_offset);
+      }
+      scores_started = false;
+      tmem_load_wait();
       tcgen05_fence_before_sync();
+      float s[16];
+#pragma unroll
+      for (int c = 0; c < 16; ++c) s[c] = __uint_as_float(raw_scores[c]);
       float d[kHeads];
       bool over = false;
 #pragma unroll
@@ -612,26 +705,23 @@ decode_umma_fp8_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap
         d[h] = row_live ? s[h] - reference[h] : -INFINITY;
         over |= d[h] > kUmmaSlack;
       }
-      const bool warp_over = __any_sync(0xffffffffu, over);
-      if (lane == 0) votes[(i & 1u) * 4 + warp] = warp_over ? 1u : 0u;
 
       // ---- P has two buffers: the PV product of two tiles ago read this one ------------
       if (i >= 2) wait_outputs_through(i - 2);
       if (live < kUmmaTileTokens) {
         // rows past the end of the sequence hold whatever the page (or an older
         // tile) held: clear them in V so that 0 * garbage cannot become NaN
-        wait_phase(full_barriers + stage * 8, i / kUmmaStages);
+        wait_phase(value_full_barriers + stage * 8, i / kUmmaStages);
         if (!row_live) {
-          const uint32_t row = smem_base + stage * kStageBytes + kUmmaTileBytes + tid * 128u;
+          const uint32_t row = smem_base + kValueRing + stage * kUmmaTileBytes + tid * 128u;
 #pragma unroll
           for (int piece = 0; piece < 8; ++piece) {
             asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};\n" ::"r"(row + piece * 16), "r"(0u) : "memory");
           }
         }
       }
-      softmax_threads_sync();  // the four votes are in
-      const uint32_t* tile_votes = const_cast<const uint32_t*>(votes) + (i & 1u) * 4;
-      if (tile_votes[0] | tile_votes[1] | tile_votes[2] | tile_votes[3]) {
+      const bool any_over = softmax_threads_any(over);
+      if (any_over) {
         // Rare: some score left the slack. Raise every head's reference to the
         // largest score of this tile and rescale what was accumulated (every PV
         // product issued so far must have landed in O first).
@@ -671,30 +761,35 @@ decode_umma_fp8_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap
         softmax_threads_sync();  // `reduce` is reused by the next slow path or item end
       }
 
+      // ---- the next tile's scores are normally ready by now: start reading them, so
+      // that the tensor-memory latency hides behind this tile's probabilities ------------
+      if (!last_of_item && !last_of_range) {
+        wait_phase(scores_barriers + ((i + 1) & 1u) * 8, (i + 1) >> 1);
+        tcgen05_fence_after_sync();
+        tmem_load16_start(raw_scores, tmem_base + ((i + 1) & 1u) * 16u + lane_offset);
+        scores_started = true;
+      }
+
       // ---- probabilities: 16 bytes of this token's column of the P tile ----------------
       {
         const uint32_t probability_tile = probability_tiles + (i & 1u) * 2048u;
-        uint32_t hi[4], lo[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const float p0 = fast_exp2(d[2 * j]), p1 = fast_exp2(d[2 * j + 1]);
           row_sum[2 * j] += p0;
           row_sum[2 * j + 1] += p1;
-          e4m3_split_pair(p0 * kUmmaProbabilityScale, p1 * kUmmaProbabilityScale, hi[j], lo[j]);
-        }
-#pragma unroll
-        for (int h = 0; h < (int)kHeads; ++h) {
-          const uint32_t hi_byte = (hi[h >> 1] >> ((h & 1) * 8)) & 0xffu;
-          const uint32_t lo_byte = (lo[h >> 1] >> ((h & 1) * 8)) & 0xffu;
-          asm volatile("st.shared.u8 [%0], %1;\n" ::"r"(probability_tile + swizzled_byte(h, tid)), "r"(hi_byte)
-                       : "memory");
-          asm volatile("st.shared.u8 [%0], %1;\n" ::"r"(probability_tile + swizzled_byte(8 + h, tid)), "r"(lo_byte)
-                       : "memory");
+          uint32_t hi, lo;
+          e4m3_split_half2(__floats2half2_rn(p0 * kUmmaProbabilityScale, p1 * kUmmaProbabilityScale), hi, lo);
+          const uint32_t even = probability_tile + p_offset[2 * j], odd = probability_tile + p_offset[2 * j + 1];
+          asm volatile("st.shared.u8 [%0], %1;\n" ::"r"(even), "r"(hi & 0xffu) : "memory");
+          asm volatile("st.shared.u8 [%0], %1;\n" ::"r"(odd), "r"(hi >> 8) : "memory");
+          asm volatile("st.shared.u8 [%0+1024], %1;\n" ::"r"(even), "r"(lo & 0xffu) : "memory");
+          asm volatile("st.shared.u8 [%0+1024], %1;\n" ::"r"(odd), "r"(lo >> 8) : "memory");
         }
       }
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
       tcgen05_fence_before_sync();
-      mbarrier_arrive(probabilities_barrier);
+      mbarrier_arrive(probabilities_barriers + (i & 1u) * 8);
 
       if (last_of_item || last_of_range) {
         wait_outputs_through(i);
