@@ -408,22 +408,25 @@ def run_b200(args):
 
     # ---- end to end through the public API with host buffers ----------------
     host_qkv = pristine_qkv.cpu().pin_memory()
-    host_positions = case.positions.cpu().pin_memory()
-    host_slots = case.slot_mapping.cpu().pin_memory()
-    host_tables = case.block_tables.cpu().pin_memory()
-    host_lengths = case.sequence_lengths.cpu().pin_memory()
+    # The step's metadata travels as one pinned buffer and one copy, as a serving
+    # engine packs it: positions and slots (int64), block tables and lengths (int32).
+    pieces = [case.positions, case.slot_mapping, case.block_tables, case.sequence_lengths]
+    sizes = [t.numel() * t.element_size() for t in pieces]
+    offsets = [sum(sizes[:i]) for i in range(len(sizes))]  # int64 pieces first: every offset stays 8-byte aligned
+    host_meta = torch.empty(sum(sizes), dtype=torch.uint8).pin_memory()
+    dev_meta = torch.empty(sum(sizes), dtype=torch.uint8, device=device)
+    for tensor, offset, size in zip(pieces, offsets, sizes):
+        host_meta[offset:offset + size].copy_(tensor.cpu().contiguous().view(torch.uint8).reshape(-1))
+    dev_positions, dev_slots, dev_tables, dev_lengths = (
+        dev_meta[offset:offset + size].view(tensor.dtype).reshape(tensor.shape)
+        for tensor, offset, size in zip(pieces, offsets, sizes))
     host_output = torch.empty(output.shape, dtype=output.dtype).pin_memory()
-    dev_positions, dev_slots = torch.empty_like(case.positions), torch.empty_like(case.slot_mapping)
-    dev_tables, dev_lengths = torch.empty_like(case.block_tables), torch.empty_like(case.sequence_lengths)
-    h2d = sum(t.numel() * t.element_size() for t in (host_qkv, host_positions, host_slots, host_tables, host_lengths))
+    h2d = host_qkv.numel() * host_qkv.element_size() + host_meta.numel()
     d2h = host_output.numel() * host_output.element_size()
 
     def e2e_step(index):
         qkv_steps[index].copy_(host_qkv, non_blocking=True)
-        dev_positions.copy_(host_positions, non_blocking=True)
-        dev_slots.copy_(host_slots, non_blocking=True)
-        dev_tables.copy_(host_tables, non_blocking=True)
-        dev_lengths.copy_(host_lengths, non_blocking=True)
+        dev_meta.copy_(host_meta, non_blocking=True)
         q, k, v = qkv_views(qkv_steps[index])
         ops.rope_paged_kv_write_(q, k, v, dev_positions, case.cos_sin_cache, rope_views[index],
                                  case.key_scales, case.value_scales, dev_slots, is_neox=is_neox)
