@@ -52,20 +52,18 @@ __device__ __forceinline__ void mbarrier_expect_tx(uint32_t barrier, uint32_t by
 }
 
 // Waits for the phase with the given parity; gives up after a bounded number
-// of attempts and reports it.
+// of attempts (about a second) and reports it.
 __device__ __forceinline__ bool mbarrier_wait(uint32_t barrier, uint32_t parity) {
-  // each attempt sleeps at most about a microsecond: the whole wait is bounded
-  // to roughly a second
-  for (uint32_t attempt = 0; attempt < (1u << 20); ++attempt) {
+  for (uint32_t attempt = 0; attempt < (1u << 24); ++attempt) {
     uint32_t done;
     asm volatile(
         "{\n"
         ".reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
         "selp.u32 %0, 1, 0, p;\n"
         "}\n"
         : "=r"(done)
-        : "r"(barrier), "r"(parity), "r"(1000u)
+        : "r"(barrier), "r"(parity)
         : "memory");
     if (done) return true;
   }

@@ -228,6 +228,21 @@ __device__ __forceinline__ bool mbarrier_wait_prompt(uint32_t barrier, uint32_t 
   return false;
 }
 
+// Non-blocking test: has the phase with this parity completed?
+__device__ __forceinline__ bool mbarrier_test(uint32_t barrier, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(done)
+      : "r"(barrier), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+
 __device__ __forceinline__ void mbarrier_arrive(uint32_t barrier) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(barrier) : "memory");
 }
@@ -418,6 +433,8 @@ decode_umma_fp8_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap
   // After one wait has expired (the device-wide flag is set by mbarrier_wait) the
   // CTA stops waiting altogether and runs to its end on whatever it has.
   auto wait_phase = [&](uint32_t barrier, uint32_t completions) {
+    // most waits find their phase complete already
+    if (mbarrier_test(barrier, completions & 1u)) return;
     if (*aborted) return;
     if (!mbarrier_wait_prompt(barrier, completions & 1u)) {
       *aborted = 1;
