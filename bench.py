@@ -41,7 +41,7 @@ FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode partition-kernel
 # launch, from the ncu captures summarised under profiles/ (bytes per launch for
 # the default workload); None until a capture exists for the workload.
-NCU_DRAM_TRAFFIC_BYTES = {"cfg2": 154_183_680 + 4_242_432}
+NCU_DRAM_TRAFFIC_BYTES = {"cfg2": 154_178_048 + 3_579_648}
 
 
 def parse_args():
