@@ -49,11 +49,12 @@
 // busy, and leaving out the MMAs does not change the time. What bounds the
 // kernel now is the softmax threads' own chain per tile, about 1.4 us (tensor
 // memory read, vote barrier, 8 exponentials, 16 byte stores, proxy fence),
-// which two CTAs per SM only half hide: 507 us on that workload against
-// 473 us for the mma.sync kernel, so this kernel is opt-in
-// (loom_cuda_set_decode_copy_engine(3)) until the chain is shorter. A switch
-// of work item costs about 5 us (state out, Q in), negligible at 70 tiles per
-// item.
+// which two CTAs per SM only half hide. A switch of work item cost about 5 us
+// (state out, Q in, first scores) and made CTAs that cover short sequences the
+// last to finish; the next item's Q is therefore published before the current
+// item is stored. 478 us on that workload against 472 us for the mma.sync
+// kernel, so this kernel is opt-in (loom_cuda_set_decode_copy_engine(3)) until
+// the chain is shorter.
 //
 // Every wait is bounded (see mbarrier_wait_prompt); after the first expiry the
 // CTA stops waiting and runs to its end, and the first expired wait is
@@ -87,8 +88,8 @@ struct UmmaSmem {
   static constexpr uint32_t kPrefix = kProbabilities + 4096;                // [sequences + 1]
   static constexpr uint32_t kBarriers = kPrefix + ((kTmaMaxSequences + 1) * 4 + 7) / 8 * 8;
   static constexpr uint32_t kTmemSlot = kBarriers + (4 * kUmmaStages + 7) * 8;  // K full/empty, V full/empty, scores[2], P[2], output[2], Q
-  static constexpr uint32_t kHeadScale = kTmemSlot + 8;                     // [8]
-  static constexpr uint32_t kReduce = kHeadScale + 32;                      // [4 warps][8]
+  static constexpr uint32_t kHeadScale = kTmemSlot + 8;                     // [2 item parities][8]
+  static constexpr uint32_t kReduce = kHeadScale + 64;                      // [4 warps][8]
   static constexpr uint32_t kWarpTotals = kReduce + 128;                    // [5]
   static constexpr uint32_t kVotes = kWarpTotals + 32;                      // [2][4]
   static constexpr uint32_t kAborted = kVotes + 32;                         // set when a wait expired
@@ -555,20 +556,20 @@ decode_umma_fp8_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap
     uint32_t item_first_tile = 0;
 
     // Writes the two E4M3 planes of the item's queries and the per-head score scales.
-    auto begin_item = [&]() {
-#pragma unroll
-      for (int h = 0; h < (int)kHeads; ++h) {
-        reference[h] = -INFINITY;
-        row_sum[h] = 0.0f;
-      }
-      const uint32_t kv_head = consumer.head;
+    // Publishes an item's queries (two E4M3 planes) and per-head score scales, and
+    // starts the load of its V scale. May run while the previous item is still
+    // being finished: the Q tile is free once the previous item's last scores
+    // have been read, and the scales of the two items use different slots.
+    float value_scale_next = 1.0f;
+    auto publish_query = [&](const StreamCursor& item_cursor, uint32_t parity) {
+      const uint32_t kv_head = item_cursor.head;
       const uint32_t live_heads = min(kHeads, p.group);
       const uint32_t head = tid >> 4, piece = tid & 15u;  // 16 threads per head, 8 dims each
       float q[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) q[j] = 0.0f;
       if (head < live_heads) {
-        const QT* row = static_cast<const QT*>(p.query) + (uint64_t)consumer.seq * p.q_token +
+        const QT* row = static_cast<const QT*>(p.query) + (uint64_t)item_cursor.seq * p.q_token +
                         ((uint64_t)kv_head * p.group + head) * p.q_head + piece * 8u;
         const uint4 packed = *reinterpret_cast<const uint4*>(row);
         const uint32_t words[4] = {packed.x, packed.y, packed.z, packed.w};
@@ -606,11 +607,21 @@ decode_umma_fp8_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap
                    : "memory");
       if (piece == 0) {
         const float key_scale = __ldg(p.key_scales + (uint64_t)kv_head * p.scale_stride);
-        head_scale[head] = p.scale_log2 * key_scale / prescale;
+        head_scale[parity * kHeads + head] = p.scale_log2 * key_scale / prescale;
       }
+      value_scale_next = __ldg(p.value_scales + (uint64_t)kv_head * p.scale_stride);
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-      mbarrier_arrive(query_barrier);  // the control warp may issue the item's first scores
-      softmax_threads_sync();          // head_scale is visible to the 128 threads
+      mbarrier_arrive(query_barrier);  // the QK warp may issue the item's first scores
+    };
+    float value_scale_now = 1.0f;
+    uint32_t item_parity = 0;
+    auto reset_item_state = [&]() {
+#pragma unroll
+      for (int h = 0; h < (int)kHeads; ++h) {
+        reference[h] = -INFINITY;
+        row_sum[h] = 0.0f;
+      }
+      value_scale_now = value_scale_next;
     };
 
     // Stores the item's result: final rows if this CTA covered the whole item,
@@ -635,8 +646,7 @@ decode_umma_fp8_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap
       const uint32_t first_cta = cta_of(item_begin);
       const uint32_t last_cta = cta_of(item_begin + item_tiles - 1);
       const uint32_t parts = last_cta - first_cta + 1;
-      const float value_scale =
-          __ldg(p.value_scales + (uint64_t)kv_head * p.scale_stride) * (1.0f / kUmmaProbabilityScale);
+      const float value_scale = value_scale_now * (1.0f / kUmmaProbabilityScale);
       const uint32_t stride = state_stride(kD);
       const uint64_t query_row = (uint64_t)item_seq * p.query_heads + (uint64_t)kv_head * p.group;
       const uint32_t dv = tid;
@@ -667,7 +677,9 @@ decode_umma_fp8_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap
       softmax_threads_sync();  // `reduce` is reused
     };
 
-    begin_item();
+    publish_query(consumer, item_parity);
+    reset_item_state();
+    softmax_threads_sync();  // the score scales are visible to the 128 threads
     // Completions of the PV products this thread has observed, per parity of the
     // tile index. A parity test cannot tell phase n from phase n - 2, so a waiter
     // must never fall two phases behind a barrier: with one barrier for the even
@@ -718,7 +730,7 @@ decode_umma_fp8_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap
       bool over = false;
 #pragma unroll
       for (int h = 0; h < (int)kHeads; ++h) {
-        s[h] = (s[h] + s[8 + h]) * head_scale[h];  // base-2 score
+        s[h] = (s[h] + s[8 + h]) * head_scale[item_parity * kHeads + h];  // base-2 score
         d[h] = row_live ? s[h] - reference[h] : -INFINITY;
         over |= d[h] > kUmmaSlack;
       }
@@ -809,12 +821,19 @@ decode_umma_fp8_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap
       mbarrier_arrive(probabilities_barriers + (i & 1u) * 8);
 
       if (last_of_item || last_of_range) {
-        wait_outputs_through(i);
-        finish_item(consumer.seq, consumer.head, consumer.tiles);
+        // The next item's Q goes out first: its load, the QK warp's reaction and the
+        // product itself then overlap the PV product and the store of this item.
+        const StreamCursor finished = consumer;
         if (!last_of_range) {
           advance(consumer);
+          publish_query(consumer, item_parity ^ 1u);
+        }
+        wait_outputs_through(i);
+        finish_item(finished.seq, finished.head, finished.tiles);  // its barriers also publish the new scales
+        if (!last_of_range) {
           item_first_tile = i + 1;
-          begin_item();
+          item_parity ^= 1u;
+          reset_item_state();
         }
       } else {
         advance(consumer);
