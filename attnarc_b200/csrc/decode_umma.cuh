@@ -685,17 +685,18 @@ decode_umma_fp8_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap
     // must never fall two phases behind a barrier: with one barrier for the even
     // tiles and one for the odd ones, the next completion of either cannot happen
     // before this thread has published the P tile it belongs to.
-    uint32_t outputs_seen[2] = {0, 0};
-    auto wait_outputs_through = [&](uint32_t tile) {  // every PV product up to `tile` has landed
-#pragma unroll
-      for (uint32_t parity = 0; parity < 2; ++parity) {
-        if (tile < parity) continue;
-        const uint32_t wanted = (tile - parity) / 2 + 1;
-        while (outputs_seen[parity] < wanted) {
-          wait_phase(output_barriers + parity * 8, outputs_seen[parity]);
-          ++outputs_seen[parity];
-        }
+    uint32_t seen_even = 0, seen_odd = 0;
+    auto wait_output_of = [&](uint32_t tile) {  // the PV product of `tile` has landed
+      const uint32_t wanted = (tile >> 1) + 1;
+      if (tile & 1u) {
+        while (seen_odd < wanted) wait_phase(output_barriers + 8, seen_odd++);
+      } else {
+        while (seen_even < wanted) wait_phase(output_barriers, seen_even++);
       }
+    };
+    auto wait_outputs_through = [&](uint32_t tile) {  // every PV product up to `tile` has landed
+      if (tile >= 1) wait_output_of(tile - 1);
+      wait_output_of(tile);
     };
 
     // byte offset of this token's column in row h of a P buffer (row 8 + h: + 1024)
@@ -736,7 +737,7 @@ decode_umma_fp8_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap
       }
 
       // ---- P has two buffers: the PV product of two tiles ago read this one ------------
-      if (i >= 2) wait_outputs_through(i - 2);
+      if (i >= 2) wait_output_of(i - 2);
       if (live < kUmmaTileTokens) {
         // rows past the end of the sequence hold whatever the page (or an older
         // tile) held: clear them in V so that 0 * garbage cannot become NaN
