@@ -12,6 +12,7 @@ only; all work happens in ``libloom_cuda_bridge.so``.
 from __future__ import annotations
 
 import enum
+import functools
 import math
 
 import torch
@@ -87,14 +88,55 @@ def _require_inference_tensors(*tensors: torch.Tensor) -> None:
 
 
 def _stream(device: torch.device) -> int:
-    return torch.cuda.current_stream(device).cuda_stream
+    """Raw handle of torch's current stream on the device."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    return torch._C._cuda_getCurrentRawStream(index)
+
+
+@functools.lru_cache(maxsize=4096)
+def _span_of(shape: tuple, stride: tuple) -> int:
+    if 0 in shape:
+        return 0
+    return 1 + sum((size - 1) * step for size, step in zip(shape, stride))
 
 
 def _span(tensor: torch.Tensor) -> int:
     """Elements from the first to one past the last addressed element."""
-    if tensor.numel() == 0:
-        return 0
-    return 1 + sum((size - 1) * stride for size, stride in zip(tensor.shape, tensor.stride()))
+    return _span_of(tuple(tensor.shape), tuple(tensor.stride()))
+
+
+class _on_device:
+    """``torch.cuda.device`` that does nothing when the device is already current."""
+
+    __slots__ = ("guard",)
+
+    def __init__(self, device: torch.device):
+        index = device.index
+        self.guard = None if index is None or index == torch.cuda.current_device() else torch.cuda.device(device)
+
+    def __enter__(self):
+        if self.guard is not None:
+            self.guard.__enter__()
+
+    def __exit__(self, *exc):
+        if self.guard is not None:
+            return self.guard.__exit__(*exc)
+        return False
+
+
+@functools.lru_cache(maxsize=1024)
+def _cached_workspace_query(device, sequences, query_heads, kv_heads, value_head_size, max_sequence_length,
+                            partition_tokens):
+    # `device` only keys the cache: the answer depends on the SM count of the current device
+    elements, tokens = _native.u64(0), _native.u32(0)
+    check(
+        library().loom_cuda_bridge_paged_decode_workspace_elements_ex(
+            sequences, query_heads, kv_heads, value_head_size, max_sequence_length, partition_tokens,
+            elements, tokens,
+        ),
+        "paged decode workspace query",
+    )
+    return int(elements.value), int(tokens.value)
 
 
 def _has_dense_nhd_inner_strides(tensor: torch.Tensor) -> bool:
@@ -213,7 +255,7 @@ def paged_decode_attention_out(
         raise RuntimeError("Loom paged decode caches must be dense-inner NHD; use paged_decode_attention_ex")
     if scale is None:
         scale = query.shape[-1] ** -0.5
-    with torch.cuda.device(query.device):
+    with _on_device(query.device):
         needed = decode_workspace_elements(query, key_cache, value_cache, block_tables,
                                            max_sequence_length=max_sequence_length, scale=scale)
         if needed and (workspace is None or workspace.numel() != needed):
@@ -252,16 +294,10 @@ def paged_decode_attention(
 
 def decode_workspace_elements_ex(sequences: int, query_heads: int, kv_heads: int, value_head_size: int,
                                  max_sequence_length: int, partition_tokens: int = 0) -> tuple[int, int]:
-    """(workspace elements, partition tokens) of a partitioned decode."""
-    elements, tokens = _native.u64(0), _native.u32(0)
-    check(
-        library().loom_cuda_bridge_paged_decode_workspace_elements_ex(
-            sequences, query_heads, kv_heads, value_head_size, max_sequence_length, partition_tokens,
-            elements, tokens,
-        ),
-        "paged decode workspace query",
-    )
-    return int(elements.value), int(tokens.value)
+    """(workspace elements, partition tokens) of a partitioned decode on the current device."""
+    device = torch.cuda.current_device() if torch.cuda.is_available() else -1
+    return _cached_workspace_query(device, int(sequences), int(query_heads), int(kv_heads), int(value_head_size),
+                                   int(max_sequence_length), int(partition_tokens))
 
 
 def paged_decode_attention_ex(
@@ -306,7 +342,7 @@ def paged_decode_attention_ex(
         output = torch.empty(shape, device=query.device, dtype=torch.float32 if emit_state else query.dtype)
     _check_decode_tensors(query, key_cache, value_cache, block_tables, sequence_lengths, output,
                           strided_query=True)
-    with torch.cuda.device(query.device):
+    with _on_device(query.device):
         needed, tokens = decode_workspace_elements_ex(sequences, query_heads, kv_heads, value_head_size,
                                                       int(max_sequence_length), partition_tokens)
         if split is None:
@@ -347,7 +383,7 @@ def merge_decode_states(states: torch.Tensor, out_dtype: torch.dtype) -> torch.T
         raise RuntimeError("decode states must be a contiguous float32 [parts, rows, Dv + 2] tensor")
     parts, rows, width = states.shape
     output = torch.empty((rows, width - 2), device=states.device, dtype=out_dtype)
-    with torch.cuda.device(states.device):
+    with _on_device(states.device):
         status = library().loom_cuda_bridge_merge_decode_states(
             states.data_ptr(), states.numel(), parts, rows, width - 2, _DTYPE_CODES[out_dtype],
             output.data_ptr(), output.numel(), _stream(states.device),
@@ -441,7 +477,7 @@ def rope_paged_kv_write_(
     )
     key_cache_pointer = kv_cache.data_ptr()
     value_cache_pointer = key_cache_pointer + kv_cache.stride(1) * kv_cache.element_size()
-    with torch.cuda.device(query.device):
+    with _on_device(query.device):
         status = library().loom_cuda_bridge_rope_paged_kv_write(
             _DTYPE_CODES[query.dtype], _native.KV_CACHE_FP8_E4M3 if fp8 else _native.KV_CACHE_NATIVE,
             query.data_ptr(), _span(query), key.data_ptr(), _span(key), value.data_ptr(), _span(value),
