@@ -128,6 +128,11 @@ decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorM
 
   const uint32_t ring_base = smem_address(smem) + warp * (Ring::kSlots * Tile::kTileBytes);
   const uint32_t barriers = smem_address(barrier_base) + warp * (Ring::kSlots * 8);
+  if (threadIdx.x == 0) {
+    // the two descriptors are fetched while the prologue runs
+    asm volatile("prefetch.tensormap [%0];\n" ::"l"(&key_map) : "memory");
+    asm volatile("prefetch.tensormap [%0];\n" ::"l"(&value_map) : "memory");
+  }
   if (lane == 0) {
 #pragma unroll
     for (int slot = 0; slot < Ring::kSlots; ++slot) mbarrier_init(barriers + slot * 8, 1);
@@ -264,9 +269,6 @@ decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorM
     issue_value = !issue_value;
   };
 
-#pragma unroll
-  for (int index = 0; index < Ring::kAhead; ++index) issue_tile();
-
   // ---- consumer -----------------------------------------------------------------
   WarpState<kD, kNT> state;
   MergeArea<kD, kNT> area(merge_base);
@@ -331,11 +333,19 @@ decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorM
     phases ^= 1u << slot;
   };
 
+  // The first item's query rows are requested before the first K/V tiles: the
+  // memory system answers in order of arrival, and behind the 96 KB of tiles that
+  // an SM asks for at once the 2 KB of Q used to arrive 2.5 us after the first K
+  // tile, with every warp waiting for it.
+  begin_item();
+#pragma unroll
+  for (int index = 0; index < Ring::kAhead; ++index) issue_tile();
+
   for (uint32_t chunk = 0; chunk < my_tiles; ++chunk) {
     // refills the slot of the V tile consumed at the end of the previous round
     issue_tile();
-    if (chunk == 0 || consumer.tile == 0) {
-      if (chunk != 0) finish_item();
+    if (chunk != 0 && consumer.tile == 0) {
+      finish_item();
       begin_item();
     }
     const uint32_t token0 = consumer.tile * kStreamTileTokens + warp_token;
