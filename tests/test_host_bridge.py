@@ -177,3 +177,27 @@ def test_out_of_scope_operators_report_unavailable(lib):
                                               ctypes.c_uint32, ctypes.c_float, ctypes.c_void_p]
     assert lib.loom_cuda_bridge_rms_norm(0, None, 0, None, 0, None, 0, 1, 1, 1e-6, None) == 3
     assert "outside the paged-decode library" in _native.last_error()
+
+
+def test_reference_dispatcher_links_against_this_bridge(lib):
+    """The reference's unmodified torch dispatcher, where it could be built."""
+    from oracle import build_reference_dispatcher
+
+    path = build_reference_dispatcher.build()
+    if path is None:
+        path = build_reference_dispatcher.OUTPUT
+        if not os.path.exists(path):
+            pytest.skip("no reference checkout and no prebuilt dispatcher")
+    import subprocess
+
+    import torch
+
+    wanted = {line.split()[-1] for line in
+              subprocess.run(["nm", "-D", "--undefined-only", path], capture_output=True, text=True).stdout.splitlines()
+              if "loom_cuda_bridge_" in line}
+    assert len(wanted) >= 10
+    missing = [name for name in sorted(wanted) if not hasattr(lib, name)]
+    assert not missing, missing
+    torch.ops.load_library(path)
+    assert torch.ops.loom_kernels.bridge_abi_version() == 2
+    assert torch.ops.loom_kernels.bridge_launch_count(9) >= 0
