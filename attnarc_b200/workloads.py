@@ -59,6 +59,11 @@ CONFIGS = {
     "cfg2": DecodeConfig("cfg2", 64, 12, 2, dtype="bf16", lengths=("uniform", 512, 4096),
                          rope_theta=1.0e6,
                          description="Qwen2.5-1.5B-shaped BF16 decode, batch 64"),
+    # cfg2's geometry inside the envelope of the reference's own CUDA kernels (contexts up to 1024
+    # tokens), for timing both on the same inputs
+    "cfg2-1024": DecodeConfig("cfg2-1024", 64, 12, 2, dtype="bf16", lengths=("uniform", 256, 1024),
+                              rope_theta=1.0e6,
+                              description="Qwen2.5-1.5B-shaped BF16 decode, batch 64, contexts up to 1024"),
     "cfg3": DecodeConfig("cfg3", 256, 32, 8, dtype="bf16", layout="HND",
                          lengths=("loguniform", 1024, 8192), partition_tokens=512,
                          description="Llama-3-8B-shaped BF16 decode, batch 256, split-K 512"),

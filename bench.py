@@ -44,6 +44,45 @@ FALLBACK_HBM_GBS = 6650.0
 NCU_DRAM_TRAFFIC_BYTES = {"cfg2": 154_178_048 + 3_579_648}
 
 
+def reference_kernels_baseline(case, config, cache_views, steps):
+    """Times the reference's own CUDA kernels (compiled for sm_100a by
+    oracle/build_reference_cuda.py, where that was possible) on the same decode
+    inputs, CUDA events over `steps` back-to-back launches after a warm-up. Only
+    for workloads inside their envelope: contexts up to 1024 tokens, NHD, native
+    cache. A baseline beside the number, never part of the measured path."""
+    from oracle import launch_abi
+
+    if not os.path.exists(launch_abi.REFERENCE):
+        return None
+    import torch
+
+    key_cache, value_cache = cache_views
+    query = case.query.contiguous()
+    arguments = (query, key_cache, value_cache, case.block_tables, case.sequence_lengths)
+    options = dict(max_sequence_length=case.max_sequence_length, scale=case.scale)
+
+    def time_library(path):
+        library = launch_abi.LaunchLibrary(path)
+        for _ in range(5):
+            library.decode(*arguments, **options)
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(steps):
+            library.decode(*arguments, **options)
+        stop.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop) / steps * 1e3
+
+    reference_us = time_library(launch_abi.REFERENCE)
+    ours_us = time_library(launch_abi.OURS)
+    return {"kernel": "reference paged_decode_attention.cu recompiled for sm_100a",
+            "protocol": "decode only through the shared launch ABI (reference split-K entry when its sizing "
+                        "function asks for it), eager back-to-back launches on one cache copy, CUDA events",
+            "us_per_launch": reference_us, "value": case.kv_bytes / (reference_us * 1e-6) / 1e9, "unit": UNIT,
+            "this_library_same_protocol_us": ours_us}
+
+
 def parse_args():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -495,6 +534,10 @@ def run_b200(args):
             from oracle import binding as ob
 
             line["cpu_baseline"] = cpu_baseline(case, args.cpu_seconds, ob.max_threads())
+        if world == 1 and case.max_sequence_length <= 1024 and config.layout == "NHD" and not fp8:
+            reference_gpu = reference_kernels_baseline(case, config, views[0], args.steps)
+            if reference_gpu is not None:
+                line["reference_gpu_baseline"] = reference_gpu
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
