@@ -64,6 +64,9 @@ CONFIGS = {
     "cfg2-1024": DecodeConfig("cfg2-1024", 64, 12, 2, dtype="bf16", lengths=("uniform", 256, 1024),
                               rope_theta=1.0e6,
                               description="Qwen2.5-1.5B-shaped BF16 decode, batch 64, contexts up to 1024"),
+    # the reference's largest published case (61.55 us on an H20, its split-K kernels; FA3 30.58 us)
+    "ref-b8-ctx1024": DecodeConfig("ref-b8-ctx1024", 8, 32, 8, dtype="bf16", lengths=("fixed", [1024] * 8),
+                                   description="the reference's largest published decode case: batch 8, context 1024"),
     "cfg3": DecodeConfig("cfg3", 256, 32, 8, dtype="bf16", layout="HND",
                          lengths=("loguniform", 1024, 8192), partition_tokens=512,
                          description="Llama-3-8B-shaped BF16 decode, batch 256, split-K 512"),

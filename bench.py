@@ -62,14 +62,22 @@ def reference_kernels_baseline(case, config, cache_views, steps):
     options = dict(max_sequence_length=case.max_sequence_length, scale=case.scale)
 
     def time_library(path):
-        library = launch_abi.LaunchLibrary(path)
+        launch, _ = launch_abi.LaunchLibrary(path).prepared_decode(*arguments, **options)
         for _ in range(5):
-            library.decode(*arguments, **options)
+            launch()
+        torch.cuda.synchronize()
+        stream = torch.cuda.Stream()
+        stream.wait_stream(torch.cuda.current_stream())
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(stream):
+            with torch.cuda.graph(graph, stream=stream):
+                for _ in range(steps):
+                    launch()
+        graph.replay()
         torch.cuda.synchronize()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
-        for _ in range(steps):
-            library.decode(*arguments, **options)
+        graph.replay()
         stop.record()
         torch.cuda.synchronize()
         return start.elapsed_time(stop) / steps * 1e3
@@ -77,8 +85,8 @@ def reference_kernels_baseline(case, config, cache_views, steps):
     reference_us = time_library(launch_abi.REFERENCE)
     ours_us = time_library(launch_abi.OURS)
     return {"kernel": "reference paged_decode_attention.cu recompiled for sm_100a",
-            "protocol": "decode only through the shared launch ABI (reference split-K entry when its sizing "
-                        "function asks for it), eager back-to-back launches on one cache copy, CUDA events",
+            "protocol": "decode only through the shared launch ABI (each library's split-K entry when its sizing "
+                        "function asks for it), a CUDA graph of the K launches on one cache copy, CUDA events",
             "us_per_launch": reference_us, "value": case.kv_bytes / (reference_us * 1e-6) / 1e9, "unit": UNIT,
             "this_library_same_protocol_us": ours_us}
 

@@ -37,31 +37,45 @@ class LaunchLibrary:
         sizing.restype = u64
         sizing.argtypes = [u32] * 6
 
-    def decode(self, query, key_cache, value_cache, block_tables, lengths, *, max_sequence_length, scale,
-               split: bool | None = None):
-        """Launch-ABI decode: dense-inner NHD caches, the split-K entry when the sizing function asks for it."""
+    def prepared_decode(self, query, key_cache, value_cache, block_tables, lengths, *, max_sequence_length, scale,
+                        split: bool | None = None):
+        """Returns (launch, output): `launch()` enqueues one decode on torch's current stream and allocates
+        nothing (so it can be captured in a CUDA graph); the split-K entry is used when the sizing function
+        asks for it."""
         batch, query_heads, dim = query.shape
         num_blocks, block, kv_heads, _ = key_cache.shape
         value_dim = value_cache.shape[3]
         output = torch.empty((batch, query_heads, value_dim), dtype=query.dtype, device=query.device)
         elements = int(self.lib.loom_cuda_paged_decode_attention_split_k_workspace_elements(
             batch, query_heads, kv_heads, dim, value_dim, max_sequence_length))
-        use_split = elements != 0 if split is None else split
-        stream = torch.cuda.current_stream(query.device).cuda_stream
+        use_split = (elements != 0 if split is None else split) and elements != 0
+        workspace = torch.empty(max(elements, 1), dtype=torch.float32, device=query.device)
         suffix = _SUFFIX[query.dtype]
-        tail = (batch, query_heads, kv_heads, dim, value_dim, num_blocks, block, key_cache.stride(0),
-                value_cache.stride(0), block_tables.shape[1], max_sequence_length, float(scale), stream)
-        if use_split and elements != 0:
-            workspace = torch.empty(elements, dtype=torch.float32, device=query.device)
-            status = getattr(self.lib, f"loom_cuda_paged_decode_attention_split_k_{suffix}")(
-                query.data_ptr(), key_cache.data_ptr(), value_cache.data_ptr(), block_tables.data_ptr(),
-                lengths.data_ptr(), output.data_ptr(), workspace.data_ptr(), elements, *tail)
+        shape = (batch, query_heads, kv_heads, dim, value_dim, num_blocks, block, key_cache.stride(0),
+                 value_cache.stride(0), block_tables.shape[1], max_sequence_length, float(scale))
+        pointers = (query.data_ptr(), key_cache.data_ptr(), value_cache.data_ptr(), block_tables.data_ptr(),
+                    lengths.data_ptr(), output.data_ptr())
+        keep = (query, key_cache, value_cache, block_tables, lengths, workspace)
+        if use_split:
+            function = getattr(self.lib, f"loom_cuda_paged_decode_attention_split_k_{suffix}")
+            arguments = pointers + (workspace.data_ptr(), elements) + shape
         else:
-            status = getattr(self.lib, f"loom_cuda_paged_decode_attention_{suffix}")(
-                query.data_ptr(), key_cache.data_ptr(), value_cache.data_ptr(), block_tables.data_ptr(),
-                lengths.data_ptr(), output.data_ptr(), *tail)
-        if status != 0:
-            raise RuntimeError(f"launch ABI status {status}")
+            function = getattr(self.lib, f"loom_cuda_paged_decode_attention_{suffix}")
+            arguments = pointers + shape
+
+        def launch(_keep=keep):
+            status = function(*arguments, torch.cuda.current_stream(query.device).cuda_stream)
+            if status != 0:
+                raise RuntimeError(f"launch ABI status {status}")
+
+        return launch, output
+
+    def decode(self, query, key_cache, value_cache, block_tables, lengths, *, max_sequence_length, scale,
+               split: bool | None = None):
+        """One launch-ABI decode (dense-inner NHD caches); returns the output tensor."""
+        launch, output = self.prepared_decode(query, key_cache, value_cache, block_tables, lengths,
+                                              max_sequence_length=max_sequence_length, scale=scale, split=split)
+        launch()
         return output
 
     def rope_write(self, query, key, value, positions, cos_sin_cache, key_cache, value_cache, key_scales,
