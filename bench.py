@@ -61,8 +61,7 @@ def reference_kernels_baseline(case, config, cache_views, steps):
     arguments = (query, key_cache, value_cache, case.block_tables, case.sequence_lengths)
     options = dict(max_sequence_length=case.max_sequence_length, scale=case.scale)
 
-    def time_library(path):
-        launch, _ = launch_abi.LaunchLibrary(path).prepared_decode(*arguments, **options)
+    def time_launch(launch):
         for _ in range(5):
             launch()
         torch.cuda.synchronize()
@@ -82,13 +81,24 @@ def reference_kernels_baseline(case, config, cache_views, steps):
         torch.cuda.synchronize()
         return start.elapsed_time(stop) / steps * 1e3
 
-    reference_us = time_library(launch_abi.REFERENCE)
-    ours_us = time_library(launch_abi.OURS)
+    def time_library(path):
+        library = launch_abi.LaunchLibrary(path)
+        decode_us = time_launch(library.prepared_decode(*arguments, **options)[0])
+        view = case.qkv.clone().view(config.batch, config.query_heads + 2 * config.kv_heads, config.head_size)
+        write_us = time_launch(library.prepared_rope_write(
+            view[:, :config.query_heads], view[:, config.query_heads:config.query_heads + config.kv_heads],
+            view[:, config.query_heads + config.kv_heads:], case.positions, case.cos_sin_cache, key_cache, value_cache,
+            case.key_scales, case.value_scales, case.slot_mapping, is_neox=config.rope_style == "neox"))
+        return decode_us, write_us
+
+    reference_us, reference_write_us = time_library(launch_abi.REFERENCE)
+    ours_us, ours_write_us = time_library(launch_abi.OURS)
     return {"kernel": "reference paged_decode_attention.cu recompiled for sm_100a",
             "protocol": "decode only through the shared launch ABI (each library's split-K entry when its sizing "
                         "function asks for it), a CUDA graph of the K launches on one cache copy, CUDA events",
             "us_per_launch": reference_us, "value": case.kv_bytes / (reference_us * 1e-6) / 1e9, "unit": UNIT,
-            "this_library_same_protocol_us": ours_us}
+            "this_library_same_protocol_us": ours_us,
+            "rope_kv_write_us": {"reference": reference_write_us, "this_library": ours_write_us}}
 
 
 def parse_args():

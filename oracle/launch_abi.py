@@ -78,14 +78,15 @@ class LaunchLibrary:
         launch()
         return output
 
-    def rope_write(self, query, key, value, positions, cos_sin_cache, key_cache, value_cache, key_scales,
-                   value_scales, slot_mapping, *, is_neox: bool):
-        """Launch-ABI RoPE + paged-KV write on [tokens, heads, dim] views and logical [blocks, block, heads, dim] caches."""
+    def prepared_rope_write(self, query, key, value, positions, cos_sin_cache, key_cache, value_cache, key_scales,
+                            value_scales, slot_mapping, *, is_neox: bool):
+        """Returns `launch()`: one launch-ABI RoPE + paged-KV write on [tokens, heads, dim] views and logical
+        [blocks, block, heads, dim] caches, on torch's current stream, without allocations."""
         tokens, query_heads, dim = query.shape
         kv_heads, value_dim = key.shape[1], value.shape[2]
         fp8 = key_cache.dtype == torch.uint8
-        stream = torch.cuda.current_stream(query.device).cuda_stream
-        status = getattr(self.lib, f"loom_cuda_rope_paged_kv_write_{_SUFFIX[query.dtype]}")(
+        function = getattr(self.lib, f"loom_cuda_rope_paged_kv_write_{_SUFFIX[query.dtype]}")
+        arguments = (
             query.data_ptr(), key.data_ptr(), value.data_ptr(), positions.data_ptr(), cos_sin_cache.data_ptr(),
             key_cache.data_ptr(), value_cache.data_ptr(), key_scales.data_ptr(), value_scales.data_ptr(),
             slot_mapping.data_ptr(),
@@ -95,6 +96,18 @@ class LaunchLibrary:
             query.stride(0), query.stride(1), key.stride(0), key.stride(1), value.stride(0), value.stride(1),
             key_cache.stride(0), key_cache.stride(1), key_cache.stride(2),
             value_cache.stride(0), value_cache.stride(1), value_cache.stride(2),
-            1 if is_neox else 0, stream)
-        if status != 0:
-            raise RuntimeError(f"launch ABI status {status}")
+            1 if is_neox else 0)
+        keep = (query, key, value, positions, cos_sin_cache, key_cache, value_cache, key_scales, value_scales,
+                slot_mapping)
+
+        def launch(_keep=keep):
+            status = function(*arguments, torch.cuda.current_stream(query.device).cuda_stream)
+            if status != 0:
+                raise RuntimeError(f"launch ABI status {status}")
+
+        return launch
+
+    def rope_write(self, query, key, value, positions, cos_sin_cache, key_cache, value_cache, key_scales,
+                   value_scales, slot_mapping, *, is_neox: bool):
+        self.prepared_rope_write(query, key, value, positions, cos_sin_cache, key_cache, value_cache, key_scales,
+                                 value_scales, slot_mapping, is_neox=is_neox)()
