@@ -7,14 +7,19 @@
 // strided / FP8-cache / partial-state entry points declared in
 // include/loom_launch.h.
 //
-// Three kernels:
-//   decode_mma_kernel      (decode_mma.cuh) 16-bit queries, head size 64 or
-//                          128, 16-byte aligned cache rows: the fast path.
+// Kernels:
+//   decode_stream_tma_kernel (decode_stream_tma.cuh) persistent CTAs that share the
+//                          batch's tiles evenly, rings fed by TMA: the default
+//                          whenever a workspace is given (16-bit queries, head
+//                          size 64 or 128, block size a multiple of 16).
+//   decode_stream_kernel   (decode_stream.cuh) the same schedule with cp.async
+//                          rings, where a tensor map cannot describe the cache.
+//   decode_umma_fp8_kernel (decode_umma.cuh) the same schedule on tcgen05.mma and
+//                          tensor memory for FP8 caches; opt-in.
+//   decode_mma_kernel      (decode_mma.cuh) one CTA per fixed partition: without
+//                          workspace, odd block sizes, caller-chosen partitions.
 //   decode_scalar_kernel   everything else (F32, odd head sizes, unaligned
 //                          views): one query head per CTA, CUDA cores.
-//   decode_stream_kernel   (decode_stream.cuh) the same math in persistent CTAs
-//                          that share the batch's tiles evenly: the default
-//                          whenever a workspace is given.
 //   merge_*_kernel         second, light kernel: combines the partial
 //                          (O, max, sum) states of a split sequence, or of
 //                          several GPUs.
