@@ -19,7 +19,9 @@
 // the 8 query heads, columns 8-15 the lo plane, and the two are added when the
 // accumulators are read. Two planes carry 7-8 significant bits, what the BF16
 // operands of the other path carry; Q is pre-scaled per head by a power of two
-// so that its largest element sits near 2^8, P by 2^4.
+// so that its largest element sits near 2^8, P by 2^4 (with the reference
+// allowed to lag by 2^4: p * 2^4 <= 2^8; a lag of 2^2 raised the reference, and
+// rescaled O in tensor memory, on 16 % of the tiles and cost 3 %).
 //
 // One thread per token row: thread r reads row r of S from tensor memory
 // (tcgen05.ld, lane = row), applies scale and mask, exponentiates against the
@@ -52,7 +54,7 @@
 // which two CTAs per SM only half hide. A switch of work item cost about 5 us
 // (state out, Q in, first scores) and made CTAs that cover short sequences the
 // last to finish; the next item's Q is therefore published before the current
-// item is stored. 478 us on that workload against 472 us for the mma.sync
+// item is stored. 450-470 us on that workload against 456 us for the mma.sync
 // kernel, so this kernel is opt-in (loom_cuda_set_decode_copy_engine(3)) until
 // the chain is shorter.
 //
@@ -77,8 +79,8 @@ constexpr uint32_t kUmmaTileBytes = 16384;   // 128 tokens x 128 bytes
 // (Giving each of a product's four MMAs columns of its own, so that they do not
 // accumulate one after the other, was measured and changed nothing.)
 constexpr uint32_t kUmmaTmemColumns = 64;
-constexpr float kUmmaSlack = 2.0f;           // p <= 2^2 before the reference moves
-constexpr float kUmmaProbabilityScale = 64.0f;
+constexpr float kUmmaSlack = 4.0f;           // p <= 2^4 before the reference moves
+constexpr float kUmmaProbabilityScale = 16.0f;
 constexpr int kUmmaCtasPerSm = 2;
 
 struct UmmaSmem {

@@ -721,7 +721,7 @@ int launch_decode(const LoomDecodeArgs& a) {
       }
       // FP8 cache, head size 128, up to 8 query heads per KV head: the tcgen05
       // kernel applies; it is selected by copy engine 3 only, because the
-      // mma.sync kernel is still the faster of the two (457 vs 478 us on the
+      // mma.sync kernel is not slower and a little more accurate (456 vs 450-470 us on the
       // Llama-3-70B-shaped FP8 workload)
       umma = tma != nullptr && fp8 && p.group <= 8 && a.head_size == 128 && a.value_head_size == 128 &&
              g_copy_engine.load(std::memory_order_relaxed) == 3;
