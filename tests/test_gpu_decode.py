@@ -421,3 +421,41 @@ def test_both_copy_engines_of_the_balanced_kernel(ops, engine, cache, layout, he
     assert route.startswith("umma") == (engine == "tma-umma" and cache == "fp8" and head_size == 128)
     helpers.assert_close(actual, expected, torch.bfloat16, f"{engine} {cache} {layout} D={head_size}")
     assert ops.decode_timeout_flag() == 0
+
+
+@pytest.mark.parametrize("sequences,route", [(1500, "mma16-balanced"), (2500, "mma16")])
+def test_large_batches_fall_back_to_the_kernels_without_a_sequence_limit(ops, sequences, route):
+    # the TMA-fed kernel keeps 1024 tile counts in shared memory, the cp.async one 2048
+    lengths = [1 + (7 * i) % 90 for i in range(sequences)]
+    config = workloads.DecodeConfig("many", sequences, 4, 2, head_size=64, dtype="bf16", lengths=("fixed", lengths))
+    case = workloads.build_case(config, DEVICE, seed=3)
+    key_cache, value_cache = case.cache_views()
+    expected = helpers.oracle_decode(case.query, key_cache, value_cache, case.block_tables, case.sequence_lengths,
+                                     scale=case.scale, max_sequence_length=case.max_sequence_length)
+    actual = ops.paged_decode_attention_ex(case.query, key_cache, value_cache, case.block_tables,
+                                           case.sequence_lengths, max_sequence_length=case.max_sequence_length,
+                                           scale=case.scale, split=True)
+    assert ops.last_decode_route() == route
+    helpers.assert_close(actual, expected, torch.bfloat16, f"{sequences} sequences")
+
+
+def test_tcgen05_kernel_emits_states_that_merge(ops):
+    config = workloads.DecodeConfig("t", 5, 16, 2, head_size=128, dtype="bf16", cache="fp8", fp8_granularity="head",
+                                    lengths=("fixed", [3, 128, 129, 700, 2100]))
+    case = workloads.build_case(config, DEVICE, seed=17)
+    key_cache, value_cache = case.cache_views()
+    scales = dict(key_scales=case.key_scales, value_scales=case.value_scales)
+    expected = helpers.oracle_decode(case.query, key_cache, value_cache, case.block_tables, case.sequence_lengths,
+                                     scale=case.scale, max_sequence_length=case.max_sequence_length, **scales)
+    ops.set_decode_copy_engine("tma-umma")
+    try:
+        states = ops.paged_decode_attention_ex(case.query, key_cache, value_cache, case.block_tables,
+                                               case.sequence_lengths, max_sequence_length=case.max_sequence_length,
+                                               scale=case.scale, split=True, emit_state=True, **scales)
+        route = ops.last_decode_route()
+    finally:
+        ops.set_decode_copy_engine("tma")
+    assert route == "umma-fp8-balanced-tma" and states.dtype == torch.float32
+    merged = ops.merge_decode_states(states.reshape(1, -1, states.shape[-1]).contiguous(), torch.bfloat16)
+    helpers.assert_close(merged.reshape(expected.shape), expected, torch.bfloat16, "tcgen05 states")
+    assert ops.decode_timeout_flag() == 0
