@@ -3,7 +3,8 @@
 The library holds the CUDA kernels, the launch ABI (``include/loom_launch.h``),
 the safe dispatch layer and the checked bridge ABI (``include/loom_bridge.h``).
 It is compiled here rather than through a JIT cache so that the built file
-travels with the source tree. Run ``python -m attnarc_b200.build``.
+travels with the source tree. Run ``python -m attnarc_b200.build``; extra nvcc
+flags (``-DLOOM_FP8_KEY_BY_ALU=1`` ...) are taken from ``LOOM_NVCC_FLAGS``.
 """
 
 from __future__ import annotations
@@ -62,7 +63,8 @@ def _compile(source: str, force: bool) -> tuple[str, str]:
     obj = os.path.join(BUILD_DIR, source + ".o")
     log = ""
     if force or _stale(obj, [path] + _headers()):
-        cmd = [nvcc_path(), *NVCC_FLAGS, "-c", path, "-o", obj]
+        extra = os.environ.get("LOOM_NVCC_FLAGS", "").split()
+        cmd = [nvcc_path(), *NVCC_FLAGS, *extra, "-c", path, "-o", obj]
         done = subprocess.run(cmd, capture_output=True, text=True)
         log = done.stdout + done.stderr
         if done.returncode != 0:

@@ -51,7 +51,12 @@
 // busy, and leaving out the MMAs does not change the time. What bounds the
 // kernel now is the softmax threads' own chain per tile, about 1.4 us (tensor
 // memory read, vote barrier, 8 exponentials, 16 byte stores, proxy fence),
-// which two CTAs per SM only half hide. A switch of work item cost about 5 us
+// which two CTAs per SM only half hide - yet a third CTA per SM (two-slot rings,
+// 80 registers) changed nothing (485 against 478 us), nor did two-slot rings at
+// two CTAs per SM, so the limit is shared by the SM or lies in the memory
+// system: with an HND cache (the 16 rows of a box contiguous, 2 KB) the same
+// kernel takes 434 us against 479 us for NHD (128-byte rows 1 KB apart), where
+// the mma.sync kernel takes 446 against 457 us. A switch of work item cost about 5 us
 // (state out, Q in, first scores) and made CTAs that cover short sequences the
 // last to finish; the next item's Q is therefore published before the current
 // item is stored. 450-470 us on that workload against 456 us for the mma.sync
@@ -95,7 +100,7 @@ struct UmmaSmem {
   static constexpr uint32_t kWarpTotals = kReduce + 128;                    // [5]
   static constexpr uint32_t kVotes = kWarpTotals + 32;                      // [2][4]
   static constexpr uint32_t kAborted = kVotes + 32;                         // set when a wait expired
-  static constexpr uint32_t kBytes = kAborted + 16 + 1024;                  // + alignment slack
+  static constexpr uint32_t kBytes = kAborted + 16;                         // the window itself is 1024-byte aligned
 };
 
 // ---- tcgen05 wrappers ---------------------------------------------------------
@@ -299,9 +304,18 @@ decode_umma_fp8_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap
   constexpr uint32_t kHeads = 8;
   constexpr uint32_t kValueRing = kUmmaStages * kUmmaTileBytes;  // byte offset of the V ring
 
-  extern __shared__ uint8_t raw_smem[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023u) & ~uintptr_t(1023));
+  // Three CTAs of 76 KB share an SM only without alignment slack: the window must
+  // start on a 1024-byte boundary (the swizzle period) by itself.
+  extern __shared__ __align__(1024) uint8_t raw_smem[];
+  uint8_t* smem = raw_smem;
   const uint32_t smem_base = smem_address(smem);
+  if (smem_base & 1023u) {
+    if (threadIdx.x == 0) {
+      atomicOr(&g_decode_timeout_flag, 1u);
+      atomicCAS(&g_decode_timeout_where, 0u, 31u << 20);
+    }
+    return;
+  }
   const uint32_t query_tile = smem_base + UmmaSmem::kQuery;
   const uint32_t probability_tiles = smem_base + UmmaSmem::kProbabilities;  // tile i uses buffer i & 1
   uint32_t* prefix = reinterpret_cast<uint32_t*>(smem + UmmaSmem::kPrefix);

@@ -464,55 +464,53 @@ def run_b200(args):
     decode_ms = decode_start.elapsed_time(decode_stop) / args.steps
 
     # ---- end to end through the public API with host buffers ----------------
-    host_qkv = pristine_qkv.cpu().pin_memory()
-    # The step's metadata travels as one pinned buffer and one copy, as a serving
-    # engine packs it: positions and slots (int64), block tables and lengths (int32).
-    pieces = [case.positions, case.slot_mapping, case.block_tables, case.sequence_lengths]
-    sizes = [t.numel() * t.element_size() for t in pieces]
-    offsets = [sum(sizes[:i]) for i in range(len(sizes))]  # int64 pieces first: every offset stays 8-byte aligned
-    host_meta = torch.empty(sum(sizes), dtype=torch.uint8).pin_memory()
-    dev_meta = torch.empty(sum(sizes), dtype=torch.uint8, device=device)
-    for tensor, offset, size in zip(pieces, offsets, sizes):
-        host_meta[offset:offset + size].copy_(tensor.cpu().contiguous().view(torch.uint8).reshape(-1))
-    dev_positions, dev_slots, dev_tables, dev_lengths = (
-        dev_meta[offset:offset + size].view(tensor.dtype).reshape(tensor.shape)
-        for tensor, offset, size in zip(pieces, offsets, sizes))
-    host_output = torch.empty(output.shape, dtype=output.dtype).pin_memory()
-    h2d = host_qkv.numel() * host_qkv.element_size() + host_meta.numel()
-    d2h = host_output.numel() * host_output.element_size()
+    # attnarc_b200.decode_step.CapturedDecodeStep: the step's inputs (packed QKV
+    # rows, positions, slots, block tables, lengths) sit in one pinned host buffer;
+    # one graph launch copies them in, runs RoPE + KV write and the decode, and
+    # copies the attention rows back to pinned memory; the host waits for them
+    # before it starts the next step. The same sequence issued call by call is
+    # timed beside it (`eager_us_per_step`).
+    from attnarc_b200.decode_step import CapturedDecodeStep
 
-    def e2e_step(index):
-        qkv_steps[index].copy_(host_qkv, non_blocking=True)
-        dev_meta.copy_(host_meta, non_blocking=True)
-        q, k, v = qkv_views(qkv_steps[index])
-        ops.rope_paged_kv_write_(q, k, v, dev_positions, case.cos_sin_cache, rope_views[index],
-                                 case.key_scales, case.value_scales, dev_slots, is_neox=is_neox)
-        key_cache, value_cache = views[index]
-        ops.paged_decode_attention_ex(q, key_cache, value_cache, dev_tables, dev_lengths,
-                                      max_sequence_length=case.max_sequence_length, scale=case.scale,
-                                      workspace=workspace, partition_tokens=partition, split=split,
-                                      output=output, **scales)
-        host_output.copy_(output, non_blocking=True)
-        torch.cuda.current_stream().synchronize()  # the step's result is needed before the next step
+    host_rows = pristine_qkv.cpu().view(sequences, query_heads + 2 * kv_heads, config.head_size)
+    captured = []
+    for index in range(copies):
+        one = CapturedDecodeStep(
+            rope_views[index], case.cos_sin_cache, sequences=sequences, query_heads=query_heads,
+            max_blocks_per_sequence=case.block_tables.shape[1], max_sequence_length=case.max_sequence_length,
+            dtype=config.torch_dtype, scale=case.scale, is_neox=is_neox,
+            key_scales=case.key_scales if fp8 else None, value_scales=case.value_scales if fp8 else None,
+            partition_tokens=config.partition_tokens)
+        one.host_qkv.copy_(host_rows)
+        one.host_positions.copy_(case.positions.cpu())
+        one.host_slot_mapping.copy_(case.slot_mapping.cpu())
+        one.host_block_tables.copy_(case.block_tables.cpu())
+        one.host_sequence_lengths.copy_(case.sequence_lengths.cpu())
+        captured.append(one.capture())
+    h2d, d2h = captured[0].h2d_bytes, captured[0].d2h_bytes
 
-    for w in range(3):
-        e2e_step(w % copies)
-    barrier()
-    e2e_start, e2e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e2e_start.record()
-    for k in range(args.steps):
-        e2e_step(k % copies)
-    e2e_stop.record()
-    barrier()
-    e2e_ms = e2e_start.elapsed_time(e2e_stop)
+    def timed_steps(run_step):
+        for w in range(3):
+            run_step(w % copies)
+        barrier()
+        first, last = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        first.record()
+        for k in range(args.steps):
+            run_step(k % copies)  # each waits for its result: the next step depends on it
+        last.record()
+        barrier()
+        return first.elapsed_time(last)
+
+    e2e_ms = timed_steps(lambda index: captured[index].run())
+    eager_ms = timed_steps(lambda index: captured[index].run_eager())
 
     # ---- reduce over ranks: the slowest rank sets the time -------------------
-    times = torch.tensor([graph_ms, e2e_ms, decode_ms], device=device, dtype=torch.float64)
+    times = torch.tensor([graph_ms, e2e_ms, decode_ms, eager_ms], device=device, dtype=torch.float64)
     total_bytes = torch.tensor([float(kv_bytes)], device=device, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
         dist.all_reduce(total_bytes, op=dist.ReduceOp.SUM)
-    graph_ms, e2e_ms, decode_ms_max = (float(x) for x in times.tolist())
+    graph_ms, e2e_ms, decode_ms_max, eager_ms_max = (float(x) for x in times.tolist())
     job_bytes = float(total_bytes.item())
 
     if rank == 0:
@@ -531,12 +529,14 @@ def run_b200(args):
                 "block_size": config.block_size, "layout": config.layout, "cache": config.cache,
                 "context_tokens_rank0": int(case.lengths.sum()), "partition_tokens": partition if split else 0,
                 "kv_bytes_per_step_rank0": kv_bytes, "parallelism": f"sequence-sharded x{world}, no collective",
-                "launch": "cuda_graph of K steps (value); eager public API (e2e)",
+                "launch": "cuda_graph of K steps (value); one captured step per launch, host waits for each (e2e)",
                 "programmatic_launch": 1 if args.programmatic_launch is None else args.programmatic_launch,
                 "l2": f"inputs rotate over {copies} cache copies of {cache_bytes / 1e6:.0f} MB (> 126 MB L2 in total)",
             },
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "us_per_step": e2e_ms / args.steps * 1e3},
+                    "us_per_step": e2e_ms / args.steps * 1e3,
+                    "eager_us_per_step": eager_ms_max / args.steps * 1e3,
+                    "api": "attnarc_b200.decode_step.CapturedDecodeStep.run"},
             "gpu_launches": launches_per_step * args.steps,
             "roofline": {
                 "bound": "hbm", "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,
