@@ -86,6 +86,14 @@ def _declare(lib):
     lib.loom_cuda_paged_decode_workspace_elements.restype = u64
     lib.loom_cuda_paged_decode_workspace_elements.argtypes = [u32] * 6
     lib.loom_cuda_merge_decode_states.argtypes = [ptr, u32, u32, u32, u32, ptr, ptr]
+    # KV block movement
+    lib.loom_cuda_bridge_kv_block_move.argtypes = [ptr, u64] * 5 + [u32, u32] + [u64] * 5 + [ptr]
+    lib.loom_cuda_bridge_kv_block_swap.argtypes = [ptr, u64] * 3 + [u32] + [u64] * 3 + [ptr]
+    lib.loom_cuda_bridge_block_table_remap.argtypes = [ptr, u64, ptr, u64, ptr]
+    lib.loom_cuda_bridge_kv_block_movement_launches.argtypes = [ctypes.POINTER(u64)]
+    lib.loom_cuda_kv_block_move.argtypes = [ptr] * 5 + [u32] * 3 + [u64] * 5 + [ptr]
+    lib.loom_cuda_kv_block_swap.argtypes = [ptr] * 3 + [u32, u32] + [u64] * 3 + [ptr]
+    lib.loom_cuda_block_table_remap.argtypes = [ptr, u64, ptr, u32, ptr]
     # partitioner
     i64p, u32p, u64p = ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(u32), ctypes.POINTER(u64)
     lib.loom_partition_by_sequence.argtypes = [i64p, u32, u32, u32p, u64p]

@@ -23,6 +23,7 @@ LIBRARY = os.path.join(PACKAGE_DIR, "libloom_cuda_bridge.so")
 SOURCES = [
     "rope_paged_kv_sm100.cu",
     "paged_decode_sm100.cu",
+    "kv_block_move_sm100.cu",
     "dispatch.cpp",
     "bridge.cpp",
     "partition.cpp",

@@ -33,6 +33,7 @@ using loom::detail::format;
 
 constexpr int kOperatorCount = 11;
 std::atomic<uint64_t> g_launch_counts[kOperatorCount];
+std::atomic<uint64_t> g_block_movement_launches{0};  // outside the reference's operator ids
 
 thread_local std::string g_last_error = "no bridge error has been recorded";
 
@@ -409,6 +410,144 @@ int loom_cuda_bridge_merge_decode_states(const float* states, uint64_t state_ele
     require_disjoint_from("output", out.range, {{"states", in.range}}, "decode merge");
     loom::merge_decode_states(in.region, parts, rows, value_head_size, kind, out.region, stream);
     record_launch(LOOM_CUDA_BRIDGE_PAGED_DECODE_ATTENTION);
+  });
+}
+
+// ---- KV block movement (no counterpart in the reference yet; checks in the bridge's style) ----
+
+namespace {
+
+// The span of a cache that `blocks` blocks of `block_bytes` at `stride` cover.
+void require_block_span(const char* name, uint64_t span_bytes, uint32_t blocks, uint64_t block_bytes,
+                        uint64_t stride) {
+  if (blocks == 0) throw invalid(format("%s holds no blocks", name));
+  if (block_bytes == 0) throw invalid("KV block size is zero bytes");
+  if (stride < block_bytes) throw invalid(format("%s block stride %llu is smaller than a block (%llu bytes)", name,
+                                                 (unsigned long long)stride, (unsigned long long)block_bytes));
+  uint64_t needed = 0;
+  if (__builtin_mul_overflow((uint64_t)(blocks - 1), stride, &needed) ||
+      __builtin_add_overflow(needed, block_bytes, &needed)) {
+    throw invalid(format("%s byte span overflows", name));
+  }
+  if (span_bytes < needed) {
+    throw invalid(format("%s span of %llu bytes is shorter than its %u blocks need (%llu bytes)", name,
+                         (unsigned long long)span_bytes, blocks, (unsigned long long)needed));
+  }
+  if (block_bytes % 16 != 0 || stride % 16 != 0) {
+    throw invalid(format("%s blocks and strides must be multiples of 16 bytes", name));
+  }
+}
+
+void raise_launch_status(int status, const char* operation) {
+  if (status == LOOM_CUDA_SUCCESS) return;
+  if (status == LOOM_CUDA_INVALID_ARGUMENT || status == LOOM_CUDA_UNSUPPORTED) {
+    throw invalid(format("%s rejected its arguments: %s", operation, loom_cuda_status_string(status)));
+  }
+  if (status == LOOM_CUDA_UNAVAILABLE) {
+    throw ExecutorFailure(ExecutorFailure::Kind::BackendUnavailable, status,
+                          format("%s: CUDA backend unavailable", operation));
+  }
+  throw loom::submission(status, loom_cuda_status_string(status));
+}
+
+// A cache pointer with its byte span: non-null, 16-byte aligned, no address overflow.
+ByteRange cache_range(const void* pointer, uint64_t bytes, const char* name) {
+  if (pointer == nullptr) throw invalid(format("%s pointer is null", name));
+  const uintptr_t start = reinterpret_cast<uintptr_t>(pointer);
+  if (start % 16 != 0) throw invalid(format("%s pointer is not aligned to 16 bytes", name));
+  uintptr_t end = 0;
+  if (__builtin_add_overflow(start, (uintptr_t)bytes, &end)) {
+    throw invalid(format("%s address range overflows usize", name));
+  }
+  return ByteRange{start, end};
+}
+
+}  // namespace
+
+int loom_cuda_bridge_kv_block_move(const void* source_key_cache, uint64_t source_key_bytes,
+                                   const void* source_value_cache, uint64_t source_value_bytes,
+                                   void* destination_key_cache, uint64_t destination_key_bytes,
+                                   void* destination_value_cache, uint64_t destination_value_bytes,
+                                   const int64_t* block_pairs, uint64_t pair_elements, uint32_t source_blocks,
+                                   uint32_t destination_blocks, uint64_t block_bytes,
+                                   uint64_t source_key_block_stride, uint64_t source_value_block_stride,
+                                   uint64_t destination_key_block_stride, uint64_t destination_value_block_stride,
+                                   void* stream) {
+  return bridge_call([&] {
+    if (pair_elements % 2 != 0) throw invalid("KV block pairs must hold two ids per pair");
+    if (pair_elements / 2 > 0xffffffffull) throw invalid("too many KV block pairs for one call");
+    cache_range(source_key_cache, source_key_bytes, "source key cache");
+    cache_range(source_value_cache, source_value_bytes, "source value cache");
+    const ByteRange written_key = cache_range(destination_key_cache, destination_key_bytes, "destination key cache");
+    const ByteRange written_value =
+        cache_range(destination_value_cache, destination_value_bytes, "destination value cache");
+    require_block_span("source key cache", source_key_bytes, source_blocks, block_bytes, source_key_block_stride);
+    require_block_span("source value cache", source_value_bytes, source_blocks, block_bytes,
+                       source_value_block_stride);
+    require_block_span("destination key cache", destination_key_bytes, destination_blocks, block_bytes,
+                       destination_key_block_stride);
+    require_block_span("destination value cache", destination_value_bytes, destination_blocks, block_bytes,
+                       destination_value_block_stride);
+    if (pair_elements == 0) return;  // nothing to move
+    const Checked pairs = borrow(block_pairs, pair_elements, 8, "KV block pairs");
+    require_disjoint_from("block pairs", pairs.range,
+                          {{"destination key cache", written_key}, {"destination value cache", written_value}},
+                          "KV block move");
+    raise_launch_status(
+        loom_cuda_kv_block_move(source_key_cache, source_value_cache, destination_key_cache,
+                                destination_value_cache, block_pairs, (uint32_t)(pair_elements / 2), source_blocks,
+                                destination_blocks, block_bytes, source_key_block_stride,
+                                source_value_block_stride, destination_key_block_stride,
+                                destination_value_block_stride, stream),
+        "KV block move");
+    g_block_movement_launches.fetch_add(1, std::memory_order_relaxed);
+  });
+}
+
+int loom_cuda_bridge_kv_block_swap(void* key_cache, uint64_t key_bytes, void* value_cache, uint64_t value_bytes,
+                                   const int64_t* block_pairs, uint64_t pair_elements, uint32_t num_blocks,
+                                   uint64_t block_bytes, uint64_t key_block_stride, uint64_t value_block_stride,
+                                   void* stream) {
+  return bridge_call([&] {
+    if (pair_elements % 2 != 0) throw invalid("KV block pairs must hold two ids per pair");
+    if (pair_elements / 2 > 0xffffffffull) throw invalid("too many KV block pairs for one call");
+    const ByteRange keys = cache_range(key_cache, key_bytes, "key cache");
+    const ByteRange values = cache_range(value_cache, value_bytes, "value cache");
+    require_block_span("key cache", key_bytes, num_blocks, block_bytes, key_block_stride);
+    require_block_span("value cache", value_bytes, num_blocks, block_bytes, value_block_stride);
+    if (pair_elements == 0) return;
+    const Checked pairs = borrow(block_pairs, pair_elements, 8, "KV block pairs");
+    require_disjoint_from("block pairs", pairs.range, {{"key cache", keys}, {"value cache", values}},
+                          "KV block swap");
+    raise_launch_status(loom_cuda_kv_block_swap(key_cache, value_cache, block_pairs, (uint32_t)(pair_elements / 2),
+                                                num_blocks, block_bytes, key_block_stride, value_block_stride,
+                                                stream),
+                        "KV block swap");
+    g_block_movement_launches.fetch_add(1, std::memory_order_relaxed);
+  });
+}
+
+int loom_cuda_bridge_block_table_remap(int32_t* block_tables, uint64_t table_elements,
+                                       const int32_t* new_block_ids, uint64_t id_elements, void* stream) {
+  return bridge_call([&] {
+    if (id_elements == 0 || id_elements > 0xffffffffull) throw invalid("new block ids must name 1..2^32-1 blocks");
+    const Checked ids = borrow(new_block_ids, id_elements, 4, "new block ids");
+    if (table_elements == 0) return;
+    const Checked tables = borrow(block_tables, table_elements, 4, "block tables");
+    require_disjoint_from("block tables", tables.range, {{"new block ids", ids.range}}, "block table remap");
+    raise_launch_status(
+        loom_cuda_block_table_remap(block_tables, table_elements, new_block_ids, (uint32_t)id_elements, stream),
+        "block table remap");
+    g_block_movement_launches.fetch_add(1, std::memory_order_relaxed);
+  });
+}
+
+int loom_cuda_bridge_kv_block_movement_launches(uint64_t* count) {
+  return bridge_call([&] {
+    if (count == nullptr || reinterpret_cast<uintptr_t>(count) % alignof(uint64_t) != 0) {
+      throw invalid("launch-count output pointer is null or misaligned");
+    }
+    *count = g_block_movement_launches.load(std::memory_order_relaxed);
   });
 }
 

@@ -1,0 +1,259 @@
+// KV block movement for a paged cache on sm_100a: move (copy, gather, scatter,
+// compact), swap, and the block-table rewrite that follows a compaction.
+//
+// The reference lists these operators as the next ones around its paged cache
+// (docs/operator-catalog.md:61 "KV block copy, swap, gather, scatter, compact,
+// and remap"; roadmap item 3 at docs/operator-catalog.md:140) but ships no
+// implementation or contract for them yet, so the entry points below are new,
+// in the style of the launch header: plain pointers, sizes, a stream.
+//
+// A block is the unit the block tables name: the K bytes of one block are one
+// contiguous span (block_size x kv_heads x dim elements in whatever order the
+// layout puts them: NHD and HND alike), and so are its V bytes. Movement is
+// therefore type- and layout-blind: spans of `block_bytes` bytes, found by a
+// block id and a byte stride between blocks. Work is cut into 16 KB chunks of
+// a span; a grid sized to the SM count walks the chunks, each thread moving
+// four 16-byte vectors per chunk with all its loads issued before its stores.
+// The kernels are bound by HBM: every byte is read once and written once.
+//
+// Block ids live on the device and are trusted engine state like block tables;
+// the kernels only skip a pair that names a block outside its cache.
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "../../include/loom_launch.h"
+#include "launch_util.cuh"
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kVectorsPerThread = 4;
+constexpr uint32_t kChunkBytes = kThreads * kVectorsPerThread * 16;  // 16 KB
+constexpr int kCtasPerSm = 8;
+
+struct MoveParams {
+  const uint8_t* source[2];  // K, V
+  uint8_t* destination[2];
+  uint64_t source_stride[2];  // bytes between blocks
+  uint64_t destination_stride[2];
+  const int64_t* pairs;  // [pair_count][2]: source block, destination block
+  uint64_t block_bytes;
+  uint32_t pair_count;
+  uint32_t source_blocks;
+  uint32_t destination_blocks;
+  uint32_t chunks_per_block;
+};
+
+__device__ __forceinline__ uint4 load_streaming(const uint8_t* address) {
+  return __ldcs(reinterpret_cast<const uint4*>(address));
+}
+
+__device__ __forceinline__ void store_streaming(uint8_t* address, uint4 value) {
+  __stcs(reinterpret_cast<uint4*>(address), value);
+}
+
+// destination block <- source block, for every pair, K and V.
+__global__ void __launch_bounds__(kThreads, kCtasPerSm) kv_block_move_kernel(const MoveParams p) {
+  loom_launch::grid_dependency_wait();
+  const uint64_t units = (uint64_t)p.pair_count * 2u * p.chunks_per_block;
+  for (uint64_t unit = blockIdx.x; unit < units; unit += gridDim.x) {
+    const uint32_t chunk = (uint32_t)(unit % p.chunks_per_block);
+    const uint64_t rest = unit / p.chunks_per_block;
+    const uint32_t which = (uint32_t)(rest & 1u);  // K and V of a pair are neighbours in the walk
+    const uint64_t pair = rest >> 1;
+    const int64_t from = __ldg(p.pairs + 2 * pair);
+    const int64_t to = __ldg(p.pairs + 2 * pair + 1);
+    if (from < 0 || from >= (int64_t)p.source_blocks || to < 0 || to >= (int64_t)p.destination_blocks) continue;
+    const uint8_t* source = p.source[which] + (uint64_t)from * p.source_stride[which];
+    uint8_t* destination = p.destination[which] + (uint64_t)to * p.destination_stride[which];
+    const uint64_t base = (uint64_t)chunk * kChunkBytes + threadIdx.x * 16u;
+    uint4 held[kVectorsPerThread];
+#pragma unroll
+    for (int j = 0; j < kVectorsPerThread; ++j) {
+      const uint64_t offset = base + (uint64_t)j * (kThreads * 16u);
+      if (offset < p.block_bytes) held[j] = load_streaming(source + offset);
+    }
+#pragma unroll
+    for (int j = 0; j < kVectorsPerThread; ++j) {
+      const uint64_t offset = base + (uint64_t)j * (kThreads * 16u);
+      if (offset < p.block_bytes) store_streaming(destination + offset, held[j]);
+    }
+  }
+}
+
+struct SwapParams {
+  uint8_t* cache[2];   // K, V
+  uint64_t stride[2];  // bytes between blocks
+  const int64_t* pairs;
+  uint64_t block_bytes;
+  uint32_t pair_count;
+  uint32_t blocks;
+  uint32_t chunks_per_block;
+};
+
+// Exchanges the two blocks of every pair, K and V.
+__global__ void __launch_bounds__(kThreads, kCtasPerSm) kv_block_swap_kernel(const SwapParams p) {
+  loom_launch::grid_dependency_wait();
+  constexpr int kHalf = kVectorsPerThread / 2;  // two blocks are held at once
+  const uint32_t chunks = p.chunks_per_block * 2u;  // chunks of 8 KB here
+  const uint64_t units = (uint64_t)p.pair_count * 2u * chunks;
+  for (uint64_t unit = blockIdx.x; unit < units; unit += gridDim.x) {
+    const uint32_t chunk = (uint32_t)(unit % chunks);
+    const uint64_t rest = unit / chunks;
+    const uint32_t which = (uint32_t)(rest & 1u);
+    const uint64_t pair = rest >> 1;
+    const int64_t left = __ldg(p.pairs + 2 * pair);
+    const int64_t right = __ldg(p.pairs + 2 * pair + 1);
+    if (left < 0 || left >= (int64_t)p.blocks || right < 0 || right >= (int64_t)p.blocks || left == right) continue;
+    uint8_t* first = p.cache[which] + (uint64_t)left * p.stride[which];
+    uint8_t* second = p.cache[which] + (uint64_t)right * p.stride[which];
+    const uint64_t base = (uint64_t)chunk * (kChunkBytes / 2) + threadIdx.x * 16u;
+    uint4 a[kHalf], b[kHalf];
+#pragma unroll
+    for (int j = 0; j < kHalf; ++j) {
+      const uint64_t offset = base + (uint64_t)j * (kThreads * 16u);
+      if (offset < p.block_bytes) {
+        a[j] = load_streaming(first + offset);
+        b[j] = load_streaming(second + offset);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < kHalf; ++j) {
+      const uint64_t offset = base + (uint64_t)j * (kThreads * 16u);
+      if (offset < p.block_bytes) {
+        store_streaming(first + offset, b[j]);
+        store_streaming(second + offset, a[j]);
+      }
+    }
+  }
+}
+
+// block_tables[i] <- new_ids[block_tables[i]] for ids inside the cache; other
+// entries (negative sentinels of unused tail entries) stay as they are.
+__global__ void __launch_bounds__(kThreads) block_table_remap_kernel(int32_t* tables, uint64_t entries,
+                                                                     const int32_t* new_ids, uint32_t blocks) {
+  loom_launch::grid_dependency_wait();
+  for (uint64_t i = (uint64_t)blockIdx.x * kThreads + threadIdx.x; i < entries; i += (uint64_t)gridDim.x * kThreads) {
+    const int32_t id = tables[i];
+    if (id >= 0 && (uint32_t)id < blocks) tables[i] = __ldg(new_ids + id);
+  }
+}
+
+int sm_count() {
+  int device = 0, count = 0;
+  if (cudaGetDevice(&device) != cudaSuccess) return 0;
+  if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
+  return count;
+}
+
+bool aligned16(const void* pointer) { return (reinterpret_cast<uintptr_t>(pointer) & 15u) == 0; }
+
+int finish(cudaError_t launch_result) {
+  if (launch_result != cudaSuccess) {
+    cudaGetLastError();
+    return LOOM_CUDA_LAUNCH_ERROR;
+  }
+  return LOOM_CUDA_SUCCESS;
+}
+
+uint32_t grid_for(uint64_t units, int sms) {
+  const uint64_t resident = (uint64_t)sms * kCtasPerSm;
+  return (uint32_t)(units < resident ? units : resident);
+}
+
+}  // namespace
+
+extern "C" {
+
+int loom_cuda_kv_block_move(const void* source_key_cache, const void* source_value_cache,
+                            void* destination_key_cache, void* destination_value_cache,
+                            const int64_t* block_pairs, uint32_t pair_count, uint32_t source_blocks,
+                            uint32_t destination_blocks, uint64_t block_bytes, uint64_t source_key_block_stride,
+                            uint64_t source_value_block_stride, uint64_t destination_key_block_stride,
+                            uint64_t destination_value_block_stride, void* stream) {
+  if (pair_count == 0) return LOOM_CUDA_SUCCESS;
+  if (!source_key_cache || !source_value_cache || !destination_key_cache || !destination_value_cache ||
+      !block_pairs || source_blocks == 0 || destination_blocks == 0 || block_bytes == 0) {
+    return LOOM_CUDA_INVALID_ARGUMENT;
+  }
+  const uint64_t strides[4] = {source_key_block_stride, source_value_block_stride, destination_key_block_stride,
+                               destination_value_block_stride};
+  for (uint64_t stride : strides) {
+    if (stride < block_bytes) return LOOM_CUDA_INVALID_ARGUMENT;
+    if (stride % 16u) return LOOM_CUDA_UNSUPPORTED;
+  }
+  if (block_bytes % 16u || !aligned16(source_key_cache) || !aligned16(source_value_cache) ||
+      !aligned16(destination_key_cache) || !aligned16(destination_value_cache)) {
+    return LOOM_CUDA_UNSUPPORTED;
+  }
+  const uint64_t chunks = (block_bytes + kChunkBytes - 1) / kChunkBytes;
+  if (chunks > 0xffffffffull) return LOOM_CUDA_UNSUPPORTED;
+  const int sms = sm_count();
+  if (sms <= 0) return LOOM_CUDA_UNAVAILABLE;
+  MoveParams p{};
+  p.source[0] = static_cast<const uint8_t*>(source_key_cache);
+  p.source[1] = static_cast<const uint8_t*>(source_value_cache);
+  p.destination[0] = static_cast<uint8_t*>(destination_key_cache);
+  p.destination[1] = static_cast<uint8_t*>(destination_value_cache);
+  p.source_stride[0] = source_key_block_stride;
+  p.source_stride[1] = source_value_block_stride;
+  p.destination_stride[0] = destination_key_block_stride;
+  p.destination_stride[1] = destination_value_block_stride;
+  p.pairs = block_pairs;
+  p.block_bytes = block_bytes;
+  p.pair_count = pair_count;
+  p.source_blocks = source_blocks;
+  p.destination_blocks = destination_blocks;
+  p.chunks_per_block = (uint32_t)chunks;
+  const uint64_t units = (uint64_t)pair_count * 2u * chunks;
+  return finish(loom_launch::launch(kv_block_move_kernel, dim3(grid_for(units, sms)), dim3(kThreads), 0,
+                                    static_cast<cudaStream_t>(stream), p));
+}
+
+int loom_cuda_kv_block_swap(void* key_cache, void* value_cache, const int64_t* block_pairs, uint32_t pair_count,
+                            uint32_t num_blocks, uint64_t block_bytes, uint64_t key_block_stride,
+                            uint64_t value_block_stride, void* stream) {
+  if (pair_count == 0) return LOOM_CUDA_SUCCESS;
+  if (!key_cache || !value_cache || !block_pairs || num_blocks == 0 || block_bytes == 0 ||
+      key_block_stride < block_bytes || value_block_stride < block_bytes) {
+    return LOOM_CUDA_INVALID_ARGUMENT;
+  }
+  if (block_bytes % 16u || key_block_stride % 16u || value_block_stride % 16u || !aligned16(key_cache) ||
+      !aligned16(value_cache)) {
+    return LOOM_CUDA_UNSUPPORTED;
+  }
+  const uint64_t chunks = (block_bytes + kChunkBytes - 1) / kChunkBytes;
+  if (chunks > 0x7fffffffull) return LOOM_CUDA_UNSUPPORTED;
+  const int sms = sm_count();
+  if (sms <= 0) return LOOM_CUDA_UNAVAILABLE;
+  SwapParams p{};
+  p.cache[0] = static_cast<uint8_t*>(key_cache);
+  p.cache[1] = static_cast<uint8_t*>(value_cache);
+  p.stride[0] = key_block_stride;
+  p.stride[1] = value_block_stride;
+  p.pairs = block_pairs;
+  p.block_bytes = block_bytes;
+  p.pair_count = pair_count;
+  p.blocks = num_blocks;
+  p.chunks_per_block = (uint32_t)chunks;
+  const uint64_t units = (uint64_t)pair_count * 2u * chunks * 2u;
+  return finish(loom_launch::launch(kv_block_swap_kernel, dim3(grid_for(units, sms)), dim3(kThreads), 0,
+                                    static_cast<cudaStream_t>(stream), p));
+}
+
+int loom_cuda_block_table_remap(int32_t* block_tables, uint64_t entries, const int32_t* new_block_ids,
+                                uint32_t num_blocks, void* stream) {
+  if (entries == 0) return LOOM_CUDA_SUCCESS;
+  if (!block_tables || !new_block_ids || num_blocks == 0) return LOOM_CUDA_INVALID_ARGUMENT;
+  const int sms = sm_count();
+  if (sms <= 0) return LOOM_CUDA_UNAVAILABLE;
+  const uint64_t wanted = (entries + kThreads - 1) / kThreads;
+  const uint64_t resident = (uint64_t)sms * 8u;
+  return finish(loom_launch::launch(block_table_remap_kernel, dim3((uint32_t)(wanted < resident ? wanted : resident)),
+                                    dim3(kThreads), 0, static_cast<cudaStream_t>(stream), block_tables, entries,
+                                    new_block_ids, num_blocks));
+}
+
+}  // extern "C"

@@ -497,6 +497,108 @@ def rope_paged_kv_write_(
     return query, key, kv_cache
 
 
+# ---- KV block movement ---------------------------------------------------------------------
+
+def kv_block_movement_launches() -> int:
+    """Successful move, swap and table-remap launches since the library was loaded."""
+    count = _native.u64(0)
+    check(library().loom_cuda_bridge_kv_block_movement_launches(count), "KV block movement launch count")
+    return int(count.value)
+
+
+def _block_spans(kv_cache: torch.Tensor, name: str):
+    """(K pointer, V pointer, span bytes, block bytes, block stride bytes) of a packed cache.
+
+    The cache is ``[blocks, 2, ...]`` with each block's K part and V part dense
+    in memory (any order of the inner axes: NHD, HND).
+    """
+    if kv_cache.dim() < 3 or kv_cache.shape[1] != 2:
+        raise RuntimeError(f"Loom KV block movement expects a [blocks, 2, ...] cache; {name} is not")
+    if kv_cache.device.type != "cuda":
+        raise RuntimeError("Loom KV block movement tensors must live on a CUDA device")
+    inner = kv_cache[0, 0]
+    block_elements = inner.numel()
+    if _span(inner) != block_elements:
+        raise RuntimeError(f"the K and V parts of a block must be dense in memory; {name} has gaps inside a block")
+    size = kv_cache.element_size()
+    block_stride = kv_cache.stride(0) * size
+    span = ((kv_cache.shape[0] - 1) * kv_cache.stride(0) + block_elements) * size
+    key_pointer = kv_cache.data_ptr()
+    value_pointer = key_pointer + kv_cache.stride(1) * size
+    return key_pointer, value_pointer, span, block_elements * size, block_stride
+
+
+def _pairs_argument(block_pairs: torch.Tensor, device: torch.device) -> torch.Tensor:
+    if block_pairs.dtype != torch.int64 or block_pairs.dim() != 2 or block_pairs.shape[1] != 2:
+        raise RuntimeError("Loom KV block pairs must be an int64 [pairs, 2] tensor")
+    if block_pairs.device != device or not block_pairs.is_contiguous():
+        raise RuntimeError("Loom KV block pairs must be contiguous and live on the cache's device")
+    return block_pairs
+
+
+def kv_block_move_(destination: torch.Tensor, source: torch.Tensor, block_pairs: torch.Tensor) -> torch.Tensor:
+    """Copies whole KV blocks: ``destination[pairs[i, 1]] = source[pairs[i, 0]]``, K and V.
+
+    Both caches are packed ``[blocks, 2, ...]`` allocations with the same block
+    shape and dtype; they may be the same tensor (copy-on-write of a shared
+    block, compaction) or different ones (gather into a staging buffer,
+    scatter back). ``block_pairs`` is int64 ``[pairs, 2]`` on the device. No
+    block may be both read and written, nor written twice, in one call.
+    """
+    _require_inference_tensors(destination, source)
+    if destination.dtype != source.dtype or destination.device != source.device:
+        raise RuntimeError("Loom KV block move needs caches of one dtype on one device")
+    pairs = _pairs_argument(block_pairs, source.device)
+    source_key, source_value, source_span, block_bytes, source_stride = _block_spans(source, "source")
+    to_key, to_value, to_span, to_block_bytes, to_stride = _block_spans(destination, "destination")
+    if block_bytes != to_block_bytes:
+        raise RuntimeError("Loom KV block move needs source and destination blocks of one size")
+    with _on_device(source.device):
+        status = library().loom_cuda_bridge_kv_block_move(
+            source_key, source_span, source_value, source_span, to_key, to_span, to_value, to_span,
+            pairs.data_ptr(), pairs.numel(), source.shape[0], destination.shape[0], block_bytes,
+            source_stride, source_stride, to_stride, to_stride, _stream(source.device),
+        )
+    check(status, "KV block move")
+    return destination
+
+
+def kv_block_swap_(kv_cache: torch.Tensor, block_pairs: torch.Tensor) -> torch.Tensor:
+    """Exchanges the contents of blocks ``pairs[i, 0]`` and ``pairs[i, 1]``, K and V, in place.
+
+    A block may occur in one pair only.
+    """
+    _require_inference_tensors(kv_cache)
+    pairs = _pairs_argument(block_pairs, kv_cache.device)
+    key, value, span, block_bytes, stride = _block_spans(kv_cache, "kv_cache")
+    with _on_device(kv_cache.device):
+        status = library().loom_cuda_bridge_kv_block_swap(
+            key, span, value, span, pairs.data_ptr(), pairs.numel(), kv_cache.shape[0], block_bytes, stride,
+            stride, _stream(kv_cache.device),
+        )
+    check(status, "KV block swap")
+    return kv_cache
+
+
+def block_table_remap_(block_tables: torch.Tensor, new_block_ids: torch.Tensor) -> torch.Tensor:
+    """``block_tables[i] = new_block_ids[block_tables[i]]`` in place, for ids inside the cache.
+
+    Entries outside ``[0, len(new_block_ids))`` (negative sentinels) stay.
+    """
+    if block_tables.dtype != torch.int32 or new_block_ids.dtype != torch.int32:
+        raise RuntimeError("Loom block tables and new block ids must be int32")
+    if (block_tables.device.type != "cuda" or new_block_ids.device != block_tables.device
+            or not block_tables.is_contiguous() or not new_block_ids.is_contiguous() or new_block_ids.dim() != 1):
+        raise RuntimeError("Loom block table remap needs contiguous tensors on one CUDA device")
+    with _on_device(block_tables.device):
+        status = library().loom_cuda_bridge_block_table_remap(
+            block_tables.data_ptr(), block_tables.numel(), new_block_ids.data_ptr(), new_block_ids.numel(),
+            _stream(block_tables.device),
+        )
+    check(status, "block table remap")
+    return block_tables
+
+
 def default_scale(head_size: int) -> float:
     return 1.0 / math.sqrt(head_size)
 

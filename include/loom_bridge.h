@@ -176,6 +176,40 @@ int loom_cuda_bridge_merge_decode_states(
     uint64_t output_elements, void* stream);
 
 /*
+ * Checked KV block movement; see loom_cuda_kv_block_move, loom_cuda_kv_block_swap
+ * and loom_cuda_block_table_remap in loom_launch.h. Every cache pointer comes
+ * with the BYTE length of its addressable span; the bridge checks that the
+ * named number of blocks fits the span at the given stride, that blocks,
+ * strides and bases are multiples of 16 bytes, and that the id buffers do not
+ * overlap what is written. K and V spans of one packed allocation may
+ * interleave. The ids themselves are device memory and are not inspected.
+ */
+int loom_cuda_bridge_kv_block_move(
+    const void* source_key_cache, uint64_t source_key_bytes,
+    const void* source_value_cache, uint64_t source_value_bytes,
+    void* destination_key_cache, uint64_t destination_key_bytes,
+    void* destination_value_cache, uint64_t destination_value_bytes,
+    const int64_t* block_pairs, uint64_t pair_elements, uint32_t source_blocks,
+    uint32_t destination_blocks, uint64_t block_bytes,
+    uint64_t source_key_block_stride, uint64_t source_value_block_stride,
+    uint64_t destination_key_block_stride,
+    uint64_t destination_value_block_stride, void* stream);
+
+int loom_cuda_bridge_kv_block_swap(
+    void* key_cache, uint64_t key_bytes, void* value_cache,
+    uint64_t value_bytes, const int64_t* block_pairs, uint64_t pair_elements,
+    uint32_t num_blocks, uint64_t block_bytes, uint64_t key_block_stride,
+    uint64_t value_block_stride, void* stream);
+
+int loom_cuda_bridge_block_table_remap(
+    int32_t* block_tables, uint64_t table_elements,
+    const int32_t* new_block_ids, uint64_t id_elements, void* stream);
+
+/* Successful launches of the three calls above since the library was loaded
+ * (kept apart from the reference's operator ids, whose range stays 0..10). */
+int loom_cuda_bridge_kv_block_movement_launches(uint64_t* count);
+
+/*
  * Capability query in the style of the reference's Backend::supports
  * (crates/loom-kernels/src/backend.rs:28-42). Returns 1 and leaves the error
  * message untouched when the contract runs on this library, 0 with the reason

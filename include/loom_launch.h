@@ -296,6 +296,60 @@ int loom_cuda_decode_timeout_flag(uint32_t* value, uint32_t reset);
 int loom_cuda_paged_decode_attention_built_in_scratch(
     const LoomDecodeArgs* args, char* error_text, uint64_t error_capacity);
 
+/* ====================================================================== *
+ * Part 3: KV block movement
+ *
+ * The reference names these operators as the next ones around its paged
+ * cache (docs/operator-catalog.md:61: "KV block copy, swap, gather, scatter,
+ * compact, and remap"; docs/operator-catalog.md:140) and has no symbol for
+ * them yet. A block is what a block-table entry names: its K bytes are one
+ * contiguous span of `block_bytes` bytes, its V bytes another, in any layout
+ * (NHD, HND) and any element type. Sizes and strides of this part count
+ * BYTES, because the movement is blind to the element type; spans, strides and
+ * base pointers must be multiples of 16 bytes (LOOM_CUDA_UNSUPPORTED
+ * otherwise). Block ids are device memory and trusted like block tables: a
+ * pair that names a block outside its cache is skipped, nothing else is
+ * checked on the device. A count of zero succeeds without a launch.
+ * ====================================================================== */
+
+/*
+ * For every pair i: block block_pairs[2 i] of the source cache is copied over
+ * block block_pairs[2 i + 1] of the destination cache, K and V. Source and
+ * destination may be the same cache (copy-on-write of a shared prefix block,
+ * compaction) or different allocations (gather into a dense staging buffer,
+ * scatter back, migration between caches). No block may be both read and
+ * written, and no destination may occur twice, in one call.
+ */
+int loom_cuda_kv_block_move(
+    const void* source_key_cache, const void* source_value_cache,
+    void* destination_key_cache, void* destination_value_cache,
+    const int64_t* block_pairs, uint32_t pair_count, uint32_t source_blocks,
+    uint32_t destination_blocks, uint64_t block_bytes,
+    uint64_t source_key_block_stride, uint64_t source_value_block_stride,
+    uint64_t destination_key_block_stride,
+    uint64_t destination_value_block_stride, void* stream);
+
+/*
+ * For every pair i: blocks block_pairs[2 i] and block_pairs[2 i + 1] of one
+ * cache exchange their contents, K and V. A block may occur in one pair only;
+ * a pair of equal ids is left alone.
+ */
+int loom_cuda_kv_block_swap(void* key_cache, void* value_cache,
+                            const int64_t* block_pairs, uint32_t pair_count,
+                            uint32_t num_blocks, uint64_t block_bytes,
+                            uint64_t key_block_stride,
+                            uint64_t value_block_stride, void* stream);
+
+/*
+ * After blocks have moved: block_tables[i] = new_block_ids[block_tables[i]]
+ * for each of the `entries` table entries whose id lies in [0, num_blocks);
+ * other entries (negative sentinels in unused tails) are left alone.
+ * new_block_ids has num_blocks elements.
+ */
+int loom_cuda_block_table_remap(int32_t* block_tables, uint64_t entries,
+                                const int32_t* new_block_ids,
+                                uint32_t num_blocks, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
