@@ -11,9 +11,9 @@
 // contiguous span (block_size x kv_heads x dim elements in whatever order the
 // layout puts them: NHD and HND alike), and so are its V bytes. Movement is
 // therefore type- and layout-blind: spans of `block_bytes` bytes, found by a
-// block id and a byte stride between blocks. Work is cut into 16 KB chunks of
+// block id and a byte stride between blocks. Work is cut into 32 KB chunks of
 // a span; a grid sized to the SM count walks the chunks, each thread moving
-// four 16-byte vectors per chunk with all its loads issued before its stores.
+// eight 16-byte vectors per chunk with all its loads issued before its stores.
 // The kernels are bound by HBM: every byte is read once and written once.
 //
 // Block ids live on the device and are trusted engine state like block tables;
@@ -29,9 +29,9 @@
 namespace {
 
 constexpr int kThreads = 256;
-constexpr int kVectorsPerThread = 4;
-constexpr uint32_t kChunkBytes = kThreads * kVectorsPerThread * 16;  // 16 KB
-constexpr int kCtasPerSm = 8;
+constexpr int kVectorsPerThread = 8;
+constexpr uint32_t kChunkBytes = kThreads * kVectorsPerThread * 16;  // 32 KB
+constexpr int kCtasPerSm = 4;  // 64 registers per thread: eight vectors in flight and no spills
 
 struct MoveParams {
   const uint8_t* source[2];  // K, V
@@ -66,8 +66,10 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) kv_block_move_kernel(con
     const int64_t from = __ldg(p.pairs + 2 * pair);
     const int64_t to = __ldg(p.pairs + 2 * pair + 1);
     if (from < 0 || from >= (int64_t)p.source_blocks || to < 0 || to >= (int64_t)p.destination_blocks) continue;
-    const uint8_t* source = p.source[which] + (uint64_t)from * p.source_stride[which];
-    uint8_t* destination = p.destination[which] + (uint64_t)to * p.destination_stride[which];
+    // (selected, not indexed: indexing the parameter arrays by a run-time value copies them to local memory)
+    const uint8_t* source = (which ? p.source[1] : p.source[0]) + (uint64_t)from * (which ? p.source_stride[1] : p.source_stride[0]);
+    uint8_t* destination = (which ? p.destination[1] : p.destination[0]) +
+                           (uint64_t)to * (which ? p.destination_stride[1] : p.destination_stride[0]);
     const uint64_t base = (uint64_t)chunk * kChunkBytes + threadIdx.x * 16u;
     uint4 held[kVectorsPerThread];
 #pragma unroll
@@ -97,7 +99,7 @@ struct SwapParams {
 __global__ void __launch_bounds__(kThreads, kCtasPerSm) kv_block_swap_kernel(const SwapParams p) {
   loom_launch::grid_dependency_wait();
   constexpr int kHalf = kVectorsPerThread / 2;  // two blocks are held at once
-  const uint32_t chunks = p.chunks_per_block * 2u;  // chunks of 8 KB here
+  const uint32_t chunks = p.chunks_per_block * 2u;  // chunks of 16 KB here
   const uint64_t units = (uint64_t)p.pair_count * 2u * chunks;
   for (uint64_t unit = blockIdx.x; unit < units; unit += gridDim.x) {
     const uint32_t chunk = (uint32_t)(unit % chunks);
@@ -107,8 +109,10 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) kv_block_swap_kernel(con
     const int64_t left = __ldg(p.pairs + 2 * pair);
     const int64_t right = __ldg(p.pairs + 2 * pair + 1);
     if (left < 0 || left >= (int64_t)p.blocks || right < 0 || right >= (int64_t)p.blocks || left == right) continue;
-    uint8_t* first = p.cache[which] + (uint64_t)left * p.stride[which];
-    uint8_t* second = p.cache[which] + (uint64_t)right * p.stride[which];
+    uint8_t* base_pointer = which ? p.cache[1] : p.cache[0];
+    const uint64_t stride = which ? p.stride[1] : p.stride[0];
+    uint8_t* first = base_pointer + (uint64_t)left * stride;
+    uint8_t* second = base_pointer + (uint64_t)right * stride;
     const uint64_t base = (uint64_t)chunk * (kChunkBytes / 2) + threadIdx.x * 16u;
     uint4 a[kHalf], b[kHalf];
 #pragma unroll
