@@ -94,6 +94,8 @@ def _declare(lib):
     lib.loom_cuda_kv_block_move.argtypes = [ptr] * 5 + [u32] * 3 + [u64] * 5 + [ptr]
     lib.loom_cuda_kv_block_swap.argtypes = [ptr] * 3 + [u32, u32] + [u64] * 3 + [ptr]
     lib.loom_cuda_block_table_remap.argtypes = [ptr, u64, ptr, u32, ptr]
+    lib.loom_cuda_set_kv_block_move_engine.argtypes = [u32]
+    lib.loom_cuda_kv_block_move_timeout_flag.argtypes = [ctypes.POINTER(u32), u32]
     # partitioner
     i64p, u32p, u64p = ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(u32), ctypes.POINTER(u64)
     lib.loom_partition_by_sequence.argtypes = [i64p, u32, u32, u32p, u64p]

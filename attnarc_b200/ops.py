@@ -506,6 +506,25 @@ def kv_block_movement_launches() -> int:
     return int(count.value)
 
 
+_BLOCK_MOVE_ENGINES = {"bulk": 0, "vector": 1}
+
+
+def set_kv_block_move_engine(engine: str) -> None:
+    """``"bulk"`` (default): cp.async.bulk through shared memory; ``"vector"``: 16-byte loads and stores."""
+    if library().loom_cuda_set_kv_block_move_engine(_BLOCK_MOVE_ENGINES[engine]) != 0:
+        raise RuntimeError(f"unknown KV block move engine {engine!r}")
+
+
+def kv_block_move_timeout_flag(device=None, reset: bool = False) -> int:
+    """Non-zero after a bounded wait of the bulk-copy move kernel expired on this device."""
+    value = _native.u32(0)
+    with _on_device(torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)):
+        status = library().loom_cuda_kv_block_move_timeout_flag(value, 1 if reset else 0)
+    if status != 0:
+        raise RuntimeError("reading the KV block move timeout flag failed")
+    return int(value.value)
+
+
 def _block_spans(kv_cache: torch.Tensor, name: str):
     """(K pointer, V pointer, span bytes, block bytes, block stride bytes) of a packed cache.
 

@@ -41,7 +41,7 @@ FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode partition-kernel
 # launch, from the ncu captures summarised under profiles/ (bytes per launch for
 # the default workload); None until a capture exists for the workload.
-NCU_DRAM_TRAFFIC_BYTES = {"cfg2": 154_178_048 + 3_579_648, "kv-move": 537_010_176 + 490_875_392}
+NCU_DRAM_TRAFFIC_BYTES = {"cfg2": 154_178_048 + 3_579_648, "kv-move": 537_019_136 + 486_040_832}
 
 
 def reference_kernels_baseline(case, config, cache_views, steps):
@@ -653,7 +653,7 @@ def run_kv_move(args):
         "gpu_launches": args.steps,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,
                      "peak_source": f"{source} copy bandwidth (also bytes read plus written)",
-                     "kernel": "kv_block_move_kernel", "us_per_launch": ms / args.steps * 1e3,
+                     "kernel": "kv_block_move_bulk_kernel", "us_per_launch": ms / args.steps * 1e3,
                      "algorithmic_bytes_per_launch": moved, "traffic": NCU_DRAM_TRAFFIC_BYTES.get("kv-move")},
         "clocks": sampler.summary(),
     }

@@ -330,6 +330,22 @@ int loom_cuda_kv_block_move(
     uint64_t destination_value_block_stride, void* stream);
 
 /*
+ * How loom_cuda_kv_block_move moves bytes: 0 (default) stages 16 KB chunks
+ * through shared memory with the bulk-copy engine (cp.async.bulk in, then out,
+ * no register round trip), 1 uses 16-byte vector loads and stores. Process-
+ * wide; results are identical.
+ */
+int loom_cuda_set_kv_block_move_engine(uint32_t engine);
+
+/*
+ * The bulk-copy kernel bounds every wait on a copy; if one ever expired, a
+ * flag on the current device is set and the affected launch left some
+ * destinations unwritten. *value receives the flag; reset != 0 clears it.
+ * Synchronous (a small device-to-host copy); never needed on a healthy device.
+ */
+int loom_cuda_kv_block_move_timeout_flag(uint32_t* value, uint32_t reset);
+
+/*
  * For every pair i: blocks block_pairs[2 i] and block_pairs[2 i + 1] of one
  * cache exchange their contents, K and V. A block may occur in one pair only;
  * a pair of equal ids is left alone.

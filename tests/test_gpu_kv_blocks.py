@@ -34,10 +34,21 @@ def block_bytes_of(allocation):
     return allocation.contiguous().view(torch.uint8).reshape(allocation.shape[0], 2, -1).cpu().numpy()
 
 
+@pytest.fixture(params=["bulk", "vector"])
+def engine(request):
+    """Both ways the move kernel moves bytes; the default is restored afterwards."""
+    from attnarc_b200 import ops
+
+    ops.set_kv_block_move_engine(request.param)
+    yield request.param
+    ops.set_kv_block_move_engine("bulk")
+    assert ops.kv_block_move_timeout_flag() == 0
+
+
 @pytest.mark.parametrize("layout", ["NHD", "HND"])
 @pytest.mark.parametrize("dtype", ["bf16", "f32", "fp8"])
 @pytest.mark.parametrize("same_cache", [True, False])
-def test_move_matches_the_oracle(layout, dtype, same_cache):
+def test_move_matches_the_oracle(layout, dtype, same_cache, engine):
     from attnarc_b200 import ops
 
     rng = np.random.default_rng(sum(map(ord, layout + dtype)) + int(same_cache))
@@ -60,8 +71,8 @@ def test_move_matches_the_oracle(layout, dtype, same_cache):
     assert ops.kv_block_movement_launches() == before + 1
 
 
-@pytest.mark.parametrize("block_size,heads,dim", [(16, 8, 128), (32, 1, 64), (16, 5, 80), (1, 1, 16)])
-def test_move_covers_block_sizes_around_the_chunk_size(block_size, heads, dim):
+@pytest.mark.parametrize("block_size,heads,dim", [(16, 8, 128), (32, 1, 64), (16, 5, 80), (1, 1, 16), (16, 9, 120)])
+def test_move_covers_block_sizes_around_the_chunk_size(block_size, heads, dim, engine):
     from attnarc_b200 import ops
 
     rng = np.random.default_rng(block_size * 1000 + heads * 10 + dim)
@@ -156,7 +167,7 @@ def test_decode_is_unchanged_by_a_compaction_of_its_cache():
     assert helpers.same_bits(before, after)
 
 
-def test_gather_then_scatter_restores_a_gigabyte_cache():
+def test_gather_then_scatter_restores_a_gigabyte_cache(engine):
     from attnarc_b200 import ops
 
     blocks, block_size, heads, dim = 2048, 16, 8, 128   # 2048 x 2 x 32 KB x 2 B = 0.27 GB per cache
