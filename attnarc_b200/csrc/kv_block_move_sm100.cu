@@ -12,12 +12,12 @@
 // layout puts them: NHD and HND alike), and so are its V bytes. Movement is
 // therefore type- and layout-blind: spans of `block_bytes` bytes, found by a
 // block id and a byte stride between blocks. The kernels are bound by HBM: every
-// byte is read once and written once. The move has two engines: by default 8 KB
-// chunks go through shared memory on the bulk-copy engine (cp.async.bulk in and
-// out, one issuing thread per CTA, 0.97-1.0 of the device's copy bandwidth);
-// the other engine, and the swap, walk 32 KB chunks with a grid sized to the SM
-// count, each thread moving eight 16-byte vectors per chunk with all its loads
-// issued before its stores (0.88-0.90).
+// byte is read once and written once. Move and swap have two engines: by default
+// 8 KB chunks go through shared memory on the bulk-copy engine (cp.async.bulk in
+// and out, one issuing thread per CTA: the move at 0.97-1.0 of the device's copy
+// bandwidth, the swap at 0.92-0.93); the other engine walks 32 KB chunks with a
+// grid sized to the SM count, each thread moving eight 16-byte vectors per chunk
+// with all its loads issued before its stores (0.88-0.90).
 //
 // Block ids live on the device and are trusted engine state like block tables;
 // the kernels only skip a pair that names a block outside its cache.
@@ -269,6 +269,95 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) kv_block_swap_kernel(con
   }
 }
 
+// The swap on the bulk-copy engine: the ring's slots work in twins. Both blocks'
+// chunks are loaded into a twin (one mbarrier counts the bytes of both loads),
+// then stored crosswise, so neither store can overtake the load of what it
+// overwrites. Refill rule, bounds on the waits and drain as in the move kernel.
+__global__ void __launch_bounds__(32, kBulkCtasPerSm) kv_block_swap_bulk_kernel(const SwapParams p) {
+  constexpr int kTwins = kBulkStages / 2;
+  constexpr int kTwinLag = 1;                  // stores still reading when the next twin is loaded
+  constexpr int kAhead = kTwins - kTwinLag;
+  static_assert(kBulkStages % 2 == 0 && kAhead >= 1, "the swap needs at least two twins of slots");
+  extern __shared__ __align__(128) uint8_t ring[];
+  uint64_t* barriers = reinterpret_cast<uint64_t*>(ring + kBulkStages * kBulkBytes);  // one per twin
+  // per twin: address of the first block's chunk, of the second block's chunk, byte count (0 = skip)
+  uint64_t* targets = reinterpret_cast<uint64_t*>(ring + kBulkStages * kBulkBytes + kBulkStages * 8);
+  if (threadIdx.x != 0) return;
+  for (int twin = 0; twin < kTwins; ++twin) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(shared_address(barriers + twin)) : "memory");
+  }
+  asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  loom_launch::grid_dependency_wait();
+
+  const uint64_t units = (uint64_t)p.pair_count * 2u * p.chunks_per_block;
+  if (blockIdx.x >= units) return;
+  const uint64_t mine = (units - blockIdx.x + gridDim.x - 1) / gridDim.x;
+  uint32_t phases = 0, pending = 0;
+
+  auto issue_loads = [&](uint64_t k) {
+    const uint32_t twin = (uint32_t)(k % kTwins);
+    const uint64_t unit = blockIdx.x + k * gridDim.x;
+    const uint32_t chunk = (uint32_t)(unit % p.chunks_per_block);
+    const uint64_t rest = unit / p.chunks_per_block;
+    const uint32_t which = (uint32_t)(rest & 1u);
+    const uint64_t pair = rest >> 1;
+    const int64_t left = __ldg(p.pairs + 2 * pair);
+    const int64_t right = __ldg(p.pairs + 2 * pair + 1);
+    targets[3 * twin + 2] = 0;
+    if (left < 0 || left >= (int64_t)p.blocks || right < 0 || right >= (int64_t)p.blocks || left == right) return;
+    const uint64_t offset = (uint64_t)chunk * kBulkBytes;
+    const uint64_t remaining = p.block_bytes - offset;
+    const uint32_t bytes = (uint32_t)(remaining < kBulkBytes ? remaining : kBulkBytes);
+    uint8_t* base_pointer = which ? p.cache[1] : p.cache[0];
+    const uint64_t stride = which ? p.stride[1] : p.stride[0];
+    uint8_t* first = base_pointer + (uint64_t)left * stride + offset;
+    uint8_t* second = base_pointer + (uint64_t)right * stride + offset;
+    targets[3 * twin] = reinterpret_cast<uint64_t>(first);
+    targets[3 * twin + 1] = reinterpret_cast<uint64_t>(second);
+    targets[3 * twin + 2] = bytes;
+    pending |= 1u << twin;
+    const uint32_t barrier = shared_address(barriers + twin);
+    const uint32_t slot = shared_address(ring + (2 * twin) * kBulkBytes);
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(barrier), "r"(2u * bytes)
+                 : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(slot),
+                 "l"(first), "r"(bytes), "r"(barrier)
+                 : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
+                     slot + kBulkBytes),
+                 "l"(second), "r"(bytes), "r"(barrier)
+                 : "memory");
+  };
+
+  const uint64_t ahead = mine < (uint64_t)kAhead ? mine : (uint64_t)kAhead;
+  for (uint64_t k = 0; k < ahead; ++k) issue_loads(k);
+  for (uint64_t k = 0; k < mine; ++k) {
+    const uint32_t twin = (uint32_t)(k % kTwins);
+    const uint32_t bytes = (uint32_t)targets[3 * twin + 2];
+    if (bytes != 0) {
+      if (!bulk_wait(shared_address(barriers + twin), (phases >> twin) & 1u)) break;
+      phases ^= 1u << twin;
+      pending &= ~(1u << twin);
+      const uint32_t slot = shared_address(ring + (2 * twin) * kBulkBytes);
+      asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;\n" ::"l"(targets[3 * twin + 1]),
+                   "r"(slot), "r"(bytes)
+                   : "memory");  // the first block's bytes go to the second block
+      asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;\n" ::"l"(targets[3 * twin]),
+                   "r"(slot + kBulkBytes), "r"(bytes)
+                   : "memory");
+    }
+    asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+    if (k + kAhead < mine) {
+      asm volatile("cp.async.bulk.wait_group.read %0;\n" ::"n"(kTwinLag) : "memory");
+      issue_loads(k + kAhead);
+    }
+  }
+  for (uint32_t twin = 0; twin < (uint32_t)kTwins; ++twin) {
+    if (pending & (1u << twin)) bulk_wait(shared_address(barriers + twin), (phases >> twin) & 1u);
+  }
+  asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory");
+}
+
 // block_tables[i] <- new_ids[block_tables[i]] for ids inside the cache; other
 // entries (negative sentinels of unused tail entries) stay as they are.
 __global__ void __launch_bounds__(kThreads) block_table_remap_kernel(int32_t* tables, uint64_t entries,
@@ -282,6 +371,21 @@ __global__ void __launch_bounds__(kThreads) block_table_remap_kernel(int32_t* ta
 
 // 0: bulk-copy engine through shared memory; 1: vector loads and stores through registers.
 std::atomic<uint32_t> g_move_engine{0};
+
+// Raises a bulk kernel's dynamic shared-memory limit once per device (bit d of `prepared`).
+template <typename Kernel>
+bool raise_shared_limit(Kernel kernel, std::atomic<uint64_t>& prepared) {
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess) return false;
+  if (device < 64 && (prepared.load(std::memory_order_acquire) & (1ull << device))) return true;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kBulkSharedBytes) !=
+      cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  if (device < 64) prepared.fetch_or(1ull << device, std::memory_order_release);
+  return true;
+}
 
 int sm_count() {
   int device = 0, count = 0;
@@ -357,17 +461,8 @@ int loom_cuda_kv_block_move(const void* source_key_cache, const void* source_val
   const uint64_t bulk_chunks = (block_bytes + kBulkBytes - 1) / kBulkBytes;
   if (bulk_chunks > 0xffffffffull) return LOOM_CUDA_UNSUPPORTED;
   p.chunks_per_block = (uint32_t)bulk_chunks;
-  static std::atomic<uint64_t> prepared{0};  // bit d: device d has the kernel's shared-memory limit raised
-  int device = 0;
-  if (cudaGetDevice(&device) != cudaSuccess) return LOOM_CUDA_UNAVAILABLE;
-  if (device >= 64 || !(prepared.load(std::memory_order_acquire) & (1ull << device))) {
-    if (cudaFuncSetAttribute(kv_block_move_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)kBulkSharedBytes) != cudaSuccess) {
-      cudaGetLastError();
-      return LOOM_CUDA_LAUNCH_ERROR;
-    }
-    if (device < 64) prepared.fetch_or(1ull << device, std::memory_order_release);
-  }
+  static std::atomic<uint64_t> prepared{0};
+  if (!raise_shared_limit(kv_block_move_bulk_kernel, prepared)) return LOOM_CUDA_LAUNCH_ERROR;
   const uint64_t units = (uint64_t)pair_count * 2u * bulk_chunks;
   const uint64_t resident = (uint64_t)sms * kBulkCtasPerSm;
   return finish(loom_launch::launch(kv_block_move_bulk_kernel, dim3((uint32_t)(units < resident ? units : resident)),
@@ -424,9 +519,20 @@ int loom_cuda_kv_block_swap(void* key_cache, void* value_cache, const int64_t* b
   p.pair_count = pair_count;
   p.blocks = num_blocks;
   p.chunks_per_block = (uint32_t)chunks;
-  const uint64_t units = (uint64_t)pair_count * 2u * chunks * 2u;
-  return finish(loom_launch::launch(kv_block_swap_kernel, dim3(grid_for(units, sms)), dim3(kThreads), 0,
-                                    static_cast<cudaStream_t>(stream), p));
+  if (g_move_engine.load(std::memory_order_relaxed) == 1) {
+    const uint64_t units = (uint64_t)pair_count * 2u * chunks * 2u;
+    return finish(loom_launch::launch(kv_block_swap_kernel, dim3(grid_for(units, sms)), dim3(kThreads), 0,
+                                      static_cast<cudaStream_t>(stream), p));
+  }
+  const uint64_t bulk_chunks = (block_bytes + kBulkBytes - 1) / kBulkBytes;
+  if (bulk_chunks > 0xffffffffull) return LOOM_CUDA_UNSUPPORTED;
+  p.chunks_per_block = (uint32_t)bulk_chunks;
+  static std::atomic<uint64_t> prepared{0};
+  if (!raise_shared_limit(kv_block_swap_bulk_kernel, prepared)) return LOOM_CUDA_LAUNCH_ERROR;
+  const uint64_t units = (uint64_t)pair_count * 2u * bulk_chunks;
+  const uint64_t resident = (uint64_t)sms * kBulkCtasPerSm;
+  return finish(loom_launch::launch(kv_block_swap_bulk_kernel, dim3((uint32_t)(units < resident ? units : resident)),
+                                    dim3(32), kBulkSharedBytes, static_cast<cudaStream_t>(stream), p));
 }
 
 int loom_cuda_block_table_remap(int32_t* block_tables, uint64_t entries, const int32_t* new_block_ids,

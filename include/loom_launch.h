@@ -330,8 +330,8 @@ int loom_cuda_kv_block_move(
     uint64_t destination_value_block_stride, void* stream);
 
 /*
- * How loom_cuda_kv_block_move moves bytes: 0 (default) stages 16 KB chunks
- * through shared memory with the bulk-copy engine (cp.async.bulk in, then out,
+ * How loom_cuda_kv_block_move and loom_cuda_kv_block_swap move bytes: 0
+ * (default) stages 8 KB chunks through shared memory with the bulk-copy engine (cp.async.bulk in, then out,
  * no register round trip), 1 uses 16-byte vector loads and stores. Process-
  * wide; results are identical.
  */

@@ -86,7 +86,7 @@ def test_move_covers_block_sizes_around_the_chunk_size(block_size, heads, dim, e
 
 
 @pytest.mark.parametrize("layout", ["NHD", "HND"])
-def test_swap_matches_the_oracle_and_undoes_itself(layout):
+def test_swap_matches_the_oracle_and_undoes_itself(layout, engine):
     from attnarc_b200 import ops
 
     rng = np.random.default_rng(7)
