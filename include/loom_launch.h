@@ -331,9 +331,9 @@ int loom_cuda_kv_block_move(
 
 /*
  * How loom_cuda_kv_block_move and loom_cuda_kv_block_swap move bytes: 0
- * (default) stages 8 KB chunks through shared memory with the bulk-copy engine (cp.async.bulk in, then out,
- * no register round trip), 1 uses 16-byte vector loads and stores. Process-
- * wide; results are identical.
+ * (default) stages 8 KB chunks through shared memory with the bulk-copy
+ * engine (cp.async.bulk in, then out, no register round trip), 1 uses 16-byte
+ * vector loads and stores. Process-wide; results are identical.
  */
 int loom_cuda_set_kv_block_move_engine(uint32_t engine);
 
