@@ -119,6 +119,15 @@ def parse_args():
     return parser.parse_args()
 
 
+def host_threads() -> int:
+    """Host cores this process may use. Not OMP_NUM_THREADS: torchrun sets that to 1
+    for every rank, which would make the CPU arm single-threaded at N > 1."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def measured_peak_gbs():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     try:
@@ -298,7 +307,7 @@ def run_reference(args):
     if args.batch:
         config = workloads.scaled(config, batch=args.batch, name=f"{config.name}-batch{args.batch}")
     case = workloads.build_case(config, "cpu", seed=args.seed)
-    threads = ob.max_threads()
+    threads = host_threads()
     steps_total = max(1, args.steps + args.warmup)
     budget = max(0.02, min(args.cpu_seconds, 150.0 / steps_total))
     probe_elapsed, probe_bytes = oracle_step_seconds(case, min(2, config.batch), threads)
@@ -551,7 +560,7 @@ def run_b200(args):
         if world == 1 and not args.no_cpu_baseline:
             from oracle import binding as ob
 
-            line["cpu_baseline"] = cpu_baseline(case, args.cpu_seconds, ob.max_threads())
+            line["cpu_baseline"] = cpu_baseline(case, args.cpu_seconds, host_threads())
         if world == 1 and case.max_sequence_length <= 1024 and config.layout == "NHD" and not fp8:
             reference_gpu = reference_kernels_baseline(case, config, views[0], args.steps)
             if reference_gpu is not None:
