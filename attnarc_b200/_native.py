@@ -86,6 +86,7 @@ def _declare(lib):
     lib.loom_cuda_paged_decode_workspace_elements.restype = u64
     lib.loom_cuda_paged_decode_workspace_elements.argtypes = [u32] * 6
     lib.loom_cuda_merge_decode_states.argtypes = [ptr, u32, u32, u32, u32, ptr, ptr]
+    lib.loom_cuda_expand_query_tokens.argtypes = [ptr, ptr, ptr, ptr, u32, u32, u32, ptr]
     # KV block movement
     lib.loom_cuda_bridge_kv_block_move.argtypes = [ptr, u64] * 5 + [u32, u32] + [u64] * 5 + [ptr]
     lib.loom_cuda_bridge_kv_block_swap.argtypes = [ptr, u64] * 3 + [u32] + [u64] * 3 + [ptr]

@@ -24,6 +24,7 @@ SOURCES = [
     "rope_paged_kv_sm100.cu",
     "paged_decode_sm100.cu",
     "kv_block_move_sm100.cu",
+    "multi_token_sm100.cu",
     "dispatch.cpp",
     "bridge.cpp",
     "partition.cpp",

@@ -497,6 +497,66 @@ def rope_paged_kv_write_(
     return query, key, kv_cache
 
 
+# ---- multi-token queries -------------------------------------------------------------------
+
+def paged_multi_token_decode_attention(
+    query: torch.Tensor,
+    key_cache: torch.Tensor,
+    value_cache: torch.Tensor,
+    block_tables: torch.Tensor,
+    sequence_lengths: torch.Tensor,
+    *,
+    max_sequence_length: int,
+    scale: float | None = None,
+    key_scales: torch.Tensor | None = None,
+    value_scales: torch.Tensor | None = None,
+    scratch: tuple[torch.Tensor, torch.Tensor] | None = None,
+) -> torch.Tensor:
+    """Causal attention of ``Tq`` new tokens per sequence over a paged cache.
+
+    ``query`` is ``[B, Tq, Hq, D]`` (contiguous); ``sequence_lengths`` counts
+    each context INCLUDING its ``Tq`` new tokens, whose K/V are already in the
+    cache. Token ``t`` attends to the first ``length - (Tq - 1 - t)`` tokens.
+    Returns ``[B, Tq, Hq, Dv]``. Caches, scales and tables as in
+    ``paged_decode_attention_ex``. ``scratch`` may carry reusable int32 tensors
+    ``([B * Tq, max_blocks], [B * Tq])`` for the expanded metadata.
+
+    This is the single-token decode run on ``B * Tq`` rows: correct for any
+    ``Tq``, but a sequence's pages are streamed once per query token.
+    """
+    if query.dim() != 4 or not query.is_contiguous():
+        raise RuntimeError("Loom multi-token decode expects a contiguous query [B, Tq, Hq, D]")
+    if block_tables.dtype != torch.int32 or sequence_lengths.dtype != torch.int32:
+        raise RuntimeError("Loom paged decode metadata must be int32")
+    if (block_tables.dim() != 2 or sequence_lengths.dim() != 1 or not block_tables.is_contiguous()
+            or not sequence_lengths.is_contiguous() or block_tables.shape[0] != query.shape[0]
+            or sequence_lengths.shape[0] != query.shape[0]):
+        raise RuntimeError("Loom multi-token decode expects block_tables [B, max_blocks] and lengths [B]")
+    if query.device.type != "cuda" or block_tables.device != query.device or sequence_lengths.device != query.device:
+        raise RuntimeError("Loom paged decode tensors must share one CUDA device")
+    sequences, query_tokens, query_heads, head_size = query.shape
+    rows, max_blocks = sequences * query_tokens, block_tables.shape[1]
+    if scratch is None:
+        scratch = (torch.empty((rows, max_blocks), dtype=torch.int32, device=query.device),
+                   torch.empty((rows,), dtype=torch.int32, device=query.device))
+    tables, lengths = scratch
+    if (tuple(tables.shape) != (rows, max_blocks) or tuple(lengths.shape) != (rows,) or tables.dtype != torch.int32
+            or lengths.dtype != torch.int32 or not tables.is_contiguous() or not lengths.is_contiguous()
+            or tables.device != query.device or lengths.device != query.device):
+        raise RuntimeError("Loom multi-token decode scratch must be int32 [B*Tq, max_blocks] and [B*Tq] on the device")
+    with _on_device(query.device):
+        status = library().loom_cuda_expand_query_tokens(
+            block_tables.data_ptr(), sequence_lengths.data_ptr(), tables.data_ptr(), lengths.data_ptr(),
+            sequences, query_tokens, max_blocks, _stream(query.device))
+    if status != 0:
+        raise RuntimeError("Loom multi-token metadata expansion failed: "
+                           + library().loom_cuda_status_string(status).decode())
+    scales = dict(key_scales=key_scales, value_scales=value_scales) if key_cache.dtype == torch.uint8 else {}
+    output = paged_decode_attention_ex(query.view(rows, query_heads, head_size), key_cache, value_cache, tables,
+                                       lengths, max_sequence_length=max_sequence_length, scale=scale, **scales)
+    return output.view(sequences, query_tokens, query_heads, output.shape[-1])
+
+
 # ---- KV block movement ---------------------------------------------------------------------
 
 def kv_block_movement_launches() -> int:

@@ -296,6 +296,27 @@ int loom_cuda_decode_timeout_flag(uint32_t* value, uint32_t reset);
 int loom_cuda_paged_decode_attention_built_in_scratch(
     const LoomDecodeArgs* args, char* error_text, uint64_t error_capacity);
 
+/*
+ * Multi-token queries (speculative verification, short chunked prefill) over
+ * the single-token decode: the reference names them as a later contract field
+ * (docs/design/paged-decode-attention.md:42-52). Writes the metadata of the
+ * expanded problem: row s * query_tokens + t of expanded_block_tables
+ * [sequences * query_tokens, max_blocks_per_sequence] is sequence s's table
+ * row, and expanded_sequence_lengths[s * query_tokens + t] =
+ * max(0, sequence_lengths[s] - (query_tokens - 1 - t)), where sequence_lengths
+ * counts the context INCLUDING the query_tokens new tokens (already written to
+ * the cache). A decode call on query rows [sequences * query_tokens, heads,
+ * dim] with this metadata is causal attention of every new token; a length of
+ * 0 yields a zero row.
+ */
+int loom_cuda_expand_query_tokens(const int32_t* block_tables,
+                                  const int32_t* sequence_lengths,
+                                  int32_t* expanded_block_tables,
+                                  int32_t* expanded_sequence_lengths,
+                                  uint32_t sequences, uint32_t query_tokens,
+                                  uint32_t max_blocks_per_sequence,
+                                  void* stream);
+
 /* ====================================================================== *
  * Part 3: KV block movement
  *
