@@ -21,6 +21,24 @@ u32, u64, f32 = ctypes.c_uint32, ctypes.c_uint64, ctypes.c_float
 ptr = ctypes.c_void_p
 
 
+class LoomDecodeArgs(ctypes.Structure):
+    """ctypes mirror of ``LoomDecodeArgs`` (include/loom_launch.h)."""
+
+    _fields_ = (
+        [(name, u32) for name in ("struct_size", "dtype", "cache_encoding", "scale_stride")]
+        + [(name, ptr) for name in ("query", "key_cache", "value_cache", "key_scales", "value_scales",
+                                    "block_tables", "sequence_lengths", "output", "workspace")]
+        + [("workspace_elements", u64)]
+        + [(name, u32) for name in ("sequences", "query_heads", "kv_heads", "head_size", "value_head_size",
+                                    "num_blocks", "block_size", "max_blocks_per_sequence", "max_sequence_length",
+                                    "partition_tokens")]
+        + [(name, u64) for name in ("key_block_stride", "key_page_stride", "key_head_stride", "value_block_stride",
+                                    "value_page_stride", "value_head_stride", "query_token_stride",
+                                    "query_head_stride")]
+        + [("scale", f32), ("emit_state", u32), ("stream", ptr)]
+    )
+
+
 class NativeLibraryMissing(ImportError):
     pass
 
@@ -87,6 +105,8 @@ def _declare(lib):
     lib.loom_cuda_paged_decode_workspace_elements.argtypes = [u32] * 6
     lib.loom_cuda_merge_decode_states.argtypes = [ptr, u32, u32, u32, u32, ptr, ptr]
     lib.loom_cuda_expand_query_tokens.argtypes = [ptr, ptr, ptr, ptr, u32, u32, u32, ptr]
+    lib.loom_cuda_multi_token_prepare.argtypes = [ptr, ptr, ptr, ptr] + [u32] * 6 + [ptr]
+    lib.loom_cuda_multi_token_finish.argtypes = [ctypes.POINTER(LoomDecodeArgs), u32, ptr]
     # KV block movement
     lib.loom_cuda_bridge_kv_block_move.argtypes = [ptr, u64] * 5 + [u32, u32] + [u64] * 5 + [ptr]
     lib.loom_cuda_bridge_kv_block_swap.argtypes = [ptr, u64] * 3 + [u32] + [u64] * 3 + [ptr]

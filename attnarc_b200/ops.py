@@ -11,6 +11,7 @@ only; all work happens in ``libloom_cuda_bridge.so``.
 
 from __future__ import annotations
 
+import ctypes
 import enum
 import functools
 import math
@@ -499,6 +500,52 @@ def rope_paged_kv_write_(
 
 # ---- multi-token queries -------------------------------------------------------------------
 
+def _multi_token_one_pass(query, key_cache, value_cache, block_tables, sequence_lengths, max_sequence_length,
+                          scale, key_scales, value_scales):
+    sequences, query_tokens, query_heads, head_size = query.shape
+    kv_heads, value_head_size = key_cache.shape[2], value_cache.shape[3]
+    fp8 = key_cache.dtype == torch.uint8
+    device = query.device
+    packed = torch.empty((sequences, query_tokens * query_heads, head_size), dtype=query.dtype, device=device)
+    prefix_lengths = torch.empty((sequences,), dtype=torch.int32, device=device)
+    lib = library()
+    with _on_device(device):
+        status = lib.loom_cuda_multi_token_prepare(
+            query.data_ptr(), packed.data_ptr(), sequence_lengths.data_ptr(), prefix_lengths.data_ptr(),
+            _DTYPE_CODES[query.dtype], sequences, query_tokens, query_heads, kv_heads, head_size, _stream(device))
+        if status != 0:
+            raise RuntimeError("Loom multi-token prepare failed: " + lib.loom_cuda_status_string(status).decode())
+        scales = dict(key_scales=key_scales, value_scales=value_scales) if fp8 else {}
+        # the rows of a (sequence, KV head) pair as one group of Tq x group heads, over the common prefix
+        states = paged_decode_attention_ex(packed, key_cache, value_cache, block_tables, prefix_lengths,
+                                           max_sequence_length=max_sequence_length, scale=scale, emit_state=True,
+                                           **scales)
+        output = torch.empty((sequences, query_tokens, query_heads, value_head_size), dtype=query.dtype,
+                             device=device)
+        args = _native.LoomDecodeArgs()
+        args.struct_size = ctypes.sizeof(_native.LoomDecodeArgs)
+        args.dtype = _DTYPE_CODES[query.dtype]
+        args.cache_encoding = _native.KV_CACHE_FP8_E4M3 if fp8 else _native.KV_CACHE_NATIVE
+        args.scale_stride = 0 if not fp8 or key_scales.numel() == 1 else 1
+        args.query, args.key_cache, args.value_cache = query.data_ptr(), key_cache.data_ptr(), value_cache.data_ptr()
+        args.key_scales = key_scales.data_ptr() if fp8 else None
+        args.value_scales = value_scales.data_ptr() if fp8 else None
+        args.block_tables, args.sequence_lengths = block_tables.data_ptr(), sequence_lengths.data_ptr()
+        args.output = output.data_ptr()
+        args.sequences, args.query_heads, args.kv_heads = sequences, query_heads, kv_heads
+        args.head_size, args.value_head_size = head_size, value_head_size
+        args.num_blocks, args.block_size = key_cache.shape[0], key_cache.shape[1]
+        args.max_blocks_per_sequence, args.max_sequence_length = block_tables.shape[1], max_sequence_length
+        args.key_block_stride, args.key_page_stride, args.key_head_stride = key_cache.stride()[:3]
+        args.value_block_stride, args.value_page_stride, args.value_head_stride = value_cache.stride()[:3]
+        args.scale = scale
+        args.stream = _stream(device)
+        status = lib.loom_cuda_multi_token_finish(ctypes.byref(args), query_tokens, states.data_ptr())
+        if status != 0:
+            raise RuntimeError("Loom multi-token finish failed: " + lib.loom_cuda_status_string(status).decode())
+    return output
+
+
 def paged_multi_token_decode_attention(
     query: torch.Tensor,
     key_cache: torch.Tensor,
@@ -511,6 +558,7 @@ def paged_multi_token_decode_attention(
     key_scales: torch.Tensor | None = None,
     value_scales: torch.Tensor | None = None,
     scratch: tuple[torch.Tensor, torch.Tensor] | None = None,
+    one_pass: bool | None = None,
 ) -> torch.Tensor:
     """Causal attention of ``Tq`` new tokens per sequence over a paged cache.
 
@@ -521,8 +569,12 @@ def paged_multi_token_decode_attention(
     ``paged_decode_attention_ex``. ``scratch`` may carry reusable int32 tensors
     ``([B * Tq, max_blocks], [B * Tq])`` for the expanded metadata.
 
-    This is the single-token decode run on ``B * Tq`` rows: correct for any
-    ``Tq``, but a sequence's pages are streamed once per query token.
+    ``one_pass`` (default: whenever head sizes are at most 256) streams the KV
+    once: the ``Tq x group`` rows of a (sequence, KV head) pair run as one GQA
+    group over the common prefix ``length - (Tq - 1)`` and a finishing kernel
+    adds each row's up to ``Tq - 1`` tail tokens. Otherwise the single-token
+    decode runs on ``B * Tq`` rows with expanded metadata (any shape, but a
+    sequence's pages are streamed once per query token).
     """
     if query.dim() != 4 or not query.is_contiguous():
         raise RuntimeError("Loom multi-token decode expects a contiguous query [B, Tq, Hq, D]")
@@ -536,6 +588,14 @@ def paged_multi_token_decode_attention(
         raise RuntimeError("Loom paged decode tensors must share one CUDA device")
     sequences, query_tokens, query_heads, head_size = query.shape
     rows, max_blocks = sequences * query_tokens, block_tables.shape[1]
+    fp8 = key_cache.dtype == torch.uint8
+    if one_pass is None:
+        one_pass = (query_tokens > 1 and head_size <= 256 and value_cache.shape[3] <= 256
+                    and not (fp8 and query.dtype == torch.float32))
+    if one_pass:
+        return _multi_token_one_pass(query, key_cache, value_cache, block_tables, sequence_lengths,
+                                     int(max_sequence_length), head_size ** -0.5 if scale is None else float(scale),
+                                     key_scales if fp8 else None, value_scales if fp8 else None)
     if scratch is None:
         scratch = (torch.empty((rows, max_blocks), dtype=torch.int32, device=query.device),
                    torch.empty((rows,), dtype=torch.int32, device=query.device))

@@ -317,6 +317,35 @@ int loom_cuda_expand_query_tokens(const int32_t* block_tables,
                                   uint32_t max_blocks_per_sequence,
                                   void* stream);
 
+/*
+ * Multi-token queries at one pass over the KV, in three launches.
+ *  1. loom_cuda_multi_token_prepare: query [sequences, query_tokens,
+ *     query_heads, head_size] (contiguous, dtype 0/1/2 = F32/F16/BF16) is
+ *     packed as [sequences, kv_heads, query_tokens, group, head_size], and
+ *     prefix_lengths[s] = max(0, sequence_lengths[s] - (query_tokens - 1)).
+ *  2. An ordinary decode (loom_cuda_paged_decode_attention_ex) of the packed
+ *     query as [sequences, query_tokens * query_heads, head_size] with
+ *     prefix_lengths and emit_state = 1: the rows of a (sequence, KV head) pair
+ *     form one GQA group over the prefix every one of them sees.
+ *  3. loom_cuda_multi_token_finish: args as for the decode, but with the
+ *     ORIGINAL query, block tables and sequence lengths (counting all new
+ *     tokens), query_heads the per-token head count, and output [sequences,
+ *     query_tokens, query_heads, value_head_size] of the query's type;
+ *     prefix_states is what step 2 wrote. Each row's up to query_tokens - 1
+ *     tail tokens are added to its state, the row is normalised and stored.
+ *     workspace, partition_tokens, emit_state and the query strides of args
+ *     are ignored. Head sizes up to 256; an FP8 cache needs a 16-bit query.
+ */
+int loom_cuda_multi_token_prepare(const void* query, void* packed_query,
+                                  const int32_t* sequence_lengths,
+                                  int32_t* prefix_lengths, uint32_t dtype,
+                                  uint32_t sequences, uint32_t query_tokens,
+                                  uint32_t query_heads, uint32_t kv_heads,
+                                  uint32_t head_size, void* stream);
+int loom_cuda_multi_token_finish(const LoomDecodeArgs* args,
+                                 uint32_t query_tokens,
+                                 const float* prefix_states);
+
 /* ====================================================================== *
  * Part 3: KV block movement
  *

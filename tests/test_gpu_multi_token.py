@@ -44,8 +44,9 @@ def test_expansion_kernel_matches_numpy():
         assert np.array_equal(out_lengths.cpu().numpy(), want_lengths)
 
 
-@pytest.mark.parametrize("name,query_tokens", [("cfg2", 3), ("cfg3", 4), ("cfg4", 2)])
-def test_multi_token_attention_matches_the_oracle_token_by_token(name, query_tokens):
+@pytest.mark.parametrize("one_pass", [True, False])
+@pytest.mark.parametrize("name,query_tokens", [("cfg2", 3), ("cfg3", 4), ("cfg4", 2), ("cfg1", 5)])
+def test_multi_token_attention_matches_the_oracle_token_by_token(name, query_tokens, one_pass):
     from attnarc_b200 import ops, workloads
 
     config = workloads.scaled(workloads.CONFIGS[name], batch=5,
@@ -60,7 +61,7 @@ def test_multi_token_attention_matches_the_oracle_token_by_token(name, query_tok
 
     got = ops.paged_multi_token_decode_attention(query, key_cache, value_cache, case.block_tables,
                                                  case.sequence_lengths, max_sequence_length=case.max_sequence_length,
-                                                 scale=case.scale, **scales)
+                                                 scale=case.scale, one_pass=one_pass, **scales)
     assert tuple(got.shape) == (5, query_tokens, config.query_heads, config.head_size)
 
     tables, visible = expanded_metadata(case.block_tables.cpu().numpy(), case.sequence_lengths.cpu().numpy(),
@@ -75,7 +76,7 @@ def test_multi_token_attention_matches_the_oracle_token_by_token(name, query_tok
     helpers.assert_close(flat[torch.from_numpy(live).to(DEVICE)], want, config.torch_dtype,
                          f"{name} Tq={query_tokens}")
     hidden = np.flatnonzero(visible == 0)
-    assert len(hidden) == (query_tokens - 2 if query_tokens > 2 else 0)
+    assert len(hidden) == max(query_tokens - 2, 0)
     assert not flat[torch.from_numpy(hidden).to(DEVICE)].any()  # a token with nothing to see yields a zero row
 
     # the last token of every sequence is the ordinary single-token decode
@@ -98,6 +99,6 @@ def test_multi_token_rejects_malformed_arguments():
     with pytest.raises(RuntimeError, match="scratch"):
         ops.paged_multi_token_decode_attention(
             query, key_cache, value_cache, case.block_tables, case.sequence_lengths,
-            max_sequence_length=case.max_sequence_length,
+            max_sequence_length=case.max_sequence_length, one_pass=False,
             scratch=(torch.zeros((3, 1), dtype=torch.int32, device=DEVICE),
                      torch.zeros((4,), dtype=torch.int32, device=DEVICE)))
