@@ -116,6 +116,10 @@ def parse_args():
     parser.add_argument("--programmatic-launch", type=int, choices=[0, 1], default=None,
                         help="programmatic dependent launch mode of the library (default: the library's, 1)")
     parser.add_argument("--cpu-seconds", type=float, default=15.0, help="CPU work per baseline sample")
+    parser.add_argument("--query-tokens", type=int, default=1,
+                        help="> 1 times ops.paged_multi_token_decode_attention on the workload (decode only)")
+    parser.add_argument("--expanded", action="store_true",
+                        help="with --query-tokens: the B x Tq single-token form instead of the one-pass form")
     return parser.parse_args()
 
 
@@ -684,6 +688,67 @@ def run_kv_move(args):
     print(json.dumps(line), flush=True)
 
 
+# ------------------------------------------------------------------ multi-token queries
+
+def run_multi_token(args):
+    """`--query-tokens N`: causal attention of N new tokens per sequence on the named workload.
+
+    One step = one `ops.paged_multi_token_decode_attention` call (pack, decode over the common
+    prefix, finish; or the expanded form). `value` = distinct KV bytes of the batch / time.
+    """
+    import torch
+
+    from attnarc_b200 import ops, workloads
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback for the product path")
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    config = workloads.CONFIGS[args.workload]
+    if args.batch:
+        config = workloads.scaled(config, batch=args.batch, name=f"{config.name}-batch{args.batch}")
+    case = workloads.build_case(config, device, seed=args.seed, fast_device_fill=True)
+    key_cache, value_cache = case.cache_views()
+    fp8 = config.cache == "fp8"
+    scales = dict(key_scales=case.key_scales, value_scales=case.value_scales) if fp8 else {}
+    query = torch.randn((config.batch, args.query_tokens, config.query_heads, config.head_size),
+                        device=device, generator=torch.Generator(device=device).manual_seed(args.seed))
+    query = query.to(config.torch_dtype)
+
+    def step():
+        return ops.paged_multi_token_decode_attention(
+            query, key_cache, value_cache, case.block_tables, case.sequence_lengths,
+            max_sequence_length=case.max_sequence_length, scale=case.scale, one_pass=not args.expanded, **scales)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as sampler:
+        start.record()
+        for _ in range(args.steps):
+            step()
+        stop.record()
+        torch.cuda.synchronize()
+    ms = start.elapsed_time(stop) / args.steps
+    peak, source = measured_peak_gbs()
+    achieved = case.kv_bytes / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "multi_token_decode_kv_read_bandwidth", "value": achieved, "unit": UNIT, "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": config.dtype if not fp8 else "u8", "data": "synthetic",
+        "config": {"workload": f"{config.name}: {config.description}", "query_tokens": args.query_tokens,
+                   "form": "expanded" if args.expanded else "one pass", "distinct_kv_bytes_per_step": case.kv_bytes,
+                   "launch": "eager operator calls, CUDA events around K steps",
+                   "l2": "KV of %.2f GB per step" % (case.kv_bytes / 1e9)},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,
+                     "peak_source": f"{source} copy bandwidth", "algorithmic_bytes_per_launch": case.kv_bytes,
+                     "traffic": None},
+        "decode_route": ops.last_decode_route(), "clocks": sampler.summary(),
+    }), flush=True)
+
+
 def main():
     args = parse_args()
     if args.workload == "kv-move" and args.impl == "reference":
@@ -692,6 +757,8 @@ def main():
                               "unavailable": "the reference lists KV block movement as planned and has no code for it"}))
     elif args.workload == "kv-move":
         run_kv_move(args)
+    elif args.query_tokens > 1 and args.impl != "reference":
+        run_multi_token(args)
     elif args.impl == "reference":
         run_reference(args)
     else:
