@@ -107,6 +107,7 @@ def _declare(lib):
     lib.loom_cuda_expand_query_tokens.argtypes = [ptr, ptr, ptr, ptr, u32, u32, u32, ptr]
     lib.loom_cuda_multi_token_prepare.argtypes = [ptr, ptr, ptr, ptr] + [u32] * 6 + [ptr]
     lib.loom_cuda_multi_token_finish.argtypes = [ctypes.POINTER(LoomDecodeArgs), u32, ptr]
+    lib.loom_cuda_paged_multi_token_decode.argtypes = [ctypes.POINTER(LoomDecodeArgs), u32, ptr, ptr, ptr]
     # KV block movement
     lib.loom_cuda_bridge_kv_block_move.argtypes = [ptr, u64] * 5 + [u32, u32] + [u64] * 5 + [ptr]
     lib.loom_cuda_bridge_kv_block_swap.argtypes = [ptr, u64] * 3 + [u32] + [u64] * 3 + [ptr]

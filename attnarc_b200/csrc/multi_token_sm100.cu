@@ -360,3 +360,32 @@ int loom_cuda_multi_token_finish(const LoomDecodeArgs* args, uint32_t query_toke
 }
 
 }  // extern "C"
+
+// The three launches as one call. `args` describes the multi-token problem as
+// loom_cuda_multi_token_finish takes it (original query, tables, lengths; output
+// [sequences, query_tokens, query_heads, value_head_size]); its workspace, if
+// any, serves the widened decode (size it for query_tokens * query_heads heads).
+extern "C" int loom_cuda_paged_multi_token_decode(const LoomDecodeArgs* args, uint32_t query_tokens,
+                                                  void* packed_query, int32_t* prefix_lengths,
+                                                  float* prefix_states) {
+  if (args == nullptr || args->struct_size != sizeof(LoomDecodeArgs) || query_tokens == 0 || !packed_query ||
+      !prefix_lengths || !prefix_states) {
+    return LOOM_CUDA_INVALID_ARGUMENT;
+  }
+  if ((uint64_t)args->query_heads * query_tokens > 0xffffffffull) return LOOM_CUDA_INVALID_ARGUMENT;
+  int status = loom_cuda_multi_token_prepare(args->query, packed_query, args->sequence_lengths, prefix_lengths,
+                                             args->dtype, args->sequences, query_tokens, args->query_heads,
+                                             args->kv_heads, args->head_size, args->stream);
+  if (status != LOOM_CUDA_SUCCESS) return status;
+  LoomDecodeArgs prefix = *args;
+  prefix.query = packed_query;
+  prefix.query_heads = args->query_heads * query_tokens;
+  prefix.query_token_stride = 0;
+  prefix.query_head_stride = 0;
+  prefix.sequence_lengths = prefix_lengths;
+  prefix.output = prefix_states;
+  prefix.emit_state = 1;
+  status = loom_cuda_paged_decode_attention_ex(&prefix);
+  if (status != LOOM_CUDA_SUCCESS) return status;
+  return loom_cuda_multi_token_finish(args, query_tokens, prefix_states);
+}

@@ -506,22 +506,17 @@ def _multi_token_one_pass(query, key_cache, value_cache, block_tables, sequence_
     kv_heads, value_head_size = key_cache.shape[2], value_cache.shape[3]
     fp8 = key_cache.dtype == torch.uint8
     device = query.device
-    packed = torch.empty((sequences, query_tokens * query_heads, head_size), dtype=query.dtype, device=device)
+    wide_heads = query_tokens * query_heads  # the rows of a (sequence, KV head) pair form one group of Tq x group
+    packed = torch.empty((sequences, wide_heads, head_size), dtype=query.dtype, device=device)
     prefix_lengths = torch.empty((sequences,), dtype=torch.int32, device=device)
+    states = torch.empty((sequences, wide_heads, value_head_size + 2), dtype=torch.float32, device=device)
+    output = torch.empty((sequences, query_tokens, query_heads, value_head_size), dtype=query.dtype, device=device)
     lib = library()
     with _on_device(device):
-        status = lib.loom_cuda_multi_token_prepare(
-            query.data_ptr(), packed.data_ptr(), sequence_lengths.data_ptr(), prefix_lengths.data_ptr(),
-            _DTYPE_CODES[query.dtype], sequences, query_tokens, query_heads, kv_heads, head_size, _stream(device))
-        if status != 0:
-            raise RuntimeError("Loom multi-token prepare failed: " + lib.loom_cuda_status_string(status).decode())
-        scales = dict(key_scales=key_scales, value_scales=value_scales) if fp8 else {}
-        # the rows of a (sequence, KV head) pair as one group of Tq x group heads, over the common prefix
-        states = paged_decode_attention_ex(packed, key_cache, value_cache, block_tables, prefix_lengths,
-                                           max_sequence_length=max_sequence_length, scale=scale, emit_state=True,
-                                           **scales)
-        output = torch.empty((sequences, query_tokens, query_heads, value_head_size), dtype=query.dtype,
-                             device=device)
+        needed, tokens = decode_workspace_elements_ex(sequences, wide_heads, kv_heads, value_head_size,
+                                                      max_sequence_length, 0)
+        split = needed > 0 and max_sequence_length > (tokens if tokens else 256)
+        workspace = torch.empty(needed, dtype=torch.float32, device=device) if split else None
         args = _native.LoomDecodeArgs()
         args.struct_size = ctypes.sizeof(_native.LoomDecodeArgs)
         args.dtype = _DTYPE_CODES[query.dtype]
@@ -532,6 +527,8 @@ def _multi_token_one_pass(query, key_cache, value_cache, block_tables, sequence_
         args.value_scales = value_scales.data_ptr() if fp8 else None
         args.block_tables, args.sequence_lengths = block_tables.data_ptr(), sequence_lengths.data_ptr()
         args.output = output.data_ptr()
+        args.workspace = workspace.data_ptr() if split else None
+        args.workspace_elements = needed if split else 0
         args.sequences, args.query_heads, args.kv_heads = sequences, query_heads, kv_heads
         args.head_size, args.value_head_size = head_size, value_head_size
         args.num_blocks, args.block_size = key_cache.shape[0], key_cache.shape[1]
@@ -540,9 +537,10 @@ def _multi_token_one_pass(query, key_cache, value_cache, block_tables, sequence_
         args.value_block_stride, args.value_page_stride, args.value_head_stride = value_cache.stride()[:3]
         args.scale = scale
         args.stream = _stream(device)
-        status = lib.loom_cuda_multi_token_finish(ctypes.byref(args), query_tokens, states.data_ptr())
+        status = lib.loom_cuda_paged_multi_token_decode(ctypes.byref(args), query_tokens, packed.data_ptr(),
+                                                        prefix_lengths.data_ptr(), states.data_ptr())
         if status != 0:
-            raise RuntimeError("Loom multi-token finish failed: " + lib.loom_cuda_status_string(status).decode())
+            raise RuntimeError("Loom multi-token decode failed: " + lib.loom_cuda_status_string(status).decode())
     return output
 
 

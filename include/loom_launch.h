@@ -346,6 +346,21 @@ int loom_cuda_multi_token_finish(const LoomDecodeArgs* args,
                                  uint32_t query_tokens,
                                  const float* prefix_states);
 
+/*
+ * The three steps above as one call. args as for loom_cuda_multi_token_finish;
+ * args->workspace / workspace_elements (may be null / 0 for short contexts)
+ * serve the decode of step 2 and are sized with
+ * loom_cuda_paged_decode_workspace_elements for query_tokens * query_heads
+ * heads. Caller-owned scratch: packed_query (as many elements as the query),
+ * prefix_lengths [sequences] and prefix_states [sequences, query_tokens *
+ * query_heads, value_head_size + 2] F32.
+ */
+int loom_cuda_paged_multi_token_decode(const LoomDecodeArgs* args,
+                                       uint32_t query_tokens,
+                                       void* packed_query,
+                                       int32_t* prefix_lengths,
+                                       float* prefix_states);
+
 /* ====================================================================== *
  * Part 3: KV block movement
  *
