@@ -387,6 +387,27 @@ bool raise_shared_limit(Kernel kernel, std::atomic<uint64_t>& prepared) {
   return true;
 }
 
+// The address a kernel uses for `pointer`: itself for device or managed memory,
+// the mapped device address for pinned host memory (`*host` set). False for
+// memory the device cannot address (pageable host memory, unknown pointers).
+bool device_view(const void* pointer, const uint8_t** view, bool* host) {
+  cudaPointerAttributes attributes{};
+  if (cudaPointerGetAttributes(&attributes, pointer) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  if (attributes.type == cudaMemoryTypeDevice || attributes.type == cudaMemoryTypeManaged) {
+    *view = static_cast<const uint8_t*>(pointer);
+    return true;
+  }
+  if (attributes.type == cudaMemoryTypeHost && attributes.devicePointer != nullptr) {
+    *view = static_cast<const uint8_t*>(attributes.devicePointer);
+    *host = true;
+    return true;
+  }
+  return false;
+}
+
 int sm_count() {
   int device = 0, count = 0;
   if (cudaGetDevice(&device) != cudaSuccess) return 0;
@@ -453,7 +474,18 @@ int loom_cuda_kv_block_move(const void* source_key_cache, const void* source_val
   p.source_blocks = source_blocks;
   p.destination_blocks = destination_blocks;
   p.chunks_per_block = (uint32_t)chunks;
-  if (g_move_engine.load(std::memory_order_relaxed) == 1) {
+  // A cache in pinned host memory (blocks swapped out on preemption, swapped in on resume) is read
+  // and written over PCIe by the vector engine; memory the device cannot address is refused.
+  bool host = false;
+  const uint8_t* destination_view[2] = {nullptr, nullptr};
+  if (!device_view(source_key_cache, &p.source[0], &host) || !device_view(source_value_cache, &p.source[1], &host) ||
+      !device_view(destination_key_cache, &destination_view[0], &host) ||
+      !device_view(destination_value_cache, &destination_view[1], &host)) {
+    return LOOM_CUDA_INVALID_ARGUMENT;
+  }
+  p.destination[0] = const_cast<uint8_t*>(destination_view[0]);
+  p.destination[1] = const_cast<uint8_t*>(destination_view[1]);
+  if (host || g_move_engine.load(std::memory_order_relaxed) == 1) {
     const uint64_t units = (uint64_t)pair_count * 2u * chunks;
     return finish(loom_launch::launch(kv_block_move_kernel, dim3(grid_for(units, sms)), dim3(kThreads), 0,
                                       static_cast<cudaStream_t>(stream), p));

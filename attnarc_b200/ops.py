@@ -643,7 +643,7 @@ def kv_block_move_timeout_flag(device=None, reset: bool = False) -> int:
     return int(value.value)
 
 
-def _block_spans(kv_cache: torch.Tensor, name: str):
+def _block_spans(kv_cache: torch.Tensor, name: str, host_allowed: bool = False):
     """(K pointer, V pointer, span bytes, block bytes, block stride bytes) of a packed cache.
 
     The cache is ``[blocks, 2, ...]`` with each block's K part and V part dense
@@ -651,8 +651,10 @@ def _block_spans(kv_cache: torch.Tensor, name: str):
     """
     if kv_cache.dim() < 3 or kv_cache.shape[1] != 2:
         raise RuntimeError(f"Loom KV block movement expects a [blocks, 2, ...] cache; {name} is not")
-    if kv_cache.device.type != "cuda":
-        raise RuntimeError("Loom KV block movement tensors must live on a CUDA device")
+    if kv_cache.device.type != "cuda" and not (host_allowed and kv_cache.device.type == "cpu"
+                                               and kv_cache.is_pinned()):
+        raise RuntimeError("Loom KV block movement tensors must live on a CUDA device"
+                           + (" or in pinned host memory" if host_allowed else ""))
     inner = kv_cache[0, 0]
     block_elements = inner.numel()
     if _span(inner) != block_elements:
@@ -679,22 +681,28 @@ def kv_block_move_(destination: torch.Tensor, source: torch.Tensor, block_pairs:
     Both caches are packed ``[blocks, 2, ...]`` allocations with the same block
     shape and dtype; they may be the same tensor (copy-on-write of a shared
     block, compaction) or different ones (gather into a staging buffer,
-    scatter back). ``block_pairs`` is int64 ``[pairs, 2]`` on the device. No
-    block may be both read and written, nor written twice, in one call.
+    scatter back). Either may also be a pinned host tensor: blocks swapped out
+    to host memory on preemption and back in on resume travel over PCIe, read or
+    written by the kernel directly. ``block_pairs`` is int64 ``[pairs, 2]`` on
+    the device, whose current stream carries the launch. No block may be both
+    read and written, nor written twice, in one call.
     """
     _require_inference_tensors(destination, source)
-    if destination.dtype != source.dtype or destination.device != source.device:
-        raise RuntimeError("Loom KV block move needs caches of one dtype on one device")
-    pairs = _pairs_argument(block_pairs, source.device)
-    source_key, source_value, source_span, block_bytes, source_stride = _block_spans(source, "source")
-    to_key, to_value, to_span, to_block_bytes, to_stride = _block_spans(destination, "destination")
+    if destination.dtype != source.dtype:
+        raise RuntimeError("Loom KV block move needs caches of one dtype")
+    device = block_pairs.device
+    if device.type != "cuda" or any(t.device.type == "cuda" and t.device != device for t in (source, destination)):
+        raise RuntimeError("Loom KV block pairs and the device caches must live on one CUDA device")
+    pairs = _pairs_argument(block_pairs, device)
+    source_key, source_value, source_span, block_bytes, source_stride = _block_spans(source, "source", True)
+    to_key, to_value, to_span, to_block_bytes, to_stride = _block_spans(destination, "destination", True)
     if block_bytes != to_block_bytes:
         raise RuntimeError("Loom KV block move needs source and destination blocks of one size")
-    with _on_device(source.device):
+    with _on_device(device):
         status = library().loom_cuda_bridge_kv_block_move(
             source_key, source_span, source_value, source_span, to_key, to_span, to_value, to_span,
             pairs.data_ptr(), pairs.numel(), source.shape[0], destination.shape[0], block_bytes,
-            source_stride, source_stride, to_stride, to_stride, _stream(source.device),
+            source_stride, source_stride, to_stride, to_stride, _stream(device),
         )
     check(status, "KV block move")
     return destination

@@ -382,8 +382,12 @@ int loom_cuda_paged_multi_token_decode(const LoomDecodeArgs* args,
  * block block_pairs[2 i + 1] of the destination cache, K and V. Source and
  * destination may be the same cache (copy-on-write of a shared prefix block,
  * compaction) or different allocations (gather into a dense staging buffer,
- * scatter back, migration between caches). No block may be both read and
- * written, and no destination may occur twice, in one call.
+ * scatter back, migration between caches). Either cache may also lie in
+ * pinned host memory (blocks swapped out on preemption, swapped in on resume):
+ * the kernel then reads or writes it over PCIe with vector loads and stores;
+ * memory the device cannot address is refused with
+ * LOOM_CUDA_INVALID_ARGUMENT. No block may be both read and written, and no
+ * destination may occur twice, in one call.
  */
 int loom_cuda_kv_block_move(
     const void* source_key_cache, const void* source_value_cache,

@@ -183,3 +183,33 @@ def test_gather_then_scatter_restores_a_gigabyte_cache(engine):
     cache.zero_()
     ops.kv_block_move_(cache, staging, gather.flip(1).contiguous())
     assert helpers.same_bits(cache, original)
+
+
+def test_blocks_swap_out_to_pinned_host_memory_and_back_in():
+    """Preemption and resume: device cache -> pinned host cache -> other blocks of the device cache."""
+    from attnarc_b200 import ops
+
+    rng = np.random.default_rng(21)
+    allocation, cache = make_cache(rng, 40, 16, 4, 128, torch.bfloat16, "NHD")
+    original = block_bytes_of(allocation)
+    host_cache = torch.zeros((12, 2, 16, 4, 128), dtype=torch.bfloat16).pin_memory()
+    order = rng.permutation(40)
+    out_pairs = np.stack([order[:10], np.arange(10)], axis=1).astype(np.int64)      # device block -> host slot
+    ops.kv_block_move_(host_cache, cache, torch.from_numpy(out_pairs).to(DEVICE))
+    torch.cuda.synchronize()
+    want_host = kv_blocks.kv_block_move(np.zeros((12, 2, original.shape[2]), dtype=np.uint8), original, out_pairs)
+    assert np.array_equal(host_cache.view(torch.uint8).reshape(12, 2, -1).numpy(), want_host)
+
+    allocation[torch.from_numpy(order[:10]).to(DEVICE)] = 0                           # the blocks are given away
+    in_pairs = np.stack([np.arange(10), order[10:20]], axis=1).astype(np.int64)      # host slot -> other blocks
+    ops.kv_block_move_(cache, host_cache, torch.from_numpy(in_pairs).to(DEVICE))
+    torch.cuda.synchronize()
+    after = block_bytes_of(allocation)
+    for slot in range(10):
+        assert np.array_equal(after[order[10 + slot]], original[order[slot]])
+        assert not after[order[slot]].any()
+    assert ops.kv_block_move_timeout_flag() == 0
+
+    pageable = torch.zeros((12, 2, 16, 4, 128), dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="pinned host memory"):
+        ops.kv_block_move_(pageable, cache, torch.from_numpy(out_pairs).to(DEVICE))
