@@ -86,7 +86,11 @@ def build(force: bool = False, verbose: bool = False) -> str:
                 print(log)
     if force or _stale(LIBRARY, objects):
         cmd = [nvcc_path(), "-shared", "-gencode", "arch=compute_100a,code=sm_100a",
-               "-Xcompiler", "-fPIC", "-o", LIBRARY, *objects]
+               "-Xcompiler", "-fPIC",
+               # Calls between this library's own entry points bind inside it: the reference's
+               # library exports the same names and may be loaded in the same process.
+               "-Xlinker", "-Bsymbolic",
+               "-o", LIBRARY, *objects]
         done = subprocess.run(cmd, capture_output=True, text=True)
         if done.returncode != 0:
             raise RuntimeError("link failed:\n" + done.stdout + done.stderr)

@@ -322,6 +322,9 @@ thread_local const char* g_last_route = "none";
 int launched(cudaError_t status) {
   if (status == cudaSuccess) return LOOM_CUDA_SUCCESS;
   cudaGetLastError();
+  // LOOM_DEBUG_LAUNCH=1 names the runtime error behind a LOOM_CUDA_LAUNCH_ERROR on stderr
+  static const bool verbose = std::getenv("LOOM_DEBUG_LAUNCH") != nullptr;
+  if (verbose) std::fprintf(stderr, "loom launch failed: %s (%s)\n", cudaGetErrorName(status), cudaGetErrorString(status));
   return LOOM_CUDA_LAUNCH_ERROR;
 }
 
