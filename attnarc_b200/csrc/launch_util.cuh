@@ -48,7 +48,16 @@ cudaError_t launch(void (*kernel)(Params...), dim3 grid, dim3 block, size_t shar
     config.attrs = &attribute;
     config.numAttrs = 1;
   }
-  return cudaLaunchKernelEx(&config, kernel, std::forward<Args>(args)...);
+  cudaError_t status = cudaLaunchKernelEx(&config, kernel, args...);
+  if (status != cudaSuccess && config.numAttrs != 0) {
+    // The attribute is an optimisation: a launch refused with it is tried once as a plain launch
+    // (a genuine configuration error fails again and is reported).
+    cudaGetLastError();
+    config.attrs = nullptr;
+    config.numAttrs = 0;
+    status = cudaLaunchKernelEx(&config, kernel, args...);
+  }
+  return status;
 }
 
 #ifdef __CUDACC__
