@@ -15,7 +15,7 @@
 // byte is read once and written once. Move and swap have two engines: by default
 // 8 KB chunks go through shared memory on the bulk-copy engine (cp.async.bulk in
 // and out, one issuing thread per CTA: the move at 0.97-1.0 of the device's copy
-// bandwidth, the swap at 0.92-0.93); the other engine walks 32 KB chunks with a
+// bandwidth, the swap, in 4 KB chunks, at 0.98); the other engine walks 32 KB chunks with a
 // grid sized to the SM count, each thread moving eight 16-byte vectors per chunk
 // with all its loads issued before its stores (0.88-0.90).
 //
@@ -273,15 +273,22 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) kv_block_swap_kernel(con
 // chunks are loaded into a twin (one mbarrier counts the bytes of both loads),
 // then stored crosswise, so neither store can overtake the load of what it
 // overwrites. Refill rule, bounds on the waits and drain as in the move kernel.
+// The swap's ring: 16 slots of 4 KB used as 8 twins. Measured (8192 / 16384 pairs of 64 KB blocks):
+// 4 KB x 16 slots, twin lag 2: 6.48-6.50 TB/s; 8 KB x 8 slots, lag 1: 5.99-6.13, lag 2: 6.16-6.18;
+// 8 KB x 12 slots x 2 CTAs/SM, lag 2: 6.18-6.24.
+constexpr uint32_t kSwapBytes = 4096;
+constexpr int kSwapStages = 16;
+constexpr uint32_t kSwapSharedBytes = kSwapStages * kSwapBytes + kSwapStages * 8 + kSwapStages * 16;
+
 __global__ void __launch_bounds__(32, kBulkCtasPerSm) kv_block_swap_bulk_kernel(const SwapParams p) {
-  constexpr int kTwins = kBulkStages / 2;
-  constexpr int kTwinLag = 1;                  // stores still reading when the next twin is loaded
+  constexpr int kTwins = kSwapStages / 2;
+  constexpr int kTwinLag = 2;                  // stores still reading when the next twin is loaded
   constexpr int kAhead = kTwins - kTwinLag;
-  static_assert(kBulkStages % 2 == 0 && kAhead >= 1, "the swap needs at least two twins of slots");
+  static_assert(kSwapStages % 2 == 0 && kAhead >= 1, "the swap needs at least two twins of slots");
   extern __shared__ __align__(128) uint8_t ring[];
-  uint64_t* barriers = reinterpret_cast<uint64_t*>(ring + kBulkStages * kBulkBytes);  // one per twin
+  uint64_t* barriers = reinterpret_cast<uint64_t*>(ring + kSwapStages * kSwapBytes);  // one per twin
   // per twin: address of the first block's chunk, of the second block's chunk, byte count (0 = skip)
-  uint64_t* targets = reinterpret_cast<uint64_t*>(ring + kBulkStages * kBulkBytes + kBulkStages * 8);
+  uint64_t* targets = reinterpret_cast<uint64_t*>(ring + kSwapStages * kSwapBytes + kSwapStages * 8);
   if (threadIdx.x != 0) return;
   for (int twin = 0; twin < kTwins; ++twin) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(shared_address(barriers + twin)) : "memory");
@@ -305,9 +312,9 @@ __global__ void __launch_bounds__(32, kBulkCtasPerSm) kv_block_swap_bulk_kernel(
     const int64_t right = __ldg(p.pairs + 2 * pair + 1);
     targets[3 * twin + 2] = 0;
     if (left < 0 || left >= (int64_t)p.blocks || right < 0 || right >= (int64_t)p.blocks || left == right) return;
-    const uint64_t offset = (uint64_t)chunk * kBulkBytes;
+    const uint64_t offset = (uint64_t)chunk * kSwapBytes;
     const uint64_t remaining = p.block_bytes - offset;
-    const uint32_t bytes = (uint32_t)(remaining < kBulkBytes ? remaining : kBulkBytes);
+    const uint32_t bytes = (uint32_t)(remaining < kSwapBytes ? remaining : kSwapBytes);
     uint8_t* base_pointer = which ? p.cache[1] : p.cache[0];
     const uint64_t stride = which ? p.stride[1] : p.stride[0];
     uint8_t* first = base_pointer + (uint64_t)left * stride + offset;
@@ -317,14 +324,14 @@ __global__ void __launch_bounds__(32, kBulkCtasPerSm) kv_block_swap_bulk_kernel(
     targets[3 * twin + 2] = bytes;
     pending |= 1u << twin;
     const uint32_t barrier = shared_address(barriers + twin);
-    const uint32_t slot = shared_address(ring + (2 * twin) * kBulkBytes);
+    const uint32_t slot = shared_address(ring + (2 * twin) * kSwapBytes);
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(barrier), "r"(2u * bytes)
                  : "memory");
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(slot),
                  "l"(first), "r"(bytes), "r"(barrier)
                  : "memory");
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
-                     slot + kBulkBytes),
+                     slot + kSwapBytes),
                  "l"(second), "r"(bytes), "r"(barrier)
                  : "memory");
   };
@@ -338,12 +345,12 @@ __global__ void __launch_bounds__(32, kBulkCtasPerSm) kv_block_swap_bulk_kernel(
       if (!bulk_wait(shared_address(barriers + twin), (phases >> twin) & 1u)) break;
       phases ^= 1u << twin;
       pending &= ~(1u << twin);
-      const uint32_t slot = shared_address(ring + (2 * twin) * kBulkBytes);
+      const uint32_t slot = shared_address(ring + (2 * twin) * kSwapBytes);
       asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;\n" ::"l"(targets[3 * twin + 1]),
                    "r"(slot), "r"(bytes)
                    : "memory");  // the first block's bytes go to the second block
       asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;\n" ::"l"(targets[3 * twin]),
-                   "r"(slot + kBulkBytes), "r"(bytes)
+                   "r"(slot + kSwapBytes), "r"(bytes)
                    : "memory");
     }
     asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
@@ -374,11 +381,11 @@ std::atomic<uint32_t> g_move_engine{0};
 
 // Raises a bulk kernel's dynamic shared-memory limit once per device (bit d of `prepared`).
 template <typename Kernel>
-bool raise_shared_limit(Kernel kernel, std::atomic<uint64_t>& prepared) {
+bool raise_shared_limit(Kernel kernel, uint32_t bytes, std::atomic<uint64_t>& prepared) {
   int device = 0;
   if (cudaGetDevice(&device) != cudaSuccess) return false;
   if (device < 64 && (prepared.load(std::memory_order_acquire) & (1ull << device))) return true;
-  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kBulkSharedBytes) !=
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) !=
       cudaSuccess) {
     cudaGetLastError();
     return false;
@@ -494,7 +501,7 @@ int loom_cuda_kv_block_move(const void* source_key_cache, const void* source_val
   if (bulk_chunks > 0xffffffffull) return LOOM_CUDA_UNSUPPORTED;
   p.chunks_per_block = (uint32_t)bulk_chunks;
   static std::atomic<uint64_t> prepared{0};
-  if (!raise_shared_limit(kv_block_move_bulk_kernel, prepared)) return LOOM_CUDA_LAUNCH_ERROR;
+  if (!raise_shared_limit(kv_block_move_bulk_kernel, kBulkSharedBytes, prepared)) return LOOM_CUDA_LAUNCH_ERROR;
   const uint64_t units = (uint64_t)pair_count * 2u * bulk_chunks;
   const uint64_t resident = (uint64_t)sms * kBulkCtasPerSm;
   return finish(loom_launch::launch(kv_block_move_bulk_kernel, dim3((uint32_t)(units < resident ? units : resident)),
@@ -556,15 +563,15 @@ int loom_cuda_kv_block_swap(void* key_cache, void* value_cache, const int64_t* b
     return finish(loom_launch::launch(kv_block_swap_kernel, dim3(grid_for(units, sms)), dim3(kThreads), 0,
                                       static_cast<cudaStream_t>(stream), p));
   }
-  const uint64_t bulk_chunks = (block_bytes + kBulkBytes - 1) / kBulkBytes;
+  const uint64_t bulk_chunks = (block_bytes + kSwapBytes - 1) / kSwapBytes;
   if (bulk_chunks > 0xffffffffull) return LOOM_CUDA_UNSUPPORTED;
   p.chunks_per_block = (uint32_t)bulk_chunks;
   static std::atomic<uint64_t> prepared{0};
-  if (!raise_shared_limit(kv_block_swap_bulk_kernel, prepared)) return LOOM_CUDA_LAUNCH_ERROR;
+  if (!raise_shared_limit(kv_block_swap_bulk_kernel, kSwapSharedBytes, prepared)) return LOOM_CUDA_LAUNCH_ERROR;
   const uint64_t units = (uint64_t)pair_count * 2u * bulk_chunks;
   const uint64_t resident = (uint64_t)sms * kBulkCtasPerSm;
   return finish(loom_launch::launch(kv_block_swap_bulk_kernel, dim3((uint32_t)(units < resident ? units : resident)),
-                                    dim3(32), kBulkSharedBytes, static_cast<cudaStream_t>(stream), p));
+                                    dim3(32), kSwapSharedBytes, static_cast<cudaStream_t>(stream), p));
 }
 
 int loom_cuda_block_table_remap(int32_t* block_tables, uint64_t entries, const int32_t* new_block_ids,
