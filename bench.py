@@ -107,7 +107,7 @@ def parse_args():
     parser.add_argument("--steps", type=int, default=200)
     parser.add_argument("--warmup", type=int, default=20)
     parser.add_argument("--impl", choices=["b200", "reference"], default="b200")
-    parser.add_argument("--workload", default="cfg2", help="cfg2 (default), cfg3, cfg4, cfg5, cfg1; kv-move times KV block movement")
+    parser.add_argument("--workload", default="cfg2", help="cfg2 (default), cfg3, cfg4, cfg5, cfg1; kv-move / kv-swap time KV block movement")
     parser.add_argument("--seed", type=int, default=0)
     parser.add_argument("--batch", type=int, default=0,
                         help="override the workload's batch size (smaller cases for profiler captures)")
@@ -606,20 +606,27 @@ def run_kv_move(args):
     host_pairs = torch.from_numpy(np.stack([order[:count], order[count:2 * count]], axis=1)).pin_memory()
     pairs = host_pairs.to(device)
     block_bytes = 2 * shape["block_size"] * shape["kv_heads"] * shape["head_size"] * 2  # K + V
-    moved = 2 * count * block_bytes  # read + written
+    swap = args.workload == "kv-swap"
+    moved = (4 if swap else 2) * count * block_bytes  # read + written (a swap reads and writes both blocks)
+
+    def operate():
+        if swap:
+            ops.kv_block_swap_(cache, pairs)
+        else:
+            ops.kv_block_move_(cache, cache, pairs)
 
     for _ in range(max(args.warmup, 3)):
-        ops.kv_block_move_(cache, cache, pairs)
+        operate()
     torch.cuda.synchronize()
     stream = torch.cuda.Stream()
     stream.wait_stream(torch.cuda.current_stream())
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.stream(stream):
-        ops.kv_block_move_(cache, cache, pairs)
+        operate()
         stream.synchronize()
         with torch.cuda.graph(graph, stream=stream):
             for _ in range(args.steps):
-                ops.kv_block_move_(cache, cache, pairs)
+                operate()
     torch.cuda.synchronize()
     graph.replay()
     torch.cuda.synchronize()
@@ -638,7 +645,7 @@ def run_kv_move(args):
     # end to end: the pairs come from pinned host memory, the host waits for the move
     def e2e_step():
         pairs.copy_(host_pairs, non_blocking=True)
-        ops.kv_block_move_(cache, cache, pairs)
+        operate()
         torch.cuda.current_stream().synchronize()
 
     for _ in range(3):
@@ -654,11 +661,12 @@ def run_kv_move(args):
     peak, source = measured_peak_gbs()
     achieved = moved / (ms / args.steps * 1e-3) / 1e9
     line = {
-        "metric": "kv_block_move_bandwidth", "value": achieved, "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+        "metric": "kv_block_swap_bandwidth" if swap else "kv_block_move_bandwidth", "value": achieved, "unit": UNIT, "n_gpus": 1, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "u8", "data": "synthetic",
-        "config": {"workload": "kv-move: %d of %d blocks of %d KB (K+V) move inside a %.1f GB BF16 cache"
-                               % (count, blocks, block_bytes // 1024, blocks * block_bytes / 1e9),
+        "config": {"workload": "%s: %d of %d blocks of %d KB (K+V) %s inside a %.1f GB BF16 cache"
+                               % (args.workload, count, blocks, block_bytes // 1024,
+                                  "swap with as many others" if swap else "move", blocks * block_bytes / 1e9),
                    "bytes_read_plus_written_per_step": moved, "l2": "1.07 GB touched per step (> 126 MB L2)"},
         "e2e": {"value": moved * args.steps / (e2e_ms * 1e-3) / 1e9, "unit": UNIT,
                 "h2d_bytes_per_step": host_pairs.numel() * 8, "d2h_bytes_per_step": 0,
@@ -666,8 +674,8 @@ def run_kv_move(args):
         "gpu_launches": args.steps,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,
                      "peak_source": f"{source} copy bandwidth (also bytes read plus written)",
-                     "kernel": "kv_block_move_bulk_kernel", "us_per_launch": ms / args.steps * 1e3,
-                     "algorithmic_bytes_per_launch": moved, "traffic": NCU_DRAM_TRAFFIC_BYTES.get("kv-move")},
+                     "kernel": "kv_block_swap_bulk_kernel" if swap else "kv_block_move_bulk_kernel", "us_per_launch": ms / args.steps * 1e3,
+                     "algorithmic_bytes_per_launch": moved, "traffic": NCU_DRAM_TRAFFIC_BYTES.get(args.workload)},
         "clocks": sampler.summary(),
     }
     if not args.no_cpu_baseline:
@@ -751,11 +759,11 @@ def run_multi_token(args):
 
 def main():
     args = parse_args()
-    if args.workload == "kv-move" and args.impl == "reference":
+    if args.workload in ("kv-move", "kv-swap") and args.impl == "reference":
         if int(os.environ.get("RANK", "0")) == 0:
             print(json.dumps({"impl": "reference",
                               "unavailable": "the reference lists KV block movement as planned and has no code for it"}))
-    elif args.workload == "kv-move":
+    elif args.workload in ("kv-move", "kv-swap"):
         run_kv_move(args)
     elif args.query_tokens > 1 and args.impl != "reference":
         run_multi_token(args)
