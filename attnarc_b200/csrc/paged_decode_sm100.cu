@@ -319,9 +319,12 @@ merge_stream_kernel(const float* __restrict__ slots, const uint32_t* __restrict_
 thread_local const char* g_last_route = "none";
 
 // Launch status of this library from a runtime status (clears a sticky error).
+thread_local cudaError_t g_last_launch_failure = cudaSuccess;  // read by loom_cuda_last_launch_failure()
+
 int launched(cudaError_t status) {
   if (status == cudaSuccess) return LOOM_CUDA_SUCCESS;
   cudaGetLastError();
+  g_last_launch_failure = status;
   // LOOM_DEBUG_LAUNCH=1 names the runtime error behind a LOOM_CUDA_LAUNCH_ERROR on stderr
   static const bool verbose = std::getenv("LOOM_DEBUG_LAUNCH") != nullptr;
   if (verbose) std::fprintf(stderr, "loom launch failed: %s (%s)\n", cudaGetErrorName(status), cudaGetErrorString(status));
@@ -1054,6 +1057,11 @@ extern "C" int loom_cuda_supports_paged_decode(uint32_t dtype, uint32_t cache_en
 }
 
 extern "C" const char* loom_cuda_last_decode_route(void) { return loom_decode::g_last_route; }
+
+extern "C" const char* loom_cuda_last_launch_failure(void) {
+  return loom_decode::g_last_launch_failure == cudaSuccess ? "none"
+                                                           : cudaGetErrorName(loom_decode::g_last_launch_failure);
+}
 
 extern "C" int loom_cuda_set_decode_copy_engine(uint32_t engine) {
   if (engine > 3) return LOOM_CUDA_INVALID_ARGUMENT;

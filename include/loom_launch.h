@@ -229,6 +229,12 @@ int loom_cuda_supports_paged_decode(uint32_t dtype, uint32_t cache_encoding,
  * ("mma16", "scalar", ...); for tests and profiling notes. */
 const char* loom_cuda_last_decode_route(void);
 
+/* Name of the CUDA runtime error behind the last LOOM_CUDA_LAUNCH_ERROR that a
+ * decode launch returned on this thread ("cudaErrorInvalidValue", ...), "none"
+ * if there was none. With LOOM_DEBUG_LAUNCH set in the environment the name is
+ * also printed on stderr when it happens. */
+const char* loom_cuda_last_launch_failure(void);
+
 /*
  * How the balanced decode kernel fills its shared-memory rings: 0 (default)
  * uses the Tensor Memory Accelerator whenever the cache can be described by a

@@ -26,3 +26,18 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+@pytest.hookimpl(hookwrapper=True)
+def pytest_runtest_makereport(item, call):
+    """A failed GPU test also reports the CUDA error behind the library's last launch failure."""
+    outcome = yield
+    report = outcome.get_result()
+    if report.when == "call" and report.failed and "gpu" in item.keywords:
+        try:
+            from attnarc_b200 import _native
+
+            name = _native.library().loom_cuda_last_launch_failure().decode()
+            report.sections.append(("loom library", f"last launch failure on this thread: {name}"))
+        except Exception:  # the library itself may be what is missing
+            pass
