@@ -41,7 +41,8 @@ FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode partition-kernel
 # launch, from the ncu captures summarised under profiles/ (bytes per launch for
 # the default workload); None until a capture exists for the workload.
-NCU_DRAM_TRAFFIC_BYTES = {"cfg2": 154_178_048 + 3_579_648, "kv-move": 537_019_136 + 486_040_832}
+NCU_DRAM_TRAFFIC_BYTES = {"cfg2": 154_178_048 + 3_579_648, "kv-move": 537_019_136 + 486_040_832,
+                          "kv-swap": 1_073_888_512 + 1_016_135_680}
 
 
 def reference_kernels_baseline(case, config, cache_views, steps):
