@@ -203,6 +203,164 @@ def _default_merge(states, dtype):
     return ops.merge_decode_states(states, dtype)
 
 
+# ------------------------------------------------------------ failure detection
+#
+# The exchange of the long-context mode is the one place where a rank waits for
+# others. Failures are detected on the host, never on the device: a peer that
+# left says so in a key-value store before it goes (or stops updating its
+# heartbeat), and a collective that does not complete within the timeout is
+# reported as a status. The codes are LoomCudaStatus values
+# (include/loom_launch.h): a caller sees the same vocabulary as from a launch.
+
+STATUS_SUCCESS = 0
+STATUS_LAUNCH_ERROR = 3
+STATUS_UNAVAILABLE = 4
+
+
+class RankHealth:
+    """Who is still taking part, kept in a ``torch.distributed`` store.
+
+    Every rank calls ``beat(step)`` between steps (one store write) and
+    ``leave()`` before it stops taking part. ``before_launch()`` is the check a
+    rank makes before it enqueues a step that contains a collective: it returns
+    ``STATUS_UNAVAILABLE`` (and says why in ``last_error``) if a peer has left
+    or has not beaten for ``stale_after`` seconds, so that the caller never
+    launches a collective nobody will join.
+    """
+
+    def __init__(self, store, rank: int, ranks: int, stale_after: float = 30.0, clock=None):
+        import time
+
+        self.store, self.rank, self.ranks = store, int(rank), int(ranks)
+        self.stale_after = float(stale_after)
+        self.clock = clock or time.monotonic
+        self.last_error = ""
+        self._seen: dict[int, tuple[bytes, float]] = {}
+        self.store.set(f"loom/alive/{self.rank}", "0")
+
+    def beat(self, step: int) -> None:
+        self.store.set(f"loom/alive/{self.rank}", str(int(step)))
+
+    def leave(self) -> None:
+        self.store.set(f"loom/alive/{self.rank}", "gone")
+
+    def before_launch(self) -> int:
+        now = self.clock()
+        for peer in range(self.ranks):
+            if peer == self.rank:
+                continue
+            key = f"loom/alive/{peer}"
+            try:
+                present = self.store.check([key])
+                value = self.store.get(key) if present else b""
+            except Exception as error:  # the store itself is gone: nobody can be reached
+                self.last_error = f"rank store unreachable: {error}"
+                return STATUS_UNAVAILABLE
+            if value == b"gone":
+                self.last_error = f"rank {peer} has left the group"
+                return STATUS_UNAVAILABLE
+            previous = self._seen.get(peer)
+            if previous is None or previous[0] != value:
+                self._seen[peer] = (value, now)
+            elif now - previous[1] > self.stale_after:
+                self.last_error = f"rank {peer} has not reported for {now - previous[1]:.1f} s"
+                return STATUS_UNAVAILABLE
+        self.last_error = ""
+        return STATUS_SUCCESS
+
+
+def guarded_all_gather(gathered: torch.Tensor, local: torch.Tensor, group=None,
+                       timeout_seconds: float | None = None) -> tuple[int, str]:
+    """``all_gather_into_tensor`` that reports instead of hanging.
+
+    Without ``timeout_seconds`` the collective is enqueued and the call returns
+    at once (the steady-state path: errors surface through the process group's
+    own timeout). With it, the host waits for completion at most that long.
+    Returns ``(status, message)``: ``STATUS_UNAVAILABLE`` when a peer did not
+    arrive in time or the group is gone, ``STATUS_LAUNCH_ERROR`` for any other
+    failure of the collective. The buffers hold no result after a failure.
+    """
+    import datetime
+
+    import torch.distributed as dist
+
+    try:
+        work = dist.all_gather_into_tensor(gathered, local, group=group, async_op=True)
+        if timeout_seconds is None:
+            work.wait()  # on a CUDA group this orders the current stream after the collective, no host wait
+            return STATUS_SUCCESS, ""
+        work.wait(datetime.timedelta(seconds=float(timeout_seconds)))
+        return STATUS_SUCCESS, ""
+    except Exception as error:  # torch raises RuntimeError / DistBackendError subclasses
+        text = str(error)
+        lowered = text.lower()
+        gone = any(word in lowered for word in ("timeout", "timed out", "connection", "closed", "reset by peer"))
+        return (STATUS_UNAVAILABLE if gone else STATUS_LAUNCH_ERROR), text
+
+
+class LongContextDecoder:
+    """The long-context mode for one batch shape: plan, index tensors and buffers made once.
+
+    Every rank holds the whole (replicated or peer-visible) block table and, in
+    its cache, the blocks of its own ranges. ``decode`` computes partial states
+    of every row (rows the rank holds nothing of give the empty state: max =
+    -inf, sum = 0, which the merge ignores), all-gathers them (``Dv + 2`` floats
+    per query head per rank) and merges: every rank gets the full ``[B, Hq, Dv]``
+    output. A step enqueues three operations (decode, all-gather, merge) and
+    builds nothing on the host. ``timeout_seconds`` bounds the host's wait for
+    the all-gather; ``health`` is consulted before anything is launched.
+    """
+
+    def __init__(self, lengths: Sequence[int], block_tables: torch.Tensor, *, query_heads: int,
+                 value_head_size: int, block_size: int, dtype: torch.dtype, group=None,
+                 split_threshold_tokens: int = 0, decode_states: DecodeStates = _default_decode_states,
+                 merge_states: MergeStates = _default_merge, timeout_seconds: float | None = None,
+                 health: RankHealth | None = None):
+        import torch.distributed as dist
+
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.plan = plan_long_context(lengths, self.world, block_size, split_threshold_tokens)[self.rank]
+        self.dtype = dtype
+        self.decode_states, self.merge_states = decode_states, merge_states
+        self.timeout_seconds, self.health = timeout_seconds, health
+        self.last_error = ""
+        device = block_tables.device
+        batch = len(lengths)
+        self.batch, self.query_heads, self.value_head_size = batch, int(query_heads), int(value_head_size)
+        first_blocks, local_lengths = [0] * batch, [0] * batch
+        for row, first, tokens in zip(self.plan.rows, self.plan.first_blocks, self.plan.lengths):
+            first_blocks[row], local_lengths[row] = first, tokens
+        width = block_tables.shape[1]
+        firsts = torch.tensor(first_blocks, dtype=torch.int64, device=device)
+        columns = (torch.arange(width, device=device).unsqueeze(0) + firsts.unsqueeze(1)).clamp_(max=width - 1)
+        self.block_tables = torch.gather(block_tables, 1, columns).contiguous()
+        self.lengths = torch.tensor(local_lengths, dtype=torch.int32, device=device)
+        self.max_sequence_length = int(max(local_lengths + [1]))
+        self.gathered = torch.empty(self.world * batch * self.query_heads * (self.value_head_size + 2),
+                                    dtype=torch.float32, device=device)
+
+    def decode(self, query: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor, *, scale: float,
+               **decode_kwargs):
+        """Returns the merged ``[B, Hq, Dv]`` rows, or a status code (int) if the step could not run."""
+        if self.health is not None:
+            status = self.health.before_launch()
+            if status != STATUS_SUCCESS:
+                self.last_error = self.health.last_error
+                return status
+        states = self.decode_states(query, key_cache, value_cache, self.block_tables, self.lengths,
+                                    max_sequence_length=self.max_sequence_length, scale=scale, **decode_kwargs)
+        status, message = guarded_all_gather(self.gathered, states.to(torch.float32).reshape(-1), self.group,
+                                             self.timeout_seconds)
+        if status != STATUS_SUCCESS:
+            self.last_error = message
+            return status
+        merged = self.merge_states(
+            self.gathered.view(self.world, self.batch * self.query_heads, self.value_head_size + 2), self.dtype)
+        return merged.reshape(self.batch, self.query_heads, self.value_head_size)
+
+
 def decode_long_context(
     query: torch.Tensor,
     key_cache: torch.Tensor,
@@ -220,34 +378,65 @@ def decode_long_context(
 ) -> torch.Tensor:
     """One decode step of a batch whose long sequences are spread over the ranks.
 
-    Every rank holds the whole (replicated or peer-visible) block table and the
-    blocks of its own ranges in its cache. Each rank computes partial states
-    for its rows, the states are all-gathered (``Dv + 2`` floats per query head
-    per rank), and every rank merges them: all ranks return the full
-    ``[B, Hq, Dv]`` output. Rows that a rank does not own contribute an empty
-    state (max = -inf, sum = 0), which the merge ignores.
+    Convenience form of ``LongContextDecoder`` for a single step (it builds the
+    plan and its tensors, which a serving loop does once per batch shape by
+    keeping the decoder). Raises ``RuntimeError`` if the exchange fails.
     """
-    import torch.distributed as dist
+    decoder = LongContextDecoder(lengths, block_tables, query_heads=query.shape[1],
+                                 value_head_size=value_cache.shape[3], block_size=block_size, dtype=query.dtype,
+                                 group=group, split_threshold_tokens=split_threshold_tokens,
+                                 decode_states=decode_states, merge_states=merge_states)
+    result = decoder.decode(query, key_cache, value_cache, scale=scale, **decode_kwargs)
+    if isinstance(result, int):
+        raise RuntimeError(f"long-context exchange failed (status {result}): {decoder.last_error}")
+    return result
 
-    world = dist.get_world_size(group)
-    rank = dist.get_rank(group)
-    plan = plan_long_context(lengths, world, block_size, split_threshold_tokens)[rank]
-    batch, query_heads, _ = query.shape
-    value_dim = value_cache.shape[3]
-    states = torch.zeros((batch, query_heads, value_dim + 2), dtype=torch.float32, device=query.device)
-    states[:, :, value_dim] = float("-inf")
-    if plan.rows:
-        local_query, tables, local_lengths = local_decode_inputs(plan, query, block_tables)
-        local_states = decode_states(local_query, key_cache, value_cache, tables, local_lengths,
-                                     max_sequence_length=int(max(plan.lengths + [1])), scale=scale,
-                                     **decode_kwargs)
-        # a split sequence appears at most once per rank, so the rows are distinct
-        states.index_copy_(0, torch.tensor(plan.rows, dtype=torch.int64, device=query.device),
-                           local_states.to(torch.float32))
-    gathered = torch.empty(world * states.numel(), dtype=torch.float32, device=query.device)
-    dist.all_gather_into_tensor(gathered, states.reshape(-1), group=group)
-    merged = merge_states(gathered.reshape(world, batch * query_heads, value_dim + 2).contiguous(), query.dtype)
-    return merged.reshape(batch, query_heads, value_dim)
+
+def decode_by_kv_head(
+    query: torch.Tensor,
+    key_cache: torch.Tensor,
+    value_cache: torch.Tensor,
+    block_tables: torch.Tensor,
+    sequence_lengths: torch.Tensor,
+    *,
+    scale: float,
+    max_sequence_length: int,
+    rank: int,
+    ranks: int,
+    key_scales: torch.Tensor | None = None,
+    value_scales: torch.Tensor | None = None,
+    decode: Callable[..., torch.Tensor] | None = None,
+    **decode_kwargs,
+) -> tuple[tuple[int, int], torch.Tensor]:
+    """Decodes this rank's KV heads of every sequence; no communication.
+
+    ``key_cache``/``value_cache`` are logical ``[blocks, block_size, Hkv, D]``
+    views of the full head range (a rank that holds only its own heads passes
+    ``ranks=1``-style arguments instead). The rank's share is the head slice
+    ``[first, first + count)`` given by the partitioner and the query heads of
+    those groups. Returns ((first query head, query head count), ``[B, count *
+    group, Dv]`` rows): disjoint column slices of the full output, the layout
+    tensor parallelism leaves them in.
+    """
+    if decode is None:
+        from . import ops
+
+        decode = ops.paged_decode_attention_ex
+    kv_heads = key_cache.shape[2]
+    group = query.shape[1] // kv_heads
+    first, count = partition_by_kv_head(kv_heads, ranks)[rank]
+    if count == 0:
+        return (first * group, 0), query.new_empty((query.shape[0], 0, value_cache.shape[3]))
+    local_query = query[:, first * group:(first + count) * group]
+    scales = {}
+    if key_scales is not None:
+        per_head = key_scales.numel() > 1
+        scales = dict(key_scales=key_scales[first:first + count].contiguous() if per_head else key_scales,
+                      value_scales=value_scales[first:first + count].contiguous() if per_head else value_scales)
+    output = decode(local_query, key_cache[:, :, first:first + count], value_cache[:, :, first:first + count],
+                    block_tables, sequence_lengths, max_sequence_length=max_sequence_length, scale=scale,
+                    **scales, **decode_kwargs)
+    return (first * group, count * group), output
 
 
 def decode_by_sequence(

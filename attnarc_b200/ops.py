@@ -378,12 +378,17 @@ def paged_decode_attention_ex(
     return output
 
 
-def merge_decode_states(states: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
-    """Merges ``[parts, rows, Dv + 2]`` F32 states into ``[rows, Dv]`` outputs."""
+def merge_decode_states(states: torch.Tensor, out_dtype: torch.dtype,
+                        output: torch.Tensor | None = None) -> torch.Tensor:
+    """Merges ``[parts, rows, Dv + 2]`` F32 states into ``[rows, Dv]`` outputs (into ``output`` if given)."""
     if states.dim() != 3 or states.dtype != torch.float32 or not states.is_contiguous():
         raise RuntimeError("decode states must be a contiguous float32 [parts, rows, Dv + 2] tensor")
     parts, rows, width = states.shape
-    output = torch.empty((rows, width - 2), device=states.device, dtype=out_dtype)
+    if output is None:
+        output = torch.empty((rows, width - 2), device=states.device, dtype=out_dtype)
+    elif (output.dtype != out_dtype or tuple(output.shape) != (rows, width - 2) or not output.is_contiguous()
+          or output.device != states.device):
+        raise RuntimeError("merge output must be a contiguous [rows, Dv] tensor of the requested dtype")
     with _on_device(states.device):
         status = library().loom_cuda_bridge_merge_decode_states(
             states.data_ptr(), states.numel(), parts, rows, width - 2, _DTYPE_CODES[out_dtype],

@@ -238,3 +238,130 @@ def test_by_sequence_decode_keeps_rows_local():
         assert_close(output[live], expected, torch.bfloat16, f"rank {rank}")
         assert all(float(output[i].abs().max()) == 0.0 for i in range(len(rows)) if i not in live)
     assert sorted(covered) == [0, 1, 2, 3]
+
+
+# ------------------------------------------------- KV-head sharding (no exchange)
+
+def test_by_kv_head_decode_covers_disjoint_column_slices():
+    query, keys, values, tables, lengths, block, scale = build_case(13)
+    live = [i for i, n in enumerate(lengths) if n > 0]
+    query, tables = query[live], tables[live]
+    lengths = torch.tensor([lengths[i] for i in live], dtype=torch.int32)
+
+    def states_as_output(q, k, v, t, n, **kwargs):
+        return numpy_merge(numpy_states(q, k, v, t, n, **kwargs).reshape(1, -1, v.shape[3] + 2),
+                           torch.bfloat16).reshape(q.shape[0], q.shape[1], v.shape[3])
+
+    expected = oracle_decode(query, keys, values, tables, lengths, scale=scale, max_sequence_length=int(lengths.max()))
+    result = torch.zeros_like(expected)
+    covered = []
+    for rank in range(2):
+        (first, count), rows = multi_gpu.decode_by_kv_head(
+            query, keys, values, tables, lengths, scale=scale, max_sequence_length=int(lengths.max()),
+            rank=rank, ranks=2, decode=states_as_output)
+        result[:, first:first + count] = rows
+        covered += list(range(first, first + count))
+    assert covered == list(range(query.shape[1]))
+    assert_close(result, expected, torch.bfloat16, "by KV head")
+    # more ranks than KV heads: the surplus ranks get an empty slice and launch nothing
+    (first, count), rows = multi_gpu.decode_by_kv_head(
+        query, keys, values, tables, lengths, scale=scale, max_sequence_length=int(lengths.max()),
+        rank=3, ranks=4, decode=lambda *a, **k: pytest.fail("an empty share must not decode"))
+    assert count == 0 and rows.shape[1] == 0
+
+
+# ------------------------------------------------- failure detection on CPU ranks
+
+def test_rank_health_reports_a_peer_that_left_or_went_silent():
+    import torch.distributed as dist
+
+    store = dist.HashStore()
+    now = [0.0]
+    mine = multi_gpu.RankHealth(store, 0, 2, stale_after=5.0, clock=lambda: now[0])
+    peer = multi_gpu.RankHealth(store, 1, 2, stale_after=5.0, clock=lambda: now[0])
+    assert mine.before_launch() == multi_gpu.STATUS_SUCCESS
+    peer.beat(1)
+    now[0] = 4.0
+    assert mine.before_launch() == multi_gpu.STATUS_SUCCESS
+    now[0] = 8.0  # 4 s since the last change: still fresh
+    assert mine.before_launch() == multi_gpu.STATUS_SUCCESS
+    now[0] = 9.5  # no beat for more than 5 s
+    assert mine.before_launch() == multi_gpu.STATUS_UNAVAILABLE and "not reported" in mine.last_error
+    peer.beat(2)
+    assert mine.before_launch() == multi_gpu.STATUS_SUCCESS
+    peer.leave()
+    assert mine.before_launch() == multi_gpu.STATUS_UNAVAILABLE and "left" in mine.last_error
+
+
+def _late_or_leaving_rank(rank, world, port, results):
+    """Rank 1 first arrives late at an exchange, then leaves between steps."""
+    import datetime
+    import time
+
+    import torch.distributed as dist
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+    store = dist.distributed_c10d._get_default_store()
+    health = multi_gpu.RankHealth(store, rank, world, stale_after=30.0)
+    try:
+        query, keys, values, tables, lengths, block, scale = build_case(11)
+        decoder = multi_gpu.LongContextDecoder(
+            lengths, tables, query_heads=query.shape[1], value_head_size=values.shape[3], block_size=block,
+            dtype=query.dtype, split_threshold_tokens=256, decode_states=numpy_states, merge_states=numpy_merge,
+            timeout_seconds=1.0, health=health)
+        # step 1: both ranks on time
+        first = decoder.decode(query, keys, values, scale=scale)
+        health.beat(1)
+        # step 2: rank 1 arrives three seconds late; rank 0 gives up after one second
+        if rank == 1:
+            time.sleep(3.0)
+        started = time.monotonic()
+        second = decoder.decode(query, keys, values, scale=scale)
+        waited = time.monotonic() - started
+        results[rank] = dict(first_ok=torch.is_tensor(first), second=second if isinstance(second, int) else "rows",
+                             waited=waited, error=decoder.last_error)
+        # step 3: rank 1 leaves between steps; rank 0 learns of it before it launches anything
+        if rank == 1:
+            health.leave()
+            store.set("loom/test/left", "1")
+        else:
+            store.wait(["loom/test/left"], datetime.timedelta(seconds=30))
+            calls = []
+            decoder.decode_states = lambda *a, **k: calls.append(1)
+            third = decoder.decode(query, keys, values, scale=scale)
+            entry = results[rank]
+            entry.update(third=third, launched=len(calls), third_error=decoder.last_error)
+            results[rank] = entry
+    finally:
+        # the late exchange left this group's collectives out of step: no barrier, no orderly shutdown
+        results[f"done{rank}"] = True
+
+
+def test_long_context_exchange_reports_a_late_and_a_departed_rank():
+    import torch.multiprocessing as mp
+
+    with socket.socket() as probe:
+        probe.bind(("127.0.0.1", 0))
+        port = probe.getsockname()[1]
+    manager = mp.Manager()
+    results = manager.dict()
+    context = mp.get_context("spawn")
+    workers = [context.Process(target=_late_or_leaving_rank, args=(rank, 2, port, results)) for rank in range(2)]
+    for worker in workers:
+        worker.start()
+    for worker in workers:
+        worker.join(120)
+    for worker in workers:
+        if worker.is_alive():
+            worker.kill()
+    assert results.get("done0") and results.get("done1")
+    zero = results[0]
+    assert zero["first_ok"]
+    # the late peer: a status within about the timeout, not a hang until it shows up
+    assert zero["second"] == multi_gpu.STATUS_UNAVAILABLE, zero
+    assert zero["waited"] < 2.5 and zero["error"]
+    # the departed peer: refused on the host, nothing launched
+    assert zero["third"] == multi_gpu.STATUS_UNAVAILABLE and zero["launched"] == 0
+    assert "left" in zero["third_error"]
