@@ -102,31 +102,51 @@ def _local_slots(case, renumber, rows: torch.Tensor) -> torch.Tensor:
     return torch.where(local_block < 0, torch.full_like(slots, -1), slots)
 
 
+def whole_case(case) -> RankShard:
+    """The whole batch as the shard of a single rank: the case's own cache, nothing copied."""
+    config = case.config
+    return RankShard(
+        mode="single GPU", rank=0, ranks=1, rows=list(range(config.batch)),
+        query_heads=(0, config.query_heads), kv_heads=(0, config.kv_heads),
+        kv_cache=case.kv_cache, rope_cache=_rope_view(case.kv_cache, config.layout),
+        block_tables=case.block_tables, sequence_lengths=case.sequence_lengths, qkv=case.qkv,
+        positions=case.positions, slot_mapping=case.slot_mapping, key_scales=case.key_scales,
+        value_scales=case.value_scales, max_sequence_length=case.max_sequence_length, kv_bytes=case.kv_bytes)
+
+
 def shard_by_sequence(case, rank: int, ranks: int) -> RankShard:
     """The sequences of ``case`` this rank owns, with their blocks packed into a local cache."""
-    config = case.config
     plan = multi_gpu.plan_by_sequence(case.lengths.tolist(), ranks)[rank]
+    return shard_rows(case, plan.rows, rank, ranks)
+
+
+def shard_rows(case, owned_rows: Sequence[int], rank: int = 0, ranks: int = 1) -> RankShard:
+    """The named sequences of ``case`` with their blocks packed into a local cache."""
+    config = case.config
+
+    owned = list(owned_rows)
+    owned_lengths = [int(case.lengths[r]) for r in owned]
     device = case.kv_cache.device
-    rows = torch.tensor(plan.rows, dtype=torch.int64, device=device)
+    rows = torch.tensor(owned, dtype=torch.int64, device=device)
     block_size = config.block_size
-    tables = case.block_tables[rows] if plan.rows else case.block_tables[:0]
-    lengths = case.sequence_lengths[rows] if plan.rows else case.sequence_lengths[:0]
+    tables = case.block_tables[rows] if owned else case.block_tables[:0]
+    lengths = case.sequence_lengths[rows] if owned else case.sequence_lengths[:0]
     blocks_per_row = (lengths + block_size - 1) // block_size
-    width = int(blocks_per_row.max()) if plan.rows else 1
+    width = int(blocks_per_row.max()) if owned else 1
     tables = tables[:, :width]
     live = torch.arange(width, device=device)[None, :] < blocks_per_row[:, None]
     wanted = tables[live].to(torch.int64)
     local_cache, renumber = _pack_blocks(case, wanted)
     local_tables = torch.where(live, renumber[tables.to(torch.int64)], torch.zeros_like(tables)).contiguous()
     return RankShard(
-        mode="by sequence", rank=rank, ranks=ranks, rows=list(plan.rows),
+        mode="by sequence", rank=rank, ranks=ranks, rows=list(owned),
         query_heads=(0, config.query_heads), kv_heads=(0, config.kv_heads),
         kv_cache=local_cache, rope_cache=_rope_view(local_cache, config.layout),
         block_tables=local_tables.to(torch.int32), sequence_lengths=lengths.contiguous(),
         qkv=case.qkv[rows].contiguous(), positions=case.positions[rows].contiguous(),
         slot_mapping=_local_slots(case, renumber, rows).contiguous(),
         key_scales=case.key_scales, value_scales=case.value_scales,
-        max_sequence_length=max(plan.lengths + [1]), kv_bytes=plan.tokens * config.kv_bytes_per_token)
+        max_sequence_length=max(owned_lengths + [1]), kv_bytes=sum(owned_lengths) * config.kv_bytes_per_token)
 
 
 def shard_by_kv_head(case, rank: int, ranks: int) -> RankShard:
@@ -287,9 +307,11 @@ class ShardedDecodeStep:
         self._graph: torch.cuda.CUDAGraph | None = None
 
     # ---- the step as stream operations ---------------------------------------------------------
-    def enqueue_kernels(self, kv_cache: torch.Tensor | None = None) -> None:
+    def enqueue_kernels(self, kv_cache: torch.Tensor | None = None, rope: bool = True,
+                        exchange: bool = True) -> None:
         """RoPE + KV write, decode and (long-context mode) exchange + merge on the current stream,
-        reading the step's inputs from the device mirror of the host buffer."""
+        reading the step's inputs from the device mirror of the host buffer. ``rope=False`` and
+        ``exchange=False`` leave those parts out (for timing the decode operator alone)."""
         import torch.distributed as dist
 
         kv_cache = self.kv_cache if kv_cache is None else kv_cache
@@ -299,15 +321,16 @@ class ShardedDecodeStep:
         query = qkv[:, :self.query_heads]
         key = qkv[:, self.query_heads:self.query_heads + self.kv_heads]
         value = qkv[:, self.query_heads + self.kv_heads:]
-        ops.rope_paged_kv_write_(query, key, value, self._pieces["positions"], self.cos_sin_cache, kv_cache,
-                                 self.key_scales, self.value_scales, self._pieces["slot_mapping"],
-                                 is_neox=self.is_neox)
+        if rope:
+            ops.rope_paged_kv_write_(query, key, value, self._pieces["positions"], self.cos_sin_cache, kv_cache,
+                                     self.key_scales, self.value_scales, self._pieces["slot_mapping"],
+                                     is_neox=self.is_neox)
         ops.paged_decode_attention_ex(
             query, kv_cache[:, 0], kv_cache[:, 1], self._pieces["block_tables"], self._pieces["sequence_lengths"],
             max_sequence_length=self.max_sequence_length, scale=self.scale, workspace=self._workspace,
             partition_tokens=self._partition, split=self._split, emit_state=self.exchange,
             output=self._states if self.exchange else self.output, **self._decode_scales)
-        if self.exchange:
+        if self.exchange and exchange:
             dist.all_gather_into_tensor(self._gathered.view(-1), self._states.view(-1), group=self.group)
             ops.merge_decode_states(self._gathered, self.output.dtype,
                                     output=self.output.view(self.sequences * self.query_heads, self.head_size))

@@ -3,9 +3,16 @@
 One step = one decode step of a serving batch: the fused RoPE + paged-KV write
 of the batch's new tokens, then paged decode attention over every cached token
 (partition kernel + log-sum-exp merge kernel). The workload is a seeded
-synthetic stand-in for the named attention geometry (default: the
-Qwen2.5-1.5B-shaped BF16 case, 64 sequences of 512..4096 tokens); no dataset or
-model weight is involved.
+synthetic stand-in for the named attention geometry; no dataset or model weight
+is involved. The headline is the largest single-GPU configuration (Llama-3-8B
+shape, BF16, 256 sequences of 1024..8192 tokens, HND cache, 512-token
+partitions); the other configurations are measured beside it and reported under
+`configs`. With N GPUs ONE global batch is spread over the ranks (strong
+scaling): by sequence, by KV head (FP8 workload) or, for the long-context
+workload, by block ranges of the long sequence with an NCCL all-gather of the
+partial states and a merge inside the step. Each rank holds only its share's
+pages and checks its rows against its own single-GPU decode of the global
+batch before anything is timed (`parity_max_abs_err`).
 
     python bench.py --gpus 1 --steps 200 --warmup 20
     python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...
@@ -13,8 +20,8 @@ model weight is involved.
 
 Rank 0 prints one JSON line. `value` is the whole-job KV-read bandwidth with all
 inputs resident in HBM (CUDA-graph replay of exactly K steps, device timed,
-max over ranks); `e2e` is the same metric through the public operator API with
-the step's inputs coming from pinned host memory and its output read back.
+max over ranks); `e2e` is the same metric through the public step API with
+the step's inputs coming from pinned host memory and its rows read back.
 """
 
 from __future__ import annotations
@@ -41,8 +48,10 @@ FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode partition-kernel
 # launch, from the ncu captures summarised under profiles/ (bytes per launch for
 # the default workload); None until a capture exists for the workload.
-NCU_DRAM_TRAFFIC_BYTES = {"cfg2": 154_178_048 + 3_579_648, "kv-move": 537_019_136 + 486_040_832,
-                          "kv-swap": 1_073_888_512 + 1_016_135_680}
+NCU_DRAM_TRAFFIC_BYTES = {"kv-move": 537_019_136 + 486_040_832, "kv-swap": 1_073_888_512 + 1_016_135_680}
+# DRAM bytes (read + written) per algorithmic KV byte of the decode kernel, from one-launch ncu
+# captures on a 24-sequence cut of each workload (cfg2: the whole batch), see profiles/.
+NCU_DRAM_TRAFFIC_PER_KV_BYTE = {"cfg2": (154_178_048 + 3_579_648) / 153_306_112}
 
 
 def reference_kernels_baseline(case, config, cache_views, steps):
@@ -108,7 +117,11 @@ def parse_args():
     parser.add_argument("--steps", type=int, default=200)
     parser.add_argument("--warmup", type=int, default=20)
     parser.add_argument("--impl", choices=["b200", "reference"], default="b200")
-    parser.add_argument("--workload", default="cfg2", help="cfg2 (default), cfg3, cfg4, cfg5, cfg1; kv-move / kv-swap time KV block movement")
+    parser.add_argument("--workload", default="cfg3",
+                        help="cfg3 (default: the largest single-GPU configuration), cfg2, cfg4, cfg5, cfg1; "
+                             "kv-move / kv-swap time KV block movement")
+    parser.add_argument("--sub-configs", default="cfg2,cfg4,cfg5",
+                        help="workloads measured beside the headline and reported under `configs` (\"none\" = skip)")
     parser.add_argument("--seed", type=int, default=0)
     parser.add_argument("--batch", type=int, default=0,
                         help="override the workload's batch size (smaller cases for profiler captures)")
@@ -201,37 +214,64 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(clocks)}
 
 
+# ------------------------------------------------------------------ workloads and sharding
+
+# How each workload is spread over N > 1 GPUs: the sharding BASELINE's configs name.
+SHARDING = {"cfg1": "by sequence", "cfg2": "by sequence", "cfg2-1024": "by sequence", "ref-b8-ctx1024": "by sequence",
+            "cfg3": "by sequence", "cfg4": "by KV head", "cfg5": "long context"}
+COLLECTIVE = {"by sequence": "no collective", "by KV head": "no collective",
+              "long context": "NCCL all-gather of (O, max, sum) states + merge kernel inside the step",
+              "single GPU": "no collective"}
+
+
+def workload_config(args, name):
+    from attnarc_b200 import workloads
+
+    config = workloads.CONFIGS[name]
+    if args.batch:
+        config = workloads.scaled(config, batch=args.batch, name=f"{config.name}-batch{args.batch}")
+    return config
+
+
+def config_record(config, lengths, world):
+    """The `config` object of a line: what is computed, identical for both arms."""
+    mode = SHARDING.get(config.name.split("-batch")[0], "by sequence") if world > 1 else "single GPU"
+    return {
+        "workload": f"{config.name}: {config.description}", "global_batch": config.batch,
+        "query_heads": config.query_heads, "kv_heads": config.kv_heads, "head_size": config.head_size,
+        "block_size": config.block_size, "layout": config.layout, "cache": config.cache,
+        "context_tokens": int(lengths.sum()), "longest_context": int(lengths.max()),
+        "kv_bytes_per_step": int(lengths.sum()) * config.kv_bytes_per_token,
+        "partition_tokens": config.partition_tokens,
+        "parallelism": ("one GPU, no collective" if world == 1 else
+                        f"one global batch {mode} over {world} GPUs, {COLLECTIVE[mode]}"),
+        "step": "fused RoPE + paged-KV write of one new token per sequence, then paged decode attention",
+    }
+
+
 # ------------------------------------------------------------------ CPU arm
 
-_HOST_ARRAYS = {}
+CPU_SAMPLE_KV_BYTES = 512 << 20  # a CPU sample step never reads more KV than this
 
 
-def _host_arrays(case):
-    """Host copies of a case in the oracle's storage convention (made once)."""
-    key = id(case)
-    if key not in _HOST_ARRAYS:
-        from oracle import torch_glue as glue
+def oracle_step_seconds(case, sequences, threads):
+    """Times the CPU oracle (RoPE + paged-KV write, then decode) on the first
+    `sequences` rows of a host-resident case; only the two oracle calls are timed."""
+    from oracle import binding as ob
+    from oracle import torch_glue as glue
 
+    c = case.config
+    host = case.extras.get("host_arrays")
+    if host is None:
         key_view, value_view = case.cache_views()
-        _HOST_ARRAYS.clear()
-        _HOST_ARRAYS[key] = dict(
+        host = dict(
             query=glue.bits(case.query), key=glue.bits(case.key), value=glue.bits(case.value),
             key_cache=glue.bits(key_view), value_cache=glue.bits(value_view),
             positions=glue.bits(case.positions), slots=glue.bits(case.slot_mapping),
             cos_sin=glue.bits(case.cos_sin_cache), tables=glue.bits(case.block_tables),
             lengths=glue.bits(case.sequence_lengths),
             key_scales=case.key_scales.cpu().numpy(), value_scales=case.value_scales.cpu().numpy())
-    return _HOST_ARRAYS[key]
-
-
-def oracle_step_seconds(case, sequences, threads):
-    """Times the CPU oracle (RoPE + paged-KV write, then decode) on the first
-    `sequences` rows of the batch; only the two oracle calls are inside the timer."""
-    from oracle import binding as ob
-    from oracle import torch_glue as glue
-
-    c = case.config
-    host = _host_arrays(case)
+        case.extras["host_arrays"] = host
     dtype = glue.ORACLE_DTYPE[c.torch_dtype]
     fp8 = c.cache == "fp8"
     width = c.head_size
@@ -269,56 +309,62 @@ def oracle_step_seconds(case, sequences, threads):
     return elapsed, tokens * c.kv_bytes_per_token
 
 
-def cpu_baseline(case, budget_seconds, threads):
-    """Oracle throughput on a bounded sample: as many sequences as fit the budget."""
+def cpu_sample_case(config, seed):
+    """A host-resident case holding the first sequences of the global batch (the batch's own
+    lengths, drawn with the bench seed; at most CPU_SAMPLE_KV_BYTES of KV), so that a CPU
+    sample never has to materialise a multi-GB cache on the host. Returns (case, global lengths)."""
+    from attnarc_b200 import workloads
+
+    lengths = workloads.sample_lengths(config, np.random.default_rng(seed))
+    cumulative = np.cumsum(lengths) * config.kv_bytes_per_token
+    sequences = int(max(1, np.searchsorted(cumulative, CPU_SAMPLE_KV_BYTES, side="right")))
+    sequences = min(sequences, config.batch)
+    sample = workloads.scaled(config, batch=sequences, lengths=("fixed", lengths[:sequences].tolist()))
+    return workloads.build_case(sample, "cpu", seed=seed), lengths
+
+
+def sequences_within(case, seconds, threads):
+    """How many of the sample's sequences one CPU step can cover in about `seconds`."""
     probe = min(2, case.config.batch)
     elapsed, sample_bytes = oracle_step_seconds(case, probe, threads)
     per_byte = elapsed / max(sample_bytes, 1)
-    total_bytes = case.kv_bytes
-    sequences = case.config.batch
-    if per_byte * total_bytes > budget_seconds:
-        cumulative = np.cumsum(case.lengths) * case.config.kv_bytes_per_token
-        sequences = int(max(1, np.searchsorted(cumulative * per_byte, budget_seconds)))
+    cumulative = np.cumsum(case.lengths) * case.config.kv_bytes_per_token
+    return int(min(case.config.batch, max(1, np.searchsorted(cumulative * per_byte, seconds))))
+
+
+def cpu_baseline(config, seed, budget_seconds, threads):
+    """Oracle throughput on a bounded sample of the workload (about `budget_seconds` of CPU work)."""
+    case, lengths = cpu_sample_case(config, seed)
+    sequences = sequences_within(case, min(2.0, budget_seconds / 4), threads)
     elapsed, sample_bytes = oracle_step_seconds(case, sequences, threads)
     repeats = int(max(1, min(50, budget_seconds / max(elapsed, 1e-6))))
     total = 0.0
     for _ in range(repeats):
         total += oracle_step_seconds(case, sequences, threads)[0]
     elapsed = total / repeats
-    single, single_bytes = oracle_step_seconds(case, min(sequences, 4), 1)
+    single, single_bytes = oracle_step_seconds(case, min(sequences, 2), 1)
     return {
-        "value": sample_bytes / elapsed / 1e9,
-        "unit": UNIT,
-        "cores": threads,
-        "kind": "port",
-        "sample": f"{repeats} steps over the first {sequences} of {case.config.batch} sequences "
-                  f"({sample_bytes / 1e6:.1f} MB of KV per step, {elapsed:.3f} s per step)",
-        "seconds_per_step": elapsed,
-        "sequences": sequences,
+        "value": sample_bytes / elapsed / 1e9, "unit": UNIT, "cores": threads, "kind": "port",
+        "sample": f"{repeats} steps (RoPE + KV write, then decode) over the first {sequences} of the global batch's "
+                  f"{config.batch} sequences ({sample_bytes / 1e6:.1f} MB of KV per step, {elapsed:.3f} s per step)",
+        "seconds_per_step": elapsed, "sequences": sequences,
         "single_thread_value": single_bytes / single / 1e9,
     }
 
 
 def run_reference(args):
-    """The reference arm: the reference's CPU implementation (this repo's C++
-    restatement of it; the Rust original cannot be built here) on all host cores."""
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+    """The reference arm: the reference's CPU implementation of the path (this repo's C++
+    restatement of its Rust oracle; the original cannot be built here) on all host cores, on
+    the same global batch at every N. Rank 0 alone works and prints."""
+    if int(os.environ.get("RANK", "0")) != 0:
         return
-    from attnarc_b200 import workloads
-    from oracle import binding as ob
-
-    config = workloads.CONFIGS[args.workload]
-    if args.batch:
-        config = workloads.scaled(config, batch=args.batch, name=f"{config.name}-batch{args.batch}")
-    case = workloads.build_case(config, "cpu", seed=args.seed)
+    world = int(os.environ.get("WORLD_SIZE", str(args.gpus)))
+    config = workload_config(args, args.workload)
+    case, lengths = cpu_sample_case(config, args.seed)
     threads = host_threads()
     steps_total = max(1, args.steps + args.warmup)
     budget = max(0.02, min(args.cpu_seconds, 150.0 / steps_total))
-    probe_elapsed, probe_bytes = oracle_step_seconds(case, min(2, config.batch), threads)
-    per_byte = probe_elapsed / max(probe_bytes, 1)
-    cumulative = np.cumsum(case.lengths) * config.kv_bytes_per_token
-    sequences = int(min(config.batch, max(1, np.searchsorted(cumulative * per_byte, budget))))
+    sequences = sequences_within(case, budget, threads)
     for _ in range(args.warmup):
         oracle_step_seconds(case, sequences, threads)
     started = time.perf_counter()
@@ -328,17 +374,15 @@ def run_reference(args):
         total_bytes += step_bytes
     elapsed = time.perf_counter() - started
     value = total_bytes / elapsed / 1e9
+    sample = (f"each step = RoPE + KV write and decode of the first {sequences} of the global batch's "
+              f"{config.batch} sequences on the host ({total_bytes / max(args.steps, 1) / 1e6:.1f} MB of KV)")
     line = {
-        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": elapsed / args.steps * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": elapsed / max(args.steps, 1) * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": config.dtype if config.cache == "native" else "u8", "data": "synthetic",
-        "config": {"workload": f"{config.name}: {config.description}", "batch": config.batch,
-                   "query_heads": config.query_heads, "kv_heads": config.kv_heads,
-                   "head_size": config.head_size, "block_size": config.block_size},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
-                         "sample": f"each step = RoPE+write and decode of the first {sequences} of "
-                                   f"{config.batch} sequences on the host"},
+        "config": config_record(config, lengths, world),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -347,233 +391,274 @@ def run_reference(args):
 
 # ------------------------------------------------------------------ GPU arm
 
-def run_b200(args):
-    import torch
-    import torch.distributed as dist
+class Ranks:
+    """Process-group plumbing of one bench process."""
 
-    from attnarc_b200 import ops, workloads
+    def __init__(self):
+        import torch
+        import torch.distributed as dist
 
-    if args.programmatic_launch is not None:
-        ops.set_programmatic_launch(args.programmatic_launch)
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback for the product path")
+        torch.cuda.set_device(self.local_rank)
+        self.device = torch.device("cuda", self.local_rank)
+        if self.world > 1:
+            dist.init_process_group("nccl", device_id=self.device)
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback for the product path")
-    torch.cuda.set_device(local_rank)
-    device = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=device)
+    def barrier(self):
+        import torch
+        import torch.distributed as dist
 
-    config = workloads.CONFIGS[args.workload]
-    if args.batch:
-        config = workloads.scaled(config, batch=args.batch, name=f"{config.name}-batch{args.batch}")
-    # Weak scaling: every rank serves its own batch of the named shape. The
-    # path needs no exchange between ranks (sequences are independent).
-    case = workloads.build_case(config, device, seed=args.seed + rank, fast_device_fill=True)
-    is_neox = config.rope_style == "neox"
-    fp8 = config.cache == "fp8"
-    kv_bytes = case.kv_bytes
-
-    # Rotate over several copies of the cache so that a step never finds its
-    # KV in the 126 MB L2 left there by the previous step.
-    cache_bytes = case.kv_cache.numel() * case.kv_cache.element_size()
-    copies = args.copies or int(min(8, max(2, (4 << 30) // max(cache_bytes, 1))))
-    caches = [case.kv_cache] + [case.kv_cache.clone() for _ in range(copies - 1)]
-    views = [workloads.logical_cache_views(c, config.layout) for c in caches]
-    rope_views = [c if config.layout == "NHD" else c.permute(0, 1, 3, 2, 4) for c in caches]
-    qkv_steps = [case.qkv.clone() for _ in range(copies)]
-    pristine_qkv = case.qkv.clone()
-
-    sequences, query_heads, kv_heads = config.batch, config.query_heads, config.kv_heads
-    needed, partition = ops.decode_workspace_elements_ex(sequences, query_heads, kv_heads, config.head_size,
-                                                         case.max_sequence_length, config.partition_tokens)
-    split = case.max_sequence_length > partition
-    workspace = torch.empty(needed, device=device, dtype=torch.float32) if split else None
-    output = torch.empty((sequences, query_heads, config.head_size), device=device, dtype=config.torch_dtype)
-    scales = dict(key_scales=case.key_scales, value_scales=case.value_scales) if fp8 else {}
-
-    def qkv_views(buffer):
-        view = buffer.view(sequences, query_heads + 2 * kv_heads, config.head_size)
-        return (view[:, :query_heads], view[:, query_heads:query_heads + kv_heads],
-                view[:, query_heads + kv_heads:])
-
-    def write_step(index):
-        q, k, v = qkv_views(qkv_steps[index])
-        ops.rope_paged_kv_write_(q, k, v, case.positions, case.cos_sin_cache, rope_views[index],
-                                 case.key_scales, case.value_scales, case.slot_mapping, is_neox=is_neox)
-        return q
-
-    def decode_step(index, q):
-        # The rotated Q is read in place from the packed QKV row (strided view).
-        key_cache, value_cache = views[index]
-        ops.paged_decode_attention_ex(q, key_cache, value_cache, case.block_tables, case.sequence_lengths,
-                                      max_sequence_length=case.max_sequence_length, scale=case.scale,
-                                      workspace=workspace, partition_tokens=partition, split=split,
-                                      output=output, **scales)
-
-    def step(index):
-        # RoPE rotates Q/K in place, so a buffer that is reused keeps turning by
-        # the same angle each time it comes round; rotations preserve the norm,
-        # so the values stay N(0,1)-like and the work per step is unchanged.
-        decode_step(index, write_step(index))
-
-    launches_per_step = 2 + (1 if split else 0)
-
-    def barrier():
-        if world > 1:
+        if self.world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for w in range(max(args.warmup, 3)):
-        step(w % copies)
-    barrier()
+    def reduce(self, values, op="max"):
+        """MAX or SUM over ranks of a list of floats."""
+        import torch
+        import torch.distributed as dist
 
-    # ---- device-resident timing: one CUDA graph holding exactly K steps ------
-    stream = torch.cuda.Stream()
-    stream.wait_stream(torch.cuda.current_stream())
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.stream(stream):
-        for w in range(3):
-            step(w % copies)
-        stream.synchronize()
-        with torch.cuda.graph(graph, stream=stream):
-            for k in range(args.steps):
-                step(k % copies)
-    barrier()
-    graph.replay()  # one untimed replay to settle the graph upload
-    barrier()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local_rank) as sampler:
-        barrier()
-        start.record()
-        graph.replay()
-        stop.record()
-        barrier()
-        # keep the GPU under the same load a little longer so the sampler sees it
-        deadline = time.time() + 0.6
-        while time.time() < deadline:
-            graph.replay()
+        tensor = torch.tensor(values, device=self.device, dtype=torch.float64)
+        if self.world > 1:
+            dist.all_reduce(tensor, op=dist.ReduceOp.MAX if op == "max" else dist.ReduceOp.SUM)
+        return [float(x) for x in tensor.tolist()]
+
+    def close(self):
+        import torch.distributed as dist
+
+        if self.world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+
+
+def single_gpu_rows(case):
+    """Attention rows of the whole batch from one GPU (this rank's), through the same operators:
+    the reference the sharded step is compared with, outside any timed region."""
+    import torch
+
+    from attnarc_b200 import ops
+
+    c = case.config
+    rows = case.qkv.clone().view(c.batch, c.query_heads + 2 * c.kv_heads, c.head_size)
+    query = rows[:, :c.query_heads]
+    ops.rope_paged_kv_write_(query, rows[:, c.query_heads:c.query_heads + c.kv_heads],
+                             rows[:, c.query_heads + c.kv_heads:], case.positions, case.cos_sin_cache,
+                             case.rope_cache_argument(), case.key_scales, case.value_scales, case.slot_mapping,
+                             is_neox=c.rope_style == "neox")
+    key_cache, value_cache = case.cache_views()
+    scales = dict(key_scales=case.key_scales, value_scales=case.value_scales) if c.cache == "fp8" else {}
+    out = ops.paged_decode_attention_ex(query, key_cache, value_cache, case.block_tables, case.sequence_lengths,
+                                        max_sequence_length=case.max_sequence_length, scale=case.scale, **scales)
+    torch.cuda.synchronize()
+    return out
+
+
+def measure_workload(args, ranks, name, steps, headline):
+    """Builds the workload's global batch, shards it over the ranks, times it; returns rank-local
+    figures already reduced over ranks (every rank gets the same record)."""
+    import torch
+
+    from attnarc_b200 import ops, sharded_step, workloads
+
+    config = workload_config(args, name)
+    world, rank, device = ranks.world, ranks.rank, ranks.device
+    is_neox = config.rope_style == "neox"
+    fp8 = config.cache == "fp8"
+    # every rank draws the same global batch (same seed), then keeps its share
+    case = workloads.build_case(config, device, seed=args.seed, fast_device_fill=True)
+    global_bytes = case.kv_bytes
+    mode = SHARDING.get(name, "by sequence") if world > 1 else "single GPU"
+    parity = None
+    if world > 1:
+        shard = sharded_step.SHARDERS[mode](case, rank, world)
+        reference_rows = single_gpu_rows(case)  # [B, Hq, D] on this rank's own copy of the global batch
+        first, count = shard.query_heads
+        index = torch.tensor(shard.rows, dtype=torch.int64, device=device)
+        reference_rows = reference_rows[index][:, first:first + count].clone()
+        cos_sin = case.cos_sin_cache
+        lengths = case.lengths
+        del case
+        torch.cuda.empty_cache()
+    else:
+        shard = sharded_step.whole_case(case)
+        cos_sin, lengths = case.cos_sin_cache, case.lengths
+
+    def make_step(rope_cache):
+        return sharded_step.ShardedDecodeStep(shard, cos_sin, rope_cache=rope_cache, dtype=config.torch_dtype,
+                                              scale=1.0 / float(np.sqrt(config.head_size)), is_neox=is_neox,
+                                              partition_tokens=config.partition_tokens)
+
+    # Rotate over several copies of the local cache so that a step never finds its KV in the
+    # 126 MB L2 left there by the previous step.
+    cache_bytes = shard.kv_cache.numel() * shard.kv_cache.element_size()
+    copies = args.copies or int(min(8, max(2, -(-(1 << 30) // max(cache_bytes, 1)))))
+    caches = [shard.kv_cache] + [shard.kv_cache.clone() for _ in range(copies - 1)]
+    layout_view = (lambda c: c) if config.layout == "NHD" else (lambda c: c.permute(0, 1, 3, 2, 4))
+    step = make_step(layout_view(caches[0]))
+    rope_views = [layout_view(c) for c in caches]
+    step.upload()
+    torch.cuda.synchronize()
+
+    if world > 1:
+        got = step.run_eager().to(device)
+        parity = float((got.float() - reference_rows.float()).abs().max()) if got.numel() else 0.0
+        tolerance = 1e-2
+        limit = tolerance + tolerance * float(reference_rows.float().abs().max()) if got.numel() else tolerance
+        if not parity <= limit:
+            raise SystemExit(f"{name}: rank {rank}'s sharded rows differ from the single-GPU decode by {parity}")
+        step.upload()  # fresh, unrotated inputs for the timed runs
         torch.cuda.synchronize()
-    graph_ms = start.elapsed_time(stop)
 
-    # ---- the decode operator on its own, for the roofline ---------------------
-    # A second graph with only the K decode calls (partition kernel + merge
-    # kernel each), timed by CUDA events on the stream that launches it.
-    decode_graph = torch.cuda.CUDAGraph()
-    with torch.cuda.stream(stream):
-        queries = [qkv_views(qkv_steps[index])[0] for index in range(copies)]
-        with torch.cuda.graph(decode_graph, stream=stream):
-            for k in range(args.steps):
-                decode_step(k % copies, queries[k % copies])
-    barrier()
-    decode_graph.replay()
-    barrier()
-    decode_start, decode_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    decode_start.record()
-    decode_graph.replay()
-    decode_stop.record()
-    barrier()
-    decode_ms = decode_start.elapsed_time(decode_stop) / args.steps
+    warmup = max(args.warmup, 3)
+    for w in range(warmup):
+        step.enqueue_kernels(rope_views[w % copies])
+    ranks.barrier()
 
-    # ---- end to end through the public API with host buffers ----------------
-    # attnarc_b200.decode_step.CapturedDecodeStep: the step's inputs (packed QKV
-    # rows, positions, slots, block tables, lengths) sit in one pinned host buffer;
-    # one graph launch copies them in, runs RoPE + KV write and the decode, and
-    # copies the attention rows back to pinned memory; the host waits for them
-    # before it starts the next step. The same sequence issued call by call is
-    # timed beside it (`eager_us_per_step`).
-    from attnarc_b200.decode_step import CapturedDecodeStep
+    def timed_graph(body):
+        stream = torch.cuda.Stream()
+        stream.wait_stream(torch.cuda.current_stream())
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(stream):
+            body(0)
+            stream.synchronize()
+            with torch.cuda.graph(graph, stream=stream):
+                for k in range(steps):
+                    body(k % copies)
+        ranks.barrier()
+        graph.replay()  # one untimed replay to settle the graph upload
+        ranks.barrier()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(ranks.local_rank) as sampler:
+            ranks.barrier()
+            start.record()
+            graph.replay()
+            stop.record()
+            ranks.barrier()
+            # keep the GPU under the same load a little longer so that the sampler sees it
+            deadline = time.time() + (0.6 if headline else 0.35)
+            while time.time() < deadline:
+                graph.replay()
+                torch.cuda.synchronize()
+            ranks.barrier()
+        return start.elapsed_time(stop), sampler.summary()
 
-    host_rows = pristine_qkv.cpu().view(sequences, query_heads + 2 * kv_heads, config.head_size)
-    captured = []
-    for index in range(copies):
-        one = CapturedDecodeStep(
-            rope_views[index], case.cos_sin_cache, sequences=sequences, query_heads=query_heads,
-            max_blocks_per_sequence=case.block_tables.shape[1], max_sequence_length=case.max_sequence_length,
-            dtype=config.torch_dtype, scale=case.scale, is_neox=is_neox,
-            key_scales=case.key_scales if fp8 else None, value_scales=case.value_scales if fp8 else None,
-            partition_tokens=config.partition_tokens)
-        one.host_qkv.copy_(host_rows)
-        one.host_positions.copy_(case.positions.cpu())
-        one.host_slot_mapping.copy_(case.slot_mapping.cpu())
-        one.host_block_tables.copy_(case.block_tables.cpu())
-        one.host_sequence_lengths.copy_(case.sequence_lengths.cpu())
-        captured.append(one.capture())
-    h2d, d2h = captured[0].h2d_bytes, captured[0].d2h_bytes
+    # ---- device-resident timing: one CUDA graph holding exactly `steps` steps ----------------
+    step_ms, clocks = timed_graph(lambda index: step.enqueue_kernels(rope_views[index]))
+    route = ops.last_decode_route() if shard.sequences else "none"
+    # ---- the decode operator alone (decode + merge kernels), for the roofline ----------------
+    decode_ms, _ = timed_graph(lambda index: step.enqueue_kernels(rope_views[index], rope=False, exchange=False))
 
-    def timed_steps(run_step):
-        for w in range(3):
-            run_step(w % copies)
-        barrier()
-        first, last = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        first.record()
-        for k in range(args.steps):
-            run_step(k % copies)  # each waits for its result: the next step depends on it
-        last.record()
-        barrier()
-        return first.elapsed_time(last)
+    record = {}
+    e2e_ms = eager_ms = None
+    if headline:
+        # ---- end to end through the public step API with host buffers ------------------------
+        captured = [make_step(view).capture() for view in rope_views]
 
-    e2e_ms = timed_steps(lambda index: captured[index].run())
-    eager_ms = timed_steps(lambda index: captured[index].run_eager())
+        def timed_steps(run_step):
+            for w in range(3):
+                run_step(w % copies)
+            ranks.barrier()
+            first, last = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            first.record()
+            for k in range(steps):
+                run_step(k % copies)  # each waits for its rows: the next step depends on them
+            last.record()
+            ranks.barrier()
+            return first.elapsed_time(last)
 
-    # ---- reduce over ranks: the slowest rank sets the time -------------------
-    times = torch.tensor([graph_ms, e2e_ms, decode_ms, eager_ms], device=device, dtype=torch.float64)
-    total_bytes = torch.tensor([float(kv_bytes)], device=device, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-        dist.all_reduce(total_bytes, op=dist.ReduceOp.SUM)
-    graph_ms, e2e_ms, decode_ms_max, eager_ms_max = (float(x) for x in times.tolist())
-    job_bytes = float(total_bytes.item())
+        e2e_ms = timed_steps(lambda index: captured[index].run())
+        eager_ms = timed_steps(lambda index: captured[index].run_eager())
 
-    if rank == 0:
-        peak, peak_kind = measured_peak_gbs()
-        value = job_bytes * args.steps / (graph_ms * 1e-3) / 1e9
-        e2e_value = job_bytes * args.steps / (e2e_ms * 1e-3) / 1e9
-        achieved = kv_bytes / (decode_ms * 1e-3) / 1e9
+    if (headline and world == 1 and shard.max_sequence_length <= 1024 and config.layout == "NHD" and not fp8):
+        reference_gpu = reference_kernels_baseline(case, config, case.cache_views(), steps)
+        if reference_gpu is not None:
+            record["reference_gpu_baseline"] = reference_gpu
+
+    launches = step.kernel_launches if shard.sequences else 0
+    step_ms, decode_ms_max = ranks.reduce([step_ms, decode_ms])
+    sums = ranks.reduce([float(shard.kv_bytes), float(step.h2d_bytes), float(step.d2h_bytes), float(launches)], "sum")
+    peak, peak_kind = measured_peak_gbs()
+    us = step_ms / steps * 1e3
+    local_decode_us = decode_ms / steps * 1e3
+    achieved = shard.kv_bytes / (local_decode_us * 1e-6) / 1e9 if shard.kv_bytes else 0.0
+    traffic = NCU_DRAM_TRAFFIC_PER_KV_BYTE.get(name)
+    record.update({
+        "workload": f"{config.name}: {config.description}", "sharding": mode, "n_gpus": world, "steps": steps,
+        "us_per_step": us, "value": global_bytes / (us * 1e-6) / 1e9, "unit": UNIT,
+        "kv_bytes_per_step": global_bytes, "kv_bytes_all_ranks": sums[0],
+        "decode_us_max_over_ranks": decode_ms_max / steps * 1e3,
+        "frac_of_measured_peak_all_gpus": global_bytes / (us * 1e-6) / 1e9 / (peak * world),
+        "roofline": {
+            "bound": "hbm", "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,
+            "peak_source": f"{peak_kind} copy bandwidth", "frac_of_nominal_8TBps": achieved / 8000.0,
+            "kernel": "decode kernel + merge kernel of rank 0 (one operator call), its own CUDA graph",
+            "us_per_launch": local_decode_us, "algorithmic_bytes_per_launch": shard.kv_bytes,
+            "traffic": None if traffic is None else int(traffic * shard.kv_bytes),
+            "traffic_source": None if traffic is None else
+            "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch on a 24-sequence cut of the workload, "
+            "scaled by KV bytes (profiles/)",
+        },
+        "decode_route": route, "clocks": clocks, "parity_max_abs_err": parity,
+        "parity_against": None if parity is None else "this rank's single-GPU decode of the global batch",
+        "l2": f"steps rotate over {copies} copies of the rank's {cache_bytes / 1e6:.0f} MB cache",
+        "gpu_launches": int(sums[3]) * steps,
+    })
+    if parity is not None:
+        record["parity_max_abs_err"] = ranks.reduce([parity])[0]
+    if headline:
+        e2e_ms, eager_ms = ranks.reduce([e2e_ms, eager_ms])
+        record["e2e"] = {"value": global_bytes * steps / (e2e_ms * 1e-3) / 1e9, "unit": UNIT,
+                         "h2d_bytes_per_step": int(sums[1]), "d2h_bytes_per_step": int(sums[2]),
+                         "us_per_step": e2e_ms / steps * 1e3, "eager_us_per_step": eager_ms / steps * 1e3,
+                         "api": "attnarc_b200.sharded_step.ShardedDecodeStep.run (one per rank)"}
+        record["config"] = config_record(config, lengths, world)
+    del caches, step
+    torch.cuda.empty_cache()
+    return record, config
+
+
+def run_b200(args):
+    from attnarc_b200 import ops
+
+    if args.programmatic_launch is not None:
+        ops.set_programmatic_launch(args.programmatic_launch)
+    ranks = Ranks()
+    head, config = measure_workload(args, ranks, args.workload, args.steps, headline=True)
+    others = {}
+    if args.sub_configs != "none":
+        names = [n for n in args.sub_configs.split(",") if n and n != args.workload]
+        for name in names:
+            others[name], _ = measure_workload(args, ranks, name, max(args.steps, 50), headline=False)
+            others[name].pop("gpu_launches", None)
+    if ranks.rank == 0:
         line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": graph_ms / args.steps,
-            "us_per_step": graph_ms / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "u8" if fp8 else config.dtype, "data": "synthetic",
-            "config": {
-                "workload": f"{config.name}: {config.description}", "batch_per_gpu": config.batch,
-                "query_heads": query_heads, "kv_heads": kv_heads, "head_size": config.head_size,
-                "block_size": config.block_size, "layout": config.layout, "cache": config.cache,
-                "context_tokens_rank0": int(case.lengths.sum()), "partition_tokens": partition if split else 0,
-                "kv_bytes_per_step_rank0": kv_bytes, "parallelism": f"sequence-sharded x{world}, no collective",
-                "launch": "cuda_graph of K steps (value); one captured step per launch, host waits for each (e2e)",
-                "programmatic_launch": 1 if args.programmatic_launch is None else args.programmatic_launch,
-                "l2": f"inputs rotate over {copies} cache copies of {cache_bytes / 1e6:.0f} MB (> 126 MB L2 in total)",
-            },
-            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "us_per_step": e2e_ms / args.steps * 1e3,
-                    "eager_us_per_step": eager_ms_max / args.steps * 1e3,
-                    "api": "attnarc_b200.decode_step.CapturedDecodeStep.run"},
-            "gpu_launches": launches_per_step * args.steps,
-            "roofline": {
-                "bound": "hbm", "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,
-                "peak_source": f"{peak_kind} copy bandwidth", "frac_of_nominal_8TBps": achieved / 8000.0,
-                "kernel": "decode partition kernel + merge kernel (one operator call)",
-                "us_per_launch": decode_ms * 1e3, "algorithmic_bytes_per_launch": kv_bytes,
-                "traffic": NCU_DRAM_TRAFFIC_BYTES.get(config.name),
-            },
-            "clocks": sampler.summary(),
-            "decode_route": ops.last_decode_route(),
+            "metric": METRIC, "value": head["value"], "unit": UNIT, "n_gpus": ranks.world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": head["us_per_step"] / 1e3,
+            "us_per_step": head["us_per_step"], "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "u8" if config.cache == "fp8" else config.dtype, "data": "synthetic",
+            "config": head["config"],
+            "protocol": {"value": "one CUDA graph of exactly K steps per rank, inputs resident, CUDA events, "
+                                  "barrier on both sides, max over ranks",
+                         "e2e": "one captured step per launch from one pinned host buffer, rows copied back, "
+                                "host waits for each",
+                         "l2": head["l2"],
+                         "programmatic_launch": 1 if args.programmatic_launch is None else args.programmatic_launch},
+            "e2e": head["e2e"], "gpu_launches": head["gpu_launches"], "roofline": head["roofline"],
+            "clocks": head["clocks"], "decode_route": head["decode_route"], "sharding": head["sharding"],
+            "parity_max_abs_err": head["parity_max_abs_err"], "parity_against": head["parity_against"],
+            "decode_us_max_over_ranks": head["decode_us_max_over_ranks"],
+            "frac_of_measured_peak_all_gpus": head["frac_of_measured_peak_all_gpus"],
+            "configs": others,
         }
-        if world == 1 and not args.no_cpu_baseline:
-            from oracle import binding as ob
-
-            line["cpu_baseline"] = cpu_baseline(case, args.cpu_seconds, host_threads())
-        if world == 1 and case.max_sequence_length <= 1024 and config.layout == "NHD" and not fp8:
-            reference_gpu = reference_kernels_baseline(case, config, views[0], args.steps)
-            if reference_gpu is not None:
-                line["reference_gpu_baseline"] = reference_gpu
+        if "reference_gpu_baseline" in head:
+            line["reference_gpu_baseline"] = head["reference_gpu_baseline"]
+        if ranks.world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(config, args.seed, args.cpu_seconds, host_threads())
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+    ranks.close()
 
 
 # ------------------------------------------------------------------ KV block movement

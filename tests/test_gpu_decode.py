@@ -302,31 +302,35 @@ def test_cfg2_full_size_against_the_oracle(ops):
 
 
 @pytest.mark.parametrize("name", ["cfg3", "cfg4", "cfg5"])
-def test_large_configs_on_a_sequence_subset(ops, name):
-    # Full-size caches are too slow for the F64 oracle; draw the configuration's
-    # lengths, keep its geometry, and check a handful of its sequences
-    # (including the longest) against the oracle.
+def test_large_configs_at_full_size_against_the_oracle(ops, name):
+    # The whole batch of each large configuration (256 sequences in an HND cache; 128 sequences
+    # over a per-head FP8 cache; the skewed batch with its 131072-token row) against the F64
+    # oracle on all host cores: the balanced schedule with items split across many CTAs, and the
+    # caller-fixed 512-token partitions the Llama-3-8B-shaped configuration names.
+    import os
+
     config = workloads.CONFIGS[name]
-    rng = np.random.default_rng(5)
-    lengths = workloads.sample_lengths(config, rng)
-    keep = np.argsort(lengths)[[0, len(lengths) // 2, -1]]
+    case = workloads.build_case(config, DEVICE, seed=6, fast_device_fill=True)
+    assert case.config.batch == config.batch and int(case.lengths.max()) == case.max_sequence_length
     if name == "cfg5":
-        keep = np.argsort(lengths)[[0, -1]]
-        chosen = np.minimum(lengths[keep], 20000)  # the 131072-token row is checked by properties below
-    else:
-        chosen = lengths[keep]
-    small = workloads.scaled(config, batch=len(chosen), lengths=("fixed", chosen.tolist()))
-    case = workloads.build_case(small, DEVICE, seed=6)
+        assert case.max_sequence_length == 131072
     key_cache, value_cache = case.cache_views()
     query = case.query.contiguous()
     scales = dict(key_scales=case.key_scales, value_scales=case.value_scales) if config.cache == "fp8" else {}
-    expected = helpers.oracle_decode(query, key_cache, value_cache, case.block_tables, case.sequence_lengths,
-                                     scale=case.scale, max_sequence_length=case.max_sequence_length, **scales)
-    actual = ops.paged_decode_attention_ex(query, key_cache, value_cache, case.block_tables,
-                                           case.sequence_lengths,
-                                           max_sequence_length=case.max_sequence_length, scale=case.scale,
-                                           partition_tokens=config.partition_tokens, split=True, **scales)
-    helpers.assert_close(actual, expected, config.torch_dtype, name)
+    threads = max(1, len(os.sched_getaffinity(0)))
+    expected = helpers.oracle_decode(query, key_cache.contiguous(), value_cache.contiguous(), case.block_tables,
+                                     case.sequence_lengths, scale=case.scale,
+                                     max_sequence_length=case.max_sequence_length, threads=threads, **scales)
+    routes = []
+    for partition in (0, 512):
+        actual = ops.paged_decode_attention_ex(query, key_cache, value_cache, case.block_tables,
+                                               case.sequence_lengths,
+                                               max_sequence_length=case.max_sequence_length, scale=case.scale,
+                                               partition_tokens=partition, split=True, **scales)
+        routes.append(ops.last_decode_route())
+        helpers.assert_close(actual, expected, config.torch_dtype, f"{name} partition_tokens={partition}")
+    assert "balanced" in routes[0] and "balanced" not in routes[1], routes
+    assert ops.decode_timeout_flag() == 0
 
 
 def test_long_context_properties_at_full_length(ops):

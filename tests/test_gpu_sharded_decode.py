@@ -58,3 +58,87 @@ def test_by_sequence_plan_covers_the_batch():
         if rows:
             result[rows] = output.cpu()
     assert_close(result, expected_output(query, keys, values, tables, lengths, scale), torch.bfloat16, "by sequence")
+
+
+# ---- the rank steps of attnarc_b200.sharded_step, one rank after the other on one GPU ----------
+
+def _small_case(name, batch, lengths, seed):
+    from attnarc_b200 import workloads
+
+    config = workloads.scaled(workloads.CONFIGS[name], batch=batch, lengths=("fixed", lengths))
+    return config, workloads.build_case(config, torch.device("cuda:0"), seed=seed)
+
+
+def _oracle_rows(case):
+    """Oracle attention rows of the global batch after the oracle's own RoPE + KV write."""
+    from tests.helpers import oracle_rope_write
+
+    config = case.config
+    key_view, value_view = case.cache_views()
+    fp8 = config.cache == "fp8"
+    scales = dict(key_scales=case.key_scales, value_scales=case.value_scales) if fp8 else {}
+    query, _, key_cache, value_cache = oracle_rope_write(
+        case.query, case.key, case.value, case.positions, case.cos_sin_cache, key_view, value_view,
+        case.slot_mapping, is_neox=config.rope_style == "neox", key_scales=case.key_scales,
+        value_scales=case.value_scales)
+    return oracle_decode(query, key_cache, value_cache, case.block_tables, case.sequence_lengths,
+                         scale=case.scale, max_sequence_length=case.max_sequence_length, **scales)
+
+
+def _step(shard, case):
+    from attnarc_b200 import sharded_step
+
+    config = case.config
+    return sharded_step.ShardedDecodeStep(shard, case.cos_sin_cache, dtype=config.torch_dtype, scale=case.scale,
+                                          is_neox=config.rope_style == "neox",
+                                          partition_tokens=config.partition_tokens)
+
+
+@pytest.mark.parametrize("name,mode,ranks", [("cfg3", "by sequence", 4), ("cfg2", "by sequence", 8),
+                                             ("cfg4", "by KV head", 8), ("cfg4", "by KV head", 2)])
+def test_rank_steps_without_exchange_cover_the_batch(name, mode, ranks):
+    from attnarc_b200 import sharded_step
+
+    config, case = _small_case(name, 6, [700, 33, 1500, 16, 257, 1024], seed=31)
+    expected = _oracle_rows(case)
+    result = torch.zeros_like(expected)
+    seen = torch.zeros(expected.shape[:2], dtype=torch.int32)
+    local_bytes = 0
+    for rank in range(ranks):
+        shard = sharded_step.SHARDERS[mode](case, rank, ranks)
+        local_bytes += shard.kv_bytes
+        assert shard.kv_cache.data_ptr() != case.kv_cache.data_ptr()  # the rank holds its own pages only
+        step = _step(shard, case)
+        eager = step.run_eager().clone()
+        rows = step.capture().run()  # the captured step repeats the eager one bit for bit
+        assert torch.equal(rows.view(torch.int16), eager.view(torch.int16))
+        placed = sharded_step.gather_rows(shard, rows, expected.shape)
+        first, count = shard.query_heads
+        if shard.rows:
+            result[shard.rows, first:first + count] = placed[shard.rows, first:first + count]
+            seen[shard.rows, first:first + count] += 1
+    assert bool((seen == 1).all()), "every (sequence, query head) row belongs to exactly one rank"
+    assert local_bytes == case.kv_bytes
+    assert_close(result, expected, config.torch_dtype, f"{name} {mode} x{ranks}")
+
+
+@pytest.mark.parametrize("ranks", [2, 8])
+def test_long_context_rank_steps_merge_to_the_oracle(ranks):
+    from attnarc_b200 import ops, sharded_step
+
+    config, case = _small_case("cfg5", 4, [9000, 40, 700, 16], seed=37)
+    expected = _oracle_rows(case)
+    batch, heads, dim = expected.shape
+    stacked = torch.zeros((ranks, batch * heads, dim + 2), dtype=torch.float32, device="cuda:0")
+    writers = 0
+    for rank in range(ranks):
+        shard = sharded_step.shard_long_context(case, rank, ranks)
+        assert shard.exchange and shard.sequences == batch
+        writers += int((shard.slot_mapping >= 0).sum())
+        step = _step(shard, case)
+        step.upload()
+        step.enqueue_kernels(exchange=False)  # this rank's states of every row (empty where it holds nothing)
+        stacked[rank] = step._states.view(batch * heads, dim + 2)
+    assert writers == batch, "the new token of every sequence is written by exactly one rank"
+    merged = ops.merge_decode_states(stacked, config.torch_dtype).view(batch, heads, dim)
+    assert_close(merged.cpu(), expected, config.torch_dtype, f"long context x{ranks}")
