@@ -380,18 +380,21 @@ __global__ void __launch_bounds__(kThreads) block_table_remap_kernel(int32_t* ta
 std::atomic<uint32_t> g_move_engine{0};
 
 // Raises a bulk kernel's dynamic shared-memory limit once per device (bit d of `prepared`).
+// Returns a LoomCudaStatus; a failure is recorded for loom_cuda_last_launch_failure().
 template <typename Kernel>
-bool raise_shared_limit(Kernel kernel, uint32_t bytes, std::atomic<uint64_t>& prepared) {
+int raise_shared_limit(Kernel kernel, uint32_t bytes, std::atomic<uint64_t>& prepared) {
   int device = 0;
-  if (cudaGetDevice(&device) != cudaSuccess) return false;
-  if (device < 64 && (prepared.load(std::memory_order_acquire) & (1ull << device))) return true;
-  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) !=
-      cudaSuccess) {
-    cudaGetLastError();
-    return false;
+  if (const cudaError_t status = cudaGetDevice(&device); status != cudaSuccess) {
+    return loom_launch::failed(status, "current device query before a KV block movement launch");
+  }
+  if (device < 64 && (prepared.load(std::memory_order_acquire) & (1ull << device))) return LOOM_CUDA_SUCCESS;
+  if (const cudaError_t status =
+          cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+      status != cudaSuccess) {
+    return loom_launch::failed(status, "shared-memory limit of a KV block movement kernel (cudaFuncSetAttribute)");
   }
   if (device < 64) prepared.fetch_or(1ull << device, std::memory_order_release);
-  return true;
+  return LOOM_CUDA_SUCCESS;
 }
 
 // The address a kernel uses for `pointer`: itself for device or managed memory,
@@ -425,11 +428,7 @@ int sm_count() {
 bool aligned16(const void* pointer) { return (reinterpret_cast<uintptr_t>(pointer) & 15u) == 0; }
 
 int finish(cudaError_t launch_result) {
-  if (launch_result != cudaSuccess) {
-    cudaGetLastError();
-    return LOOM_CUDA_LAUNCH_ERROR;
-  }
-  return LOOM_CUDA_SUCCESS;
+  return loom_launch::failed(launch_result, "KV block movement kernel launch");
 }
 
 uint32_t grid_for(uint64_t units, int sms) {
@@ -501,7 +500,7 @@ int loom_cuda_kv_block_move(const void* source_key_cache, const void* source_val
   if (bulk_chunks > 0xffffffffull) return LOOM_CUDA_UNSUPPORTED;
   p.chunks_per_block = (uint32_t)bulk_chunks;
   static std::atomic<uint64_t> prepared{0};
-  if (!raise_shared_limit(kv_block_move_bulk_kernel, kBulkSharedBytes, prepared)) return LOOM_CUDA_LAUNCH_ERROR;
+  if (const int limit = raise_shared_limit(kv_block_move_bulk_kernel, kBulkSharedBytes, prepared); limit != LOOM_CUDA_SUCCESS) return limit;
   const uint64_t units = (uint64_t)pair_count * 2u * bulk_chunks;
   const uint64_t resident = (uint64_t)sms * kBulkCtasPerSm;
   return finish(loom_launch::launch(kv_block_move_bulk_kernel, dim3((uint32_t)(units < resident ? units : resident)),
@@ -558,7 +557,16 @@ int loom_cuda_kv_block_swap(void* key_cache, void* value_cache, const int64_t* b
   p.pair_count = pair_count;
   p.blocks = num_blocks;
   p.chunks_per_block = (uint32_t)chunks;
-  if (g_move_engine.load(std::memory_order_relaxed) == 1) {
+  // As for a move: a cache in pinned host memory is exchanged over PCIe by the vector engine through
+  // its mapped device address; memory the device cannot address is refused before any launch.
+  bool host = false;
+  const uint8_t* view[2] = {nullptr, nullptr};
+  if (!device_view(key_cache, &view[0], &host) || !device_view(value_cache, &view[1], &host)) {
+    return LOOM_CUDA_INVALID_ARGUMENT;
+  }
+  p.cache[0] = const_cast<uint8_t*>(view[0]);
+  p.cache[1] = const_cast<uint8_t*>(view[1]);
+  if (host || g_move_engine.load(std::memory_order_relaxed) == 1) {
     const uint64_t units = (uint64_t)pair_count * 2u * chunks * 2u;
     return finish(loom_launch::launch(kv_block_swap_kernel, dim3(grid_for(units, sms)), dim3(kThreads), 0,
                                       static_cast<cudaStream_t>(stream), p));
@@ -567,7 +575,7 @@ int loom_cuda_kv_block_swap(void* key_cache, void* value_cache, const int64_t* b
   if (bulk_chunks > 0xffffffffull) return LOOM_CUDA_UNSUPPORTED;
   p.chunks_per_block = (uint32_t)bulk_chunks;
   static std::atomic<uint64_t> prepared{0};
-  if (!raise_shared_limit(kv_block_swap_bulk_kernel, kSwapSharedBytes, prepared)) return LOOM_CUDA_LAUNCH_ERROR;
+  if (const int limit = raise_shared_limit(kv_block_swap_bulk_kernel, kSwapSharedBytes, prepared); limit != LOOM_CUDA_SUCCESS) return limit;
   const uint64_t units = (uint64_t)pair_count * 2u * bulk_chunks;
   const uint64_t resident = (uint64_t)sms * kBulkCtasPerSm;
   return finish(loom_launch::launch(kv_block_swap_bulk_kernel, dim3((uint32_t)(units < resident ? units : resident)),

@@ -23,9 +23,48 @@
 #include <cuda_runtime.h>
 
 #include <atomic>
+#include <cstdio>
+#include <cstdlib>
 #include <utility>
 
 namespace loom_launch {
+
+// ---- what went wrong, for the caller who only sees LOOM_CUDA_LAUNCH_ERROR -----------------
+//
+// Every runtime call on a launch path of this library (kernel launches, the
+// shared-memory limit of a kernel, device queries) reports its failure through
+// `failed()`: the error and the place are remembered per thread (read with
+// loom_cuda_last_launch_failure), printed when LOOM_DEBUG_LAUNCH is set, and the
+// runtime's own last-error slot is cleared so that the failure cannot be
+// mistaken for the result of a later call.
+struct Failure {
+  cudaError_t error;
+  const char* where;
+};
+inline Failure& last_failure() {
+  static thread_local Failure failure{cudaSuccess, "none"};
+  return failure;
+}
+
+// Launches that the runtime refused with the programmatic-launch attribute and
+// that were then issued as plain launches (process-wide count).
+inline std::atomic<uint64_t>& plain_retries() {
+  static std::atomic<uint64_t> count{0};
+  return count;
+}
+
+// LoomCudaStatus of a runtime status: 0 (success) or 3 (launch error).
+inline int failed(cudaError_t status, const char* where) {
+  if (status == cudaSuccess) return 0;
+  cudaGetLastError();
+  last_failure() = Failure{status, where};
+  static const bool verbose = std::getenv("LOOM_DEBUG_LAUNCH") != nullptr;
+  if (verbose) {
+    std::fprintf(stderr, "loom launch failed at %s: %s (%s)\n", where, cudaGetErrorName(status),
+                 cudaGetErrorString(status));
+  }
+  return 3;
+}
 
 // 0 = plain launches; 1 = programmatic launch.
 inline std::atomic<uint32_t>& programmatic_mode() {
@@ -52,7 +91,13 @@ cudaError_t launch(void (*kernel)(Params...), dim3 grid, dim3 block, size_t shar
   if (status != cudaSuccess && config.numAttrs != 0) {
     // The attribute is an optimisation: a launch refused with it is tried once as a plain launch
     // (a genuine configuration error fails again and is reported).
+    static const bool verbose = std::getenv("LOOM_DEBUG_LAUNCH") != nullptr;
+    if (verbose) {
+      std::fprintf(stderr, "loom: launch with the programmatic attribute refused (%s), retried as a plain launch\n",
+                   cudaGetErrorName(status));
+    }
     cudaGetLastError();
+    plain_retries().fetch_add(1, std::memory_order_relaxed);
     config.attrs = nullptr;
     config.numAttrs = 0;
     status = cudaLaunchKernelEx(&config, kernel, args...);

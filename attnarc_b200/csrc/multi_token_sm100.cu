@@ -73,11 +73,7 @@ extern "C" int loom_cuda_expand_query_tokens(const int32_t* block_tables, const 
       expand_query_tokens_kernel, dim3((uint32_t)(wanted < resident ? wanted : resident)), dim3(kThreads), 0,
       static_cast<cudaStream_t>(stream), block_tables, sequence_lengths, expanded_block_tables,
       expanded_sequence_lengths, sequences, query_tokens, max_blocks_per_sequence);
-  if (status != cudaSuccess) {
-    cudaGetLastError();
-    return LOOM_CUDA_LAUNCH_ERROR;
-  }
-  return LOOM_CUDA_SUCCESS;
+  return loom_launch::failed(status, "query-token expansion kernel launch");
 }
 
 // ---- one pass over the KV for all query tokens ------------------------------------------
@@ -268,11 +264,7 @@ int device_sms() {
   return sms;
 }
 
-int launch_status(cudaError_t status) {
-  if (status == cudaSuccess) return LOOM_CUDA_SUCCESS;
-  cudaGetLastError();
-  return LOOM_CUDA_LAUNCH_ERROR;
-}
+int launch_status(cudaError_t status) { return loom_launch::failed(status, "multi-token kernel launch"); }
 
 }  // namespace
 

@@ -318,17 +318,10 @@ merge_stream_kernel(const float* __restrict__ slots, const uint32_t* __restrict_
 
 thread_local const char* g_last_route = "none";
 
-// Launch status of this library from a runtime status (clears a sticky error).
-thread_local cudaError_t g_last_launch_failure = cudaSuccess;  // read by loom_cuda_last_launch_failure()
-
-int launched(cudaError_t status) {
-  if (status == cudaSuccess) return LOOM_CUDA_SUCCESS;
-  cudaGetLastError();
-  g_last_launch_failure = status;
-  // LOOM_DEBUG_LAUNCH=1 names the runtime error behind a LOOM_CUDA_LAUNCH_ERROR on stderr
-  static const bool verbose = std::getenv("LOOM_DEBUG_LAUNCH") != nullptr;
-  if (verbose) std::fprintf(stderr, "loom launch failed: %s (%s)\n", cudaGetErrorName(status), cudaGetErrorString(status));
-  return LOOM_CUDA_LAUNCH_ERROR;
+// Launch status of this library from a runtime status; the error and where it arose are kept
+// for loom_cuda_last_launch_failure().
+int launched(cudaError_t status, const char* where = "decode kernel launch") {
+  return loom_launch::failed(status, where);
 }
 
 bool aligned16(const void* pointer) { return (reinterpret_cast<uintptr_t>(pointer) & 15u) == 0; }
@@ -384,7 +377,9 @@ int launch_mma(const DecodeParams& p, cudaStream_t stream) {
   static std::atomic<uint64_t> configured{0};
   constexpr int kBytes = mma_smem_bytes<kFp8, kD, kNT>();
   auto kernel = decode_mma_kernel<QT, kFp8, kD, kNT>;
-  if (ensure_smem(kernel, kBytes, configured) != cudaSuccess) return LOOM_CUDA_LAUNCH_ERROR;
+  if (const cudaError_t limit = ensure_smem(kernel, kBytes, configured); limit != cudaSuccess) {
+    return launched(limit, "shared-memory limit of a decode kernel (cudaFuncSetAttribute)");
+  }
   const uint32_t head_chunks = (p.group + 8 * kNT - 1) / (8 * kNT);
   const dim3 grid(p.sequences * p.max_partitions, p.kv_heads * head_chunks, 1);
   return launched(loom_launch::launch(kernel, grid, dim3(kMmaThreads), kBytes, stream, p));
@@ -395,7 +390,9 @@ int launch_stream(const DecodeParams& p, uint32_t ctas, cudaStream_t stream) {
   static std::atomic<uint64_t> configured{0};
   constexpr int kBytes = StreamRing<kFp8, kD, kNT>::kSmemBytes;
   auto kernel = decode_stream_kernel<QT, kFp8, kD, kNT>;
-  if (ensure_smem(kernel, kBytes, configured) != cudaSuccess) return LOOM_CUDA_LAUNCH_ERROR;
+  if (const cudaError_t limit = ensure_smem(kernel, kBytes, configured); limit != cudaSuccess) {
+    return launched(limit, "shared-memory limit of a decode kernel (cudaFuncSetAttribute)");
+  }
   return launched(loom_launch::launch(kernel, dim3(ctas), dim3(kMmaThreads), kBytes, stream, p));
 }
 
@@ -497,7 +494,9 @@ int launch_stream_tma(const DecodeParams& p, uint32_t ctas, const CacheMaps& map
   static std::atomic<uint64_t> configured{0};
   constexpr int kBytes = TmaRing<kFp8, kD, kNT>::kSmemBytes;
   auto kernel = decode_stream_tma_kernel<QT, kFp8, kD, kNT>;
-  if (ensure_smem(kernel, kBytes, configured) != cudaSuccess) return LOOM_CUDA_LAUNCH_ERROR;
+  if (const cudaError_t limit = ensure_smem(kernel, kBytes, configured); limit != cudaSuccess) {
+    return launched(limit, "shared-memory limit of a decode kernel (cudaFuncSetAttribute)");
+  }
   return launched(loom_launch::launch(kernel, dim3(ctas), dim3(kMmaThreads), kBytes, stream, p, maps.key, maps.value,
                                       maps.axes));
 }
@@ -507,7 +506,9 @@ int launch_umma_fp8(const DecodeParams& p, uint32_t ctas, const CacheMaps& maps,
   static std::atomic<uint64_t> configured{0};
   constexpr int kBytes = UmmaSmem::kBytes;
   auto kernel = decode_umma_fp8_kernel<QT>;
-  if (ensure_smem(kernel, kBytes, configured) != cudaSuccess) return LOOM_CUDA_LAUNCH_ERROR;
+  if (const cudaError_t limit = ensure_smem(kernel, kBytes, configured); limit != cudaSuccess) {
+    return launched(limit, "shared-memory limit of a decode kernel (cudaFuncSetAttribute)");
+  }
   return launched(loom_launch::launch(kernel, dim3(ctas), dim3(kUmmaThreads), kBytes, stream, p, maps.key, maps.value,
                                       maps.axes));
 }
@@ -828,7 +829,7 @@ int launch_decode(const LoomDecodeArgs& a) {
     else LOOM_MERGE(__nv_bfloat16);
 #undef LOOM_MERGE
   }
-  return launched(merge_status);
+  return launched(merge_status, "merge kernel launch");
 }
 
 // The reference ABI: dense-inner NHD caches, block stride free.
@@ -919,6 +920,10 @@ float* built_in_scratch_address(cudaError_t* failure) {
 void explain(char* text, uint64_t capacity, const char* format, unsigned long long a = 0,
              unsigned long long b = 0) {
   if (text != nullptr && capacity != 0) std::snprintf(text, (size_t)capacity, format, a, b);
+}
+
+void explain_text(char* text, uint64_t capacity, const char* message) {
+  if (text != nullptr && capacity != 0) std::snprintf(text, (size_t)capacity, "%s", message);
 }
 
 }  // namespace loom_decode
@@ -1028,7 +1033,7 @@ extern "C" int loom_cuda_merge_decode_states(const float* states, uint32_t parts
   else if (out_dtype == 1) LOOM_MERGE(__half);
   else LOOM_MERGE(__nv_bfloat16);
 #undef LOOM_MERGE
-  return launched(status);
+  return launched(status, "merge kernel launch");
 }
 
 extern "C" int loom_cuda_supports_paged_decode(uint32_t dtype, uint32_t cache_encoding, uint32_t sequences,
@@ -1059,8 +1064,15 @@ extern "C" int loom_cuda_supports_paged_decode(uint32_t dtype, uint32_t cache_en
 extern "C" const char* loom_cuda_last_decode_route(void) { return loom_decode::g_last_route; }
 
 extern "C" const char* loom_cuda_last_launch_failure(void) {
-  return loom_decode::g_last_launch_failure == cudaSuccess ? "none"
-                                                           : cudaGetErrorName(loom_decode::g_last_launch_failure);
+  const loom_launch::Failure& failure = loom_launch::last_failure();
+  if (failure.error == cudaSuccess) return "none";
+  static thread_local char text[192];
+  std::snprintf(text, sizeof(text), "%s at %s", cudaGetErrorName(failure.error), failure.where);
+  return text;
+}
+
+extern "C" uint64_t loom_cuda_plain_launch_retries(void) {
+  return loom_launch::plain_retries().load(std::memory_order_relaxed);
 }
 
 extern "C" int loom_cuda_set_decode_copy_engine(uint32_t engine) {
@@ -1142,6 +1154,6 @@ extern "C" int loom_cuda_paged_decode_attention_built_in_scratch(const LoomDecod
   with_scratch.workspace = scratch;
   with_scratch.workspace_elements = kBuiltInScratchFloats;
   const int status = launch_decode(with_scratch);
-  if (status != LOOM_CUDA_SUCCESS) explain(error_text, error_capacity, loom_cuda_status_string(status));
+  if (status != LOOM_CUDA_SUCCESS) explain_text(error_text, error_capacity, loom_cuda_status_string(status));
   return status;
 }

@@ -394,24 +394,23 @@ int launch_typed(const RopeParams& p, cudaStream_t stream) {
                                (uint64_t)p.kv_heads * (tail_units + value_units);
     const uint64_t blocks = ((uint64_t)p.tokens * per_token + kThreads - 1) / kThreads;
     if (per_token > 0xffffffffull || blocks > 0x7fffffffull) return LOOM_CUDA_INVALID_ARGUMENT;
-    if (loom_launch::launch(rope_paged_kv_vector_kernel<T, kFp8>, dim3((uint32_t)blocks), dim3(kThreads), 0,
-                            stream, p, rotary_units, tail_units, value_units, (uint32_t)per_token) != cudaSuccess) {
-      cudaGetLastError();
-      return LOOM_CUDA_LAUNCH_ERROR;
-    }
+    return loom_launch::failed(
+        loom_launch::launch(rope_paged_kv_vector_kernel<T, kFp8>, dim3((uint32_t)blocks), dim3(kThreads), 0, stream,
+                            p, rotary_units, tail_units, value_units, (uint32_t)per_token),
+        "RoPE + paged-KV write kernel launch");
   } else {
     const uint64_t per_token =
         (uint64_t)heads * (p.rotary_dim / 2) +
         (uint64_t)p.kv_heads * ((p.head_size - p.rotary_dim) + p.value_head_size);
     const uint64_t blocks = ((uint64_t)p.tokens * per_token + kThreads - 1) / kThreads;
     if (per_token > 0xffffffffull || blocks > 0x7fffffffull) return LOOM_CUDA_INVALID_ARGUMENT;
-    if (loom_launch::launch(rope_paged_kv_scalar_kernel<T, kFp8>, dim3((uint32_t)blocks), dim3(kThreads), 0,
-                            stream, p, (uint32_t)per_token) != cudaSuccess) {
-      cudaGetLastError();
-      return LOOM_CUDA_LAUNCH_ERROR;
-    }
+    // The status is this launch's own: an error that some earlier call of the process left in the
+    // runtime's last-error slot is not this operator's failure and is not looked at.
+    return loom_launch::failed(
+        loom_launch::launch(rope_paged_kv_scalar_kernel<T, kFp8>, dim3((uint32_t)blocks), dim3(kThreads), 0, stream,
+                            p, (uint32_t)per_token),
+        "RoPE + paged-KV write kernel launch");
   }
-  return cudaGetLastError() == cudaSuccess ? LOOM_CUDA_SUCCESS : LOOM_CUDA_LAUNCH_ERROR;
 }
 
 // Argument rules of the reference launcher (rope_paged_kv.cu:231-250).
