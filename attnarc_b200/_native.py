@@ -84,6 +84,9 @@ def _declare(lib):
     lib.loom_cuda_last_decode_route.argtypes = []
     lib.loom_cuda_last_launch_failure.restype = ctypes.c_char_p
     lib.loom_cuda_last_launch_failure.argtypes = []
+    lib.loom_cuda_plain_launch_retries.restype = u64
+    lib.loom_cuda_plain_launch_retries.argtypes = []
+    lib.loom_cuda_set_wait_policy.argtypes = [u32, u32]
     lib.loom_cuda_set_decode_copy_engine.argtypes = [u32]
     lib.loom_cuda_set_programmatic_launch.argtypes = [u32]
     lib.loom_cuda_decode_timeout_flag.argtypes = [ctypes.POINTER(u32), u32]

@@ -46,6 +46,8 @@ struct DecodeParams {
   uint64_t k_block, k_page, k_head, v_block, v_page, v_head;  // element strides
   uint64_t q_token, q_head;                                   // element strides of the query
   float scale_log2;  // softmax scale * log2(e)
+  uint32_t wait_attempts;         // polls after which a wait on a copy barrier gives up
+  uint32_t wait_unmatched_bytes;  // self-test: barriers are armed for this many bytes too many
 };
 
 // ---------------------------------------------------------------- PTX

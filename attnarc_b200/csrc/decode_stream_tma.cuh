@@ -20,9 +20,13 @@
 // beyond the sequence length before using them, and masks the matching scores,
 // so stale cache contents cannot reach the output.
 //
-// Every wait on an mbarrier is bounded. If a wait ever expires the kernel sets
-// a flag in global memory (readable with loom_cuda_decode_timeout_flag), stops
-// waiting and runs to completion on whatever the ring holds.
+// Every wait on an mbarrier is bounded (the limit is a launch parameter). If a
+// wait of a warp ever expires the kernel sets a flag in global memory (readable
+// with loom_cuda_decode_timeout_flag) and that warp stops for good: it issues no
+// further copy, gives each copy it still has in flight one more bounded wait,
+// never waits or computes again, and only keeps walking its tiles so that it
+// meets the CTA barriers of the item boundaries. The rows of the affected work
+// items are then wrong, which is what the flag tells the host.
 #pragma once
 
 #include <cuda.h>
@@ -51,10 +55,14 @@ __device__ __forceinline__ void mbarrier_expect_tx(uint32_t barrier, uint32_t by
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(barrier), "r"(bytes) : "memory");
 }
 
-// Waits for the phase with the given parity; gives up after a bounded number
-// of attempts (about a second) and reports it.
-__device__ __forceinline__ bool mbarrier_wait(uint32_t barrier, uint32_t parity) {
-  for (uint32_t attempt = 0; attempt < (1u << 24); ++attempt) {
+// Polls of a wait before it gives up when the launch does not say otherwise (about a second).
+constexpr uint32_t kDefaultWaitAttempts = 1u << 24;
+
+// Waits for the phase with the given parity; gives up after `limit` attempts
+// and reports it.
+__device__ __forceinline__ bool mbarrier_wait(uint32_t barrier, uint32_t parity,
+                                              uint32_t limit = kDefaultWaitAttempts) {
+  for (uint32_t attempt = 0; attempt < limit; ++attempt) {
     uint32_t done;
     asm volatile(
         "{\n"
@@ -238,6 +246,9 @@ decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorM
   };
   fetch_block();
 
+  // bit s = parity the next use of slot s completes; kAborted = a wait of this warp has expired
+  constexpr uint32_t kAborted = 1u << 31;
+  uint32_t phases = 0;
   uint32_t issue_left = 2 * my_tiles;  // ring tiles not yet issued (even = K, odd = V of a chunk)
   uint32_t issue_slot = 0;
   bool issue_value = false;
@@ -245,7 +256,7 @@ decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorM
     if (issue_left == 0) return;
     --issue_left;
     const uint32_t token0 = producer.tile * kStreamTileTokens + warp_token;
-    if (token0 < producer.length && lane == 0) {
+    if (token0 < producer.length && lane == 0 && !(phases & kAborted)) {
       const uint32_t destination = ring_base + issue_slot * Tile::kTileBytes;
       const uint32_t barrier = barriers + issue_slot * 8;
       const int32_t c1 = (int32_t)(head_inner ? producer_head : producer_page);
@@ -253,7 +264,7 @@ decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorM
       // generic-proxy reads of this slot (ldmatrix of its previous tile) come
       // before the async-proxy write that refills it
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-      mbarrier_expect_tx(barrier, Tile::kTileBytes);
+      mbarrier_expect_tx(barrier, Tile::kTileBytes + p.wait_unmatched_bytes);
       const CUtensorMap* map = issue_value ? &value_map : &key_map;
 #pragma unroll
       for (int box = 0; box < Ring::kBoxes; ++box) {
@@ -274,7 +285,6 @@ decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorM
   MergeArea<kD, kNT> area(merge_base);
   StreamCursor consumer = start;
   const uint32_t stride = state_stride(kD);
-  uint32_t phases = 0;  // bit s = parity the next use of slot s completes
   uint32_t consume_slot = 0;
 
   uint32_t item_seq = 0, item_head = 0, item_tiles = 0;
@@ -328,8 +338,20 @@ decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorM
     }
   };
 
-  auto wait_slot = [&](uint32_t slot) {
-    mbarrier_wait(barriers + slot * 8, (phases >> slot) & 1u);
+  auto wait_slot = [&](uint32_t slot, uint32_t chunk) {
+    if (phases & kAborted) return;
+    if (!mbarrier_wait(barriers + slot * 8, (phases >> slot) & 1u, p.wait_attempts)) {
+      // First expiry of this warp. The copies issued after this one may still be on their way
+      // into this CTA's shared memory: each gets one more bounded wait (a slot whose tile lay
+      // beyond the sequence end was never armed and just uses up its polls), then the warp stops.
+      atomicCAS(&g_decode_timeout_where, 0u, (1u << 20) | ((chunk & 0x7ffffu) << 1));
+      for (uint32_t other = slot + 1 == (uint32_t)Ring::kSlots ? 0u : slot + 1; other != issue_slot;
+           other = other + 1 == (uint32_t)Ring::kSlots ? 0u : other + 1) {
+        mbarrier_wait(barriers + other * 8, (phases >> other) & 1u, p.wait_attempts);
+      }
+      phases |= kAborted;
+      return;
+    }
     phases ^= 1u << slot;
   };
 
@@ -349,7 +371,7 @@ decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorM
       begin_item();
     }
     const uint32_t token0 = consumer.tile * kStreamTileTokens + warp_token;
-    const bool has_rows = token0 < consumer.length;  // warp-uniform
+    const bool has_rows = token0 < consumer.length && !(phases & kAborted);  // warp-uniform
     const uint32_t live_rows = has_rows ? min(16u, consumer.length - token0) : 0u;
     const uint32_t k_slot = consume_slot;
     const uint32_t v_slot = k_slot + 1 == (uint32_t)Ring::kSlots ? 0u : k_slot + 1;
@@ -358,7 +380,7 @@ decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorM
     // ---- K tile ------------------------------------------------------------
     uint32_t pb[kNT][2];
     if (has_rows) {
-      wait_slot(k_slot);
+      wait_slot(k_slot, chunk);
       float s[kNT][4];
       chunk_scores<QT, kFp8, kD, kNT, true>(s, state, ring_base + k_slot * Tile::kTileBytes, lane);
       chunk_softmax<QT, kFp8, kD, kNT>(pb, s, state, live_rows, g);
@@ -368,7 +390,7 @@ decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorM
 
     // ---- V tile ------------------------------------------------------------
     if (has_rows) {
-      wait_slot(v_slot);
+      wait_slot(v_slot, chunk);
       const uint32_t v_tile = ring_base + v_slot * Tile::kTileBytes;
       if (live_rows < 16u) {
         // rows past the end of the sequence hold whatever the page held: clear them

@@ -218,8 +218,8 @@ __device__ __forceinline__ uint32_t swizzled_byte(uint32_t row, uint32_t column)
 // Bounded wait without a suspend hint: the handshakes between the control warp
 // and the softmax warps sit on the critical path of every tile, and a sleeping
 // waiter wakes up too late. Gives up after about a second of polling.
-__device__ __forceinline__ bool mbarrier_wait_prompt(uint32_t barrier, uint32_t parity) {
-  for (uint32_t attempt = 0; attempt < (1u << 24); ++attempt) {
+__device__ __forceinline__ bool mbarrier_wait_prompt(uint32_t barrier, uint32_t parity, uint32_t limit) {
+  for (uint32_t attempt = 0; attempt < limit; ++attempt) {
     uint32_t done;
     asm volatile(
         "{\n"
@@ -453,7 +453,7 @@ decode_umma_fp8_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap
     // most waits find their phase complete already
     if (mbarrier_test(barrier, completions & 1u)) return;
     if (*aborted) return;
-    if (!mbarrier_wait_prompt(barrier, completions & 1u)) {
+    if (!mbarrier_wait_prompt(barrier, completions & 1u, p.wait_attempts)) {
       *aborted = 1;
       const uint32_t kind = (barrier - full_barriers) >> 3;  // index into the barrier block
       atomicCAS(&g_decode_timeout_where, 0u, ((kind + 1u) << 20) | ((completions & 0x7ffffu) << 1));
@@ -499,11 +499,12 @@ decode_umma_fp8_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap
       describe(current);
       next = current;
       for (uint32_t tile = 0; tile < my_tiles; ++tile) {
+        if (*aborted) break;  // after an expired wait no further copy is started
         if (tile + 1 < my_tiles) describe(next);
         const uint32_t slot = tile % kUmmaStages;
         // the slot's previous tile has been read by its product
         if (tile >= (uint32_t)kUmmaStages) wait_phase(empty + slot * 8, tile / kUmmaStages - 1);
-        if (lane == 0) mbarrier_expect_tx(full + slot * 8, current.boxes * 2048u);
+        if (lane == 0) mbarrier_expect_tx(full + slot * 8, current.boxes * 2048u + p.wait_unmatched_bytes);
         __syncwarp();
         if (lane < current.boxes) {
           const int32_t block = (int32_t)clamp_block(current.block, p.num_blocks);
@@ -861,6 +862,12 @@ decode_umma_fp8_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap
   // ---- release tensor memory -----------------------------------------------------------
   tcgen05_fence_before_sync();
   __syncthreads();
+  if (*aborted) {
+    // Copies started before the expiry may still be on their way into this CTA's shared memory,
+    // and nobody waits for them any more: let them land before the CTA gives its memory back.
+    for (int pause = 0; pause < 64; ++pause) __nanosleep(1000);
+    __syncthreads();
+  }
   if (control) tmem_free(tmem_base, kUmmaTmemColumns);
 }
 

@@ -48,6 +48,8 @@ struct MoveParams {
   uint32_t source_blocks;
   uint32_t destination_blocks;
   uint32_t chunks_per_block;
+  uint32_t wait_attempts;         // polls after which a wait on a copy barrier gives up
+  uint32_t wait_unmatched_bytes;  // self-test: barriers are armed for this many bytes too many
 };
 
 __device__ __forceinline__ uint4 load_streaming(const uint8_t* address) {
@@ -124,8 +126,10 @@ __device__ __forceinline__ uint32_t shared_address(const void* pointer) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(pointer));
 }
 
-__device__ __forceinline__ bool bulk_wait(uint32_t barrier, uint32_t parity) {
-  for (uint32_t attempt = 0; attempt < (1u << 22); ++attempt) {
+constexpr uint32_t kDefaultBulkWaitAttempts = 1u << 22;
+
+__device__ __forceinline__ bool bulk_wait(uint32_t barrier, uint32_t parity, uint32_t limit) {
+  for (uint32_t attempt = 0; attempt < limit; ++attempt) {
     uint32_t done;
     asm volatile(
         "{\n"
@@ -183,7 +187,9 @@ __global__ void __launch_bounds__(32, kBulkCtasPerSm) kv_block_move_bulk_kernel(
     targets[2 * slot + 1] = bytes;
     pending |= 1u << slot;
     const uint32_t barrier = shared_address(barriers + slot);
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(barrier), "r"(bytes) : "memory");
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(barrier),
+                 "r"(bytes + p.wait_unmatched_bytes)
+                 : "memory");
     asm volatile(
         "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
             shared_address(ring + slot * kBulkBytes)),
@@ -198,7 +204,7 @@ __global__ void __launch_bounds__(32, kBulkCtasPerSm) kv_block_move_bulk_kernel(
     const uint32_t slot = (uint32_t)(k % kBulkStages);
     const uint32_t bytes = (uint32_t)targets[2 * slot + 1];
     if (bytes != 0) {
-      if (!bulk_wait(shared_address(barriers + slot), (phases >> slot) & 1u)) break;
+      if (!bulk_wait(shared_address(barriers + slot), (phases >> slot) & 1u, p.wait_attempts)) break;
       phases ^= 1u << slot;
       pending &= ~(1u << slot);
       asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;\n" ::"l"(targets[2 * slot]),
@@ -215,7 +221,7 @@ __global__ void __launch_bounds__(32, kBulkCtasPerSm) kv_block_move_bulk_kernel(
   // Only after an expired wait can loads still be on their way into this CTA's
   // shared memory: give each of them one more bounded wait before the CTA ends.
   for (uint32_t slot = 0; slot < (uint32_t)kBulkStages; ++slot) {
-    if (pending & (1u << slot)) bulk_wait(shared_address(barriers + slot), (phases >> slot) & 1u);
+    if (pending & (1u << slot)) bulk_wait(shared_address(barriers + slot), (phases >> slot) & 1u, p.wait_attempts);
   }
   asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory");
 }
@@ -228,6 +234,8 @@ struct SwapParams {
   uint32_t pair_count;
   uint32_t blocks;
   uint32_t chunks_per_block;
+  uint32_t wait_attempts;
+  uint32_t wait_unmatched_bytes;
 };
 
 // Exchanges the two blocks of every pair, K and V.
@@ -325,7 +333,7 @@ __global__ void __launch_bounds__(32, kBulkCtasPerSm) kv_block_swap_bulk_kernel(
     pending |= 1u << twin;
     const uint32_t barrier = shared_address(barriers + twin);
     const uint32_t slot = shared_address(ring + (2 * twin) * kSwapBytes);
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(barrier), "r"(2u * bytes)
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(barrier), "r"(2u * bytes + p.wait_unmatched_bytes)
                  : "memory");
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(slot),
                  "l"(first), "r"(bytes), "r"(barrier)
@@ -342,7 +350,7 @@ __global__ void __launch_bounds__(32, kBulkCtasPerSm) kv_block_swap_bulk_kernel(
     const uint32_t twin = (uint32_t)(k % kTwins);
     const uint32_t bytes = (uint32_t)targets[3 * twin + 2];
     if (bytes != 0) {
-      if (!bulk_wait(shared_address(barriers + twin), (phases >> twin) & 1u)) break;
+      if (!bulk_wait(shared_address(barriers + twin), (phases >> twin) & 1u, p.wait_attempts)) break;
       phases ^= 1u << twin;
       pending &= ~(1u << twin);
       const uint32_t slot = shared_address(ring + (2 * twin) * kSwapBytes);
@@ -360,7 +368,7 @@ __global__ void __launch_bounds__(32, kBulkCtasPerSm) kv_block_swap_bulk_kernel(
     }
   }
   for (uint32_t twin = 0; twin < (uint32_t)kTwins; ++twin) {
-    if (pending & (1u << twin)) bulk_wait(shared_address(barriers + twin), (phases >> twin) & 1u);
+    if (pending & (1u << twin)) bulk_wait(shared_address(barriers + twin), (phases >> twin) & 1u, p.wait_attempts);
   }
   asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory");
 }
@@ -480,6 +488,8 @@ int loom_cuda_kv_block_move(const void* source_key_cache, const void* source_val
   p.source_blocks = source_blocks;
   p.destination_blocks = destination_blocks;
   p.chunks_per_block = (uint32_t)chunks;
+  p.wait_attempts = loom_launch::wait_attempts(kDefaultBulkWaitAttempts);
+  p.wait_unmatched_bytes = loom_launch::wait_unmatched_bytes();
   // A cache in pinned host memory (blocks swapped out on preemption, swapped in on resume) is read
   // and written over PCIe by the vector engine; memory the device cannot address is refused.
   bool host = false;
@@ -557,6 +567,8 @@ int loom_cuda_kv_block_swap(void* key_cache, void* value_cache, const int64_t* b
   p.pair_count = pair_count;
   p.blocks = num_blocks;
   p.chunks_per_block = (uint32_t)chunks;
+  p.wait_attempts = loom_launch::wait_attempts(kDefaultBulkWaitAttempts);
+  p.wait_unmatched_bytes = loom_launch::wait_unmatched_bytes();
   // As for a move: a cache in pinned host memory is exchanged over PCIe by the vector engine through
   // its mapped device address; memory the device cannot address is refused before any launch.
   bool host = false;

@@ -53,6 +53,27 @@ inline std::atomic<uint64_t>& plain_retries() {
   return count;
 }
 
+// ---- bounded waits ---------------------------------------------------------------------------
+//
+// Every wait of a kernel on a copy barrier gives up after a number of polls and the kernel then
+// records the expiry, stops copying, gives the copies still in flight one more bounded wait and
+// runs to its end. The limit is a launch-time value: `attempts` polls (0 = each kernel's own
+// default, about a second). `unmatched_bytes` is a self-test: every copy barrier is armed for that
+// many bytes MORE than its copy delivers, so the first wait of every ring runs out although the
+// data arrives; with a small `attempts` this exercises the expiry path in microseconds, without
+// any fault. Process-wide; read at each launch.
+inline std::atomic<uint64_t>& wait_policy_word() {
+  static std::atomic<uint64_t> word{0};  // attempts | unmatched_bytes << 32
+  return word;
+}
+inline uint32_t wait_attempts(uint32_t kernel_default) {
+  const uint32_t chosen = (uint32_t)(wait_policy_word().load(std::memory_order_relaxed) & 0xffffffffu);
+  return chosen != 0 ? chosen : kernel_default;
+}
+inline uint32_t wait_unmatched_bytes() {
+  return (uint32_t)(wait_policy_word().load(std::memory_order_relaxed) >> 32);
+}
+
 // LoomCudaStatus of a runtime status: 0 (success) or 3 (launch error).
 inline int failed(cudaError_t status, const char* where) {
   if (status == cudaSuccess) return 0;

@@ -707,6 +707,8 @@ int launch_decode(const LoomDecodeArgs& a) {
   p.q_head = dense_query ? a.head_size : a.query_head_stride;
   p.q_token = dense_query ? (uint64_t)a.query_heads * a.head_size : a.query_token_stride;
   p.scale_log2 = a.scale * kLog2e;
+  p.wait_attempts = loom_launch::wait_attempts(kDefaultWaitAttempts);
+  p.wait_unmatched_bytes = loom_launch::wait_unmatched_bytes();
 
   const bool use_mma = mma_route_fits(a, fp8);
   const bool partitioned = a.workspace != nullptr || a.workspace_elements != 0;
@@ -1087,6 +1089,14 @@ extern "C" int loom_cuda_set_programmatic_launch(uint32_t mode) {
   return LOOM_CUDA_SUCCESS;
 }
 
+extern "C" int loom_cuda_set_wait_policy(uint32_t attempts, uint32_t unmatched_bytes) {
+  // 16-byte multiples keep the armed byte count a value the copy engine could in principle deliver
+  if (unmatched_bytes % 16u != 0 || unmatched_bytes > (1u << 20)) return LOOM_CUDA_INVALID_ARGUMENT;
+  loom_launch::wait_policy_word().store((uint64_t)attempts | ((uint64_t)unmatched_bytes << 32),
+                                        std::memory_order_relaxed);
+  return LOOM_CUDA_SUCCESS;
+}
+
 extern "C" int loom_cuda_decode_timeout_flag(uint32_t* value, uint32_t reset) {
   if (value == nullptr) return LOOM_CUDA_INVALID_ARGUMENT;
   unsigned int flag = 0;
@@ -1100,9 +1110,10 @@ extern "C" int loom_cuda_decode_timeout_flag(uint32_t* value, uint32_t reset) {
     return LOOM_CUDA_LAUNCH_ERROR;
   }
   *value = flag | where;
-  if (reset != 0 && flag != 0) {
+  if (reset != 0 && (flag | where) != 0) {
     const unsigned int zero = 0;
-    if (cudaMemcpyToSymbol(loom_decode::g_decode_timeout_flag, &zero, sizeof(zero)) != cudaSuccess) {
+    if (cudaMemcpyToSymbol(loom_decode::g_decode_timeout_flag, &zero, sizeof(zero)) != cudaSuccess ||
+        cudaMemcpyToSymbol(loom_decode::g_decode_timeout_where, &zero, sizeof(zero)) != cudaSuccess) {
       cudaGetLastError();
       return LOOM_CUDA_LAUNCH_ERROR;
     }

@@ -82,6 +82,27 @@ def decode_timeout_flag(device=None, reset: bool = False) -> int:
     return int(value.value)
 
 
+def set_wait_policy(attempts: int = 0, unmatched_bytes: int = 0) -> None:
+    """Limit of the kernels' waits on copy barriers (0 = default, about a second).
+
+    ``unmatched_bytes`` > 0 is the self-test of the expiry path: barriers are armed
+    for more bytes than arrive, every ring's first wait runs out after ``attempts``
+    polls, the kernels set their timeout flag and return. Results of launches made
+    under it are invalid; call ``set_wait_policy()`` to return to service."""
+    if library().loom_cuda_set_wait_policy(int(attempts), int(unmatched_bytes)) != 0:
+        raise ValueError("unmatched_bytes must be a multiple of 16 of at most 1 MiB")
+
+
+def plain_launch_retries() -> int:
+    """Launches refused with the programmatic-launch attribute and issued plain instead."""
+    return int(library().loom_cuda_plain_launch_retries())
+
+
+def last_launch_failure() -> str:
+    """CUDA error and call site behind this thread's last launch error (``"none"`` if none)."""
+    return library().loom_cuda_last_launch_failure().decode()
+
+
 def _require_inference_tensors(*tensors: torch.Tensor) -> None:
     for tensor in tensors:
         if tensor.requires_grad:

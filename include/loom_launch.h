@@ -229,11 +229,20 @@ int loom_cuda_supports_paged_decode(uint32_t dtype, uint32_t cache_encoding,
  * ("mma16", "scalar", ...); for tests and profiling notes. */
 const char* loom_cuda_last_decode_route(void);
 
-/* Name of the CUDA runtime error behind the last LOOM_CUDA_LAUNCH_ERROR that a
- * decode launch returned on this thread ("cudaErrorInvalidValue", ...), "none"
- * if there was none. With LOOM_DEBUG_LAUNCH set in the environment the name is
- * also printed on stderr when it happens. */
+/* The CUDA runtime error behind the last LOOM_CUDA_LAUNCH_ERROR that any launch
+ * function of this library returned on this thread, and the runtime call it
+ * came from ("cudaErrorInvalidValue at shared-memory limit of a decode kernel
+ * (cudaFuncSetAttribute)", ...); "none" if there was none. Kernel launches,
+ * shared-memory limits and device queries of the decode, RoPE, multi-token and
+ * KV block movement paths all report here. With LOOM_DEBUG_LAUNCH set in the
+ * environment the same text is printed on stderr when it happens. */
 const char* loom_cuda_last_launch_failure(void);
+
+/* Launches that the runtime refused with the programmatic-launch attribute and
+ * that this library then issued as plain launches, since the process started.
+ * 0 in a healthy process; a non-zero count makes a refused attribute visible
+ * instead of silent. */
+uint64_t loom_cuda_plain_launch_retries(void);
 
 /*
  * How the balanced decode kernel fills its shared-memory rings: 0 (default)
@@ -258,12 +267,31 @@ int loom_cuda_set_decode_copy_engine(uint32_t engine);
 int loom_cuda_set_programmatic_launch(uint32_t mode);
 
 /*
- * The TMA-fed kernel bounds every wait on a copy; if one ever expires it sets a
- * flag on the device instead of hanging. This reads the flag of the current
- * device into *value (0 = never happened) and optionally clears it. Unlike the
- * launch functions this call synchronises with the device.
+ * The TMA-fed kernels bound every wait on a copy; if one ever expires the warp
+ * concerned sets a flag on the device instead of hanging, starts no further
+ * copy, gives the copies it has in flight one more bounded wait and does
+ * nothing more (the rows of its work items are then wrong: the flag is the
+ * status). This reads the flag of the current device into *value (0 = never
+ * happened; otherwise bit 0 is set and the upper bits say which wait expired
+ * first) and optionally clears it. Unlike the launch functions this call
+ * synchronises with the device.
  */
 int loom_cuda_decode_timeout_flag(uint32_t* value, uint32_t reset);
+
+/*
+ * Limit of those waits, for the decode kernels and the KV block movement
+ * kernels alike. Process-wide, read at each launch.
+ *   attempts         polls of a barrier before a wait gives up; 0 = each
+ *                    kernel's default (about a second).
+ *   unmatched_bytes  0 in service. A non-zero multiple of 16 is a self-test:
+ *                    every copy barrier is armed for that many bytes more than
+ *                    its copy delivers, so the first wait of every ring runs out
+ *                    although the data arrives. With a small `attempts` the
+ *                    expiry path (flag, no further copies, drain, return) is
+ *                    exercised in microseconds and without any fault; results
+ *                    of such a launch are invalid by construction.
+ */
+int loom_cuda_set_wait_policy(uint32_t attempts, uint32_t unmatched_bytes);
 
 /*
  * Partitioned decode without a caller workspace. This entry point has no
@@ -291,6 +319,9 @@ int loom_cuda_decode_timeout_flag(uint32_t* value, uint32_t reset);
  *  - the first call on each device looks up the block's device address (one
  *    runtime query, no allocation). Make that first call outside any stream
  *    capture;
+ *  - the address is looked up, and remembered, for the device that is CURRENT
+ *    when the call is made: make the device that owns args->stream current
+ *    first, as for every other function of this header;
  *  - all calls on a device share the one block, and it keeps whatever the last
  *    call left there. No clearing is needed, because a call writes every word
  *    it later reads. Two such calls that can overlap on the GPU (different

@@ -6,8 +6,9 @@ fixed its memory budget at start-up, a handler that must not stall the device
 with an allocation, a plug-in that only ever receives input and output
 buffers). `loom_cuda_paged_decode_attention_built_in_scratch` serves them from a
 16 MiB block inside the library. This file checks, through the C ABI, that it
-gives the same answer as the workspace-taking entry point on two calls in a
-row, and that it refuses shapes that do not fit its block.
+gives the same answer as the workspace-taking entry point (and as the CPU
+oracle) on two calls in a row, that the device's free memory does not change
+across a call, and that it refuses shapes that do not fit its block.
 
 It is named to be collected last, so that a run stopping at the first failure
 has already run every other test.
@@ -19,6 +20,7 @@ import pytest
 import torch
 
 from attnarc_b200 import _native, workloads
+from tests import helpers
 
 u32, u64, ptr = ctypes.c_uint32, ctypes.c_uint64, ctypes.c_void_p
 BUILT_IN_SCRATCH_FLOATS = 4 * 1024 * 1024
@@ -98,14 +100,26 @@ def test_built_in_scratch_matches_the_workspace_entry_point_twice(lib, partition
         assert lib.loom_cuda_paged_decode_attention_ex(ctypes.byref(reference_args)) == 0
 
         scratch_args = decode_args(case, query, actual, partition_tokens)
+        torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info(device)
         status = lib.loom_cuda_paged_decode_attention_built_in_scratch(ctypes.byref(scratch_args), message, 256)
         assert status == 0, message.value.decode()
         torch.cuda.synchronize()
+        if call == 1:
+            # the first call on a device may make the runtime load the block's module; from then on
+            # the entry point must leave the device's free memory exactly as it found it
+            free_after, _ = torch.cuda.mem_get_info(device)
+            assert free_after == free_before, "the entry point must not allocate device memory"
 
         # same kernels, same arithmetic: the tolerance of the parity tests, in practice bit-equal
         assert torch.isfinite(actual.float()).all()
         assert torch.allclose(actual.float(), expected.float(), rtol=1e-2, atol=1e-2)
         assert torch.equal(actual, expected)
+        # and a third party: the CPU oracle, so that the library is not only compared with itself
+        key_cache, value_cache = case.cache_views()
+        oracle = helpers.oracle_decode(query, key_cache, value_cache, case.block_tables, case.sequence_lengths,
+                                       scale=case.scale, max_sequence_length=case.max_sequence_length)
+        helpers.assert_close(actual, oracle, torch.bfloat16, f"built-in scratch, call {call}")
 
 
 @pytest.mark.gpu
