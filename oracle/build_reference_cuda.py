@@ -11,7 +11,7 @@ to its 1024-token limit) and ``bench.py --workload cfg2-1024`` times it beside
 this library. Without a reference checkout nothing is built and both are
 skipped.
 
-Usage:  python oracle/build_reference_cuda.py [reference root]
+Usage:  python oracle/build_reference_cuda.py [reference root]   (default: $LOOM_REFERENCE_ROOT, else ../reference beside this repository)
 """
 
 from __future__ import annotations
@@ -27,8 +27,13 @@ OUTPUT = os.path.join(OUTPUT_DIR, "libloom_cuda_reference.so")
 SOURCES = ("paged_decode_attention.cu", "rope_paged_kv.cu", "rms_norm.cu")
 
 
-def build(reference_root: str = "/root/reference", verbose: bool = False) -> str | None:
+def build(reference_root: str | None = None, verbose: bool = False) -> str | None:
     """Returns the path of the built library, or None if there is no reference checkout."""
+    from oracle.reference_root import reference_root as locate
+
+    reference_root = reference_root or locate()
+    if reference_root is None:
+        return OUTPUT if os.path.exists(OUTPUT) else None
     cuda_dir = os.path.join(reference_root, "crates", "loom-cuda-sys", "cuda")
     sources = [os.path.join(cuda_dir, "src", name) for name in SOURCES]
     if not all(os.path.exists(path) for path in sources):
@@ -48,5 +53,6 @@ def build(reference_root: str = "/root/reference", verbose: bool = False) -> str
 
 
 if __name__ == "__main__":
-    result = build(sys.argv[1] if len(sys.argv) > 1 else "/root/reference", verbose=True)
+    sys.path.insert(0, os.path.dirname(HERE))
+    result = build(sys.argv[1] if len(sys.argv) > 1 else None, verbose=True)
     print(result if result else "no reference checkout: nothing built")

@@ -14,7 +14,7 @@ Nothing of the reference is copied: the only output is
 ``oracle/_ref/libloom_kernels_torch.so`` (git-ignored). Without a reference
 checkout the script does nothing and the GPU test is skipped.
 
-Usage:  python oracle/build_reference_dispatcher.py [reference root]
+Usage:  python oracle/build_reference_dispatcher.py [reference root]   (default: $LOOM_REFERENCE_ROOT, else ../reference beside this repository)
 """
 
 from __future__ import annotations
@@ -31,8 +31,13 @@ OUTPUT = os.path.join(OUTPUT_DIR, "libloom_kernels_torch.so")
 BRIDGE_DIR = os.path.join(ROOT, "attnarc_b200")
 
 
-def build(reference_root: str = "/root/reference", verbose: bool = False) -> str | None:
+def build(reference_root: str | None = None, verbose: bool = False) -> str | None:
     """Returns the path of the built dispatcher, or None if there is no reference checkout."""
+    from oracle.reference_root import reference_root as locate
+
+    reference_root = reference_root or locate()
+    if reference_root is None:
+        return OUTPUT if os.path.exists(OUTPUT) else None
     sources = sorted(glob.glob(os.path.join(reference_root, "python", "csrc", "*.cpp")))
     bridge_header_dir = os.path.join(reference_root, "crates", "loom-cuda-bridge", "include")
     if not sources or not os.path.isdir(bridge_header_dir):
@@ -63,5 +68,6 @@ def build(reference_root: str = "/root/reference", verbose: bool = False) -> str
 
 
 if __name__ == "__main__":
-    result = build(sys.argv[1] if len(sys.argv) > 1 else "/root/reference", verbose=True)
+    sys.path.insert(0, os.path.dirname(HERE))
+    result = build(sys.argv[1] if len(sys.argv) > 1 else None, verbose=True)
     print(result if result else "no reference checkout: nothing built")
