@@ -36,6 +36,7 @@ class LoomDecodeArgs(ctypes.Structure):
                                     "value_page_stride", "value_head_stride", "query_token_stride",
                                     "query_head_stride")]
         + [("scale", f32), ("emit_state", u32), ("stream", ptr)]
+        + [("sliding_window", u32), ("logits_soft_cap", f32)]
     )
 
 
@@ -73,6 +74,9 @@ def _declare(lib):
     )
     lib.loom_cuda_bridge_paged_decode_attention_ex.argtypes = (
         [u32, u32] + [ptr, u64] * 9 + [u32] * 7 + [u64] * 6 + [u32, u32, u32, f32, u32, u64, u64, ptr]
+    )
+    lib.loom_cuda_bridge_paged_decode_attention_with_options.argtypes = (
+        [u32, u32] + [ptr, u64] * 9 + [u32] * 7 + [u64] * 6 + [u32, u32, u32, f32, u32, u64, u64, u32, f32, ptr]
     )
     lib.loom_cuda_bridge_merge_decode_states.argtypes = [ptr, u64, u32, u32, u32, u32, ptr, u64, ptr]
     lib.loom_cuda_bridge_supports_paged_decode.argtypes = [u32] * 11 + [f32]

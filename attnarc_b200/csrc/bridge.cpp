@@ -326,7 +326,7 @@ int loom_cuda_bridge_paged_decode_workspace_elements_ex(uint32_t sequences, uint
   });
 }
 
-int loom_cuda_bridge_paged_decode_attention_ex(
+int loom_cuda_bridge_paged_decode_attention_with_options(
     uint32_t dtype, uint32_t cache_encoding, const void* query, uint64_t query_elements,
     const void* key_cache, uint64_t key_cache_elements, const void* value_cache,
     uint64_t value_cache_elements, const float* key_scales, uint64_t key_scale_elements,
@@ -338,7 +338,8 @@ int loom_cuda_bridge_paged_decode_attention_ex(
     uint64_t key_page_stride, uint64_t key_head_stride, uint64_t value_block_stride,
     uint64_t value_page_stride, uint64_t value_head_stride, uint32_t max_blocks_per_sequence,
     uint32_t max_sequence_length, uint32_t partition_tokens, float scale, uint32_t emit_state,
-    uint64_t query_token_stride, uint64_t query_head_stride, void* stream) {
+    uint64_t query_token_stride, uint64_t query_head_stride, uint32_t sliding_window, float logits_soft_cap,
+    void* stream) {
   return bridge_call([&] {
     const DType kind = scalar_kind(dtype);
     const size_t width = loom::size_in_bytes(kind);
@@ -349,6 +350,8 @@ int loom_cuda_bridge_paged_decode_attention_ex(
                                                           key_head_stride, value_block_stride,
                                                           value_page_stride, value_head_stride);
     loom::DecodeOptions options;
+    options.sliding_window = sliding_window;
+    options.logits_soft_cap = logits_soft_cap;
     options.partition_tokens = partition_tokens;
     options.emit_state = emit_state != 0;
     options.query_token_stride = (size_t)query_token_stride;
@@ -398,6 +401,29 @@ int loom_cuda_bridge_paged_decode_attention_ex(
                                          lengths.region, out.region, spec, layout, options, stream);
     record_launch(LOOM_CUDA_BRIDGE_PAGED_DECODE_ATTENTION);
   });
+}
+
+int loom_cuda_bridge_paged_decode_attention_ex(
+    uint32_t dtype, uint32_t cache_encoding, const void* query, uint64_t query_elements,
+    const void* key_cache, uint64_t key_cache_elements, const void* value_cache,
+    uint64_t value_cache_elements, const float* key_scales, uint64_t key_scale_elements,
+    const float* value_scales, uint64_t value_scale_elements, const int32_t* block_tables,
+    uint64_t block_table_elements, const int32_t* sequence_lengths, uint64_t sequence_length_elements,
+    void* output, uint64_t output_elements, float* workspace, uint64_t workspace_elements,
+    uint32_t sequences, uint32_t query_heads, uint32_t kv_heads, uint32_t head_size,
+    uint32_t value_head_size, uint32_t num_blocks, uint32_t block_size, uint64_t key_block_stride,
+    uint64_t key_page_stride, uint64_t key_head_stride, uint64_t value_block_stride,
+    uint64_t value_page_stride, uint64_t value_head_stride, uint32_t max_blocks_per_sequence,
+    uint32_t max_sequence_length, uint32_t partition_tokens, float scale, uint32_t emit_state,
+    uint64_t query_token_stride, uint64_t query_head_stride, void* stream) {
+  return loom_cuda_bridge_paged_decode_attention_with_options(
+      dtype, cache_encoding, query, query_elements, key_cache, key_cache_elements, value_cache,
+      value_cache_elements, key_scales, key_scale_elements, value_scales, value_scale_elements, block_tables,
+      block_table_elements, sequence_lengths, sequence_length_elements, output, output_elements, workspace,
+      workspace_elements, sequences, query_heads, kv_heads, head_size, value_head_size, num_blocks, block_size,
+      key_block_stride, key_page_stride, key_head_stride, value_block_stride, value_page_stride,
+      value_head_stride, max_blocks_per_sequence, max_sequence_length, partition_tokens, scale, emit_state,
+      query_token_stride, query_head_stride, 0u, 0.0f, stream);
 }
 
 int loom_cuda_bridge_merge_decode_states(const float* states, uint64_t state_elements, uint32_t parts,

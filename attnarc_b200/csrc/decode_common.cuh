@@ -46,6 +46,11 @@ struct DecodeParams {
   uint64_t k_block, k_page, k_head, v_block, v_page, v_head;  // element strides
   uint64_t q_token, q_head;                                   // element strides of the query
   float scale_log2;  // softmax scale * log2(e)
+  // Options beyond the reference's contract (its design note lists both as later contract fields,
+  // docs/design/paged-decode-attention.md:42-52). 0 = off.
+  uint32_t sliding_window;  // a query sees only the last `sliding_window` tokens of its sequence
+  float soft_cap_log2;      // logits soft cap * log2(e): score -> cap * tanh(score / cap)
+  float inv_soft_cap_log2;
   uint32_t wait_attempts;         // polls after which a wait on a copy barrier gives up
   uint32_t wait_unmatched_bytes;  // self-test: barriers are armed for this many bytes too many
 };
@@ -158,6 +163,22 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float low, float high) {
 __device__ __forceinline__ uint32_t pack_f16x2(float low, float high) {
   __half2 pair = __floats2half2_rn(low, high);
   return *reinterpret_cast<uint32_t*>(&pair);
+}
+
+// First token a query sees under a sliding window of `window` tokens (0 = no window).
+__device__ __forceinline__ uint32_t window_begin(uint32_t length, uint32_t window) {
+  return (window != 0u && length > window) ? length - window : 0u;
+}
+
+// cap * tanh(score / cap) for a score in base-2 units (cap2 = cap * log2(e), inv_cap2 = 1 / cap2),
+// as tanh(x) = 1 - 2 / (exp(2x) + 1): two special-function operations, absolute error of tanh
+// below 1e-6 (the one-instruction tanh.approx is off by up to 5e-4, which a cap of 30..50
+// multiplies into the exponent).
+__device__ __forceinline__ float soft_capped(float score2, float cap2, float inv_cap2) {
+  const float doubled = fminf(score2 * inv_cap2 * (2.0f * kLog2e), 64.0f);
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(e) : "f"(doubled));
+  return cap2 * (1.0f - __fdividef(2.0f, e + 1.0f));
 }
 
 // Physical block of a logical block, clamped so that a corrupt table entry can

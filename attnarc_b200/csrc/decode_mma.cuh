@@ -256,25 +256,44 @@ __device__ __forceinline__ void chunk_scores(float (&s)[kNT][4], const WarpState
 // of the O accumulators from the chunk; one warp vote decides.
 constexpr float kSoftmaxSlack = 8.0f;
 
+//
+// Options: rows below `dead_rows` are masked too (the tokens before a sliding window's first
+// token); with `cap2` != 0 every score passes through the soft cap before the exponent.
 template <typename QT, bool kFp8, int kD, int kNT>
 __device__ __forceinline__ void chunk_softmax(uint32_t (&pb)[kNT][2], const float (&s)[kNT][4],
                                               WarpState<kD, kNT>& state, uint32_t live_rows,
-                                              uint32_t g) {
+                                              uint32_t g, uint32_t dead_rows = 0u, float cap2 = 0.0f,
+                                              float inv_cap2 = 0.0f) {
   constexpr bool kBf16Mma = !kFp8 && std::is_same<QT, __nv_bfloat16>::value;
   constexpr int kKSteps = kD / 16;
+  // score in base-2 units of a raw accumulator
+  auto score = [&](float raw, float head_scale) {
+    const float scaled = raw * head_scale;
+    return cap2 != 0.0f ? soft_capped(scaled, cap2, inv_cap2) : scaled;
+  };
   // exponents relative to the current reference
   float d[kNT][4];
   bool over = false;
+  if (cap2 != 0.0f) {  // warp-uniform
 #pragma unroll
-  for (int nt = 0; nt < kNT; ++nt) {
-    d[nt][0] = fmaf(s[nt][0], state.head_scale[nt][0], -state.row_max[nt][0]);
-    d[nt][1] = fmaf(s[nt][1], state.head_scale[nt][1], -state.row_max[nt][1]);
-    d[nt][2] = fmaf(s[nt][2], state.head_scale[nt][0], -state.row_max[nt][0]);
-    d[nt][3] = fmaf(s[nt][3], state.head_scale[nt][1], -state.row_max[nt][1]);
+    for (int nt = 0; nt < kNT; ++nt) {
+      d[nt][0] = score(s[nt][0], state.head_scale[nt][0]) - state.row_max[nt][0];
+      d[nt][1] = score(s[nt][1], state.head_scale[nt][1]) - state.row_max[nt][1];
+      d[nt][2] = score(s[nt][2], state.head_scale[nt][0]) - state.row_max[nt][0];
+      d[nt][3] = score(s[nt][3], state.head_scale[nt][1]) - state.row_max[nt][1];
+    }
+  } else {
+#pragma unroll
+    for (int nt = 0; nt < kNT; ++nt) {
+      d[nt][0] = fmaf(s[nt][0], state.head_scale[nt][0], -state.row_max[nt][0]);
+      d[nt][1] = fmaf(s[nt][1], state.head_scale[nt][1], -state.row_max[nt][1]);
+      d[nt][2] = fmaf(s[nt][2], state.head_scale[nt][0], -state.row_max[nt][0]);
+      d[nt][3] = fmaf(s[nt][3], state.head_scale[nt][1], -state.row_max[nt][1]);
+    }
   }
-  if (live_rows < 16u) {  // warp-uniform
-    const bool low_live = g < live_rows;
-    const bool high_live = (g + 8u) < live_rows;
+  if (live_rows < 16u || dead_rows != 0u) {  // warp-uniform
+    const bool low_live = g < live_rows && g >= dead_rows;
+    const bool high_live = (g + 8u) < live_rows && (g + 8u) >= dead_rows;
 #pragma unroll
     for (int nt = 0; nt < kNT; ++nt) {
       if (!low_live) d[nt][0] = d[nt][1] = -INFINITY;
@@ -290,10 +309,10 @@ __device__ __forceinline__ void chunk_softmax(uint32_t (&pb)[kNT][2], const floa
 #pragma unroll
     for (int nt = 0; nt < kNT; ++nt) {
       const bool low_dead = d[nt][0] == -INFINITY, high_dead = d[nt][2] == -INFINITY;
-      const float v0 = low_dead ? -INFINITY : s[nt][0] * state.head_scale[nt][0];
-      const float v1 = low_dead ? -INFINITY : s[nt][1] * state.head_scale[nt][1];
-      const float v2 = high_dead ? -INFINITY : s[nt][2] * state.head_scale[nt][0];
-      const float v3 = high_dead ? -INFINITY : s[nt][3] * state.head_scale[nt][1];
+      const float v0 = low_dead ? -INFINITY : score(s[nt][0], state.head_scale[nt][0]);
+      const float v1 = low_dead ? -INFINITY : score(s[nt][1], state.head_scale[nt][1]);
+      const float v2 = high_dead ? -INFINITY : score(s[nt][2], state.head_scale[nt][0]);
+      const float v3 = high_dead ? -INFINITY : score(s[nt][3], state.head_scale[nt][1]);
       float max0 = fmaxf(v0, v2), max1 = fmaxf(v1, v3);
 #pragma unroll
       for (int offset = 4; offset < 32; offset <<= 1) {
@@ -498,10 +517,15 @@ __global__ void __launch_bounds__(kMmaThreads, 2) decode_mma_kernel(const Decode
   const uint32_t first_head = (blockIdx.y % head_chunks) * kHeads;  // within the group
 
   const uint32_t length = clamp_length(p.sequence_lengths[seq], p.max_sequence_length);
-  const uint32_t part_begin = part * p.partition_tokens;
-  if (part_begin >= length && part != 0) return;  // empty partition
-  const uint32_t part_end = min(length, part_begin + p.partition_tokens);
-  const uint32_t n_parts = length == 0 ? 1u : (length + p.partition_tokens - 1) / p.partition_tokens;
+  // Under a sliding window the sequence effectively starts at `visible`: partitions wholly before
+  // it do nothing, the one holding it starts at the 16-token chunk of that token.
+  const uint32_t visible = window_begin(length, p.sliding_window);
+  const uint32_t first_part = visible / p.partition_tokens;
+  if ((part * p.partition_tokens >= length && part != 0) || part < first_part) return;  // empty partition
+  const uint32_t part_begin = max(part * p.partition_tokens, visible & ~15u);
+  const uint32_t part_end = min(length, (part + 1) * p.partition_tokens);
+  const uint32_t n_parts =
+      length == 0 ? 1u : (length + p.partition_tokens - 1) / p.partition_tokens - first_part;
   const uint32_t n_chunks = part_end > part_begin ? (part_end - part_begin + 15u) / 16u : 0u;
   const uint32_t my_chunks = n_chunks > warp ? (n_chunks - warp + kMmaWarps - 1) / kMmaWarps : 0u;
   const uint32_t live_heads = min((uint32_t)kHeads, p.group - first_head);
@@ -595,11 +619,13 @@ __global__ void __launch_bounds__(kMmaThreads, 2) decode_mma_kernel(const Decode
     const uint32_t stage = smem_base + (i % Tile::kStages) * Tile::kStageBytes;
     const uint32_t token0 = part_begin + (warp + i * kMmaWarps) * 16u;
     const uint32_t live_rows = part_end - token0;  // >= 1; rows beyond it are zero filled
+    const uint32_t dead_rows = visible > token0 ? visible - token0 : 0u;  // tokens before the window
 
     float s[kNT][4];
     chunk_scores<QT, kFp8, kD, kNT>(s, state, stage, lane);
     uint32_t pb[kNT][2];
-    chunk_softmax<QT, kFp8, kD, kNT>(pb, s, state, live_rows, g);
+    chunk_softmax<QT, kFp8, kD, kNT>(pb, s, state, live_rows, g, dead_rows, p.soft_cap_log2,
+                                     p.inv_soft_cap_log2);
     chunk_values<QT, kFp8, kD, kNT>(state, pb, stage + Tile::kTileBytes, lane);
   }
   cp_async_wait<0>();

@@ -50,6 +50,19 @@ struct StreamCursor {
   uint32_t seq, head, tile, tiles, length;
 };
 
+// Under a sliding window a sequence's line of tiles starts at the tile holding the first token
+// the query sees; without one (window 0) that is tile 0.
+__device__ __forceinline__ uint32_t stream_first_tile(uint32_t length, uint32_t window) {
+  return window_begin(length, window) / kStreamTileTokens;
+}
+__device__ __forceinline__ uint32_t stream_tiles(uint32_t length, uint32_t window) {
+  return (length + kStreamTileTokens - 1) / kStreamTileTokens - stream_first_tile(length, window);
+}
+// Does the 16-token chunk at token0 hold a token the query sees?
+__device__ __forceinline__ bool stream_chunk_live(uint32_t token0, uint32_t length, uint32_t window) {
+  return token0 < length && token0 + 16u > window_begin(length, window);
+}
+
 template <typename QT, bool kFp8, int kD, int kNT>
 __global__ void __launch_bounds__(kMmaThreads, 2) decode_stream_kernel(const DecodeParams p) {
   using Tile = MmaTile<kFp8, kD>;
@@ -75,7 +88,7 @@ __global__ void __launch_bounds__(kMmaThreads, 2) decode_stream_kernel(const Dec
     uint32_t local = 0;
     for (uint32_t s = begin; s < end; ++s) {
       const uint32_t length = clamp_length(__ldg(p.sequence_lengths + s), p.max_sequence_length);
-      local += (length + kStreamTileTokens - 1) / kStreamTileTokens;
+      local += stream_tiles(length, p.sliding_window);
     }
     uint32_t inclusive = local;
 #pragma unroll
@@ -90,7 +103,7 @@ __global__ void __launch_bounds__(kMmaThreads, 2) decode_stream_kernel(const Dec
     for (uint32_t s = begin; s < end; ++s) {
       prefix[s] = running;
       const uint32_t length = clamp_length(__ldg(p.sequence_lengths + s), p.max_sequence_length);
-      running += (length + kStreamTileTokens - 1) / kStreamTileTokens;
+      running += stream_tiles(length, p.sliding_window);
     }
     if (threadIdx.x == kMmaThreads - 1) prefix[p.sequences] = running;
     __syncthreads();
@@ -158,9 +171,10 @@ __global__ void __launch_bounds__(kMmaThreads, 2) decode_stream_kernel(const Dec
   uint32_t producer_block = 0;
   auto fetch_block = [&]() {
     // block id of the producer cursor's chunk for this warp, looked up one chunk early
-    const uint32_t token0 = producer.tile * kStreamTileTokens + warp_token;
+    const uint32_t token0 =
+        (stream_first_tile(producer.length, p.sliding_window) + producer.tile) * kStreamTileTokens + warp_token;
     producer_block = 0;
-    if (token0 < producer.length) {
+    if (stream_chunk_live(token0, producer.length, p.sliding_window)) {
       producer_block = clamp_block(
           __ldg(p.block_tables + (uint64_t)producer.seq * p.max_blocks_per_sequence + token0 / p.block_size),
           p.num_blocks);
@@ -172,8 +186,9 @@ __global__ void __launch_bounds__(kMmaThreads, 2) decode_stream_kernel(const Dec
   auto issue_tile = [&](uint32_t index) {
     if ((index >> 1) < my_tiles) {
       const bool is_value = index & 1u;
-      const uint32_t token0 = producer.tile * kStreamTileTokens + warp_token;
-      if (token0 < producer.length) {
+      const uint32_t token0 =
+          (stream_first_tile(producer.length, p.sliding_window) + producer.tile) * kStreamTileTokens + warp_token;
+      if (stream_chunk_live(token0, producer.length, p.sliding_window)) {
         const uint32_t slot = ring_base + (index % Ring::kSlots) * Tile::kTileBytes;
         const uint32_t kv_head = producer.head / head_chunks;
         const uint32_t page0 = token0 % p.block_size;
@@ -270,14 +285,18 @@ __global__ void __launch_bounds__(kMmaThreads, 2) decode_stream_kernel(const Dec
       if (chunk != 0) finish_item();
       begin_item();
     }
-    const uint32_t token0 = consumer.tile * kStreamTileTokens + warp_token;
-    const bool has_rows = token0 < consumer.length;  // warp-uniform
+    const uint32_t token0 =
+        (stream_first_tile(consumer.length, p.sliding_window) + consumer.tile) * kStreamTileTokens + warp_token;
+    const bool has_rows = stream_chunk_live(token0, consumer.length, p.sliding_window);  // warp-uniform
     uint32_t pb[kNT][2];
     if (has_rows) {
       const uint32_t k_tile = ring_base + ((2 * chunk) % Ring::kSlots) * Tile::kTileBytes;
+      const uint32_t visible = window_begin(consumer.length, p.sliding_window);
       float s[kNT][4];
       chunk_scores<QT, kFp8, kD, kNT>(s, state, k_tile, lane);
-      chunk_softmax<QT, kFp8, kD, kNT>(pb, s, state, consumer.length - token0, g);
+      chunk_softmax<QT, kFp8, kD, kNT>(pb, s, state, consumer.length - token0, g,
+                                       visible > token0 ? visible - token0 : 0u, p.soft_cap_log2,
+                                       p.inv_soft_cap_log2);
     }
     // ---- V tile ------------------------------------------------------------
     cp_async_wait<Ring::kAhead - 1>();

@@ -157,7 +157,7 @@ decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorM
     uint32_t local = 0;
     for (uint32_t s = begin; s < end; ++s) {
       const uint32_t length = clamp_length(__ldg(p.sequence_lengths + s), p.max_sequence_length);
-      local += (length + kStreamTileTokens - 1) / kStreamTileTokens;
+      local += stream_tiles(length, p.sliding_window);
     }
     uint32_t inclusive = local;
 #pragma unroll
@@ -172,7 +172,7 @@ decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorM
     for (uint32_t s = begin; s < end; ++s) {
       prefix[s] = running;
       const uint32_t length = clamp_length(__ldg(p.sequence_lengths + s), p.max_sequence_length);
-      running += (length + kStreamTileTokens - 1) / kStreamTileTokens;
+      running += stream_tiles(length, p.sliding_window);
     }
     if (threadIdx.x == kMmaThreads - 1) prefix[p.sequences] = running;
     __syncthreads();
@@ -232,11 +232,12 @@ decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorM
   StreamCursor producer = start;
   uint32_t producer_block = 0, producer_page = 0, producer_head = 0;
   auto fetch_block = [&]() {
-    const uint32_t token0 = producer.tile * kStreamTileTokens + warp_token;
+    const uint32_t token0 =
+        (stream_first_tile(producer.length, p.sliding_window) + producer.tile) * kStreamTileTokens + warp_token;
     producer_block = 0;
     producer_page = 0;
     producer_head = head_chunks == 1 ? producer.head : producer.head / head_chunks;
-    if (token0 < producer.length) {
+    if (stream_chunk_live(token0, producer.length, p.sliding_window)) {
       // block_size is a multiple of 16 on this route, so a 16-token tile never straddles blocks
       const uint32_t logical = p.block_shift < 32u ? token0 >> p.block_shift : token0 / p.block_size;
       producer_page = token0 - logical * p.block_size;
@@ -255,8 +256,9 @@ decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorM
   auto issue_tile = [&]() {
     if (issue_left == 0) return;
     --issue_left;
-    const uint32_t token0 = producer.tile * kStreamTileTokens + warp_token;
-    if (token0 < producer.length && lane == 0 && !(phases & kAborted)) {
+    const uint32_t token0 =
+        (stream_first_tile(producer.length, p.sliding_window) + producer.tile) * kStreamTileTokens + warp_token;
+    if (stream_chunk_live(token0, producer.length, p.sliding_window) && lane == 0 && !(phases & kAborted)) {
       const uint32_t destination = ring_base + issue_slot * Tile::kTileBytes;
       const uint32_t barrier = barriers + issue_slot * 8;
       const int32_t c1 = (int32_t)(head_inner ? producer_head : producer_page);
@@ -370,8 +372,10 @@ decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorM
       finish_item();
       begin_item();
     }
-    const uint32_t token0 = consumer.tile * kStreamTileTokens + warp_token;
-    const bool has_rows = token0 < consumer.length && !(phases & kAborted);  // warp-uniform
+    const uint32_t token0 =
+        (stream_first_tile(consumer.length, p.sliding_window) + consumer.tile) * kStreamTileTokens + warp_token;
+    const bool has_rows =
+        stream_chunk_live(token0, consumer.length, p.sliding_window) && !(phases & kAborted);  // warp-uniform
     const uint32_t live_rows = has_rows ? min(16u, consumer.length - token0) : 0u;
     const uint32_t k_slot = consume_slot;
     const uint32_t v_slot = k_slot + 1 == (uint32_t)Ring::kSlots ? 0u : k_slot + 1;
@@ -383,7 +387,9 @@ decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorM
       wait_slot(k_slot, chunk);
       float s[kNT][4];
       chunk_scores<QT, kFp8, kD, kNT, true>(s, state, ring_base + k_slot * Tile::kTileBytes, lane);
-      chunk_softmax<QT, kFp8, kD, kNT>(pb, s, state, live_rows, g);
+      const uint32_t visible = window_begin(consumer.length, p.sliding_window);
+      chunk_softmax<QT, kFp8, kD, kNT>(pb, s, state, live_rows, g, visible > token0 ? visible - token0 : 0u,
+                                       p.soft_cap_log2, p.inv_soft_cap_log2);
     }
     __syncwarp();
     issue_tile();  // refills the slot of the K tile just consumed

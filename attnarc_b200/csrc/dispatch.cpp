@@ -2,6 +2,8 @@
 
 #include "dispatch.hpp"
 
+#include <cmath>
+
 #include <limits>
 
 #include "../../include/loom_launch.h"
@@ -232,6 +234,11 @@ void paged_decode_attention_strided(DType call_dtype, Region query, Region key_c
     a.value_scales = static_cast<const float*>(options.value_scales.pointer);
   }
   a.emit_state = options.emit_state ? 1 : 0;
+  if (!std::isfinite(options.logits_soft_cap) || options.logits_soft_cap < 0.0f) {
+    throw invalid("paged decode logits soft cap must be finite and not negative");
+  }
+  a.sliding_window = options.sliding_window;
+  a.logits_soft_cap = options.logits_soft_cap;
   if (options.workspace.pointer != nullptr || options.workspace.elements != 0) {
     const uint32_t tokens = decode_partition_tokens(spec, options.partition_tokens);
     const size_t required = decode_workspace_elements(spec, tokens);

@@ -64,6 +64,9 @@ struct DecodeOptions {
   bool emit_state = false;
   // Element strides of the query between sequences and heads; both 0 = dense.
   size_t query_token_stride = 0, query_head_stride = 0;
+  // Options the reference lists as later contract fields (docs/design/paged-decode-attention.md:42-52).
+  uint32_t sliding_window = 0;   // > 0: only the last `sliding_window` tokens are attended to
+  float logits_soft_cap = 0.0f;  // > 0: score -> cap * tanh(score / cap)
 };
 
 uint32_t decode_partition_tokens(const PagedDecodeAttentionSpec& spec, uint32_t requested);

@@ -296,8 +296,14 @@ int loom_cuda_multi_token_prepare(const void* query, void* packed_query, const i
 #undef LOOM_PREPARE
 }
 
-int loom_cuda_multi_token_finish(const LoomDecodeArgs* args, uint32_t query_tokens, const float* prefix_states) {
-  if (args == nullptr || args->struct_size != sizeof(LoomDecodeArgs) || prefix_states == nullptr ||
+int loom_cuda_multi_token_finish(const LoomDecodeArgs* caller_args, uint32_t query_tokens,
+                                 const float* prefix_states) {
+  LoomDecodeArgs current;
+  if (!loom_cuda_read_decode_args(caller_args, &current)) return LOOM_CUDA_INVALID_ARGUMENT;
+  const LoomDecodeArgs* args = &current;
+  // a window or a soft cap per query token is not part of the multi-token forms
+  if (args->sliding_window != 0 || args->logits_soft_cap != 0.0f) return LOOM_CUDA_UNSUPPORTED;
+  if (prefix_states == nullptr ||
       query_tokens == 0 || !args->query || !args->key_cache || !args->value_cache || !args->block_tables ||
       !args->sequence_lengths || !args->output || args->sequences == 0 || args->query_heads == 0 ||
       args->kv_heads == 0 || args->query_heads % args->kv_heads != 0 || args->block_size == 0 ||
@@ -357,13 +363,16 @@ int loom_cuda_multi_token_finish(const LoomDecodeArgs* args, uint32_t query_toke
 // loom_cuda_multi_token_finish takes it (original query, tables, lengths; output
 // [sequences, query_tokens, query_heads, value_head_size]); its workspace, if
 // any, serves the widened decode (size it for query_tokens * query_heads heads).
-extern "C" int loom_cuda_paged_multi_token_decode(const LoomDecodeArgs* args, uint32_t query_tokens,
+extern "C" int loom_cuda_paged_multi_token_decode(const LoomDecodeArgs* caller_args, uint32_t query_tokens,
                                                   void* packed_query, int32_t* prefix_lengths,
                                                   float* prefix_states) {
-  if (args == nullptr || args->struct_size != sizeof(LoomDecodeArgs) || query_tokens == 0 || !packed_query ||
+  LoomDecodeArgs current;
+  if (!loom_cuda_read_decode_args(caller_args, &current) || query_tokens == 0 || !packed_query ||
       !prefix_lengths || !prefix_states) {
     return LOOM_CUDA_INVALID_ARGUMENT;
   }
+  const LoomDecodeArgs* args = &current;
+  if (args->sliding_window != 0 || args->logits_soft_cap != 0.0f) return LOOM_CUDA_UNSUPPORTED;
   if ((uint64_t)args->query_heads * query_tokens > 0xffffffffull) return LOOM_CUDA_INVALID_ARGUMENT;
   int status = loom_cuda_multi_token_prepare(args->query, packed_query, args->sequence_lengths, prefix_lengths,
                                              args->dtype, args->sequences, query_tokens, args->query_heads,

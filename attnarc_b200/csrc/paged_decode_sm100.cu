@@ -35,6 +35,7 @@
 #include <cmath>
 #include <cstdint>
 #include <cstdio>
+#include <cstring>
 #include <limits>
 #include <type_traits>
 
@@ -111,10 +112,13 @@ __global__ void __launch_bounds__(kScalarThreads) decode_scalar_kernel(const Dec
   const uint32_t kv_head = query_head / p.group;
 
   const uint32_t length = clamp_length(p.sequence_lengths[seq], p.max_sequence_length);
-  const uint32_t part_begin = part * p.partition_tokens;
-  if (part_begin >= length && part != 0) return;
-  const uint32_t part_end = min(length, part_begin + p.partition_tokens);
-  const uint32_t n_parts = length == 0 ? 1u : (length + p.partition_tokens - 1) / p.partition_tokens;
+  const uint32_t visible = window_begin(length, p.sliding_window);  // first token a sliding window lets through
+  const uint32_t first_part = visible / p.partition_tokens;
+  if ((part * p.partition_tokens >= length && part != 0) || part < first_part) return;
+  const uint32_t part_begin = max(part * p.partition_tokens, visible);
+  const uint32_t part_end = min(length, (part + 1) * p.partition_tokens);
+  const uint32_t n_parts =
+      length == 0 ? 1u : (length + p.partition_tokens - 1) / p.partition_tokens - first_part;
 
   const QT* query = static_cast<const QT*>(p.query) + (uint64_t)seq * p.q_token + (uint64_t)query_head * p.q_head;
   for (uint32_t d = threadIdx.x; d < p.head_size; d += kScalarThreads) q_shared[d] = widen<QT>(query[d]);
@@ -138,7 +142,8 @@ __global__ void __launch_bounds__(kScalarThreads) decode_scalar_kernel(const Dec
     const CT* v_row = values + (uint64_t)block * p.v_block + (uint64_t)page * p.v_page + (uint64_t)kv_head * p.v_head;
     float dot = 0.0f;
     for (uint32_t d = lane; d < p.head_size; d += 32) dot = fmaf(q_shared[d], widen<CT>(k_row[d]), dot);
-    const float score = warp_sum(dot) * score_scale;
+    float score = warp_sum(dot) * score_scale;
+    if (p.soft_cap_log2 != 0.0f) score = soft_capped(score, p.soft_cap_log2, p.inv_soft_cap_log2);
     const float new_max = fmaxf(running_max, score);
     const float alpha = exp2f(running_max - new_max);
     const float weight = exp2f(score - new_max);
@@ -267,18 +272,20 @@ __global__ void __launch_bounds__(kMergeThreads)
 merge_states_kernel(const float* __restrict__ states, uint64_t row_stride, uint64_t part_stride,
                     uint32_t value_head_size, uint32_t fixed_parts,
                     const int32_t* __restrict__ sequence_lengths, uint32_t rows_per_sequence,
-                    uint32_t partition_tokens, uint32_t max_sequence_length, void* output,
-                    uint32_t emit_state) {
+                    uint32_t partition_tokens, uint32_t max_sequence_length, uint32_t sliding_window,
+                    void* output, uint32_t emit_state) {
   loom_launch::grid_dependency_wait();
   const uint32_t row = blockIdx.x;
-  uint32_t parts = fixed_parts;
+  uint32_t parts = fixed_parts, first_part = 0;
   if (sequence_lengths != nullptr) {
     const uint32_t length = clamp_length(sequence_lengths[row / rows_per_sequence], max_sequence_length);
-    parts = (length + partition_tokens - 1) / partition_tokens;
+    // partitions wholly before a sliding window's first token were skipped by the decode kernel
+    first_part = window_begin(length, sliding_window) / partition_tokens;
+    parts = (length + partition_tokens - 1) / partition_tokens - first_part;
     if (parts <= 1) return;
   }
-  merge_row<OT>(states + (uint64_t)row * row_stride, parts, part_stride, value_head_size, row, output,
-                emit_state);
+  merge_row<OT>(states + (uint64_t)row * row_stride + (uint64_t)first_part * part_stride, parts, part_stride,
+                value_head_size, row, output, emit_state);
 }
 
 // Merge after the balanced kernel: the item table says which CTAs hold parts of
@@ -670,7 +677,8 @@ int launch_decode(const LoomDecodeArgs& a) {
       a.key_block_stride == 0 || a.key_page_stride == 0 || a.key_head_stride == 0 ||
       a.value_block_stride == 0 || a.value_page_stride == 0 || a.value_head_stride == 0 ||
       ((a.query_token_stride == 0) != (a.query_head_stride == 0)) ||
-      (a.query_head_stride != 0 && a.query_head_stride < a.head_size)) {
+      (a.query_head_stride != 0 && a.query_head_stride < a.head_size) ||
+      !std::isfinite(a.logits_soft_cap) || a.logits_soft_cap < 0.0f) {
     return LOOM_CUDA_INVALID_ARGUMENT;
   }
 
@@ -707,6 +715,9 @@ int launch_decode(const LoomDecodeArgs& a) {
   p.q_head = dense_query ? a.head_size : a.query_head_stride;
   p.q_token = dense_query ? (uint64_t)a.query_heads * a.head_size : a.query_token_stride;
   p.scale_log2 = a.scale * kLog2e;
+  p.sliding_window = a.sliding_window;
+  p.soft_cap_log2 = a.logits_soft_cap * kLog2e;
+  p.inv_soft_cap_log2 = a.logits_soft_cap > 0.0f ? 1.0f / (a.logits_soft_cap * kLog2e) : 0.0f;
   p.wait_attempts = loom_launch::wait_attempts(kDefaultWaitAttempts);
   p.wait_unmatched_bytes = loom_launch::wait_unmatched_bytes();
 
@@ -733,7 +744,8 @@ int launch_decode(const LoomDecodeArgs& a) {
       // mma.sync kernel is not slower and a little more accurate (456 vs 450-470 us on the
       // Llama-3-70B-shaped FP8 workload)
       umma = tma != nullptr && fp8 && p.group <= 8 && a.head_size == 128 && a.value_head_size == 128 &&
-             g_copy_engine.load(std::memory_order_relaxed) == 3;
+             g_copy_engine.load(std::memory_order_relaxed) == 3 && a.sliding_window == 0 &&
+             a.logits_soft_cap == 0.0f;  // the options live in the mma.sync kernels only
       const uint32_t ctas = stream_ctas_for_launch(
           umma ? (uint32_t)kUmmaCtasPerSm : (tma != nullptr && p.group <= 8 ? (fp8 ? 4u : 3u) : kStreamCtasPerSm));
       if (ctas != 0 && stream_shape(a.sequences, a.query_heads, a.kv_heads, a.value_head_size, ctas, &shape) &&
@@ -825,7 +837,7 @@ int launch_decode(const LoomDecodeArgs& a) {
       merge_states_kernel<type>, dim3(grid), dim3(kMergeThreads), 0, stream,                      \
       static_cast<const float*>(p.partials), row_stride, part_stride, p.value_head_size, 0u,      \
       static_cast<const int32_t*>(p.sequence_lengths), p.query_heads, p.partition_tokens,         \
-      p.max_sequence_length, p.output, p.emit_state)
+      p.max_sequence_length, p.sliding_window, p.output, p.emit_state)
     if (p.emit_state || a.dtype == 0) LOOM_MERGE(float);
     else if (a.dtype == 1) LOOM_MERGE(__half);
     else LOOM_MERGE(__nv_bfloat16);
@@ -1009,10 +1021,22 @@ extern "C" uint64_t loom_cuda_paged_decode_workspace_elements(uint32_t sequences
                                                partition_tokens);
 }
 
+// Copies a caller's LoomDecodeArgs of either known layout into the current one (options off for
+// the shorter layout). False for a null pointer or an unknown struct_size.
+extern "C" int loom_cuda_read_decode_args(const LoomDecodeArgs* args, LoomDecodeArgs* out) {
+  if (args == nullptr || out == nullptr) return 0;
+  if (args->struct_size != sizeof(LoomDecodeArgs) && args->struct_size != LOOM_DECODE_ARGS_BASE_SIZE) return 0;
+  *out = LoomDecodeArgs{};
+  std::memcpy(out, args, args->struct_size);
+  out->struct_size = sizeof(LoomDecodeArgs);
+  return 1;
+}
+
 extern "C" int loom_cuda_paged_decode_attention_ex(const LoomDecodeArgs* args) {
-  if (args == nullptr || args->struct_size != sizeof(LoomDecodeArgs)) return LOOM_CUDA_INVALID_ARGUMENT;
-  if (args->partition_tokens % 16 != 0) return LOOM_CUDA_INVALID_ARGUMENT;
-  return loom_decode::launch_decode(*args);
+  LoomDecodeArgs current;
+  if (!loom_cuda_read_decode_args(args, &current)) return LOOM_CUDA_INVALID_ARGUMENT;
+  if (current.partition_tokens % 16 != 0) return LOOM_CUDA_INVALID_ARGUMENT;
+  return loom_decode::launch_decode(current);
 }
 
 extern "C" int loom_cuda_merge_decode_states(const float* states, uint32_t parts, uint32_t rows,
@@ -1030,7 +1054,7 @@ extern "C" int loom_cuda_merge_decode_states(const float* states, uint32_t parts
 #define LOOM_MERGE(type)                                                                               \
   status = loom_launch::launch(merge_states_kernel<type>, dim3(rows), dim3(kMergeThreads), 0,          \
                                cuda_stream, states, row_stride, part_stride, value_head_size, parts,   \
-                               static_cast<const int32_t*>(nullptr), 1u, 1u, 0u, output, 0u)
+                               static_cast<const int32_t*>(nullptr), 1u, 1u, 0u, 0u, output, 0u)
   if (out_dtype == 0) LOOM_MERGE(float);
   else if (out_dtype == 1) LOOM_MERGE(__half);
   else LOOM_MERGE(__nv_bfloat16);
@@ -1130,11 +1154,13 @@ extern "C" int loom_cuda_paged_decode_attention_built_in_scratch(const LoomDecod
                                                                   uint64_t error_capacity) {
   using namespace loom_decode;
   explain(error_text, error_capacity, "ok");
-  if (args == nullptr || args->struct_size != sizeof(LoomDecodeArgs) || args->partition_tokens % 16 != 0 ||
-      args->kv_heads == 0 || args->query_heads % args->kv_heads != 0) {
+  LoomDecodeArgs current;
+  if (!loom_cuda_read_decode_args(args, &current) || current.partition_tokens % 16 != 0 ||
+      current.kv_heads == 0 || current.query_heads % current.kv_heads != 0) {
     explain(error_text, error_capacity, "decode arguments are not well formed");
     return LOOM_CUDA_INVALID_ARGUMENT;
   }
+  args = &current;
   const uint64_t needed =
       args->partition_tokens == 0
           ? auto_workspace_elements(args->sequences, args->query_heads, args->kv_heads, args->value_head_size,

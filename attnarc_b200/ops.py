@@ -338,6 +338,8 @@ def paged_decode_attention_ex(
     split: bool | None = None,
     emit_state: bool = False,
     output: torch.Tensor | None = None,
+    sliding_window: int = 0,
+    logits_soft_cap: float = 0.0,
 ) -> torch.Tensor:
     """Decode over caches of any stride order, native or FP8 E4M3.
 
@@ -348,7 +350,10 @@ def paged_decode_attention_ex(
     partitioned path (default: when the context spans several partitions);
     ``emit_state`` returns F32 ``[B, Hq, Dv + 2]`` partial states. ``query``
     may be a strided view (unit innermost stride), e.g. the rotated Q inside a
-    packed QKV row.
+    packed QKV row. ``sliding_window`` W > 0 lets a query see only the last W
+    tokens of its sequence; ``logits_soft_cap`` c > 0 turns every scaled score
+    s into ``c * tanh(s / c)`` before the softmax (both are options the
+    reference names as later contract fields; 0 = off).
     """
     _require_inference_tensors(query, key_cache, value_cache)
     sequences, query_heads, head_size = query.shape
@@ -375,7 +380,7 @@ def paged_decode_attention_ex(
         else:
             workspace = None
         scales = (key_scales, value_scales) if fp8 else (None, None)
-        status = library().loom_cuda_bridge_paged_decode_attention_ex(
+        status = library().loom_cuda_bridge_paged_decode_attention_with_options(
             _DTYPE_CODES[query.dtype], _native.KV_CACHE_FP8_E4M3 if fp8 else _native.KV_CACHE_NATIVE,
             query.data_ptr(), _span(query), key_cache.data_ptr(), _span(key_cache),
             value_cache.data_ptr(), _span(value_cache),
@@ -393,7 +398,7 @@ def paged_decode_attention_ex(
             block_tables.shape[1], int(max_sequence_length), partition_tokens if split else 0, float(scale),
             1 if emit_state else 0,
             0 if query.is_contiguous() else query.stride(0), 0 if query.is_contiguous() else query.stride(1),
-            _stream(query.device),
+            int(sliding_window), float(logits_soft_cap), _stream(query.device),
         )
     check(status, "paged decode attention")
     return output

@@ -163,6 +163,33 @@ int loom_cuda_bridge_paged_decode_attention_ex(
     uint32_t partition_tokens, float scale, uint32_t emit_state,
     uint64_t query_token_stride, uint64_t query_head_stride, void* stream);
 
+/*
+ * The same call with the two attention options the reference names as later
+ * contract fields (docs/design/paged-decode-attention.md:42-52), both off at 0:
+ * sliding_window W > 0 lets a query see only the last W tokens of its sequence;
+ * logits_soft_cap c > 0 (finite) turns every scaled score s into
+ * c * tanh(s / c) before the softmax.
+ */
+int loom_cuda_bridge_paged_decode_attention_with_options(
+    uint32_t dtype, uint32_t cache_encoding, const void* query,
+    uint64_t query_elements, const void* key_cache,
+    uint64_t key_cache_elements, const void* value_cache,
+    uint64_t value_cache_elements, const float* key_scales,
+    uint64_t key_scale_elements, const float* value_scales,
+    uint64_t value_scale_elements, const int32_t* block_tables,
+    uint64_t block_table_elements, const int32_t* sequence_lengths,
+    uint64_t sequence_length_elements, void* output, uint64_t output_elements,
+    float* workspace, uint64_t workspace_elements, uint32_t sequences,
+    uint32_t query_heads, uint32_t kv_heads, uint32_t head_size,
+    uint32_t value_head_size, uint32_t num_blocks, uint32_t block_size,
+    uint64_t key_block_stride, uint64_t key_page_stride,
+    uint64_t key_head_stride, uint64_t value_block_stride,
+    uint64_t value_page_stride, uint64_t value_head_stride,
+    uint32_t max_blocks_per_sequence, uint32_t max_sequence_length,
+    uint32_t partition_tokens, float scale, uint32_t emit_state,
+    uint64_t query_token_stride, uint64_t query_head_stride,
+    uint32_t sliding_window, float logits_soft_cap, void* stream);
+
 int loom_cuda_bridge_paged_decode_workspace_elements_ex(
     uint32_t sequences, uint32_t query_heads, uint32_t kv_heads,
     uint32_t value_head_size, uint32_t max_sequence_length,

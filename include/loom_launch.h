@@ -23,6 +23,7 @@
 #ifndef LOOM_LAUNCH_H_
 #define LOOM_LAUNCH_H_
 
+#include <stddef.h>
 #include <stdint.h>
 
 #ifdef __cplusplus
@@ -142,7 +143,8 @@ LOOM_DECLARE_ROPE_WRITE(bf16, uint16_t)
 /*
  * Everything a decode launch needs, in one plain struct, so that the additive
  * entry points do not multiply into one symbol per combination. Zero-fill it,
- * then set the fields; `struct_size` must be sizeof(LoomDecodeArgs).
+ * then set the fields; `struct_size` must be sizeof(LoomDecodeArgs) (or
+ * LOOM_DECODE_ARGS_BASE_SIZE, see the end of the struct).
  */
 typedef struct LoomDecodeArgs {
   uint32_t struct_size;
@@ -174,7 +176,25 @@ typedef struct LoomDecodeArgs {
   uint32_t emit_state;     /* 1 = write [sequences, query_heads, Dv + 2] F32   */
                            /* states (O unnormalised, max, sum) instead of O  */
   void* stream;
+  /* Options the reference names as later contract fields
+   * (docs/design/paged-decode-attention.md:42-52). Added at the end: a caller
+   * built against the struct without them passes its smaller struct_size
+   * (LOOM_DECODE_ARGS_BASE_SIZE) and gets both off. They apply to the
+   * single-token decode; the multi-token entry points refuse them. */
+  uint32_t sliding_window; /* W > 0: the query sees only the last W tokens of  */
+                           /* its sequence (positions length - W .. length - 1) */
+  float logits_soft_cap;   /* c > 0: every scaled score s becomes              */
+                           /* c * tanh(s / c) before the softmax               */
 } LoomDecodeArgs;
+
+/* struct_size of the LoomDecodeArgs layout that ends with `stream`. */
+#define LOOM_DECODE_ARGS_BASE_SIZE ((uint32_t)offsetof(LoomDecodeArgs, sliding_window))
+
+/* Copies a caller's LoomDecodeArgs of either known layout into `out` in the
+ * current layout (options off for the base layout). Returns 1, or 0 for a null
+ * pointer or an unknown struct_size. Host only; every entry point that takes a
+ * LoomDecodeArgs reads it through this. */
+int loom_cuda_read_decode_args(const LoomDecodeArgs* args, LoomDecodeArgs* out);
 
 /* Partition length (tokens) the fixed-partition kernels default to. */
 uint32_t loom_cuda_paged_decode_default_partition_tokens(

@@ -290,6 +290,23 @@ def check_rope_kv_spec(spec: RopeKvSpec):
 
 # -------------------------------------------------------------- operators
 
+import contextlib
+
+
+@contextlib.contextmanager
+def decode_options(sliding_window: int = 0, logits_soft_cap: float = 0.0):
+    """Decode calls inside the block use a sliding window and/or a logits soft cap (extensions,
+    parity unpinned); the reference's arithmetic is restored on exit."""
+    library = lib()
+    library.oracle_set_decode_options.argtypes = [ctypes.c_uint64, ctypes.c_double]
+    if library.oracle_set_decode_options(int(sliding_window), float(logits_soft_cap)) != 0:
+        raise ValueError("logits_soft_cap must be finite and not negative")
+    try:
+        yield
+    finally:
+        library.oracle_set_decode_options(0, 0.0)
+
+
 def paged_decode_attention(call_dtype, query, key_cache, value_cache, block_tables,
                            sequence_lengths, output, spec: DecodeSpec, threads: int = 1):
     """Runs the reference decode in place on ``output``; raises OracleError."""

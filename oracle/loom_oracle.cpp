@@ -413,6 +413,16 @@ inline usize cache_offset(const oracle_decode_spec& s, usize sequence,
          head_size;
 }
 
+// Options beyond the reference's contract (its design note lists sliding windows
+// and logits soft caps as later contract fields,
+// docs/design/paged-decode-attention.md:42-52; parity unpinned). Process-wide,
+// set by oracle_set_decode_options: with a window of W > 0 tokens a query only
+// sees the last W positions of its sequence; with a cap c > 0 every scaled score
+// s becomes c * tanh(s / c) before the softmax. Zero (the default) is the
+// reference's arithmetic, untouched.
+static uint64_t g_sliding_window = 0;
+static double g_logits_soft_cap = 0.0;
+
 // One (sequence, query head): attention.rs:294-353. `KeyAt`/`ValueAt` return
 // the F32 value of a cache element given its NHD offset and KV head; for the
 // native cache that is a plain widening.
@@ -432,11 +442,14 @@ void attend_one(const oracle_decode_spec& s, const typename Q::Storage* query,
     for (usize d = 0; d < s.head_size; ++d) {
       sum += (double)Q::to_f32(q[d]) * (double)key_at(key_offset + d, kv_head);
     }
-    return sum * (double)s.scale;
+    const double scaled = sum * (double)s.scale;
+    return g_logits_soft_cap > 0.0 ? g_logits_soft_cap * std::tanh(scaled / g_logits_soft_cap) : scaled;
   };
+  const usize first_position =
+      (g_sliding_window > 0 && sequence_length > g_sliding_window) ? sequence_length - (usize)g_sliding_window : 0;
 
   double maximum = -std::numeric_limits<double>::infinity();
-  for (usize position = 0; position < sequence_length; ++position) {
+  for (usize position = first_position; position < sequence_length; ++position) {
     const usize key_offset =
         cache_offset(s, sequence, position, kv_head, s.head_size, block_tables);
     // f64::max ignores a NaN operand, as fmax does.
@@ -445,7 +458,7 @@ void attend_one(const oracle_decode_spec& s, const typename Q::Storage* query,
 
   double denominator = 0.0;
   std::vector<double> accumulator(s.value_head_size, 0.0);
-  for (usize position = 0; position < sequence_length; ++position) {
+  for (usize position = first_position; position < sequence_length; ++position) {
     const usize key_offset =
         cache_offset(s, sequence, position, kv_head, s.head_size, block_tables);
     const double weight = std::exp(score(key_offset) - maximum);
@@ -821,6 +834,13 @@ int oracle_rotary_spec_check(const oracle_rotary_spec* spec, oracle_error* error
 int oracle_rope_kv_spec_check(const oracle_rope_kv_spec* spec,
                               oracle_error* error) {
   return check_rope_kv_spec(*spec, error);
+}
+
+int oracle_set_decode_options(uint64_t sliding_window, double logits_soft_cap) {
+  if (!(logits_soft_cap >= 0.0) || !std::isfinite(logits_soft_cap)) return 1;
+  g_sliding_window = sliding_window;
+  g_logits_soft_cap = logits_soft_cap;
+  return 0;
 }
 
 int oracle_paged_decode_attention(

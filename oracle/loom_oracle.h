@@ -123,6 +123,15 @@ int oracle_paged_decode_attention(
     uint64_t sequence_lengths_len, void* output, uint64_t output_len,
     const oracle_decode_spec* spec, int32_t threads, oracle_error* error);
 
+/* Extension (parity unpinned; the reference's design note names both as later
+ * contract fields, docs/design/paged-decode-attention.md:42-52): options of the
+ * two decode functions, process-wide, not thread-safe against running calls.
+ * sliding_window W > 0: a query sees only the last W positions of its sequence.
+ * logits_soft_cap c > 0: each scaled score s becomes c * tanh(s / c) before the
+ * softmax. (0, 0) restores the reference's arithmetic. Returns 0, or 1 for a
+ * negative or non-finite cap. */
+int oracle_set_decode_options(uint64_t sliding_window, double logits_soft_cap);
+
 /* Extension (parity unpinned): the caches hold FP8 E4M3FN bytes; each element
  * is decoded to F32, multiplied in F32 by its static scale (scale_stride 0 =
  * per tensor, 1 = per KV head), and then fed to the same F64 attention. */

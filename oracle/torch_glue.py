@@ -39,8 +39,15 @@ def from_bits(array: np.ndarray, dtype: torch.dtype, shape) -> torch.Tensor:
 
 
 def oracle_decode(query, key_cache, value_cache, block_tables, sequence_lengths, *, scale,
-                  max_sequence_length, key_scales=None, value_scales=None, threads=8) -> torch.Tensor:
-    """Reference output for logical [blocks, block, heads, D] cache views (any strides)."""
+                  max_sequence_length, key_scales=None, value_scales=None, threads=8, sliding_window=0,
+                  logits_soft_cap=0.0) -> torch.Tensor:
+    """Reference output for logical [blocks, block, heads, D] cache views (any strides).
+    ``sliding_window`` / ``logits_soft_cap`` are the unpinned extensions of ``ob.decode_options``."""
+    if sliding_window or logits_soft_cap:
+        with ob.decode_options(sliding_window, logits_soft_cap):
+            return oracle_decode(query, key_cache, value_cache, block_tables, sequence_lengths, scale=scale,
+                                 max_sequence_length=max_sequence_length, key_scales=key_scales,
+                                 value_scales=value_scales, threads=threads)
     sequences, query_heads, head_size = query.shape
     num_blocks, block_size, kv_heads, _ = key_cache.shape
     value_head_size = value_cache.shape[3]

@@ -463,3 +463,59 @@ def test_tcgen05_kernel_emits_states_that_merge(ops):
     merged = ops.merge_decode_states(states.reshape(1, -1, states.shape[-1]).contiguous(), torch.bfloat16)
     helpers.assert_close(merged.reshape(expected.shape), expected, torch.bfloat16, "tcgen05 states")
     assert ops.decode_timeout_flag() == 0
+
+
+# ---- sliding window and logits soft cap (options beyond the reference's contract; parity unpinned:
+# the expectation is the oracle's F64 attention restricted to the window / with capped scores) -------
+
+@pytest.mark.parametrize("name,batch,lengths", [
+    ("cfg2", 5, [1, 63, 200, 1100, 4096]),
+    ("cfg3", 4, [64, 1000, 2049, 5000]),
+    ("cfg4", 4, [17, 900, 3000, 6000]),
+    ("cfg1", 3, [5, 130, 512]),
+])
+@pytest.mark.parametrize("window,cap", [(0, 30.0), (128, 0.0), (1000, 0.0), (333, 20.0)])
+def test_sliding_window_and_soft_cap_against_the_oracle(ops, name, batch, lengths, window, cap):
+    config = workloads.scaled(workloads.CONFIGS[name], batch=batch, lengths=("fixed", lengths))
+    case = workloads.build_case(config, DEVICE, seed=13)
+    key_cache, value_cache = case.cache_views()
+    query = (case.query * 3.0).contiguous()  # scores large enough for the cap to bend them
+    scales = dict(key_scales=case.key_scales, value_scales=case.value_scales) if config.cache == "fp8" else {}
+    expected = helpers.oracle_decode(query, key_cache, value_cache, case.block_tables, case.sequence_lengths,
+                                     scale=case.scale, max_sequence_length=case.max_sequence_length,
+                                     sliding_window=window, logits_soft_cap=cap, **scales)
+    plain = helpers.oracle_decode(query, key_cache, value_cache, case.block_tables, case.sequence_lengths,
+                                  scale=case.scale, max_sequence_length=case.max_sequence_length, **scales)
+    assert not torch.allclose(expected.float(), plain.float(), atol=2e-2), "the options must matter in this case"
+    routes = set()
+    for split, partition in ((False, 0), (True, 0), (True, 256)):
+        actual = ops.paged_decode_attention_ex(query, key_cache, value_cache, case.block_tables,
+                                               case.sequence_lengths,
+                                               max_sequence_length=case.max_sequence_length, scale=case.scale,
+                                               split=split, partition_tokens=partition,
+                                               sliding_window=window, logits_soft_cap=cap, **scales)
+        routes.add(ops.last_decode_route())
+        helpers.assert_close(actual, expected, config.torch_dtype,
+                             f"{name} window={window} cap={cap} split={split} partition={partition}")
+    if name != "cfg1":
+        assert any("balanced" in route for route in routes), routes
+
+
+def test_options_are_refused_where_they_do_not_apply(ops):
+    config = workloads.scaled(workloads.CONFIGS["cfg2"], batch=2, lengths=("fixed", [40, 300]))
+    case = workloads.build_case(config, DEVICE, seed=3)
+    key_cache, value_cache = case.cache_views()
+    with pytest.raises(helpers_bridge_error()):
+        ops.paged_decode_attention_ex(case.query.contiguous(), key_cache, value_cache, case.block_tables,
+                                      case.sequence_lengths, max_sequence_length=case.max_sequence_length,
+                                      scale=case.scale, logits_soft_cap=float("nan"))
+    with pytest.raises(helpers_bridge_error()):
+        ops.paged_decode_attention_ex(case.query.contiguous(), key_cache, value_cache, case.block_tables,
+                                      case.sequence_lengths, max_sequence_length=case.max_sequence_length,
+                                      scale=case.scale, logits_soft_cap=-1.0)
+
+
+def helpers_bridge_error():
+    from attnarc_b200 import BridgeError
+
+    return BridgeError

@@ -201,3 +201,33 @@ def test_reference_dispatcher_links_against_this_bridge(lib):
     torch.ops.load_library(path)
     assert torch.ops.loom_kernels.bridge_abi_version() == 2
     assert torch.ops.loom_kernels.bridge_launch_count(9) >= 0
+
+
+def test_decode_args_of_both_layouts_are_read_and_others_refused():
+    """LoomDecodeArgs grew at its end (sliding window, logits soft cap): a caller built against the
+    shorter layout passes its own struct_size and gets both options off."""
+    import ctypes
+
+    from attnarc_b200 import _native
+
+    lib = _native.library()
+    lib.loom_cuda_read_decode_args.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
+    full = ctypes.sizeof(_native.LoomDecodeArgs)
+    base = _native.LoomDecodeArgs.sliding_window.offset
+    assert full == base + 8
+
+    source = _native.LoomDecodeArgs()
+    source.sequences, source.sliding_window, source.logits_soft_cap = 7, 99, 2.5
+    out = _native.LoomDecodeArgs()
+    source.struct_size = full
+    assert lib.loom_cuda_read_decode_args(ctypes.byref(source), ctypes.byref(out)) == 1
+    assert (out.sequences, out.sliding_window, out.logits_soft_cap, out.struct_size) == (7, 99, 2.5, full)
+    source.struct_size = base  # the older layout: whatever follows `stream` is not read
+    assert lib.loom_cuda_read_decode_args(ctypes.byref(source), ctypes.byref(out)) == 1
+    assert (out.sequences, out.sliding_window, out.logits_soft_cap, out.struct_size) == (7, 0, 0.0, full)
+    for bad in (0, base - 8, full + 8):
+        source.struct_size = bad
+        assert lib.loom_cuda_read_decode_args(ctypes.byref(source), ctypes.byref(out)) == 0
+    assert lib.loom_cuda_read_decode_args(None, ctypes.byref(out)) == 0
+    # launch entry points refuse an unknown layout before touching anything
+    assert lib.loom_cuda_paged_decode_attention_ex(ctypes.byref(source)) == 1
