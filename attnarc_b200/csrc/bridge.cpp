@@ -339,7 +339,7 @@ int loom_cuda_bridge_paged_decode_attention_with_options(
     uint64_t value_page_stride, uint64_t value_head_stride, uint32_t max_blocks_per_sequence,
     uint32_t max_sequence_length, uint32_t partition_tokens, float scale, uint32_t emit_state,
     uint64_t query_token_stride, uint64_t query_head_stride, uint32_t sliding_window, float logits_soft_cap,
-    void* stream) {
+    uint32_t flags, void* stream) {
   return bridge_call([&] {
     const DType kind = scalar_kind(dtype);
     const size_t width = loom::size_in_bytes(kind);
@@ -352,6 +352,7 @@ int loom_cuda_bridge_paged_decode_attention_with_options(
     loom::DecodeOptions options;
     options.sliding_window = sliding_window;
     options.logits_soft_cap = logits_soft_cap;
+    options.flags = flags;
     options.partition_tokens = partition_tokens;
     options.emit_state = emit_state != 0;
     options.query_token_stride = (size_t)query_token_stride;
@@ -423,7 +424,14 @@ int loom_cuda_bridge_paged_decode_attention_ex(
       workspace_elements, sequences, query_heads, kv_heads, head_size, value_head_size, num_blocks, block_size,
       key_block_stride, key_page_stride, key_head_stride, value_block_stride, value_page_stride,
       value_head_stride, max_blocks_per_sequence, max_sequence_length, partition_tokens, scale, emit_state,
-      query_token_stride, query_head_stride, 0u, 0.0f, stream);
+      query_token_stride, query_head_stride, 0u, 0.0f, 0u, stream);
+}
+
+int loom_cuda_bridge_prepare_decode_workspace(float* workspace, uint64_t workspace_elements, void* stream) {
+  return bridge_call([&] {
+    const Checked ws = borrow(workspace, workspace_elements, 4, "paged decode split-K workspace");
+    loom::prepare_decode_workspace(ws.region, stream);
+  });
 }
 
 int loom_cuda_bridge_merge_decode_states(const float* states, uint64_t state_elements, uint32_t parts,

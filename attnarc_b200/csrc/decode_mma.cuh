@@ -497,7 +497,7 @@ __device__ __forceinline__ void combine_and_store(MergeArea<kD, kNT> area, uint3
 // `partition_tokens`); used for the workspace-free single pass, for block sizes
 // that are not a multiple of 16, and when the caller fixes the partition length.
 // ----------------------------------------------------------------------------
-template <typename QT, bool kFp8, int kD, int kNT>
+template <typename QT, bool kFp8, int kD, int kNT, bool kOptions>
 __global__ void __launch_bounds__(kMmaThreads, 2) decode_mma_kernel(const DecodeParams p) {
   using Tile = MmaTile<kFp8, kD>;
   constexpr int kHeads = 8 * kNT;
@@ -519,7 +519,7 @@ __global__ void __launch_bounds__(kMmaThreads, 2) decode_mma_kernel(const Decode
   const uint32_t length = clamp_length(p.sequence_lengths[seq], p.max_sequence_length);
   // Under a sliding window the sequence effectively starts at `visible`: partitions wholly before
   // it do nothing, the one holding it starts at the 16-token chunk of that token.
-  const uint32_t visible = window_begin(length, p.sliding_window);
+  const uint32_t visible = window_begin(length, kOptions ? p.sliding_window : 0u);
   const uint32_t first_part = visible / p.partition_tokens;
   if ((part * p.partition_tokens >= length && part != 0) || part < first_part) return;  // empty partition
   const uint32_t part_begin = max(part * p.partition_tokens, visible & ~15u);
@@ -624,8 +624,8 @@ __global__ void __launch_bounds__(kMmaThreads, 2) decode_mma_kernel(const Decode
     float s[kNT][4];
     chunk_scores<QT, kFp8, kD, kNT>(s, state, stage, lane);
     uint32_t pb[kNT][2];
-    chunk_softmax<QT, kFp8, kD, kNT>(pb, s, state, live_rows, g, dead_rows, p.soft_cap_log2,
-                                     p.inv_soft_cap_log2);
+    chunk_softmax<QT, kFp8, kD, kNT>(pb, s, state, live_rows, g, dead_rows, kOptions ? p.soft_cap_log2 : 0.0f,
+                                     kOptions ? p.inv_soft_cap_log2 : 0.0f);
     chunk_values<QT, kFp8, kD, kNT>(state, pb, stage + Tile::kTileBytes, lane);
   }
   cp_async_wait<0>();

@@ -63,7 +63,7 @@ __device__ __forceinline__ bool stream_chunk_live(uint32_t token0, uint32_t leng
   return token0 < length && token0 + 16u > window_begin(length, window);
 }
 
-template <typename QT, bool kFp8, int kD, int kNT>
+template <typename QT, bool kFp8, int kD, int kNT, bool kOptions>
 __global__ void __launch_bounds__(kMmaThreads, 2) decode_stream_kernel(const DecodeParams p) {
   using Tile = MmaTile<kFp8, kD>;
   using Ring = StreamRing<kFp8, kD, kNT>;
@@ -88,7 +88,7 @@ __global__ void __launch_bounds__(kMmaThreads, 2) decode_stream_kernel(const Dec
     uint32_t local = 0;
     for (uint32_t s = begin; s < end; ++s) {
       const uint32_t length = clamp_length(__ldg(p.sequence_lengths + s), p.max_sequence_length);
-      local += stream_tiles(length, p.sliding_window);
+      local += stream_tiles(length, kOptions ? p.sliding_window : 0u);
     }
     uint32_t inclusive = local;
 #pragma unroll
@@ -103,7 +103,7 @@ __global__ void __launch_bounds__(kMmaThreads, 2) decode_stream_kernel(const Dec
     for (uint32_t s = begin; s < end; ++s) {
       prefix[s] = running;
       const uint32_t length = clamp_length(__ldg(p.sequence_lengths + s), p.max_sequence_length);
-      running += stream_tiles(length, p.sliding_window);
+      running += stream_tiles(length, kOptions ? p.sliding_window : 0u);
     }
     if (threadIdx.x == kMmaThreads - 1) prefix[p.sequences] = running;
     __syncthreads();
@@ -166,15 +166,16 @@ __global__ void __launch_bounds__(kMmaThreads, 2) decode_stream_kernel(const Dec
   const uint32_t copy_row = lane / Tile::kSegs;
   const uint32_t copy_col = lane % Tile::kSegs;
   const uint32_t warp_token = warp * 16u;
+  const uint32_t window = kOptions ? p.sliding_window : 0u;  // the plain instantiation carries no window arithmetic
 
   StreamCursor producer = start;
   uint32_t producer_block = 0;
   auto fetch_block = [&]() {
     // block id of the producer cursor's chunk for this warp, looked up one chunk early
     const uint32_t token0 =
-        (stream_first_tile(producer.length, p.sliding_window) + producer.tile) * kStreamTileTokens + warp_token;
+        (stream_first_tile(producer.length, window) + producer.tile) * kStreamTileTokens + warp_token;
     producer_block = 0;
-    if (stream_chunk_live(token0, producer.length, p.sliding_window)) {
+    if (stream_chunk_live(token0, producer.length, window)) {
       producer_block = clamp_block(
           __ldg(p.block_tables + (uint64_t)producer.seq * p.max_blocks_per_sequence + token0 / p.block_size),
           p.num_blocks);
@@ -187,8 +188,8 @@ __global__ void __launch_bounds__(kMmaThreads, 2) decode_stream_kernel(const Dec
     if ((index >> 1) < my_tiles) {
       const bool is_value = index & 1u;
       const uint32_t token0 =
-          (stream_first_tile(producer.length, p.sliding_window) + producer.tile) * kStreamTileTokens + warp_token;
-      if (stream_chunk_live(token0, producer.length, p.sliding_window)) {
+          (stream_first_tile(producer.length, window) + producer.tile) * kStreamTileTokens + warp_token;
+      if (stream_chunk_live(token0, producer.length, window)) {
         const uint32_t slot = ring_base + (index % Ring::kSlots) * Tile::kTileBytes;
         const uint32_t kv_head = producer.head / head_chunks;
         const uint32_t page0 = token0 % p.block_size;
@@ -286,17 +287,17 @@ __global__ void __launch_bounds__(kMmaThreads, 2) decode_stream_kernel(const Dec
       begin_item();
     }
     const uint32_t token0 =
-        (stream_first_tile(consumer.length, p.sliding_window) + consumer.tile) * kStreamTileTokens + warp_token;
-    const bool has_rows = stream_chunk_live(token0, consumer.length, p.sliding_window);  // warp-uniform
+        (stream_first_tile(consumer.length, window) + consumer.tile) * kStreamTileTokens + warp_token;
+    const bool has_rows = stream_chunk_live(token0, consumer.length, window);  // warp-uniform
     uint32_t pb[kNT][2];
     if (has_rows) {
       const uint32_t k_tile = ring_base + ((2 * chunk) % Ring::kSlots) * Tile::kTileBytes;
-      const uint32_t visible = window_begin(consumer.length, p.sliding_window);
+      const uint32_t visible = window_begin(consumer.length, window);
       float s[kNT][4];
       chunk_scores<QT, kFp8, kD, kNT>(s, state, k_tile, lane);
       chunk_softmax<QT, kFp8, kD, kNT>(pb, s, state, consumer.length - token0, g,
-                                       visible > token0 ? visible - token0 : 0u, p.soft_cap_log2,
-                                       p.inv_soft_cap_log2);
+                                       visible > token0 ? visible - token0 : 0u,
+                                       kOptions ? p.soft_cap_log2 : 0.0f, kOptions ? p.inv_soft_cap_log2 : 0.0f);
     }
     // ---- V tile ------------------------------------------------------------
     cp_async_wait<Ring::kAhead - 1>();

@@ -31,6 +31,7 @@
 
 #include <cuda.h>
 
+#include "decode_merge.cuh"
 #include "decode_stream.cuh"
 
 namespace loom_decode {
@@ -111,7 +112,10 @@ struct TmaRing {
   static constexpr int kSmemBytes = kRingBytes + kMergeBytes + kPrefixBytes + 4 + kBarrierBytes + 1024;
 };
 
-template <typename QT, bool kFp8, int kD, int kNT>
+// kOptions: the instantiation that knows the sliding window and the logits soft cap. The plain one
+// carries none of their arithmetic: an FP8 cache makes this kernel instruction-bound, and the
+// window's tile bookkeeping alone cost it 12 % there.
+template <typename QT, bool kFp8, int kD, int kNT, bool kOptions>
 __global__ void __launch_bounds__(kMmaThreads, (TmaRing<kFp8, kD, kNT>::kCtasPerSm))
 decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap key_map,
                          const __grid_constant__ CUtensorMap value_map, const TmaAxes axes) {
@@ -128,6 +132,7 @@ decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorM
   uint8_t* barrier_base = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(prefix + kTmaMaxSequences + 1) + 7u) & ~uintptr_t(7));
   __shared__ uint32_t warp_totals[kMmaWarps];
+  __shared__ uint32_t merge_turn;  // this CTA drew the last ticket of the item it just finished
 
   const uint32_t warp = threadIdx.x >> 5;
   const uint32_t lane = threadIdx.x & 31u;
@@ -147,7 +152,10 @@ decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorM
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   }
-  loom_launch::grid_dependency_wait();
+  // Everything up to the first query load reads only lengths and block tables. When the caller
+  // vouches that those were written before the preceding kernel started (early_metadata), this
+  // prologue runs while that kernel (the step's RoPE + KV write) is still at work.
+  if (!p.early_metadata) loom_launch::grid_dependency_wait();
 
   // ---- tiles per sequence, exclusive prefix sum -----------------------------
   {
@@ -157,7 +165,7 @@ decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorM
     uint32_t local = 0;
     for (uint32_t s = begin; s < end; ++s) {
       const uint32_t length = clamp_length(__ldg(p.sequence_lengths + s), p.max_sequence_length);
-      local += stream_tiles(length, p.sliding_window);
+      local += stream_tiles(length, kOptions ? p.sliding_window : 0u);
     }
     uint32_t inclusive = local;
 #pragma unroll
@@ -172,7 +180,7 @@ decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorM
     for (uint32_t s = begin; s < end; ++s) {
       prefix[s] = running;
       const uint32_t length = clamp_length(__ldg(p.sequence_lengths + s), p.max_sequence_length);
-      running += stream_tiles(length, p.sliding_window);
+      running += stream_tiles(length, kOptions ? p.sliding_window : 0u);
     }
     if (threadIdx.x == kMmaThreads - 1) prefix[p.sequences] = running;
     __syncthreads();
@@ -186,6 +194,27 @@ decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorM
   const uint64_t extra = total_tiles % ctas;
   const uint64_t range_begin = blockIdx.x * share + min((uint64_t)blockIdx.x, extra);
   const uint64_t range_end = range_begin + share + (blockIdx.x < extra ? 1u : 0u);
+  if (p.fused_merge && blockIdx.x == 0) {
+    // No CTA visits an empty sequence and no merge kernel follows: its rows are written here.
+    loom_launch::grid_dependency_wait();
+    const uint32_t stride = state_stride(kD);
+    for (uint32_t s = 0; s < p.sequences; ++s) {
+      if (prefix[s + 1] != prefix[s]) continue;
+      for (uint32_t index = threadIdx.x; index < p.query_heads * kD; index += kMmaThreads) {
+        const uint64_t row = (uint64_t)s * p.query_heads + index / kD;
+        if (p.emit_state) {
+          float* out = static_cast<float*>(p.output) + row * stride;
+          out[index % kD] = 0.0f;
+          if (index % kD == 0) {
+            out[kD] = -INFINITY;
+            out[kD + 1] = 0.0f;
+          }
+        } else {
+          static_cast<QT*>(p.output)[row * kD + index % kD] = QT(0.0f);
+        }
+      }
+    }
+  }
   if (range_begin >= range_end) return;
   auto cta_of = [&](uint64_t tile) -> uint32_t {
     const uint64_t boundary = extra * (share + 1);
@@ -228,16 +257,28 @@ decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorM
   // instruction stream of the eight..twelve resident warps is what limits this
   // kernel once HBM is kept busy.
   const uint32_t warp_token = warp * 16u;
+  // first token of this warp's 16-token chunk of a cursor's tile, and whether the chunk holds a
+  // token the query sees
+  auto chunk_token = [&](const StreamCursor& c) -> uint32_t {
+    if constexpr (kOptions) {
+      return (stream_first_tile(c.length, p.sliding_window) + c.tile) * kStreamTileTokens + warp_token;
+    } else {
+      return c.tile * kStreamTileTokens + warp_token;
+    }
+  };
+  auto chunk_live = [&](uint32_t token0, const StreamCursor& c) -> bool {
+    if constexpr (kOptions) return stream_chunk_live(token0, c.length, p.sliding_window);
+    else return token0 < c.length;
+  };
   const bool head_inner = axes.head < axes.page;  // NHD-like: the head stride is the smaller one
   StreamCursor producer = start;
   uint32_t producer_block = 0, producer_page = 0, producer_head = 0;
   auto fetch_block = [&]() {
-    const uint32_t token0 =
-        (stream_first_tile(producer.length, p.sliding_window) + producer.tile) * kStreamTileTokens + warp_token;
+    const uint32_t token0 = chunk_token(producer);
     producer_block = 0;
     producer_page = 0;
     producer_head = head_chunks == 1 ? producer.head : producer.head / head_chunks;
-    if (stream_chunk_live(token0, producer.length, p.sliding_window)) {
+    if (chunk_live(token0, producer)) {
       // block_size is a multiple of 16 on this route, so a 16-token tile never straddles blocks
       const uint32_t logical = p.block_shift < 32u ? token0 >> p.block_shift : token0 / p.block_size;
       producer_page = token0 - logical * p.block_size;
@@ -256,9 +297,8 @@ decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorM
   auto issue_tile = [&]() {
     if (issue_left == 0) return;
     --issue_left;
-    const uint32_t token0 =
-        (stream_first_tile(producer.length, p.sliding_window) + producer.tile) * kStreamTileTokens + warp_token;
-    if (stream_chunk_live(token0, producer.length, p.sliding_window) && lane == 0 && !(phases & kAborted)) {
+    const uint32_t token0 = chunk_token(producer);
+    if (chunk_live(token0, producer) && lane == 0 && !(phases & kAborted)) {
       const uint32_t destination = ring_base + issue_slot * Tile::kTileBytes;
       const uint32_t barrier = barriers + issue_slot * 8;
       const int32_t c1 = (int32_t)(head_inner ? producer_head : producer_page);
@@ -334,9 +374,38 @@ decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorM
       combine_and_store<QT, kD, kNT>(area, live_heads, value_scale, nullptr, 0,
                                      p.partials + (item + blockIdx.x) * kHeads * stride, stride);
     }
-    if (threadIdx.x == 0 && blockIdx.x == first_cta) {
-      p.item_meta[2 * item] = first_cta;
-      p.item_meta[2 * item + 1] = parts;
+    if (!p.fused_merge) {
+      // a merge kernel follows: tell it which CTAs hold the parts of this item
+      if (threadIdx.x == 0 && blockIdx.x == first_cta) {
+        p.item_meta[2 * item] = first_cta;
+        p.item_meta[2 * item + 1] = parts;
+      }
+    } else if (parts > 1) {
+      // The item's word is a ticket, zero at launch. Every CTA publishes its part (fence, then
+      // one atomic increment); the one that draws the last ticket sees all parts, merges them
+      // into the output rows and leaves the ticket zero for the next launch.
+      __threadfence();
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        uint32_t* ticket = p.item_meta + 2 * item;
+        const bool last = atomicAdd(ticket, 1u) + 1u == parts;
+        if (last) *ticket = 0u;
+        merge_turn = last ? 1u : 0u;
+      }
+      __syncthreads();
+      if (merge_turn) {
+        __threadfence();
+        const float* first_part = p.partials + (item + first_cta) * kHeads * stride;
+        for (uint32_t head = 0; head < live_heads; ++head) {
+          if (p.emit_state) {
+            merge_row<float, true>(first_part + head * stride, parts, (uint64_t)kHeads * stride, kD,
+                                   query_row + head, p.output, 1u);
+          } else {
+            merge_row<QT, true>(first_part + head * stride, parts, (uint64_t)kHeads * stride, kD, query_row + head,
+                                p.output, 0u);
+          }
+        }
+      }
     }
   };
 
@@ -357,6 +426,10 @@ decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorM
     phases ^= 1u << slot;
   };
 
+  // From here on the kernel reads what the preceding kernel wrote (the rotated Q, the new token's
+  // K and V) and writes its outputs.
+  if (p.early_metadata) loom_launch::grid_dependency_wait();
+
   // The first item's query rows are requested before the first K/V tiles: the
   // memory system answers in order of arrival, and behind the 96 KB of tiles that
   // an SM asks for at once the 2 KB of Q used to arrive 2.5 us after the first K
@@ -372,10 +445,8 @@ decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorM
       finish_item();
       begin_item();
     }
-    const uint32_t token0 =
-        (stream_first_tile(consumer.length, p.sliding_window) + consumer.tile) * kStreamTileTokens + warp_token;
-    const bool has_rows =
-        stream_chunk_live(token0, consumer.length, p.sliding_window) && !(phases & kAborted);  // warp-uniform
+    const uint32_t token0 = chunk_token(consumer);
+    const bool has_rows = chunk_live(token0, consumer) && !(phases & kAborted);  // warp-uniform
     const uint32_t live_rows = has_rows ? min(16u, consumer.length - token0) : 0u;
     const uint32_t k_slot = consume_slot;
     const uint32_t v_slot = k_slot + 1 == (uint32_t)Ring::kSlots ? 0u : k_slot + 1;
@@ -387,9 +458,13 @@ decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorM
       wait_slot(k_slot, chunk);
       float s[kNT][4];
       chunk_scores<QT, kFp8, kD, kNT, true>(s, state, ring_base + k_slot * Tile::kTileBytes, lane);
-      const uint32_t visible = window_begin(consumer.length, p.sliding_window);
-      chunk_softmax<QT, kFp8, kD, kNT>(pb, s, state, live_rows, g, visible > token0 ? visible - token0 : 0u,
-                                       p.soft_cap_log2, p.inv_soft_cap_log2);
+      if constexpr (kOptions) {
+        const uint32_t visible = window_begin(consumer.length, p.sliding_window);
+        chunk_softmax<QT, kFp8, kD, kNT>(pb, s, state, live_rows, g, visible > token0 ? visible - token0 : 0u,
+                                         p.soft_cap_log2, p.inv_soft_cap_log2);
+      } else {
+        chunk_softmax<QT, kFp8, kD, kNT>(pb, s, state, live_rows, g);
+      }
     }
     __syncwarp();
     issue_tile();  // refills the slot of the K tile just consumed

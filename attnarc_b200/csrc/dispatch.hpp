@@ -67,6 +67,7 @@ struct DecodeOptions {
   // Options the reference lists as later contract fields (docs/design/paged-decode-attention.md:42-52).
   uint32_t sliding_window = 0;   // > 0: only the last `sliding_window` tokens are attended to
   float logits_soft_cap = 0.0f;  // > 0: score -> cap * tanh(score / cap)
+  uint32_t flags = 0;            // LOOM_DECODE_* promises (include/loom_launch.h)
 };
 
 uint32_t decode_partition_tokens(const PagedDecodeAttentionSpec& spec, uint32_t requested);
@@ -76,6 +77,9 @@ void paged_decode_attention_strided(DType call_dtype, Region query, Region key_c
                                     Region block_tables, Region sequence_lengths, Region output,
                                     const PagedDecodeAttentionSpec& spec, const StridedDecodeLayout& layout,
                                     const DecodeOptions& options, void* stream);
+
+// Zeroes a decode workspace once, so that later launches may carry LOOM_DECODE_WORKSPACE_PREPARED.
+void prepare_decode_workspace(Region workspace, void* stream);
 
 void merge_decode_states(Region states, uint32_t parts, uint32_t rows, uint32_t value_head_size,
                          DType out_dtype, Region output, void* stream);

@@ -11,13 +11,15 @@
 // depend on the mode. A kernel launched without the attribute, or after
 // something that is not a kernel, passes the wait at once.
 //
-// No kernel here signals its dependents early (griddepcontrol.launch_dependents
-// at the top): measured on the RoPE -> decode -> merge chain, early signals let
-// the next step's persistent decode CTAs occupy SMs while this step's merge
-// still needed them, and a 39 us step became 46 us. Without early signals the
-// same chain runs in 37.9 us. A signal in the decode kernel alone (after its
-// last chunk, so that only the small merge kernel is set up early) changed
-// nothing: 34.2 -> 34.1 us for decode + merge.
+// Only the RoPE + KV-write kernel signals its dependents early
+// (griddepcontrol.launch_dependents at its top): the decode kernel that follows
+// it in a step then sets itself up, and with stable metadata runs its whole
+// prologue, while the rotation is still at work. The decode and merge kernels do
+// not signal early: measured on the RoPE -> decode -> merge chain, early signals
+// from all three let the next step's persistent decode CTAs occupy SMs while this
+// step's merge still needed them, and a 39 us step became 46 us. A signal in the
+// decode kernel alone (after its last chunk, so that only the small merge kernel
+// is set up early) changed nothing: 34.2 -> 34.1 us for decode + merge.
 #pragma once
 
 #include <cuda_runtime.h>
@@ -129,6 +131,13 @@ cudaError_t launch(void (*kernel)(Params...), dim3 grid, dim3 block, size_t shar
 #ifdef __CUDACC__
 // Blocks until every kernel this one depends on has completed and flushed.
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+
+// Lets the next kernel of the stream, if it was launched with the programmatic attribute, become
+// resident once every CTA of this grid has got here. That kernel still sees this one's results
+// only after its own grid_dependency_wait.
+__device__ __forceinline__ void release_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+}
 
 #endif
 

@@ -41,6 +41,7 @@
 
 #include "../../include/loom_launch.h"
 #include "decode_common.cuh"
+#include "decode_merge.cuh"
 #include "decode_mma.cuh"
 #include "decode_stream.cuh"
 #include "decode_stream_tma.cuh"
@@ -67,17 +68,6 @@ __device__ __forceinline__ float widen<uint8_t>(uint8_t value) {
   // E4M3 byte -> F16 (exact) -> F32
   const __half_raw raw = __nv_cvt_fp8_to_halfraw(value, __NV_E4M3);
   return __half2float(__half(raw));
-}
-
-template <typename T>
-__device__ __forceinline__ void narrow_store(T* out, float value);
-template <>
-__device__ __forceinline__ void narrow_store<float>(float* out, float value) { *out = value; }
-template <>
-__device__ __forceinline__ void narrow_store<__half>(__half* out, float value) { *out = __float2half_rn(value); }
-template <>
-__device__ __forceinline__ void narrow_store<__nv_bfloat16>(__nv_bfloat16* out, float value) {
-  *out = __float2bfloat16_rn(value);
 }
 
 __device__ __forceinline__ float warp_sum(float value) {
@@ -204,65 +194,6 @@ __global__ void __launch_bounds__(kScalarThreads) decode_scalar_kernel(const Dec
 
 // ============================================================= merge kernel
 
-constexpr int kMergeThreads = 128;
-
-// Merges `parts` states of one output row. Part i lives at base + i*part_stride
-// and holds O (value_head_size floats), max (natural-log units) and sum. Each
-// thread owns value dims and folds the parts in batches of eight whose loads
-// are all issued before any is used: one round trip to memory per batch, no
-// shared memory, no barrier, no shuffle. max and sum are recomputed by every
-// thread from the same broadcast loads.
-template <typename OT>
-__device__ __forceinline__ void merge_row(const float* __restrict__ base, uint32_t parts,
-                                          uint64_t part_stride, uint32_t value_head_size, uint64_t row,
-                                          void* output, uint32_t emit_state) {
-  constexpr int kBatch = 8;
-  for (uint32_t dv = threadIdx.x; dv < value_head_size; dv += kMergeThreads) {
-    float top = -INFINITY, total = 0.0f, acc = 0.0f;
-    for (uint32_t first = 0; first < parts; first += kBatch) {
-      float part_max[kBatch], part_sum[kBatch], part_o[kBatch];
-#pragma unroll
-      for (int j = 0; j < kBatch; ++j) {
-        const bool live = first + j < parts;
-        const float* state = base + (uint64_t)(live ? first + j : first) * part_stride;
-        part_sum[j] = live ? __ldg(state + value_head_size + 1) : 0.0f;
-        part_max[j] = __ldg(state + value_head_size);
-        part_o[j] = __ldg(state + dv);
-      }
-      float batch_top = top;
-#pragma unroll
-      for (int j = 0; j < kBatch; ++j) {
-        if (part_sum[j] > 0.0f) batch_top = fmaxf(batch_top, part_max[j]);
-      }
-      if (batch_top > -INFINITY) {
-        const float rescale = exp2f((top - batch_top) * kLog2e);  // 0 when top is still -inf
-        total *= rescale;
-        acc *= rescale;
-#pragma unroll
-        for (int j = 0; j < kBatch; ++j) {
-          if (part_sum[j] > 0.0f) {
-            const float factor = exp2f((part_max[j] - batch_top) * kLog2e);
-            total += part_sum[j] * factor;
-            acc += part_o[j] * factor;
-          }
-        }
-        top = batch_top;
-      }
-    }
-    if (emit_state) {
-      float* out = static_cast<float*>(output) + row * state_stride(value_head_size);
-      out[dv] = acc;
-      if (dv == 0) {
-        out[value_head_size] = top;
-        out[value_head_size + 1] = total;
-      }
-    } else {
-      narrow_store<OT>(static_cast<OT*>(output) + row * value_head_size + dv,
-                       total > 0.0f ? acc / total : 0.0f);
-    }
-  }
-}
-
 // One CTA per output row. Part `i` of row `r` lives at
 // states + r*row_stride + i*part_stride. With sequence_lengths the part count
 // is ceil(length / partition_tokens) and rows with a single part are skipped
@@ -381,10 +312,11 @@ uint32_t stream_ctas_for_sizing() {
 
 template <typename QT, bool kFp8, int kD, int kNT>
 int launch_mma(const DecodeParams& p, cudaStream_t stream) {
-  static std::atomic<uint64_t> configured{0};
+  static std::atomic<uint64_t> configured_masks[2];  // one per instantiation (plain, with options)
   constexpr int kBytes = mma_smem_bytes<kFp8, kD, kNT>();
-  auto kernel = decode_mma_kernel<QT, kFp8, kD, kNT>;
-  if (const cudaError_t limit = ensure_smem(kernel, kBytes, configured); limit != cudaSuccess) {
+  const bool options = p.sliding_window != 0 || p.soft_cap_log2 != 0.0f;
+  auto kernel = options ? decode_mma_kernel<QT, kFp8, kD, kNT, true> : decode_mma_kernel<QT, kFp8, kD, kNT, false>;
+  if (const cudaError_t limit = ensure_smem(kernel, kBytes, configured_masks[options ? 1 : 0]); limit != cudaSuccess) {
     return launched(limit, "shared-memory limit of a decode kernel (cudaFuncSetAttribute)");
   }
   const uint32_t head_chunks = (p.group + 8 * kNT - 1) / (8 * kNT);
@@ -394,10 +326,12 @@ int launch_mma(const DecodeParams& p, cudaStream_t stream) {
 
 template <typename QT, bool kFp8, int kD, int kNT>
 int launch_stream(const DecodeParams& p, uint32_t ctas, cudaStream_t stream) {
-  static std::atomic<uint64_t> configured{0};
+  static std::atomic<uint64_t> configured_masks[2];  // one per instantiation (plain, with options)
   constexpr int kBytes = StreamRing<kFp8, kD, kNT>::kSmemBytes;
-  auto kernel = decode_stream_kernel<QT, kFp8, kD, kNT>;
-  if (const cudaError_t limit = ensure_smem(kernel, kBytes, configured); limit != cudaSuccess) {
+  const bool options = p.sliding_window != 0 || p.soft_cap_log2 != 0.0f;
+  auto kernel =
+      options ? decode_stream_kernel<QT, kFp8, kD, kNT, true> : decode_stream_kernel<QT, kFp8, kD, kNT, false>;
+  if (const cudaError_t limit = ensure_smem(kernel, kBytes, configured_masks[options ? 1 : 0]); limit != cudaSuccess) {
     return launched(limit, "shared-memory limit of a decode kernel (cudaFuncSetAttribute)");
   }
   return launched(loom_launch::launch(kernel, dim3(ctas), dim3(kMmaThreads), kBytes, stream, p));
@@ -498,10 +432,12 @@ bool build_cache_maps(const LoomDecodeArgs& a, bool fp8, CacheMaps* maps) {
 
 template <typename QT, bool kFp8, int kD, int kNT>
 int launch_stream_tma(const DecodeParams& p, uint32_t ctas, const CacheMaps& maps, cudaStream_t stream) {
-  static std::atomic<uint64_t> configured{0};
+  static std::atomic<uint64_t> configured_masks[2];  // one per instantiation (plain, with options)
   constexpr int kBytes = TmaRing<kFp8, kD, kNT>::kSmemBytes;
-  auto kernel = decode_stream_tma_kernel<QT, kFp8, kD, kNT>;
-  if (const cudaError_t limit = ensure_smem(kernel, kBytes, configured); limit != cudaSuccess) {
+  const bool options = p.sliding_window != 0 || p.soft_cap_log2 != 0.0f;
+  auto kernel = options ? decode_stream_tma_kernel<QT, kFp8, kD, kNT, true>
+                        : decode_stream_tma_kernel<QT, kFp8, kD, kNT, false>;
+  if (const cudaError_t limit = ensure_smem(kernel, kBytes, configured_masks[options ? 1 : 0]); limit != cudaSuccess) {
     return launched(limit, "shared-memory limit of a decode kernel (cudaFuncSetAttribute)");
   }
   return launched(loom_launch::launch(kernel, dim3(ctas), dim3(kMmaThreads), kBytes, stream, p, maps.key, maps.value,
@@ -678,7 +614,8 @@ int launch_decode(const LoomDecodeArgs& a) {
       a.value_block_stride == 0 || a.value_page_stride == 0 || a.value_head_stride == 0 ||
       ((a.query_token_stride == 0) != (a.query_head_stride == 0)) ||
       (a.query_head_stride != 0 && a.query_head_stride < a.head_size) ||
-      !std::isfinite(a.logits_soft_cap) || a.logits_soft_cap < 0.0f) {
+      !std::isfinite(a.logits_soft_cap) || a.logits_soft_cap < 0.0f ||
+      (a.flags & ~(LOOM_DECODE_WORKSPACE_PREPARED | LOOM_DECODE_STABLE_METADATA)) != 0 || a.reserved != 0) {
     return LOOM_CUDA_INVALID_ARGUMENT;
   }
 
@@ -778,6 +715,10 @@ int launch_decode(const LoomDecodeArgs& a) {
       tma = nullptr;
       umma = false;
     }
+    // the caller's promises only matter to the balanced TMA-fed mma.sync kernel
+    const bool promises_apply = tma != nullptr && !umma;
+    p.fused_merge = promises_apply && (a.flags & LOOM_DECODE_WORKSPACE_PREPARED) ? 1u : 0u;
+    p.early_metadata = promises_apply && (a.flags & LOOM_DECODE_STABLE_METADATA) ? 1u : 0u;
     if (umma) {
       g_last_route = "umma-fp8-balanced-tma";
       status = a.dtype == 1 ? launch_umma_fp8<__half>(p, stream_ctas, maps, stream)
@@ -812,6 +753,10 @@ int launch_decode(const LoomDecodeArgs& a) {
   }
   if (status != LOOM_CUDA_SUCCESS || !partitioned) return status;
   if (stream_ctas == 0 && p.max_partitions <= 1) return status;
+  if (p.fused_merge) {  // the decode kernel merged the split items itself
+    g_last_route = fp8 ? "mma16-fp8-balanced-tma-merged" : "mma16-balanced-tma-merged";
+    return status;
+  }
 
   // Second kernel: merge the parts of every row that was split.
   const uint64_t rows = (uint64_t)p.sequences * p.query_heads;
@@ -1030,6 +975,15 @@ extern "C" int loom_cuda_read_decode_args(const LoomDecodeArgs* args, LoomDecode
   std::memcpy(out, args, args->struct_size);
   out->struct_size = sizeof(LoomDecodeArgs);
   return 1;
+}
+
+extern "C" int loom_cuda_prepare_decode_workspace(float* workspace, uint64_t workspace_elements, void* stream) {
+  if (workspace == nullptr || workspace_elements == 0 || workspace_elements > (~0ull >> 2)) {
+    return LOOM_CUDA_INVALID_ARGUMENT;
+  }
+  return loom_decode::launched(
+      cudaMemsetAsync(workspace, 0, workspace_elements * sizeof(float), static_cast<cudaStream_t>(stream)),
+      "zeroing a decode workspace (cudaMemsetAsync)");
 }
 
 extern "C" int loom_cuda_paged_decode_attention_ex(const LoomDecodeArgs* args) {

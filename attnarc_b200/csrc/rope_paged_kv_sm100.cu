@@ -173,6 +173,7 @@ rope_paged_kv_vector_kernel(const RopeParams p, uint32_t rotary_units_per_head,
   constexpr int kVec = Vec16<T>::kCount;
   // launched early by programmatic dependent launch: global memory is touched
   // only after the kernels before this one have completed
+  loom_launch::release_dependents();  // the decode kernel of the step may set itself up meanwhile
   loom_launch::grid_dependency_wait();
   const uint64_t flat = (uint64_t)blockIdx.x * kThreads + threadIdx.x;
   const uint64_t total = (uint64_t)p.tokens * units_per_token;
@@ -287,6 +288,7 @@ __device__ __forceinline__ void store_cache_scalar(void* cache, uint64_t offset,
 template <typename T, bool kFp8>
 __global__ void __launch_bounds__(kThreads)
 rope_paged_kv_scalar_kernel(const RopeParams p, uint32_t units_per_token) {
+  loom_launch::release_dependents();  // the decode kernel of the step may set itself up meanwhile
   loom_launch::grid_dependency_wait();
   const uint64_t flat = (uint64_t)blockIdx.x * kThreads + threadIdx.x;
   const uint64_t total = (uint64_t)p.tokens * units_per_token;

@@ -292,7 +292,8 @@ class ShardedDecodeStep:
             partition_tokens)
         self._partition = partition
         self._split = self.max_sequence_length > partition
-        self._workspace = (torch.empty(needed, device=self.device, dtype=torch.float32)
+        # zeroed once: the balanced kernel then merges split sequences itself, without a merge launch
+        self._workspace = (ops.prepare_decode_workspace(torch.empty(needed, device=self.device, dtype=torch.float32))
                            if self._split and needed else None)
         rows = (self.sequences, self.query_heads, self.head_size)
         self.output = torch.zeros(rows, device=self.device, dtype=dtype)
@@ -329,7 +330,9 @@ class ShardedDecodeStep:
             query, kv_cache[:, 0], kv_cache[:, 1], self._pieces["block_tables"], self._pieces["sequence_lengths"],
             max_sequence_length=self.max_sequence_length, scale=self.scale, workspace=self._workspace,
             partition_tokens=self._partition, split=self._split, emit_state=self.exchange,
-            output=self._states if self.exchange else self.output, **self._decode_scales)
+            output=self._states if self.exchange else self.output, workspace_prepared=True,
+            # lengths and tables arrive with the upload, before the RoPE launch that precedes the decode
+            stable_metadata=rope, **self._decode_scales)
         if self.exchange and exchange:
             dist.all_gather_into_tensor(self._gathered.view(-1), self._states.view(-1), group=self.group)
             ops.merge_decode_states(self._gathered, self.output.dtype,

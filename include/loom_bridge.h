@@ -168,7 +168,8 @@ int loom_cuda_bridge_paged_decode_attention_ex(
  * contract fields (docs/design/paged-decode-attention.md:42-52), both off at 0:
  * sliding_window W > 0 lets a query see only the last W tokens of its sequence;
  * logits_soft_cap c > 0 (finite) turns every scaled score s into
- * c * tanh(s / c) before the softmax.
+ * c * tanh(s / c) before the softmax. `flags` carries the caller's
+ * LOOM_DECODE_* promises (0 = none).
  */
 int loom_cuda_bridge_paged_decode_attention_with_options(
     uint32_t dtype, uint32_t cache_encoding, const void* query,
@@ -188,7 +189,15 @@ int loom_cuda_bridge_paged_decode_attention_with_options(
     uint32_t max_blocks_per_sequence, uint32_t max_sequence_length,
     uint32_t partition_tokens, float scale, uint32_t emit_state,
     uint64_t query_token_stride, uint64_t query_head_stride,
-    uint32_t sliding_window, float logits_soft_cap, void* stream);
+    uint32_t sliding_window, float logits_soft_cap, uint32_t flags,
+    void* stream);
+
+/* Checked form of loom_cuda_prepare_decode_workspace: zeroes a decode workspace
+ * once so that later calls may pass LOOM_DECODE_WORKSPACE_PREPARED in `flags`
+ * (include/loom_launch.h says what the two flag bits promise). */
+int loom_cuda_bridge_prepare_decode_workspace(float* workspace,
+                                              uint64_t workspace_elements,
+                                              void* stream);
 
 int loom_cuda_bridge_paged_decode_workspace_elements_ex(
     uint32_t sequences, uint32_t query_heads, uint32_t kv_heads,

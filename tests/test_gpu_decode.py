@@ -486,7 +486,10 @@ def test_sliding_window_and_soft_cap_against_the_oracle(ops, name, batch, length
                                      sliding_window=window, logits_soft_cap=cap, **scales)
     plain = helpers.oracle_decode(query, key_cache, value_cache, case.block_tables, case.sequence_lengths,
                                   scale=case.scale, max_sequence_length=case.max_sequence_length, **scales)
-    assert not torch.allclose(expected.float(), plain.float(), atol=2e-2), "the options must matter in this case"
+    if cap or window < max(lengths):
+        assert not torch.allclose(expected.float(), plain.float(), atol=2e-2), "the options must matter in this case"
+    else:  # a window wider than every context changes nothing
+        assert torch.equal(expected, plain)
     routes = set()
     for split, partition in ((False, 0), (True, 0), (True, 256)):
         actual = ops.paged_decode_attention_ex(query, key_cache, value_cache, case.block_tables,
