@@ -214,7 +214,7 @@ def test_decode_args_of_both_layouts_are_read_and_others_refused():
     lib.loom_cuda_read_decode_args.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
     full = ctypes.sizeof(_native.LoomDecodeArgs)
     base = _native.LoomDecodeArgs.sliding_window.offset
-    assert full == base + 8
+    assert full == base + 16  # sliding window, soft cap, flags, reserved
 
     source = _native.LoomDecodeArgs()
     source.sequences, source.sliding_window, source.logits_soft_cap = 7, 99, 2.5
