@@ -15,7 +15,7 @@ LIBRARY_PATH = os.path.join(_PACKAGE_DIR, "libloom_cuda_bridge.so")
 SUCCESS, INVALID_ARGUMENT, LAUNCH_ERROR, UNAVAILABLE = 0, 1, 2, 3
 F32, F16, BF16 = 0, 1, 2
 KV_CACHE_NATIVE, KV_CACHE_FP8_E4M3 = 0, 1
-DECODE_WORKSPACE_PREPARED, DECODE_STABLE_METADATA = 1, 2
+DECODE_STABLE_METADATA = 2
 BRIDGE_ABI_VERSION = 2
 
 u32, u64, f32 = ctypes.c_uint32, ctypes.c_uint64, ctypes.c_float
@@ -79,7 +79,6 @@ def _declare(lib):
     lib.loom_cuda_bridge_paged_decode_attention_with_options.argtypes = (
         [u32, u32] + [ptr, u64] * 9 + [u32] * 7 + [u64] * 6 + [u32, u32, u32, f32, u32, u64, u64, u32, f32, u32, ptr]
     )
-    lib.loom_cuda_bridge_prepare_decode_workspace.argtypes = [ptr, u64, ptr]
     lib.loom_cuda_bridge_merge_decode_states.argtypes = [ptr, u64, u32, u32, u32, u32, ptr, u64, ptr]
     lib.loom_cuda_bridge_supports_paged_decode.argtypes = [u32] * 11 + [f32]
     lib.loom_cuda_bridge_supports_rope_paged_kv_write.argtypes = [u32] * 11

@@ -427,13 +427,6 @@ int loom_cuda_bridge_paged_decode_attention_ex(
       query_token_stride, query_head_stride, 0u, 0.0f, 0u, stream);
 }
 
-int loom_cuda_bridge_prepare_decode_workspace(float* workspace, uint64_t workspace_elements, void* stream) {
-  return bridge_call([&] {
-    const Checked ws = borrow(workspace, workspace_elements, 4, "paged decode split-K workspace");
-    loom::prepare_decode_workspace(ws.region, stream);
-  });
-}
-
 int loom_cuda_bridge_merge_decode_states(const float* states, uint64_t state_elements, uint32_t parts,
                                          uint32_t rows, uint32_t value_head_size, uint32_t out_dtype,
                                          void* output, uint64_t output_elements, void* stream) {

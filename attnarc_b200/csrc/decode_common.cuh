@@ -51,11 +51,8 @@ struct DecodeParams {
   uint32_t sliding_window;  // a query sees only the last `sliding_window` tokens of its sequence
   float soft_cap_log2;      // logits soft cap * log2(e): score -> cap * tanh(score / cap)
   float inv_soft_cap_log2;
-  // Balanced TMA-fed kernel only. fused_merge: the workspace's per-item words are tickets that are
-  // zero at launch; the last CTA to finish a split item merges its parts, no merge kernel follows.
-  // early_metadata: lengths and block tables were written before the kernel preceding this one in
-  // the stream started, so they may be read before that kernel has completed.
-  uint32_t fused_merge;
+  // Balanced TMA-fed kernel only: lengths and block tables were written before the kernel
+  // preceding this one in the stream started, so they may be read before that kernel has completed.
   uint32_t early_metadata;
   uint32_t wait_attempts;         // polls after which a wait on a copy barrier gives up
   uint32_t wait_unmatched_bytes;  // self-test: barriers are armed for this many bytes too many

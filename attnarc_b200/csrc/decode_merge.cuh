@@ -1,5 +1,4 @@
-// Log-sum-exp merge of partial (O, max, sum) states: the arithmetic shared by the merge kernels
-// and by the decode kernel that merges the parts of a split work item itself.
+// Log-sum-exp merge of partial (O, max, sum) states: the arithmetic of the merge kernels.
 //
 // Replaces the merge of the reference's split-K path
 // (crates/loom-cuda-sys/cuda/src/paged_decode_attention.cu:749-853), whose factors are computed
@@ -32,11 +31,7 @@ constexpr int kMergeThreads = 128;
 // are all issued before any is used: one round trip to memory per batch, no
 // shared memory, no barrier, no shuffle. max and sum are recomputed by every
 // thread from the same broadcast loads.
-//
-// kCoherent: the states were written by other CTAs of the SAME kernel (the caller has observed
-// their completion through a fenced atomic): they are read with ld.global.cg, past the L1 and
-// the read-only path, which only hold what was true when the kernel started.
-template <typename OT, bool kCoherent = false>
+template <typename OT>
 __device__ __forceinline__ void merge_row(const float* __restrict__ base, uint32_t parts,
                                           uint64_t part_stride, uint32_t value_head_size, uint64_t row,
                                           void* output, uint32_t emit_state) {
@@ -49,15 +44,9 @@ __device__ __forceinline__ void merge_row(const float* __restrict__ base, uint32
       for (int j = 0; j < kBatch; ++j) {
         const bool live = first + j < parts;
         const float* state = base + (uint64_t)(live ? first + j : first) * part_stride;
-        if constexpr (kCoherent) {
-          part_sum[j] = live ? __ldcg(state + value_head_size + 1) : 0.0f;
-          part_max[j] = __ldcg(state + value_head_size);
-          part_o[j] = __ldcg(state + dv);
-        } else {
-          part_sum[j] = live ? __ldg(state + value_head_size + 1) : 0.0f;
-          part_max[j] = __ldg(state + value_head_size);
-          part_o[j] = __ldg(state + dv);
-        }
+        part_sum[j] = live ? __ldg(state + value_head_size + 1) : 0.0f;
+        part_max[j] = __ldg(state + value_head_size);
+        part_o[j] = __ldg(state + dv);
       }
       float batch_top = top;
 #pragma unroll

@@ -31,7 +31,6 @@
 
 #include <cuda.h>
 
-#include "decode_merge.cuh"
 #include "decode_stream.cuh"
 
 namespace loom_decode {
@@ -132,7 +131,6 @@ decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorM
   uint8_t* barrier_base = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(prefix + kTmaMaxSequences + 1) + 7u) & ~uintptr_t(7));
   __shared__ uint32_t warp_totals[kMmaWarps];
-  __shared__ uint32_t merge_turn;  // this CTA drew the last ticket of the item it just finished
 
   const uint32_t warp = threadIdx.x >> 5;
   const uint32_t lane = threadIdx.x & 31u;
@@ -194,27 +192,6 @@ decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorM
   const uint64_t extra = total_tiles % ctas;
   const uint64_t range_begin = blockIdx.x * share + min((uint64_t)blockIdx.x, extra);
   const uint64_t range_end = range_begin + share + (blockIdx.x < extra ? 1u : 0u);
-  if (p.fused_merge && blockIdx.x == 0) {
-    // No CTA visits an empty sequence and no merge kernel follows: its rows are written here.
-    loom_launch::grid_dependency_wait();
-    const uint32_t stride = state_stride(kD);
-    for (uint32_t s = 0; s < p.sequences; ++s) {
-      if (prefix[s + 1] != prefix[s]) continue;
-      for (uint32_t index = threadIdx.x; index < p.query_heads * kD; index += kMmaThreads) {
-        const uint64_t row = (uint64_t)s * p.query_heads + index / kD;
-        if (p.emit_state) {
-          float* out = static_cast<float*>(p.output) + row * stride;
-          out[index % kD] = 0.0f;
-          if (index % kD == 0) {
-            out[kD] = -INFINITY;
-            out[kD + 1] = 0.0f;
-          }
-        } else {
-          static_cast<QT*>(p.output)[row * kD + index % kD] = QT(0.0f);
-        }
-      }
-    }
-  }
   if (range_begin >= range_end) return;
   auto cta_of = [&](uint64_t tile) -> uint32_t {
     const uint64_t boundary = extra * (share + 1);
@@ -374,38 +351,9 @@ decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorM
       combine_and_store<QT, kD, kNT>(area, live_heads, value_scale, nullptr, 0,
                                      p.partials + (item + blockIdx.x) * kHeads * stride, stride);
     }
-    if (!p.fused_merge) {
-      // a merge kernel follows: tell it which CTAs hold the parts of this item
-      if (threadIdx.x == 0 && blockIdx.x == first_cta) {
-        p.item_meta[2 * item] = first_cta;
-        p.item_meta[2 * item + 1] = parts;
-      }
-    } else if (parts > 1) {
-      // The item's word is a ticket, zero at launch. Every CTA publishes its part (fence, then
-      // one atomic increment); the one that draws the last ticket sees all parts, merges them
-      // into the output rows and leaves the ticket zero for the next launch.
-      __threadfence();
-      __syncthreads();
-      if (threadIdx.x == 0) {
-        uint32_t* ticket = p.item_meta + 2 * item;
-        const bool last = atomicAdd(ticket, 1u) + 1u == parts;
-        if (last) *ticket = 0u;
-        merge_turn = last ? 1u : 0u;
-      }
-      __syncthreads();
-      if (merge_turn) {
-        __threadfence();
-        const float* first_part = p.partials + (item + first_cta) * kHeads * stride;
-        for (uint32_t head = 0; head < live_heads; ++head) {
-          if (p.emit_state) {
-            merge_row<float, true>(first_part + head * stride, parts, (uint64_t)kHeads * stride, kD,
-                                   query_row + head, p.output, 1u);
-          } else {
-            merge_row<QT, true>(first_part + head * stride, parts, (uint64_t)kHeads * stride, kD, query_row + head,
-                                p.output, 0u);
-          }
-        }
-      }
+    if (threadIdx.x == 0 && blockIdx.x == first_cta) {
+      p.item_meta[2 * item] = first_cta;
+      p.item_meta[2 * item + 1] = parts;
     }
   };
 

@@ -239,7 +239,7 @@ void paged_decode_attention_strided(DType call_dtype, Region query, Region key_c
   }
   a.sliding_window = options.sliding_window;
   a.logits_soft_cap = options.logits_soft_cap;
-  if ((options.flags & ~(LOOM_DECODE_WORKSPACE_PREPARED | LOOM_DECODE_STABLE_METADATA)) != 0) {
+  if ((options.flags & ~LOOM_DECODE_STABLE_METADATA) != 0) {
     throw invalid("paged decode flags contain an unknown bit");
   }
   a.flags = options.flags;
@@ -256,14 +256,6 @@ void paged_decode_attention_strided(DType call_dtype, Region query, Region key_c
     a.partition_tokens = tokens;
   }
   status_result(loom_cuda_paged_decode_attention_ex(&a));
-}
-
-void prepare_decode_workspace(Region workspace, void* stream) {
-  if (workspace.pointer == nullptr || workspace.elements == 0) {
-    throw invalid("paged decode split-K workspace is empty");
-  }
-  status_result(loom_cuda_prepare_decode_workspace(static_cast<float*>(const_cast<void*>(workspace.pointer)),
-                                                   workspace.elements, stream));
 }
 
 void merge_decode_states(Region states, uint32_t parts, uint32_t rows, uint32_t value_head_size,

@@ -78,9 +78,6 @@ void paged_decode_attention_strided(DType call_dtype, Region query, Region key_c
                                     const PagedDecodeAttentionSpec& spec, const StridedDecodeLayout& layout,
                                     const DecodeOptions& options, void* stream);
 
-// Zeroes a decode workspace once, so that later launches may carry LOOM_DECODE_WORKSPACE_PREPARED.
-void prepare_decode_workspace(Region workspace, void* stream);
-
 void merge_decode_states(Region states, uint32_t parts, uint32_t rows, uint32_t value_head_size,
                          DType out_dtype, Region output, void* stream);
 

@@ -615,7 +615,7 @@ int launch_decode(const LoomDecodeArgs& a) {
       ((a.query_token_stride == 0) != (a.query_head_stride == 0)) ||
       (a.query_head_stride != 0 && a.query_head_stride < a.head_size) ||
       !std::isfinite(a.logits_soft_cap) || a.logits_soft_cap < 0.0f ||
-      (a.flags & ~(LOOM_DECODE_WORKSPACE_PREPARED | LOOM_DECODE_STABLE_METADATA)) != 0 || a.reserved != 0) {
+      (a.flags & ~LOOM_DECODE_STABLE_METADATA) != 0 || a.reserved != 0) {
     return LOOM_CUDA_INVALID_ARGUMENT;
   }
 
@@ -715,9 +715,8 @@ int launch_decode(const LoomDecodeArgs& a) {
       tma = nullptr;
       umma = false;
     }
-    // the caller's promises only matter to the balanced TMA-fed mma.sync kernel
+    // the caller's promise only matters to the balanced TMA-fed mma.sync kernel
     const bool promises_apply = tma != nullptr && !umma;
-    p.fused_merge = promises_apply && (a.flags & LOOM_DECODE_WORKSPACE_PREPARED) ? 1u : 0u;
     p.early_metadata = promises_apply && (a.flags & LOOM_DECODE_STABLE_METADATA) ? 1u : 0u;
     if (umma) {
       g_last_route = "umma-fp8-balanced-tma";
@@ -753,10 +752,6 @@ int launch_decode(const LoomDecodeArgs& a) {
   }
   if (status != LOOM_CUDA_SUCCESS || !partitioned) return status;
   if (stream_ctas == 0 && p.max_partitions <= 1) return status;
-  if (p.fused_merge) {  // the decode kernel merged the split items itself
-    g_last_route = fp8 ? "mma16-fp8-balanced-tma-merged" : "mma16-balanced-tma-merged";
-    return status;
-  }
 
   // Second kernel: merge the parts of every row that was split.
   const uint64_t rows = (uint64_t)p.sequences * p.query_heads;
@@ -975,15 +970,6 @@ extern "C" int loom_cuda_read_decode_args(const LoomDecodeArgs* args, LoomDecode
   std::memcpy(out, args, args->struct_size);
   out->struct_size = sizeof(LoomDecodeArgs);
   return 1;
-}
-
-extern "C" int loom_cuda_prepare_decode_workspace(float* workspace, uint64_t workspace_elements, void* stream) {
-  if (workspace == nullptr || workspace_elements == 0 || workspace_elements > (~0ull >> 2)) {
-    return LOOM_CUDA_INVALID_ARGUMENT;
-  }
-  return loom_decode::launched(
-      cudaMemsetAsync(workspace, 0, workspace_elements * sizeof(float), static_cast<cudaStream_t>(stream)),
-      "zeroing a decode workspace (cudaMemsetAsync)");
 }
 
 extern "C" int loom_cuda_paged_decode_attention_ex(const LoomDecodeArgs* args) {

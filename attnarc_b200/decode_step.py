@@ -126,8 +126,7 @@ class CapturedDecodeStep:
             partition_tokens)
         self._partition = partition
         self._split = self.max_sequence_length > partition
-        # zeroed once: the balanced kernel then merges split sequences itself, without a merge launch
-        self._workspace = (ops.prepare_decode_workspace(torch.empty(needed, device=self.device, dtype=torch.float32))
+        self._workspace = (torch.empty(needed, device=self.device, dtype=torch.float32)
                            if self._split and needed else None)
         self.output = torch.empty((self.sequences, self.query_heads, self.head_size), device=self.device,
                                   dtype=dtype)
@@ -150,7 +149,6 @@ class CapturedDecodeStep:
             query, self.kv_cache[:, 0], self.kv_cache[:, 1], self._pieces["block_tables"],
             self._pieces["sequence_lengths"], max_sequence_length=self.max_sequence_length, scale=self.scale,
             workspace=self._workspace, partition_tokens=self._partition, split=self._split, output=self.output,
-            workspace_prepared=True,
             stable_metadata=True,  # lengths and tables arrive with the copy above, before the RoPE launch
             **self._decode_scales)
         self.host_output.copy_(self.output, non_blocking=True)

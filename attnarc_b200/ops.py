@@ -340,7 +340,6 @@ def paged_decode_attention_ex(
     output: torch.Tensor | None = None,
     sliding_window: int = 0,
     logits_soft_cap: float = 0.0,
-    workspace_prepared: bool = False,
     stable_metadata: bool = False,
 ) -> torch.Tensor:
     """Decode over caches of any stride order, native or FP8 E4M3.
@@ -357,10 +356,7 @@ def paged_decode_attention_ex(
     s into ``c * tanh(s / c)`` before the softmax (both are options the
     reference names as later contract fields; 0 = off).
 
-    Two promises let a serving loop shed work. ``workspace_prepared``: the
-    caller's ``workspace`` went through ``prepare_decode_workspace`` once and has
-    only been used by decode calls since; the balanced kernel then merges split
-    sequences itself and no merge kernel is launched. ``stable_metadata``:
+    ``stable_metadata`` is a promise that lets a serving loop shed latency:
     ``block_tables`` and ``sequence_lengths`` were written before the operation
     preceding this call in the stream began (e.g. before the step's RoPE + KV
     write); the kernel then plans its work while that operation still runs.
@@ -387,7 +383,6 @@ def paged_decode_attention_ex(
         if split:
             if workspace is None or workspace.numel() < needed:
                 workspace = torch.empty(needed, device=query.device, dtype=torch.float32)
-                workspace_prepared = False  # a fresh allocation holds anything
         else:
             workspace = None
         scales = (key_scales, value_scales) if fp8 else (None, None)
@@ -410,24 +405,11 @@ def paged_decode_attention_ex(
             1 if emit_state else 0,
             0 if query.is_contiguous() else query.stride(0), 0 if query.is_contiguous() else query.stride(1),
             int(sliding_window), float(logits_soft_cap),
-            (_native.DECODE_WORKSPACE_PREPARED if workspace_prepared and workspace is not None else 0)
-            | (_native.DECODE_STABLE_METADATA if stable_metadata else 0),
+            _native.DECODE_STABLE_METADATA if stable_metadata else 0,
             _stream(query.device),
         )
     check(status, "paged decode attention")
     return output
-
-
-def prepare_decode_workspace(workspace: torch.Tensor) -> torch.Tensor:
-    """Zeroes a decode workspace on the current stream: the one-time preparation that lets later
-    ``paged_decode_attention_ex`` calls pass ``workspace_prepared=True``."""
-    if workspace.dtype != torch.float32 or not workspace.is_contiguous() or workspace.device.type != "cuda":
-        raise RuntimeError("a decode workspace is a contiguous float32 CUDA tensor")
-    with _on_device(workspace.device):
-        check(library().loom_cuda_bridge_prepare_decode_workspace(workspace.data_ptr(), workspace.numel(),
-                                                                  _stream(workspace.device)),
-              "decode workspace preparation")
-    return workspace
 
 
 def merge_decode_states(states: torch.Tensor, out_dtype: torch.dtype,

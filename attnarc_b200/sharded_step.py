@@ -229,11 +229,13 @@ class ShardedDecodeStep:
     allocated once; nothing is planned or allocated per step. ``group`` is the
     process group of the exchange; ``health`` (``multi_gpu.RankHealth``) makes
     ``run`` return a status instead of launching when a peer has left.
+    ``early_metadata`` is the ``stable_metadata`` promise of
+    ``ops.paged_decode_attention_ex``, which the step can make for the caller.
     """
 
     def __init__(self, shard: RankShard, cos_sin_cache: torch.Tensor, *, rope_cache: torch.Tensor | None = None,
                  dtype: torch.dtype, scale: float, is_neox: bool, partition_tokens: int = 0, group=None,
-                 health: "multi_gpu.RankHealth | None" = None):
+                 health: "multi_gpu.RankHealth | None" = None, early_metadata: bool = True):
         kv_cache = shard.rope_cache if rope_cache is None else rope_cache
         self.shard = shard
         self.device = kv_cache.device
@@ -249,6 +251,9 @@ class ShardedDecodeStep:
         self._decode_scales = (dict(key_scales=shard.key_scales, value_scales=shard.value_scales)
                                if self.fp8 else {})
         self.group, self.health = group, health
+        # what the step promises the decode (ops.paged_decode_attention_ex): lengths and tables arrive
+        # with the upload, before the RoPE launch
+        self.early_metadata = bool(early_metadata)
         self.exchange = bool(shard.exchange)
         self.ranks = shard.ranks
 
@@ -292,8 +297,7 @@ class ShardedDecodeStep:
             partition_tokens)
         self._partition = partition
         self._split = self.max_sequence_length > partition
-        # zeroed once: the balanced kernel then merges split sequences itself, without a merge launch
-        self._workspace = (ops.prepare_decode_workspace(torch.empty(needed, device=self.device, dtype=torch.float32))
+        self._workspace = (torch.empty(needed, device=self.device, dtype=torch.float32)
                            if self._split and needed else None)
         rows = (self.sequences, self.query_heads, self.head_size)
         self.output = torch.zeros(rows, device=self.device, dtype=dtype)
@@ -330,9 +334,8 @@ class ShardedDecodeStep:
             query, kv_cache[:, 0], kv_cache[:, 1], self._pieces["block_tables"], self._pieces["sequence_lengths"],
             max_sequence_length=self.max_sequence_length, scale=self.scale, workspace=self._workspace,
             partition_tokens=self._partition, split=self._split, emit_state=self.exchange,
-            output=self._states if self.exchange else self.output, workspace_prepared=True,
-            # lengths and tables arrive with the upload, before the RoPE launch that precedes the decode
-            stable_metadata=rope, **self._decode_scales)
+            output=self._states if self.exchange else self.output, stable_metadata=self.early_metadata,
+            **self._decode_scales)
         if self.exchange and exchange:
             dist.all_gather_into_tensor(self._gathered.view(-1), self._states.view(-1), group=self.group)
             ops.merge_decode_states(self._gathered, self.output.dtype,

@@ -127,6 +127,8 @@ def parse_args():
                         help="override the workload's batch size (smaller cases for profiler captures)")
     parser.add_argument("--copies", type=int, default=0, help="cache copies rotated between steps (0 = auto)")
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--late-metadata", action="store_true",
+                        help="do not promise stable metadata: the decode kernel plans after the grid dependency wait")
     parser.add_argument("--programmatic-launch", type=int, choices=[0, 1], default=None,
                         help="programmatic dependent launch mode of the library (default: the library's, 1)")
     parser.add_argument("--cpu-seconds", type=float, default=15.0, help="CPU work per baseline sample")
@@ -489,7 +491,8 @@ def measure_workload(args, ranks, name, steps, headline):
     def make_step(rope_cache):
         return sharded_step.ShardedDecodeStep(shard, cos_sin, rope_cache=rope_cache, dtype=config.torch_dtype,
                                               scale=1.0 / float(np.sqrt(config.head_size)), is_neox=is_neox,
-                                              partition_tokens=config.partition_tokens)
+                                              partition_tokens=config.partition_tokens,
+                                              early_metadata=not args.late_metadata)
 
     # Rotate over several copies of the local cache so that a step never finds its KV in the
     # 126 MB L2 left there by the previous step.

@@ -169,7 +169,7 @@ int loom_cuda_bridge_paged_decode_attention_ex(
  * sliding_window W > 0 lets a query see only the last W tokens of its sequence;
  * logits_soft_cap c > 0 (finite) turns every scaled score s into
  * c * tanh(s / c) before the softmax. `flags` carries the caller's
- * LOOM_DECODE_* promises (0 = none).
+ * LOOM_DECODE_* promises (0 = none; include/loom_launch.h).
  */
 int loom_cuda_bridge_paged_decode_attention_with_options(
     uint32_t dtype, uint32_t cache_encoding, const void* query,
@@ -192,12 +192,6 @@ int loom_cuda_bridge_paged_decode_attention_with_options(
     uint32_t sliding_window, float logits_soft_cap, uint32_t flags,
     void* stream);
 
-/* Checked form of loom_cuda_prepare_decode_workspace: zeroes a decode workspace
- * once so that later calls may pass LOOM_DECODE_WORKSPACE_PREPARED in `flags`
- * (include/loom_launch.h says what the two flag bits promise). */
-int loom_cuda_bridge_prepare_decode_workspace(float* workspace,
-                                              uint64_t workspace_elements,
-                                              void* stream);
 
 int loom_cuda_bridge_paged_decode_workspace_elements_ex(
     uint32_t sequences, uint32_t query_heads, uint32_t kv_heads,

@@ -190,17 +190,9 @@ typedef struct LoomDecodeArgs {
 } LoomDecodeArgs;
 
 /*
- * LoomDecodeArgs.flags. Each is a promise by the caller that lets the launch
- * skip work; without them nothing is assumed.
+ * LoomDecodeArgs.flags: promises by the caller that let the launch skip work;
+ * without them nothing is assumed.
  *
- * LOOM_DECODE_WORKSPACE_PREPARED: `workspace` was zeroed once
- *   (loom_cuda_prepare_decode_workspace, or any memset) after it was allocated
- *   and has since been written by decode launches of this library only. The
- *   balanced kernel then merges the parts of a split sequence itself (the last
- *   CTA to finish a (sequence, KV head) item does it, found through a ticket in
- *   the workspace that every launch leaves at zero again) and no merge kernel is
- *   launched. After a launch whose timeout flag was raised
- *   (loom_cuda_decode_timeout_flag) prepare the workspace again.
  * LOOM_DECODE_STABLE_METADATA: block_tables and sequence_lengths were written
  *   before the operation that precedes this launch in the stream began (in a
  *   serving step: before the RoPE + KV-write launch). The balanced kernel then
@@ -208,7 +200,6 @@ typedef struct LoomDecodeArgs {
  *   is still running; the query, the caches and the outputs are still only
  *   touched after it has completed.
  */
-#define LOOM_DECODE_WORKSPACE_PREPARED 1u
 #define LOOM_DECODE_STABLE_METADATA 2u
 
 /* struct_size of the LoomDecodeArgs layout that ends with `stream`. */
@@ -237,12 +228,6 @@ uint64_t loom_cuda_paged_decode_workspace_elements(
     uint32_t sequences, uint32_t query_heads, uint32_t kv_heads,
     uint32_t value_head_size, uint32_t max_sequence_length,
     uint32_t partition_tokens);
-
-/* Zeroes a decode workspace on `stream` (one memset, asynchronous): the one-time
- * preparation LOOM_DECODE_WORKSPACE_PREPARED asks for. */
-int loom_cuda_prepare_decode_workspace(float* workspace,
-                                       uint64_t workspace_elements,
-                                       void* stream);
 
 /* General decode: any stride order, native or FP8 cache, optional workspace. */
 int loom_cuda_paged_decode_attention_ex(const LoomDecodeArgs* args);

@@ -524,49 +524,37 @@ def helpers_bridge_error():
     return BridgeError
 
 
-# ---- the caller's promises: a prepared workspace (the kernel merges split sequences itself) and
-# stable metadata (the kernel plans its work before the preceding kernel has completed) -------------
+# ---- the caller's promise of stable metadata: the kernel plans its work before the preceding kernel
+# has completed; results must not change ------------------------------------------------------------
 
 @pytest.mark.parametrize("name,lengths", [
     ("cfg2", [1, 0, 700, 4096, 64, 2049, 0, 333]),
     ("cfg4", [5000, 16, 0, 1200]),
     ("cfg5", [40000, 300, 0, 7]),
 ])
-@pytest.mark.parametrize("emit_state", [False, True])
-def test_prepared_workspace_merges_inside_the_decode_kernel(ops, name, lengths, emit_state):
+def test_stable_metadata_changes_nothing_but_the_timing(ops, name, lengths):
     config = workloads.scaled(workloads.CONFIGS[name], batch=len(lengths), lengths=("fixed", [max(n, 1) for n in lengths]))
     case = workloads.build_case(config, DEVICE, seed=17)
     case.sequence_lengths.copy_(torch.tensor(lengths, dtype=torch.int32))  # empty sequences included
     key_cache, value_cache = case.cache_views()
-    query = case.query.contiguous()
     scales = dict(key_scales=case.key_scales, value_scales=case.value_scales) if config.cache == "fp8" else {}
-    common = dict(max_sequence_length=case.max_sequence_length, scale=case.scale, split=True, emit_state=emit_state,
-                  **scales)
-    separate = ops.paged_decode_attention_ex(query, key_cache, value_cache, case.block_tables,
-                                             case.sequence_lengths, **common)
-    assert ops.last_decode_route().endswith("balanced-tma")
-    needed, _ = ops.decode_workspace_elements_ex(len(lengths), config.query_heads, config.kv_heads, config.head_size,
-                                                 case.max_sequence_length)
-    workspace = ops.prepare_decode_workspace(torch.full((needed,), float("nan"), device=DEVICE))
-    for call in range(3):  # the tickets must be back at zero after every launch
-        merged = ops.paged_decode_attention_ex(query, key_cache, value_cache, case.block_tables,
-                                               case.sequence_lengths, workspace=workspace,
-                                               workspace_prepared=True, stable_metadata=call == 2, **common)
-        assert ops.last_decode_route().endswith("balanced-tma-merged")
-        if emit_state:
-            # same parts, same arithmetic: the states may differ in the order the parts were folded
-            live = torch.tensor([n > 0 for n in lengths], device=DEVICE)
-            assert torch.allclose(merged[live], separate[live], rtol=1e-5, atol=1e-5)
-            assert bool((merged[~live][..., -1] == 0).all()) and bool((merged[~live][..., :-2] == 0).all())
-        else:
-            assert torch.equal(merged, separate), f"call {call}"
-    if not emit_state:
-        live = [i for i, n in enumerate(lengths) if n > 0]
-        expected = helpers.oracle_decode(query[live], key_cache, value_cache, case.block_tables[live],
-                                         case.sequence_lengths[live], scale=case.scale,
-                                         max_sequence_length=case.max_sequence_length, **scales)
-        helpers.assert_close(merged[live], expected, config.torch_dtype, f"{name} merged in the decode kernel")
-        assert bool((merged[[i for i, n in enumerate(lengths) if n == 0]] == 0).all())
+    rows = case.qkv.view(len(lengths), config.query_heads + 2 * config.kv_heads, config.head_size)
+    outputs = []
+    for stable in (False, True):
+        qkv = rows.clone()
+        query = qkv[:, :config.query_heads]
+        # a RoPE launch directly before the decode, as in a serving step: with the promise the decode
+        # kernel starts planning while this one is still rotating
+        ops.rope_paged_kv_write_(query, qkv[:, config.query_heads:config.query_heads + config.kv_heads],
+                                 qkv[:, config.query_heads + config.kv_heads:], case.positions, case.cos_sin_cache,
+                                 case.rope_cache_argument(), case.key_scales, case.value_scales, case.slot_mapping,
+                                 is_neox=config.rope_style == "neox")
+        outputs.append(ops.paged_decode_attention_ex(query, key_cache, value_cache, case.block_tables,
+                                                     case.sequence_lengths,
+                                                     max_sequence_length=case.max_sequence_length, scale=case.scale,
+                                                     split=True, stable_metadata=stable, **scales))
+        assert ops.last_decode_route().endswith("balanced-tma")
+    assert torch.equal(outputs[0], outputs[1])
     assert ops.decode_timeout_flag() == 0
 
 
@@ -577,5 +565,5 @@ def test_unknown_decode_flags_are_refused(ops):
 
     args = _native.LoomDecodeArgs()
     args.struct_size = ctypes.sizeof(_native.LoomDecodeArgs)
-    args.flags = 4
+    args.flags = 1
     assert _native.library().loom_cuda_paged_decode_attention_ex(ctypes.byref(args)) == 1
