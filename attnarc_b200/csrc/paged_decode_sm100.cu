@@ -481,11 +481,19 @@ int launch_mma_shape(const DecodeParams& p, uint32_t stream_ctas, const CacheMap
   return wide ? launch_mma<QT, kFp8, 64, 2>(p, stream) : launch_mma<QT, kFp8, 64, 1>(p, stream);
 }
 
+// Shared memory of the CUDA-core kernel: the query row, one O row per warp, (max, sum) per warp.
+// One predicate for the launch and for loom_cuda_supports_paged_decode.
+size_t scalar_smem_bytes(uint32_t head_size, uint32_t value_head_size) {
+  return ((size_t)head_size + (size_t)kScalarWarps * value_head_size + 2 * kScalarWarps) * sizeof(float);
+}
+bool scalar_smem_fits(uint32_t head_size, uint32_t value_head_size) {
+  return scalar_smem_bytes(head_size, value_head_size) <= 48 * 1024;
+}
+
 template <typename QT, typename CT>
 int launch_scalar(const DecodeParams& p, cudaStream_t stream) {
-  const size_t bytes =
-      ((size_t)p.head_size + (size_t)kScalarWarps * p.value_head_size + 2 * kScalarWarps) * sizeof(float);
-  if (bytes > 48 * 1024) return LOOM_CUDA_UNSUPPORTED;
+  const size_t bytes = scalar_smem_bytes(p.head_size, p.value_head_size);
+  if (!scalar_smem_fits(p.head_size, p.value_head_size)) return LOOM_CUDA_UNSUPPORTED;
   const dim3 grid(p.sequences * p.max_partitions, p.query_heads, 1);
   return launched(loom_launch::launch(decode_scalar_kernel<QT, CT>, grid, dim3(kScalarThreads), bytes, stream, p));
 }
@@ -1019,9 +1027,12 @@ extern "C" int loom_cuda_supports_paged_decode(uint32_t dtype, uint32_t cache_en
   } else if (max_sequence_length > (1u << 30) ||
              (uint64_t)sequences * query_heads > 0x7fffffffull || query_heads > 65535u) {
     why = "paged decode attention shape exceeds the CUDA ABI";
-  } else if (value_head_size > 32u * loom_decode::kScalarMaxValueRegs &&
-             !(head_size == value_head_size && (head_size == 64 || head_size == 128))) {
+  } else if (!(head_size == value_head_size && (head_size == 64 || head_size == 128)) &&
+             value_head_size > 32u * loom_decode::kScalarMaxValueRegs) {
     why = "B200 paged decode attention supports value heads of at most 512 elements";
+  } else if (!loom_decode::scalar_smem_fits(head_size, value_head_size)) {
+    // any shape may end on the CUDA-core route (F32, unaligned views); its shared memory bounds the head size
+    why = "B200 paged decode attention head size exceeds the shared memory of its general kernel";
   }
   if (reason != nullptr) *reason = why != nullptr ? why : "supported";
   return why == nullptr ? 1 : 0;

@@ -50,8 +50,11 @@ FALLBACK_HBM_GBS = 6650.0
 # the default workload); None until a capture exists for the workload.
 NCU_DRAM_TRAFFIC_BYTES = {"kv-move": 537_019_136 + 486_040_832, "kv-swap": 1_073_888_512 + 1_016_135_680}
 # DRAM bytes (read + written) per algorithmic KV byte of the decode kernel, from one-launch ncu
-# captures on a 24-sequence cut of each workload (cfg2: the whole batch), see profiles/.
-NCU_DRAM_TRAFFIC_PER_KV_BYTE = {"cfg2": (154_178_048 + 3_579_648) / 153_306_112}
+# captures (dram__bytes_read.sum + dram__bytes_write.sum of the first captured launch) on a
+# 24-sequence cut of cfg3 and cfg4 and on the whole of cfg2 and cfg5; traffic grows with the
+# token count, so a full launch is this ratio times its KV bytes
+# (profiles/decode_dram_traffic_all_configs.md).
+NCU_DRAM_TRAFFIC_PER_KV_BYTE = {"cfg2": 1.0267, "cfg3": 1.0170, "cfg4": 1.0137, "cfg5": 1.0056}
 
 
 def reference_kernels_baseline(case, config, cache_views, steps):
@@ -601,8 +604,8 @@ def measure_workload(args, ranks, name, steps, headline):
             "us_per_launch": local_decode_us, "algorithmic_bytes_per_launch": shard.kv_bytes,
             "traffic": None if traffic is None else int(traffic * shard.kv_bytes),
             "traffic_source": None if traffic is None else
-            "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch on a 24-sequence cut of the workload, "
-            "scaled by KV bytes (profiles/)",
+            "ncu dram__bytes_read.sum + dram__bytes_write.sum of one decode launch on a cut of the workload, "
+            "scaled by KV bytes (profiles/decode_dram_traffic_all_configs.md)",
         },
         "decode_route": route, "clocks": clocks, "parity_max_abs_err": parity,
         "parity_against": None if parity is None else "this rank's single-GPU decode of the global batch",

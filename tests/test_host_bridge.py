@@ -231,3 +231,43 @@ def test_decode_args_of_both_layouts_are_read_and_others_refused():
     assert lib.loom_cuda_read_decode_args(None, ctypes.byref(out)) == 0
     # launch entry points refuse an unknown layout before touching anything
     assert lib.loom_cuda_paged_decode_attention_ex(ctypes.byref(source)) == 1
+
+
+def test_capability_answer_agrees_with_the_launch_for_oversized_heads():
+    """`loom_cuda_supports_paged_decode` and the launch share one predicate for the general kernel's
+    shared memory: a shape the query refuses is refused by the launch with LOOM_CUDA_UNSUPPORTED,
+    before any CUDA call (so this runs without a device)."""
+    import ctypes
+
+    from attnarc_b200 import _native
+
+    lib = _native.library()
+    lib.loom_cuda_supports_paged_decode.argtypes = [ctypes.c_uint32] * 11 + [ctypes.POINTER(ctypes.c_char_p)]
+    reason = ctypes.c_char_p()
+
+    def supported(dtype, head_size, value_head_size):
+        return lib.loom_cuda_supports_paged_decode(dtype, 0, 2, 4, 2, head_size, value_head_size, 8, 16, 4, 64,
+                                                   ctypes.byref(reason))
+
+    def launch_status(dtype, head_size, value_head_size):
+        args = _native.LoomDecodeArgs()
+        args.struct_size = ctypes.sizeof(_native.LoomDecodeArgs)
+        args.dtype = dtype
+        fake = 0x10000  # never dereferenced on the host; the refusal comes before any launch
+        for name in ("query", "key_cache", "value_cache", "block_tables", "sequence_lengths", "output"):
+            setattr(args, name, fake)
+        args.sequences, args.query_heads, args.kv_heads = 2, 4, 2
+        args.head_size, args.value_head_size = head_size, value_head_size
+        args.num_blocks, args.block_size, args.max_blocks_per_sequence, args.max_sequence_length = 8, 16, 4, 64
+        args.key_block_stride, args.key_page_stride, args.key_head_stride = 16 * 2 * head_size, 2 * head_size, head_size
+        args.value_block_stride = 16 * 2 * value_head_size
+        args.value_page_stride, args.value_head_stride = 2 * value_head_size, value_head_size
+        args.scale = 0.1
+        return lib.loom_cuda_paged_decode_attention_ex(ctypes.byref(args))
+
+    assert supported(0, 128, 128) == 1 and supported(2, 256, 256) == 1
+    for dtype, head_size, value_head_size in ((0, 16384, 256), (2, 20000, 64), (1, 12288, 512)):
+        assert supported(dtype, head_size, value_head_size) == 0, reason.value
+        assert b"shared memory" in reason.value
+        assert launch_status(dtype, head_size, value_head_size) == 2  # LOOM_CUDA_UNSUPPORTED
+    assert supported(0, 64, 1024) == 0 and launch_status(0, 64, 1024) == 2  # value heads beyond 512 elements
