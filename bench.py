@@ -461,6 +461,45 @@ def single_gpu_rows(case):
     return out
 
 
+def reference_abi_single_pass_us(case, launches=5):
+    """Times `loom_cuda_paged_decode_attention_bf16` / `_f16`, the reference-shaped entry point WITHOUT
+    a workspace (one CTA walks a whole context), on a dense-inner NHD native cache. On long contexts
+    and small batches this uses a handful of SMs: the figure is on record so that callers of the
+    reference ABI know to use its split-K entry (or the `_ex` entry) with a workspace there."""
+    import torch
+
+    from attnarc_b200 import _native
+
+    c = case.config
+    if c.layout != "NHD" or c.cache != "native" or c.dtype not in ("bf16", "f16"):
+        return None
+    lib = _native.library()
+    entry = getattr(lib, f"loom_cuda_paged_decode_attention_{c.dtype}")
+    key_cache, value_cache = case.cache_views()
+    query = case.query.contiguous()
+    output = torch.empty_like(query)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def launch():
+        status = entry(query.data_ptr(), key_cache.data_ptr(), value_cache.data_ptr(), case.block_tables.data_ptr(),
+                       case.sequence_lengths.data_ptr(), output.data_ptr(), c.batch, c.query_heads, c.kv_heads,
+                       c.head_size, c.head_size, case.num_blocks, c.block_size, key_cache.stride(0),
+                       value_cache.stride(0), case.block_tables.shape[1], case.max_sequence_length, case.scale,
+                       stream)
+        if status != 0:
+            raise SystemExit(f"reference-shaped decode entry failed with status {status}")
+
+    launch()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(launches):
+        launch()
+    stop.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(stop) / launches * 1e3
+
+
 def measure_workload(args, ranks, name, steps, headline):
     """Builds the workload's global batch, shards it over the ranks, times it; returns rank-local
     figures already reduced over ranks (every rank gets the same record)."""
@@ -582,6 +621,15 @@ def measure_workload(args, ranks, name, steps, headline):
         reference_gpu = reference_kernels_baseline(case, config, case.cache_views(), steps)
         if reference_gpu is not None:
             record["reference_gpu_baseline"] = reference_gpu
+
+    if world == 1 and name == "cfg5":
+        single_pass_us = reference_abi_single_pass_us(case)
+        if single_pass_us is not None:
+            record["reference_abi_without_workspace"] = {
+                "us_per_launch": single_pass_us,
+                "note": "loom_cuda_paged_decode_attention_bf16 without a workspace: one CTA per (sequence, KV head) "
+                        "walks the whole context; with a workspace (split-K entry) the same call takes the "
+                        "decode time of this record"}
 
     launches = step.kernel_launches if shard.sequences else 0
     step_ms, decode_ms_max = ranks.reduce([step_ms, decode_ms])
