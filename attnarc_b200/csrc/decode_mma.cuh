@@ -59,9 +59,9 @@ struct MmaTile {
 
 // Shared memory the cross-warp merge needs: per warp 8*kNT heads of kD + 4
 // floats of O, plus one max and one sum per head.
-template <int kNT, int kD>
+template <int kNT, int kD, int kWarps = kMmaWarps>
 constexpr int mma_merge_bytes() {
-  return kMmaWarps * (8 * kNT) * (kD + 4 + 2) * 4;
+  return kWarps * (8 * kNT) * (kD + 4 + 2) * 4;
 }
 
 template <bool kFp8, int kD, int kNT>
@@ -398,8 +398,8 @@ __device__ __forceinline__ void chunk_values(WarpState<kD, kNT>& state, const ui
   }
 }
 
-// Layout of the cross-warp merge area.
-template <int kD, int kNT>
+// Layout of the cross-warp merge area (kWarps warps compute: four, unless a kernel says otherwise).
+template <int kD, int kNT, int kWarps = kMmaWarps>
 struct MergeArea {
   static constexpr int kHeads = 8 * kNT;
   static constexpr int kORow = kD + 4;
@@ -408,15 +408,15 @@ struct MergeArea {
   float* sum;  // [warps][kHeads]
   __device__ __forceinline__ explicit MergeArea(void* base) {
     o = reinterpret_cast<float*>(base);
-    max = o + kMmaWarps * kHeads * kORow;
-    sum = max + kMmaWarps * kHeads;
+    max = o + kWarps * kHeads * kORow;
+    sum = max + kWarps * kHeads;
   }
 };
 
 // Completes a warp's row sums and parks its state in the merge area. The
 // caller brackets this with CTA barriers.
-template <bool kFp8, int kD, int kNT>
-__device__ __forceinline__ void park_warp_state(MergeArea<kD, kNT> area, WarpState<kD, kNT>& state,
+template <bool kFp8, int kD, int kNT, int kWarps = kMmaWarps>
+__device__ __forceinline__ void park_warp_state(MergeArea<kD, kNT, kWarps> area, WarpState<kD, kNT>& state,
                                                 uint32_t warp, uint32_t g, uint32_t t) {
   constexpr int kHeads = 8 * kNT;
   constexpr int kORow = kD + 4;
@@ -450,26 +450,27 @@ __device__ __forceinline__ void park_warp_state(MergeArea<kD, kNT> area, WarpSta
   }
 }
 
-// Merges the four parked warp states and stores, per live head, either the
+// Merges the parked warp states and stores, per live head, either the
 // normalised output row (`final_out`, type QT) or an F32 state row
-// (`state_rows` + head * state_head_stride floats).
-template <typename QT, int kD, int kNT>
-__device__ __forceinline__ void combine_and_store(MergeArea<kD, kNT> area, uint32_t live_heads,
+// (`state_rows` + head * state_head_stride floats). Called by the kWarps
+// computing warps of the CTA (threads 0 .. 32 * kWarps - 1).
+template <typename QT, int kD, int kNT, int kWarps = kMmaWarps>
+__device__ __forceinline__ void combine_and_store(MergeArea<kD, kNT, kWarps> area, uint32_t live_heads,
                                                   float value_scale, QT* final_out,
                                                   uint64_t final_head_stride, float* state_rows,
                                                   uint64_t state_head_stride) {
   constexpr int kHeads = 8 * kNT;
   constexpr int kORow = kD + 4;
-  for (uint32_t index = threadIdx.x; index < live_heads * kD; index += kMmaThreads) {
+  for (uint32_t index = threadIdx.x; index < live_heads * kD; index += kWarps * 32) {
     const uint32_t head = index / kD;
     const uint32_t dv = index % kD;
     float top = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < kMmaWarps; ++w) top = fmaxf(top, area.max[w * kHeads + head]);
+    for (int w = 0; w < kWarps; ++w) top = fmaxf(top, area.max[w * kHeads + head]);
     float acc = 0.0f, total = 0.0f;
     if (top > -INFINITY) {
 #pragma unroll
-      for (int w = 0; w < kMmaWarps; ++w) {
+      for (int w = 0; w < kWarps; ++w) {
         const float factor = fast_exp2(area.max[w * kHeads + head] - top);
         acc += area.o[((size_t)w * kHeads + head) * kORow + dv] * factor;
         total += area.sum[w * kHeads + head] * factor;

@@ -44,6 +44,7 @@
 #include "decode_merge.cuh"
 #include "decode_mma.cuh"
 #include "decode_stream.cuh"
+#include "decode_stream_split.cuh"
 #include "decode_stream_tma.cuh"
 #include "decode_umma.cuh"
 
@@ -444,6 +445,19 @@ int launch_stream_tma(const DecodeParams& p, uint32_t ctas, const CacheMaps& map
                                       maps.axes));
 }
 
+// The balanced kernel with a copy-issuing warp (FP8 caches, up to 8 query heads per KV head, no options).
+template <typename QT, int kD>
+int launch_stream_split(const DecodeParams& p, uint32_t ctas, const CacheMaps& maps, cudaStream_t stream) {
+  static std::atomic<uint64_t> configured{0};
+  using Ring = SplitRing<true, kD>;
+  auto kernel = decode_stream_split_kernel<QT, true, kD>;
+  if (const cudaError_t limit = ensure_smem(kernel, Ring::kSmemBytes, configured); limit != cudaSuccess) {
+    return launched(limit, "shared-memory limit of a decode kernel (cudaFuncSetAttribute)");
+  }
+  return launched(loom_launch::launch(kernel, dim3(ctas), dim3(Ring::kThreads), Ring::kSmemBytes, stream, p, maps.key,
+                                      maps.value, maps.axes));
+}
+
 template <typename QT>
 int launch_umma_fp8(const DecodeParams& p, uint32_t ctas, const CacheMaps& maps, cudaStream_t stream) {
   static std::atomic<uint64_t> configured{0};
@@ -673,6 +687,7 @@ int launch_decode(const LoomDecodeArgs& a) {
   CacheMaps maps;
   const CacheMaps* tma = nullptr;
   bool umma = false;
+  bool split = false;  // the balanced kernel with a copy-issuing warp
   if (partitioned) {
     if (a.workspace == nullptr || (reinterpret_cast<uintptr_t>(a.workspace) & 3u) != 0) {
       return LOOM_CUDA_INVALID_ARGUMENT;
@@ -691,13 +706,19 @@ int launch_decode(const LoomDecodeArgs& a) {
       umma = tma != nullptr && fp8 && p.group <= 8 && a.head_size == 128 && a.value_head_size == 128 &&
              g_copy_engine.load(std::memory_order_relaxed) == 3 && a.sliding_window == 0 &&
              a.logits_soft_cap == 0.0f;  // the options live in the mma.sync kernels only
+      // FP8 cache, up to 8 query heads per KV head, no window or soft cap: the kernel whose copies are
+      // issued by a warp of their own (copy engine 2 keeps the unsplit kernel, for comparisons)
+      split = tma != nullptr && !umma && fp8 && p.group <= 8 && a.sliding_window == 0 &&
+              a.logits_soft_cap == 0.0f && g_copy_engine.load(std::memory_order_relaxed) != 2;
       const uint32_t ctas = stream_ctas_for_launch(
-          umma ? (uint32_t)kUmmaCtasPerSm : (tma != nullptr && p.group <= 8 ? (fp8 ? 4u : 3u) : kStreamCtasPerSm));
+          umma    ? (uint32_t)kUmmaCtasPerSm
+          : split ? 2u
+                  : (tma != nullptr && p.group <= 8 ? (fp8 ? 4u : 3u) : kStreamCtasPerSm));
       if (ctas != 0 && stream_shape(a.sequences, a.query_heads, a.kv_heads, a.value_head_size, ctas, &shape) &&
           a.workspace_elements >= shape.total_elements) {
         stream_ctas = ctas;
         p.item_meta = reinterpret_cast<uint32_t*>(a.workspace + shape.slot_elements);
-        p.partition_tokens = kStreamTileTokens;
+        p.partition_tokens = split ? (uint32_t)SplitRing<true, 128>::kTileTokens : kStreamTileTokens;
         p.max_partitions = 1;
       }
     }
@@ -722,6 +743,7 @@ int launch_decode(const LoomDecodeArgs& a) {
     if (stream_ctas == 0) {
       tma = nullptr;
       umma = false;
+      split = false;
     }
     // the caller's promise only matters to the balanced TMA-fed mma.sync kernel
     const bool promises_apply = tma != nullptr && !umma;
@@ -730,6 +752,15 @@ int launch_decode(const LoomDecodeArgs& a) {
       g_last_route = "umma-fp8-balanced-tma";
       status = a.dtype == 1 ? launch_umma_fp8<__half>(p, stream_ctas, maps, stream)
                             : launch_umma_fp8<__nv_bfloat16>(p, stream_ctas, maps, stream);
+    } else if (split) {
+      g_last_route = "mma16-fp8-balanced-producer-tma";
+      if (a.head_size == 128) {
+        status = a.dtype == 1 ? launch_stream_split<__half, 128>(p, stream_ctas, maps, stream)
+                              : launch_stream_split<__nv_bfloat16, 128>(p, stream_ctas, maps, stream);
+      } else {
+        status = a.dtype == 1 ? launch_stream_split<__half, 64>(p, stream_ctas, maps, stream)
+                              : launch_stream_split<__nv_bfloat16, 64>(p, stream_ctas, maps, stream);
+      }
     } else {
     if (stream_ctas == 0) g_last_route = fp8 ? "mma16-fp8" : "mma16";
     else if (tma != nullptr) g_last_route = fp8 ? "mma16-fp8-balanced-tma" : "mma16-balanced-tma";

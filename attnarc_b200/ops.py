@@ -64,9 +64,11 @@ def set_programmatic_launch(mode: int) -> None:
 
 
 def set_decode_copy_engine(engine: str) -> None:
-    """How the balanced kernel is fed: ``"tma"`` (default), ``"cp_async"``
-    (per-lane copies) or ``"tma-umma"`` (TMA, and the tcgen05 kernel where it
-    applies: FP8 cache, head size 128, up to 8 query heads per KV head)."""
+    """How the balanced kernel is fed: ``"tma"`` (default; over an FP8 cache the
+    copies are issued by a warp of their own), ``"cp_async"`` (per-lane copies),
+    ``"tma-mma"`` (TMA with every computing warp feeding its own ring) or
+    ``"tma-umma"`` (TMA, and the tcgen05 kernel where it applies: FP8 cache,
+    head size 128, up to 8 query heads per KV head)."""
     code = {"tma": 0, "cp_async": 1, "tma-mma": 2, "tma-umma": 3}[engine]
     if library().loom_cuda_set_decode_copy_engine(code) != 0:
         raise RuntimeError("could not select the decode copy engine")

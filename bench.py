@@ -130,6 +130,8 @@ def parse_args():
                         help="override the workload's batch size (smaller cases for profiler captures)")
     parser.add_argument("--copies", type=int, default=0, help="cache copies rotated between steps (0 = auto)")
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--copy-engine", choices=["tma", "cp_async", "tma-mma", "tma-umma"], default=None,
+                        help="how the balanced decode kernel is fed (default: the library's choice)")
     parser.add_argument("--late-metadata", action="store_true",
                         help="do not promise stable metadata: the decode kernel plans after the grid dependency wait")
     parser.add_argument("--programmatic-launch", type=int, choices=[0, 1], default=None,
@@ -679,6 +681,8 @@ def run_b200(args):
 
     if args.programmatic_launch is not None:
         ops.set_programmatic_launch(args.programmatic_launch)
+    if args.copy_engine is not None:
+        ops.set_decode_copy_engine(args.copy_engine)
     ranks = Ranks()
     head, config = measure_workload(args, ranks, args.workload, args.steps, headline=True)
     others = {}

@@ -282,11 +282,14 @@ uint64_t loom_cuda_plain_launch_retries(void);
 /*
  * How the balanced decode kernel fills its shared-memory rings: 0 (default)
  * uses the Tensor Memory Accelerator whenever the cache can be described by a
- * tensor map, 1 always uses per-lane cp.async copies, 3 is 0 plus the tcgen05
- * kernel (E4M3 operands read by the tensor cores straight from shared memory,
+ * tensor map, and over an FP8 cache (up to 8 query heads per KV head, no window
+ * or soft cap) the kernel whose copies are issued by a warp of their own; 1
+ * always uses per-lane cp.async copies; 2 is 0 without that copy-issuing warp
+ * (every computing warp feeds its own ring); 3 is 0 plus the tcgen05 kernel
+ * (E4M3 operands read by the tensor cores straight from shared memory,
  * accumulators in tensor memory) for FP8 caches with head size 128 and up to 8
- * query heads per KV head (2 is 0). Process-wide; meant for comparisons and as
- * a switch to fall back on.
+ * query heads per KV head. Process-wide; meant for comparisons and as a switch
+ * to fall back on.
  */
 int loom_cuda_set_decode_copy_engine(uint32_t engine);
 

@@ -25,12 +25,15 @@ def ops():
     module.set_wait_policy()
     yield module
     module.set_wait_policy()
+    module.set_decode_copy_engine("tma")
     module.decode_timeout_flag(reset=True)
     module.kv_block_move_timeout_flag(reset=True)
 
 
-@pytest.mark.parametrize("name", ["cfg2", "cfg4"])
-def test_an_expired_wait_of_the_decode_kernel_sets_the_flag_and_returns(ops, name):
+@pytest.mark.parametrize("name,engine", [("cfg2", "tma"), ("cfg4", "tma"), ("cfg4", "tma-mma")])
+def test_an_expired_wait_of_the_decode_kernel_sets_the_flag_and_returns(ops, name, engine):
+    # cfg4 / tma: the FP8 kernel whose copies are issued by a warp of their own; tma-mma: every warp feeds itself
+    ops.set_decode_copy_engine(engine)
     config = workloads.scaled(workloads.CONFIGS[name], batch=3, lengths=("fixed", [700, 64, 300]))
     case = workloads.build_case(config, DEVICE, seed=9)
     key_cache, value_cache = case.cache_views()
@@ -47,7 +50,9 @@ def test_an_expired_wait_of_the_decode_kernel_sets_the_flag_and_returns(ops, nam
     expected = helpers.oracle_decode(query, key_cache, value_cache, case.block_tables, case.sequence_lengths,
                                      scale=case.scale, max_sequence_length=case.max_sequence_length, **scales)
     helpers.assert_close(decode(), expected, config.torch_dtype, "before")
-    assert "balanced-tma" in ops.last_decode_route()
+    route = ops.last_decode_route()
+    assert "balanced" in route and route.endswith("-tma")
+    assert ("producer" in route) == (name == "cfg4" and engine == "tma")
     assert ops.decode_timeout_flag() == 0
 
     ops.set_wait_policy(attempts=400, unmatched_bytes=16)
