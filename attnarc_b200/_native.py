@@ -128,6 +128,17 @@ def _declare(lib):
     lib.loom_cuda_block_table_remap.argtypes = [ptr, u64, ptr, u32, ptr]
     lib.loom_cuda_set_kv_block_move_engine.argtypes = [u32]
     lib.loom_cuda_kv_block_move_timeout_flag.argtypes = [ctypes.POINTER(u32), u32]
+    # peer exchange of partial states
+    lib.loom_cuda_peer_exchange_bytes.restype = u64
+    lib.loom_cuda_peer_exchange_bytes.argtypes = [u32, u32, u32]
+    lib.loom_cuda_peer_exchange_create.argtypes = [u64, ctypes.POINTER(ptr), ctypes.c_char_p, u64]
+    lib.loom_cuda_peer_exchange_open.argtypes = [ctypes.c_char_p, u64, ctypes.POINTER(ptr)]
+    lib.loom_cuda_peer_exchange_close.argtypes = [ptr]
+    lib.loom_cuda_peer_exchange_destroy.argtypes = [ptr]
+    lib.loom_cuda_peer_exchange_reset.argtypes = [ptr, u64, ptr]
+    lib.loom_cuda_peer_exchange_status.argtypes = [ptr, ctypes.POINTER(u64), ctypes.POINTER(u32)]
+    lib.loom_cuda_peer_exchange_push.argtypes = [ptr, ctypes.POINTER(ptr), u32, u32, u32, u32, ptr]
+    lib.loom_cuda_peer_exchange_merge.argtypes = [ptr, u32, u32, u32, u32, ptr, ptr]
     # partitioner
     i64p, u32p, u64p = ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(u32), ctypes.POINTER(u64)
     lib.loom_partition_by_sequence.argtypes = [i64p, u32, u32, u32p, u64p]

@@ -25,6 +25,7 @@ SOURCES = [
     "paged_decode_sm100.cu",
     "kv_block_move_sm100.cu",
     "multi_token_sm100.cu",
+    "peer_exchange_sm100.cu",
     "dispatch.cpp",
     "bridge.cpp",
     "partition.cpp",

@@ -298,6 +298,112 @@ def guarded_all_gather(gathered: torch.Tensor, local: torch.Tensor, group=None,
         return (STATUS_UNAVAILABLE if gone else STATUS_LAUNCH_ERROR), text
 
 
+class PeerExchange:
+    """The long-context exchange over peer memory instead of a library all-gather.
+
+    Every rank owns an exchange buffer in its GPU's memory (created and shared
+    with CUDA IPC by the library, ``include/loom_launch.h``: the peer exchange
+    section). ``push`` stores this rank's F32 ``[rows, Dv + 2]`` states straight
+    into every peer's buffer over NVLink and ``merge`` waits (bounded) for all
+    parts of the step in its own buffer and writes the merged ``[rows, Dv]`` rows:
+    two kernels of this library per step, no communication-library call, nothing
+    allocated after construction. The handles are exchanged once, here, with
+    ``all_gather_object`` on ``group`` (any backend). Every rank must run every
+    step; ``status()`` (synchronous) tells how many steps completed and whether a
+    wait ever ran out, after which every rank calls ``reset()`` and the ranks
+    meet at a host barrier before the next step.
+
+    ``buffers`` lets a test hand over buffers that already live in one process
+    (several ranks emulated on one GPU); nothing is opened or exchanged then.
+    """
+
+    def __init__(self, rows: int, value_head_size: int, *, group=None, rank: int | None = None,
+                 world: int | None = None, buffers: Sequence[int] | None = None):
+        import torch.distributed as dist
+
+        self._lib = _native.library()
+        self.rows, self.value_head_size = int(rows), int(value_head_size)
+        self.world = int(world) if world is not None else dist.get_world_size(group)
+        self.rank = int(rank) if rank is not None else dist.get_rank(group)
+        self.bytes = int(self._lib.loom_cuda_peer_exchange_bytes(self.world, self.rows, self.value_head_size))
+        if self.bytes == 0:
+            raise ValueError("peer exchange: unsupported shape (at most 16 ranks; rows * (Dv + 2) a multiple of 4)")
+        self._opened: list[int] = []
+        self._own = None
+        if buffers is not None:
+            pointers = [int(b) for b in buffers]
+        else:
+            own = ctypes.c_void_p()
+            handle = ctypes.create_string_buffer(64)
+            status = self._lib.loom_cuda_peer_exchange_create(self.bytes, ctypes.byref(own), handle, 64)
+            if status != 0:
+                raise RuntimeError(f"peer exchange buffer could not be created (status {status}): "
+                                   + self._lib.loom_cuda_last_launch_failure().decode())
+            self._own = own.value
+            handles: list = [None] * self.world
+            dist.all_gather_object(handles, handle.raw, group=group)
+            pointers = []
+            for peer, raw in enumerate(handles):
+                if peer == self.rank:
+                    pointers.append(self._own)
+                    continue
+                mapped = ctypes.c_void_p()
+                status = self._lib.loom_cuda_peer_exchange_open(raw, len(raw), ctypes.byref(mapped))
+                if status != 0:
+                    raise RuntimeError(f"rank {peer}'s exchange buffer could not be mapped (status {status}): "
+                                       + self._lib.loom_cuda_last_launch_failure().decode())
+                self._opened.append(mapped.value)
+                pointers.append(mapped.value)
+        self.buffer = pointers[self.rank]
+        self._pointers = (ctypes.c_void_p * self.world)(*pointers)
+
+    def push(self, states: torch.Tensor) -> None:
+        """Enqueues the stores of this rank's states into every rank's buffer on the current stream."""
+        if (states.dtype != torch.float32 or not states.is_contiguous()
+                or states.numel() != self.rows * (self.value_head_size + 2)):
+            raise RuntimeError("peer exchange expects contiguous float32 [rows, Dv + 2] states")
+        from . import ops
+
+        status = self._lib.loom_cuda_peer_exchange_push(states.data_ptr(), self._pointers, self.rank, self.world,
+                                                        self.rows, self.value_head_size, ops._stream(states.device))
+        if status != 0:
+            raise RuntimeError(f"peer exchange push failed (status {status})")
+
+    def merge(self, output: torch.Tensor) -> torch.Tensor:
+        """Enqueues the wait for all ranks' parts and their merge into ``output`` ``[rows, Dv]``."""
+        from . import ops
+
+        if (output.dtype not in ops._DTYPE_CODES or not output.is_contiguous()
+                or output.numel() != self.rows * self.value_head_size):
+            raise RuntimeError("peer exchange merges into a contiguous [rows, Dv] tensor of a supported type")
+        status = self._lib.loom_cuda_peer_exchange_merge(self.buffer, self.world, self.rows, self.value_head_size,
+                                                         ops._DTYPE_CODES[output.dtype], output.data_ptr(),
+                                                         ops._stream(output.device))
+        if status != 0:
+            raise RuntimeError(f"peer exchange merge failed (status {status})")
+        return output
+
+    def status(self) -> tuple[int, int]:
+        """(steps completed, error word) of this rank's buffer; waits for the device."""
+        steps, error = _native.u64(0), _native.u32(0)
+        if self._lib.loom_cuda_peer_exchange_status(self.buffer, ctypes.byref(steps), ctypes.byref(error)) != 0:
+            raise RuntimeError("peer exchange status could not be read")
+        return int(steps.value), int(error.value)
+
+    def reset(self, stream: int = 0) -> None:
+        if self._lib.loom_cuda_peer_exchange_reset(self.buffer, self.bytes, stream) != 0:
+            raise RuntimeError("peer exchange buffer could not be reset")
+
+    def close(self) -> None:
+        """Unmaps the peers' buffers and frees this rank's own (call after a barrier: peers may still push)."""
+        for pointer in self._opened:
+            self._lib.loom_cuda_peer_exchange_close(pointer)
+        self._opened = []
+        if self._own is not None:
+            self._lib.loom_cuda_peer_exchange_destroy(self._own)
+            self._own = None
+
+
 class LongContextDecoder:
     """The long-context mode for one batch shape: plan, index tensors and buffers made once.
 

@@ -224,9 +224,13 @@ class ShardedDecodeStep:
     of the whole batch on every rank).
 
     Long-context mode: the decode emits F32 (O, max, sum) states of every row
-    (an absent row gives the empty state), ``all_gather_into_tensor`` moves them
-    and ``loom_cuda_merge_decode_states`` merges. The exchange buffers are
-    allocated once; nothing is planned or allocated per step. ``group`` is the
+    (an absent row gives the empty state); with ``exchange="peer"`` (default)
+    this library's push kernel stores them into every peer's exchange buffer
+    over NVLink and its merge kernel waits for all parts and merges
+    (``multi_gpu.PeerExchange``), with ``exchange="nccl"``
+    ``all_gather_into_tensor`` moves them and ``loom_cuda_merge_decode_states``
+    merges. The exchange buffers are set up once; nothing is planned or
+    allocated per step, and every rank must run every step. ``group`` is the
     process group of the exchange; ``health`` (``multi_gpu.RankHealth``) makes
     ``run`` return a status instead of launching when a peer has left.
     ``early_metadata`` is the ``stable_metadata`` promise of
@@ -235,7 +239,8 @@ class ShardedDecodeStep:
 
     def __init__(self, shard: RankShard, cos_sin_cache: torch.Tensor, *, rope_cache: torch.Tensor | None = None,
                  dtype: torch.dtype, scale: float, is_neox: bool, partition_tokens: int = 0, group=None,
-                 health: "multi_gpu.RankHealth | None" = None, early_metadata: bool = True):
+                 health: "multi_gpu.RankHealth | None" = None, early_metadata: bool = True,
+                 exchange: str = "peer"):
         kv_cache = shard.rope_cache if rope_cache is None else rope_cache
         self.shard = shard
         self.device = kv_cache.device
@@ -303,12 +308,22 @@ class ShardedDecodeStep:
         self.output = torch.zeros(rows, device=self.device, dtype=dtype)
         self.host_output = torch.zeros(rows, dtype=dtype).pin_memory()
         self.d2h_bytes = self.host_output.numel() * self.host_output.element_size()
+        self.peer_exchange = None
         if self.exchange:
             self._states = torch.zeros((self.sequences, self.query_heads, self.head_size + 2), device=self.device,
                                        dtype=torch.float32)
-            self._gathered = torch.zeros((self.ranks, self.sequences * self.query_heads, self.head_size + 2),
-                                         device=self.device, dtype=torch.float32)
-        self.kernel_launches = 2 + (1 if self._split else 0) + (1 if self.exchange else 0)
+            if exchange == "peer":
+                # this library's own push + merge kernels over NVLink peer memory (set up once, here)
+                self.peer_exchange = multi_gpu.PeerExchange(self.sequences * self.query_heads, self.head_size,
+                                                            group=group)
+            elif exchange == "nccl":
+                self._gathered = torch.zeros((self.ranks, self.sequences * self.query_heads, self.head_size + 2),
+                                             device=self.device, dtype=torch.float32)
+            else:
+                raise ValueError("exchange is 'peer' or 'nccl'")
+        # RoPE, decode, its merge; the exchange adds push + merge of this library (or the library merge after NCCL)
+        self.kernel_launches = (2 + (1 if self._split else 0)
+                                + ((2 if self.peer_exchange is not None else 1) if self.exchange else 0))
         self._graph: torch.cuda.CUDAGraph | None = None
 
     # ---- the step as stream operations ---------------------------------------------------------
@@ -337,9 +352,13 @@ class ShardedDecodeStep:
             output=self._states if self.exchange else self.output, stable_metadata=self.early_metadata,
             **self._decode_scales)
         if self.exchange and exchange:
-            dist.all_gather_into_tensor(self._gathered.view(-1), self._states.view(-1), group=self.group)
-            ops.merge_decode_states(self._gathered, self.output.dtype,
-                                    output=self.output.view(self.sequences * self.query_heads, self.head_size))
+            rows = self.output.view(self.sequences * self.query_heads, self.head_size)
+            if self.peer_exchange is not None:
+                self.peer_exchange.push(self._states)
+                self.peer_exchange.merge(rows)
+            else:
+                dist.all_gather_into_tensor(self._gathered.view(-1), self._states.view(-1), group=self.group)
+                ops.merge_decode_states(self._gathered, self.output.dtype, output=rows)
 
     def upload(self) -> None:
         self._device.copy_(self._host, non_blocking=True)

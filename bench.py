@@ -132,6 +132,9 @@ def parse_args():
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--copy-engine", choices=["tma", "cp_async", "tma-mma", "tma-umma"], default=None,
                         help="how the balanced decode kernel is fed (default: the library's choice)")
+    parser.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
+                        help="long-context mode at N > 1: this library's push/merge kernels over peer memory "
+                             "(default) or an NCCL all-gather followed by the merge kernel")
     parser.add_argument("--late-metadata", action="store_true",
                         help="do not promise stable metadata: the decode kernel plans after the grid dependency wait")
     parser.add_argument("--programmatic-launch", type=int, choices=[0, 1], default=None,
@@ -227,7 +230,8 @@ class ClockSampler:
 SHARDING = {"cfg1": "by sequence", "cfg2": "by sequence", "cfg2-1024": "by sequence", "ref-b8-ctx1024": "by sequence",
             "cfg3": "by sequence", "cfg4": "by KV head", "cfg5": "long context"}
 COLLECTIVE = {"by sequence": "no collective", "by KV head": "no collective",
-              "long context": "NCCL all-gather of (O, max, sum) states + merge kernel inside the step",
+              "long context": "(O, max, sum) states exchanged inside the step (push + merge kernels over NVLink peer "
+                              "memory; --exchange nccl: NCCL all-gather + merge kernel)",
               "single GPU": "no collective"}
 
 
@@ -536,7 +540,7 @@ def measure_workload(args, ranks, name, steps, headline):
         return sharded_step.ShardedDecodeStep(shard, cos_sin, rope_cache=rope_cache, dtype=config.torch_dtype,
                                               scale=1.0 / float(np.sqrt(config.head_size)), is_neox=is_neox,
                                               partition_tokens=config.partition_tokens,
-                                              early_metadata=not args.late_metadata)
+                                              early_metadata=not args.late_metadata, exchange=args.exchange)
 
     # Rotate over several copies of the local cache so that a step never finds its KV in the
     # 126 MB L2 left there by the previous step.
@@ -584,13 +588,15 @@ def measure_workload(args, ranks, name, steps, headline):
             graph.replay()
             stop.record()
             ranks.barrier()
-            # keep the GPU under the same load a little longer so that the sampler sees it
-            deadline = time.time() + (0.6 if headline else 0.35)
-            while time.time() < deadline:
+            elapsed_ms = start.elapsed_time(stop)
+            # Keep the GPU under the same load a little longer so that the sampler sees it. Every rank
+            # replays the SAME number of times (derived from the slowest rank's time): a step that
+            # exchanges states needs every rank in every step.
+            slowest_ms = ranks.reduce([elapsed_ms])[0]
+            for _ in range(int(min(5000, max(1, (600.0 if headline else 350.0) / max(slowest_ms, 1e-3))))):
                 graph.replay()
-                torch.cuda.synchronize()
             ranks.barrier()
-        return start.elapsed_time(stop), sampler.summary()
+        return elapsed_ms, sampler.summary()
 
     # ---- device-resident timing: one CUDA graph holding exactly `steps` steps ----------------
     step_ms, clocks = timed_graph(lambda index: step.enqueue_kernels(rope_views[index]))

@@ -437,6 +437,58 @@ int loom_cuda_paged_multi_token_decode(const LoomDecodeArgs* args,
                                        float* prefix_states);
 
 /* ====================================================================== *
+ * Exchange of partial decode states between the GPUs of one node
+ *
+ * No counterpart in the reference (docs/operator-catalog.md:109 lists
+ * distributed split-KV as planned). For the long-context mode, in which every
+ * GPU holds one block range of a sequence and produces partial (O, max, sum)
+ * states (emit_state): instead of an all-gather by a communication library
+ * followed by loom_cuda_merge_decode_states, every GPU PUSHES its states into
+ * every peer's exchange buffer with plain stores over NVLink, and MERGES what
+ * has arrived in its own buffer. One process per GPU; `world` GPUs, at most
+ * LOOM_CUDA_PEER_EXCHANGE_MAX_RANKS.
+ *
+ * Set-up, once: every rank creates its buffer (device memory of the current
+ * device, zeroed; this is the only allocating function of the library), sends
+ * the returned handle bytes to the other ranks by any means, and opens theirs.
+ * rank_buffers[r] is then rank r's buffer as this process sees it (its own
+ * pointer for r == rank). Per step, on every rank, in this order on one stream:
+ * push, then merge. Every rank must run every step: the kernels count steps in
+ * the buffers and a rank that skips one leaves the others waiting (bounded: a
+ * wait that runs out sets the buffer's error word, the step's rows are then
+ * invalid; loom_cuda_peer_exchange_status reads it, and after an error every
+ * rank resets its buffer and the ranks synchronise on the host before the next
+ * step). states: [rows, value_head_size + 2] F32 as emit_state writes them,
+ * 16-byte aligned, rows * (value_head_size + 2) a multiple of 4.
+ * ====================================================================== */
+#define LOOM_CUDA_PEER_EXCHANGE_MAX_RANKS 16
+#define LOOM_CUDA_PEER_EXCHANGE_HANDLE_BYTES 64
+
+/* Size of a rank's exchange buffer; 0 for an invalid shape. */
+uint64_t loom_cuda_peer_exchange_bytes(uint32_t world, uint32_t rows,
+                                       uint32_t value_head_size);
+int loom_cuda_peer_exchange_create(uint64_t bytes, void** buffer,
+                                   unsigned char* handle,
+                                   uint64_t handle_capacity);
+int loom_cuda_peer_exchange_open(const unsigned char* handle,
+                                 uint64_t handle_bytes, void** buffer);
+int loom_cuda_peer_exchange_close(void* peer_buffer);
+int loom_cuda_peer_exchange_destroy(void* buffer);
+/* Zeroes a rank's own buffer (step counters, arrivals, error) on `stream`. */
+int loom_cuda_peer_exchange_reset(void* buffer, uint64_t bytes, void* stream);
+/* Synchronous read of a rank's own buffer: steps completed, error word. */
+int loom_cuda_peer_exchange_status(const void* buffer,
+                                   uint64_t* completed_steps, uint32_t* error);
+int loom_cuda_peer_exchange_push(const float* states,
+                                 void* const* rank_buffers, uint32_t rank,
+                                 uint32_t world, uint32_t rows,
+                                 uint32_t value_head_size, void* stream);
+/* out_dtype as LoomDecodeArgs.dtype; output [rows, value_head_size]. */
+int loom_cuda_peer_exchange_merge(void* buffer, uint32_t world, uint32_t rows,
+                                  uint32_t value_head_size, uint32_t out_dtype,
+                                  void* output, void* stream);
+
+/* ====================================================================== *
  * Part 3: KV block movement
  *
  * The reference names these operators as the next ones around its paged

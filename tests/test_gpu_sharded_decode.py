@@ -89,9 +89,11 @@ def _step(shard, case):
     from attnarc_b200 import sharded_step
 
     config = case.config
+    # one process emulates the ranks here: no process group exists, so the exchange buffers of the NCCL
+    # form (plain tensors) are asked for; the exchange itself is not run by these tests
     return sharded_step.ShardedDecodeStep(shard, case.cos_sin_cache, dtype=config.torch_dtype, scale=case.scale,
                                           is_neox=config.rope_style == "neox",
-                                          partition_tokens=config.partition_tokens)
+                                          partition_tokens=config.partition_tokens, exchange="nccl")
 
 
 @pytest.mark.parametrize("name,mode,ranks", [("cfg3", "by sequence", 4), ("cfg2", "by sequence", 8),
@@ -142,3 +144,76 @@ def test_long_context_rank_steps_merge_to_the_oracle(ranks):
     assert writers == batch, "the new token of every sequence is written by exactly one rank"
     merged = ops.merge_decode_states(stacked, config.torch_dtype).view(batch, heads, dim)
     assert_close(merged.cpu(), expected, config.torch_dtype, f"long context x{ranks}")
+
+
+# ---- the exchange over peer memory (multi_gpu.PeerExchange), ranks emulated on one GPU ---------------
+#
+# Kernels that wait for each other must not run as separate launches on one device. The emulation
+# therefore enqueues every rank's push before the first merge: each merge finds all parts in place
+# and never waits for a later launch.
+
+def _emulated_exchanges(world, rows, dim):
+    import ctypes
+
+    from attnarc_b200 import _native
+
+    lib = _native.library()
+    size = lib.loom_cuda_peer_exchange_bytes(world, rows, dim)
+    assert size > 0
+    buffers = [torch.zeros(size, dtype=torch.uint8, device="cuda:0") for _ in range(world)]
+    pointers = [b.data_ptr() for b in buffers]
+    return buffers, [multi_gpu.PeerExchange(rows, dim, rank=r, world=world, buffers=pointers) for r in range(world)]
+
+
+@pytest.mark.parametrize("world", [1, 2, 8])
+def test_peer_exchange_merges_like_the_merge_operator_step_after_step(world):
+    from attnarc_b200 import ops
+
+    rows, dim = 64, 128
+    buffers, exchanges = _emulated_exchanges(world, rows, dim)
+    generator = torch.Generator(device="cuda:0").manual_seed(world)
+    for step in range(5):  # both generations of the buffers, counters that keep growing
+        states = torch.randn((world, rows, dim + 2), device="cuda:0", generator=generator)
+        states[:, :, dim + 1] = states[:, :, dim + 1].abs() + 0.1       # sums of exponentials are positive
+        if world > 1:
+            states[1, ::3, dim + 1] = 0.0                                # rank 1 holds nothing of every third row
+            states[1, ::3, dim] = float("-inf")
+        expected = ops.merge_decode_states(states.contiguous(), torch.float32)
+        for rank, exchange in enumerate(exchanges):
+            exchange.push(states[rank].contiguous())
+        outputs = [exchange.merge(torch.empty((rows, dim), dtype=torch.float32, device="cuda:0"))
+                   for exchange in exchanges]
+        torch.cuda.synchronize()
+        for rank, output in enumerate(outputs):
+            # the same log-sum-exp merge, folded in another order
+            assert torch.allclose(output, expected, rtol=1e-5, atol=1e-5), f"step {step} rank {rank}"
+    assert all(exchange.status() == (5, 0) for exchange in exchanges)
+
+
+def test_peer_exchange_reports_a_part_that_never_arrives():
+    from attnarc_b200 import ops
+
+    rows, dim = 8, 64
+    buffers, exchanges = _emulated_exchanges(2, rows, dim)
+    states = torch.rand((rows, dim + 2), device="cuda:0") + 0.5
+    ops.set_wait_policy(attempts=2000)
+    try:
+        exchanges[0].push(states)  # rank 1 never pushes: rank 0's wait for it must run out, not hang
+        output = exchanges[0].merge(torch.full((rows, dim), 7.0, dtype=torch.float32, device="cuda:0"))
+        torch.cuda.synchronize()
+    finally:
+        ops.set_wait_policy()
+    steps, error = exchanges[0].status()
+    assert error == 1 and steps == 1
+    assert bool((output == 0).all()), "rows of a step with a missing part are zeroed, never half merged"
+    # after an error every rank resets its buffer; the next step is clean
+    for exchange in exchanges:
+        exchange.reset()
+    for exchange in exchanges:
+        exchange.push(states)
+    merged = exchanges[1].merge(torch.empty((rows, dim), dtype=torch.float32, device="cuda:0"))
+    exchanges[0].merge(torch.empty((rows, dim), dtype=torch.float32, device="cuda:0"))
+    torch.cuda.synchronize()
+    assert exchanges[1].status() == (1, 0)
+    twice = torch.stack([states, states]).contiguous()
+    assert torch.allclose(merged, ops.merge_decode_states(twice, torch.float32), rtol=1e-6, atol=1e-6)
