@@ -365,3 +365,31 @@ def test_long_context_exchange_reports_a_late_and_a_departed_rank():
     # the departed peer: refused on the host, nothing launched
     assert zero["third"] == multi_gpu.STATUS_UNAVAILABLE and zero["launched"] == 0
     assert "left" in zero["third_error"]
+
+
+# ------------------------------------------------- peer exchange: host-side arithmetic and refusals
+
+def test_peer_exchange_sizes_and_argument_checks_need_no_device():
+    import ctypes
+
+    from attnarc_b200 import _native
+
+    lib = _native.library()
+    header = 192  # step counter, ticket, error word, 16 arrival counters, reserve
+    assert lib.loom_cuda_peer_exchange_bytes(8, 256, 128) == header + 2 * 8 * 256 * 130 * 4
+    assert lib.loom_cuda_peer_exchange_bytes(1, 2, 126) == header + 2 * 1 * 2 * 128 * 4
+    for world, rows, dim in ((0, 8, 128), (17, 8, 128), (2, 0, 128), (2, 8, 0), (2, 1, 129)):
+        assert lib.loom_cuda_peer_exchange_bytes(world, rows, dim) == 0  # too many ranks, empty, or not 16-byte rows
+    fake = 0x100000
+    buffers = (ctypes.c_void_p * 2)(fake, fake)
+    # refused before any CUDA call: misaligned states, rank outside the world, a missing peer buffer, bad dtype
+    assert lib.loom_cuda_peer_exchange_push(fake + 4, buffers, 0, 2, 8, 128, None) == 1
+    assert lib.loom_cuda_peer_exchange_push(fake, buffers, 2, 2, 8, 128, None) == 1
+    assert lib.loom_cuda_peer_exchange_push(fake, (ctypes.c_void_p * 2)(fake, None), 0, 2, 8, 128, None) == 1
+    assert lib.loom_cuda_peer_exchange_merge(fake, 2, 8, 128, 3, fake, None) == 1
+    assert lib.loom_cuda_peer_exchange_merge(None, 2, 8, 128, 2, fake, None) == 1
+    handle = ctypes.create_string_buffer(64)
+    out = ctypes.c_void_p()
+    assert lib.loom_cuda_peer_exchange_create(16, ctypes.byref(out), handle, 64) == 1   # smaller than the header
+    assert lib.loom_cuda_peer_exchange_create(4096, ctypes.byref(out), handle, 8) == 1  # no room for the handle
+    assert lib.loom_cuda_peer_exchange_open(handle, 8, ctypes.byref(out)) == 1
