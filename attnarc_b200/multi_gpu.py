@@ -298,6 +298,11 @@ def guarded_all_gather(gathered: torch.Tensor, local: torch.Tensor, group=None,
         return (STATUS_UNAVAILABLE if gone else STATUS_LAUNCH_ERROR), text
 
 
+class PeerExchangeUnavailable(RuntimeError):
+    """The peer exchange could not be set up on some rank; raised on EVERY rank of the group, so that
+    all of them can fall back to the library all-gather together."""
+
+
 class PeerExchange:
     """The long-context exchange over peer memory instead of a library all-gather.
 
@@ -333,27 +338,38 @@ class PeerExchange:
         if buffers is not None:
             pointers = [int(b) for b in buffers]
         else:
+            # Every rank takes part in both collectives below whatever happens to it, and all ranks reach
+            # the same verdict: a rank that raised on its own would leave the others waiting for it.
             own = ctypes.c_void_p()
             handle = ctypes.create_string_buffer(64)
             status = self._lib.loom_cuda_peer_exchange_create(self.bytes, ctypes.byref(own), handle, 64)
+            problem = None
             if status != 0:
-                raise RuntimeError(f"peer exchange buffer could not be created (status {status}): "
-                                   + self._lib.loom_cuda_last_launch_failure().decode())
-            self._own = own.value
+                problem = (f"rank {self.rank}: exchange buffer not created (status {status}, "
+                           + self._lib.loom_cuda_last_launch_failure().decode() + ")")
+            else:
+                self._own = own.value
             handles: list = [None] * self.world
-            dist.all_gather_object(handles, handle.raw, group=group)
+            dist.all_gather_object(handles, None if problem else handle.raw, group=group)
             pointers = []
             for peer, raw in enumerate(handles):
-                if peer == self.rank:
-                    pointers.append(self._own)
+                if peer == self.rank or problem is not None or raw is None:
+                    pointers.append(self._own or 0)
                     continue
                 mapped = ctypes.c_void_p()
                 status = self._lib.loom_cuda_peer_exchange_open(raw, len(raw), ctypes.byref(mapped))
                 if status != 0:
-                    raise RuntimeError(f"rank {peer}'s exchange buffer could not be mapped (status {status}): "
-                                       + self._lib.loom_cuda_last_launch_failure().decode())
+                    problem = (f"rank {self.rank}: rank {peer}'s exchange buffer not mapped (status {status}, "
+                               + self._lib.loom_cuda_last_launch_failure().decode() + ")")
+                    pointers.append(0)
+                    continue
                 self._opened.append(mapped.value)
                 pointers.append(mapped.value)
+            problems: list = [None] * self.world
+            dist.all_gather_object(problems, problem, group=group)
+            if any(problems):
+                self.close()
+                raise PeerExchangeUnavailable("; ".join(text for text in problems if text))
         self.buffer = pointers[self.rank]
         self._pointers = (ctypes.c_void_p * self.world)(*pointers)
 

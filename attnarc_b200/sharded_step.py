@@ -313,9 +313,18 @@ class ShardedDecodeStep:
             self._states = torch.zeros((self.sequences, self.query_heads, self.head_size + 2), device=self.device,
                                        dtype=torch.float32)
             if exchange == "peer":
-                # this library's own push + merge kernels over NVLink peer memory (set up once, here)
-                self.peer_exchange = multi_gpu.PeerExchange(self.sequences * self.query_heads, self.head_size,
-                                                            group=group)
+                # this library's own push + merge kernels over NVLink peer memory (set up once, here);
+                # where some rank cannot share its buffer every rank learns of it and all use NCCL
+                try:
+                    self.peer_exchange = multi_gpu.PeerExchange(self.sequences * self.query_heads, self.head_size,
+                                                                group=group)
+                except multi_gpu.PeerExchangeUnavailable as problem:
+                    import warnings
+
+                    warnings.warn(f"peer exchange unavailable, using the NCCL all-gather instead: {problem}")
+                    exchange = "nccl"
+            if self.peer_exchange is not None:
+                pass
             elif exchange == "nccl":
                 self._gathered = torch.zeros((self.ranks, self.sequences * self.query_heads, self.head_size + 2),
                                              device=self.device, dtype=torch.float32)

@@ -663,6 +663,9 @@ def measure_workload(args, ranks, name, steps, headline):
             "ncu dram__bytes_read.sum + dram__bytes_write.sum of one decode launch on a cut of the workload, "
             "scaled by KV bytes (profiles/decode_dram_traffic_all_configs.md)",
         },
+        "exchange": (None if not shard.exchange else
+                     "push + merge kernels over NVLink peer memory" if step.peer_exchange is not None else
+                     "NCCL all-gather + merge kernel"),
         "decode_route": route, "clocks": clocks, "parity_max_abs_err": parity,
         "parity_against": None if parity is None else "this rank's single-GPU decode of the global batch",
         "l2": f"steps rotate over {copies} copies of the rank's {cache_bytes / 1e6:.0f} MB cache",
