@@ -339,7 +339,7 @@ class PeerExchange:
             pointers = [int(b) for b in buffers]
         else:
             # Every rank takes part in both collectives below whatever happens to it, and all ranks reach
-            # the same verdict: a rank that raised on its own would leave the others waiting for it.
+            # the same conclusion: a rank that raised on its own would leave the others waiting for it.
             own = ctypes.c_void_p()
             handle = ctypes.create_string_buffer(64)
             status = self._lib.loom_cuda_peer_exchange_create(self.bytes, ctypes.byref(own), handle, 64)
