@@ -392,9 +392,9 @@ class PeerExchange:
         if (output.dtype not in ops._DTYPE_CODES or not output.is_contiguous()
                 or output.numel() != self.rows * self.value_head_size):
             raise RuntimeError("peer exchange merges into a contiguous [rows, Dv] tensor of a supported type")
+        stream = ops._stream(output.device if output.device.type == "cuda" else torch.device("cuda", torch.cuda.current_device()))
         status = self._lib.loom_cuda_peer_exchange_merge(self.buffer, self.world, self.rows, self.value_head_size,
-                                                         ops._DTYPE_CODES[output.dtype], output.data_ptr(),
-                                                         ops._stream(output.device))
+                                                         ops._DTYPE_CODES[output.dtype], output.data_ptr(), stream)
         if status != 0:
             raise RuntimeError(f"peer exchange merge failed (status {status})")
         return output

@@ -230,10 +230,14 @@ def _check_decode_tensors(query, key_cache, value_cache, block_tables, sequence_
         raise RuntimeError("Loom paged decode expects query [B,Hq,D] and caches [blocks,block,Hkv,D]")
     if block_tables.dim() != 2 or sequence_lengths.dim() != 1:
         raise RuntimeError("Loom paged decode expects block_tables [B,max_blocks] and lengths [B]")
-    if query.device.type != "cuda" or any(
-        t.device != query.device for t in (key_cache, value_cache, block_tables, sequence_lengths, output)
+    # the output may also be pinned host memory: the last kernel then stores the rows straight over
+    # PCIe and no device-to-host copy follows (pinned allocations are addressable by the device)
+    output_ok = output.device == query.device or (output.device.type == "cpu" and output.is_pinned())
+    if query.device.type != "cuda" or not output_ok or any(
+        t.device != query.device for t in (key_cache, value_cache, block_tables, sequence_lengths)
     ):
-        raise RuntimeError("Loom paged decode tensors must share one CUDA device")
+        raise RuntimeError("Loom paged decode tensors must share one CUDA device "
+                           "(the output may instead be pinned host memory)")
     if query.dtype not in _DTYPE_CODES:
         raise RuntimeError("Loom paged decode supports float32, float16 and bfloat16 queries")
     if block_tables.dtype != torch.int32 or sequence_lengths.dtype != torch.int32:
@@ -423,7 +427,7 @@ def merge_decode_states(states: torch.Tensor, out_dtype: torch.dtype,
     if output is None:
         output = torch.empty((rows, width - 2), device=states.device, dtype=out_dtype)
     elif (output.dtype != out_dtype or tuple(output.shape) != (rows, width - 2) or not output.is_contiguous()
-          or output.device != states.device):
+          or not (output.device == states.device or (output.device.type == "cpu" and output.is_pinned()))):
         raise RuntimeError("merge output must be a contiguous [rows, Dv] tensor of the requested dtype")
     with _on_device(states.device):
         status = library().loom_cuda_bridge_merge_decode_states(

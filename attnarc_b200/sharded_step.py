@@ -240,7 +240,7 @@ class ShardedDecodeStep:
     def __init__(self, shard: RankShard, cos_sin_cache: torch.Tensor, *, rope_cache: torch.Tensor | None = None,
                  dtype: torch.dtype, scale: float, is_neox: bool, partition_tokens: int = 0, group=None,
                  health: "multi_gpu.RankHealth | None" = None, early_metadata: bool = True,
-                 exchange: str = "peer"):
+                 exchange: str = "peer", rows_to_host: bool = False):
         kv_cache = shard.rope_cache if rope_cache is None else rope_cache
         self.shard = shard
         self.device = kv_cache.device
@@ -305,8 +305,11 @@ class ShardedDecodeStep:
         self._workspace = (torch.empty(needed, device=self.device, dtype=torch.float32)
                            if self._split and needed else None)
         rows = (self.sequences, self.query_heads, self.head_size)
-        self.output = torch.zeros(rows, device=self.device, dtype=dtype)
         self.host_output = torch.zeros(rows, dtype=dtype).pin_memory()
+        # rows_to_host: the step's last kernel stores the rows into the pinned buffer itself (posted
+        # writes over PCIe while it runs) and the device-to-host copy that would follow it is dropped
+        self.rows_to_host = bool(rows_to_host)
+        self.output = self.host_output if self.rows_to_host else torch.zeros(rows, device=self.device, dtype=dtype)
         self.d2h_bytes = self.host_output.numel() * self.host_output.element_size()
         self.peer_exchange = None
         if self.exchange:
@@ -375,7 +378,8 @@ class ShardedDecodeStep:
     def _enqueue(self) -> None:
         self.upload()
         self.enqueue_kernels()
-        self.host_output.copy_(self.output, non_blocking=True)
+        if not self.rows_to_host:
+            self.host_output.copy_(self.output, non_blocking=True)
 
     def run_eager(self) -> torch.Tensor:
         with torch.cuda.device(self.device):
@@ -408,6 +412,17 @@ class ShardedDecodeStep:
         self._graph.replay()
         torch.cuda.current_stream(self.device).synchronize()
         return self.host_output
+
+
+    def close(self) -> None:
+        """Drops the recorded graph and the exchange buffers. In the long-context mode call it on every
+        rank after a barrier (peers store into a rank's buffer until their last step has completed)
+        and before the process group is destroyed (a graph holding a captured collective must not
+        outlive its communicator)."""
+        self._graph = None
+        if self.peer_exchange is not None:
+            self.peer_exchange.close()
+            self.peer_exchange = None
 
 
 def gather_rows(shard: RankShard, local_rows: torch.Tensor, global_shape: Sequence[int]) -> torch.Tensor:

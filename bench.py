@@ -135,6 +135,8 @@ def parse_args():
     parser.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
                         help="long-context mode at N > 1: this library's push/merge kernels over peer memory "
                              "(default) or an NCCL all-gather followed by the merge kernel")
+    parser.add_argument("--rows-to-host", action="store_true",
+                        help="the step's last kernel stores the attention rows into pinned host memory itself")
     parser.add_argument("--late-metadata", action="store_true",
                         help="do not promise stable metadata: the decode kernel plans after the grid dependency wait")
     parser.add_argument("--programmatic-launch", type=int, choices=[0, 1], default=None,
@@ -540,7 +542,8 @@ def measure_workload(args, ranks, name, steps, headline):
         return sharded_step.ShardedDecodeStep(shard, cos_sin, rope_cache=rope_cache, dtype=config.torch_dtype,
                                               scale=1.0 / float(np.sqrt(config.head_size)), is_neox=is_neox,
                                               partition_tokens=config.partition_tokens,
-                                              early_metadata=not args.late_metadata, exchange=args.exchange)
+                                              early_metadata=not args.late_metadata, exchange=args.exchange,
+                                              rows_to_host=args.rows_to_host)
 
     # Rotate over several copies of the local cache so that a step never finds its KV in the
     # 126 MB L2 left there by the previous step.

@@ -18,7 +18,11 @@ pytestmark = pytest.mark.gpu
 
 
 def _rank(rank, world, port, results):
+    import faulthandler
+
     import torch.distributed as dist
+
+    faulthandler.dump_traceback_later(120, exit=True)  # a rank that stops making progress says where, and ends
 
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -57,7 +61,11 @@ def test_long_context_exchange_over_nccl():
 
 
 def _peer_rank(rank, world, port, results):
+    import faulthandler
+
     import torch.distributed as dist
+
+    faulthandler.dump_traceback_later(120, exit=True)  # a rank that stops making progress says where, and ends
 
     from attnarc_b200 import sharded_step, workloads
 
@@ -81,6 +89,12 @@ def _peer_rank(rank, world, port, results):
             if step.peer_exchange is not None:
                 assert step.peer_exchange.status() == (5, 0)  # eager + the capture's own run + three replays
             rows[exchange] = replayed
+            # a CUDA graph that holds a captured NCCL collective must be gone before the group is
+            # destroyed, and peers must have stopped pushing before a rank frees its exchange buffer
+            torch.cuda.synchronize()
+            dist.barrier()
+            step.close()
+            del step
         dist.barrier()
         results[rank] = rows
     finally:
