@@ -135,8 +135,9 @@ def parse_args():
     parser.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
                         help="long-context mode at N > 1: this library's push/merge kernels over peer memory "
                              "(default) or an NCCL all-gather followed by the merge kernel")
-    parser.add_argument("--rows-to-host", action="store_true",
-                        help="the step's last kernel stores the attention rows into pinned host memory itself")
+    parser.add_argument("--rows-by-copy", action="store_true",
+                        help="end-to-end step: copy the attention rows to the host after the last kernel instead "
+                             "of letting that kernel store them into pinned host memory itself")
     parser.add_argument("--late-metadata", action="store_true",
                         help="do not promise stable metadata: the decode kernel plans after the grid dependency wait")
     parser.add_argument("--programmatic-launch", type=int, choices=[0, 1], default=None,
@@ -538,12 +539,12 @@ def measure_workload(args, ranks, name, steps, headline):
         shard = sharded_step.whole_case(case)
         cos_sin, lengths = case.cos_sin_cache, case.lengths
 
-    def make_step(rope_cache):
+    def make_step(rope_cache, rows_to_host=False):
         return sharded_step.ShardedDecodeStep(shard, cos_sin, rope_cache=rope_cache, dtype=config.torch_dtype,
                                               scale=1.0 / float(np.sqrt(config.head_size)), is_neox=is_neox,
                                               partition_tokens=config.partition_tokens,
                                               early_metadata=not args.late_metadata, exchange=args.exchange,
-                                              rows_to_host=args.rows_to_host)
+                                              rows_to_host=rows_to_host)
 
     # Rotate over several copies of the local cache so that a step never finds its KV in the
     # 126 MB L2 left there by the previous step.
@@ -611,7 +612,9 @@ def measure_workload(args, ranks, name, steps, headline):
     e2e_ms = eager_ms = None
     if headline:
         # ---- end to end through the public step API with host buffers ------------------------
-        captured = [make_step(view).capture() for view in rope_views]
+        # (the end-to-end step lets its last kernel store the rows into the pinned buffer itself, unless
+        # --rows-by-copy asks for the device-to-host copy after it; the resident steps above write to HBM)
+        captured = [make_step(view, rows_to_host=not args.rows_by_copy).capture() for view in rope_views]
 
         def timed_steps(run_step):
             for w in range(3):
@@ -712,8 +715,8 @@ def run_b200(args):
             "config": head["config"],
             "protocol": {"value": "one CUDA graph of exactly K steps per rank, inputs resident, CUDA events, "
                                   "barrier on both sides, max over ranks",
-                         "e2e": "one captured step per launch from one pinned host buffer, rows copied back, "
-                                "host waits for each",
+                         "e2e": "one captured step per launch: inputs copied from one pinned host buffer, rows stored "
+                                "into pinned host memory by the step's last kernel, host waits for each",
                          "l2": head["l2"],
                          "programmatic_launch": 1 if args.programmatic_launch is None else args.programmatic_launch},
             "e2e": head["e2e"], "gpu_launches": head["gpu_launches"], "roofline": head["roofline"],

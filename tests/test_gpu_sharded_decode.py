@@ -217,3 +217,23 @@ def test_peer_exchange_reports_a_part_that_never_arrives():
     assert exchanges[1].status() == (1, 0)
     twice = torch.stack([states, states]).contiguous()
     assert torch.allclose(merged, ops.merge_decode_states(twice, torch.float32), rtol=1e-6, atol=1e-6)
+
+
+@pytest.mark.parametrize("name", ["cfg2", "cfg3", "cfg4"])
+def test_rows_stored_into_pinned_memory_by_the_last_kernel_equal_the_copied_rows(name):
+    # rows_to_host: the pinned buffer is the kernels' output; no device-to-host copy follows them
+    from attnarc_b200 import sharded_step
+
+    config, case = _small_case(name, 5, [700, 33, 1500, 16, 4000], seed=41)
+    shard = sharded_step.whole_case(case)
+    common = dict(dtype=config.torch_dtype, scale=case.scale, is_neox=config.rope_style == "neox",
+                  partition_tokens=config.partition_tokens)
+    copied = sharded_step.ShardedDecodeStep(shard, case.cos_sin_cache, rope_cache=shard.rope_cache.clone(), **common)
+    stored = sharded_step.ShardedDecodeStep(shard, case.cos_sin_cache, rope_cache=shard.rope_cache.clone(),
+                                            rows_to_host=True, **common)
+    assert stored.output.is_pinned() and stored.output.data_ptr() == stored.host_output.data_ptr()
+    want = copied.run_eager().clone()
+    assert torch.equal(stored.run_eager().view(torch.int16), want.view(torch.int16))
+    stored.host_output.zero_()
+    assert torch.equal(stored.capture().run().view(torch.int16), want.view(torch.int16))
+    assert_close(want, _oracle_rows(case), config.torch_dtype, f"{name} rows to host")
