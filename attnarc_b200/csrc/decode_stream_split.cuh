@@ -26,6 +26,14 @@
 // 256 threads at up to 128 registers, two CTAs per SM (14 computing warps per
 // SM), 112-token tiles (7 warps x 16 tokens), five 2 KB slots per ring.
 //
+// Software pipelining inside a computing warp: the value product of a chunk is
+// not issued after its softmax but together with the score product of the
+// warp's next chunk (chunk_scores_and_values), the two being independent. The
+// conversions of one then hide the tensor-core latency of the other; a warp
+// holds the V slot of one chunk and the K slot of the next at the same time,
+// which the ring order (K, V, K, V ...) allows without a deeper ring. At the
+// end of a work item and of the CTA's range the deferred product runs alone.
+//
 // Every wait is bounded (the limit is a launch parameter). A computing warp
 // whose wait expires sets the device flag and the CTA's abort word and stops
 // waiting and computing; the producer then issues nothing more, the other
@@ -39,6 +47,41 @@ namespace loom_decode {
 
 __device__ __forceinline__ void mbarrier_release(uint32_t barrier) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(barrier) : "memory");
+}
+
+
+// QK^T of one chunk and P.V of the chunk before it in one instruction stream (FP8 cache): the two
+// products are independent of each other (the probabilities of the earlier chunk are already in
+// `pb`), so the conversions of one hide the tensor-core latency of the other. Same arithmetic as
+// chunk_scores followed by chunk_values.
+template <typename QT, int kD>
+__device__ __forceinline__ void chunk_scores_and_values(float (&s)[1][4], WarpState<kD, 1>& state, uint32_t k_tile,
+                                                        const uint32_t (&pb)[1][2], uint32_t v_tile,
+                                                        uint32_t lane) {
+  using Tile = MmaTile<true, kD>;
+  constexpr int kKSteps = kD / 16;
+  const uint32_t ld_row = (lane & 7u) + ((lane >> 3) & 1u) * 8u;
+  const uint32_t ld_col = lane >> 4;
+  s[0][0] = s[0][1] = s[0][2] = s[0][3] = 0.0f;
+#pragma unroll
+  for (int pair = 0; pair < kKSteps / 2; ++pair) {
+    uint32_t rk[4], rv[4];
+    ldmatrix_x4(rk, k_tile + tile_offset<Tile::kSegs, true>(ld_row, 2 * pair + ld_col));
+    ldmatrix_x4_trans(rv, v_tile + tile_offset<Tile::kSegs, true>(ld_row, 2 * pair + ld_col));
+    uint32_t a[4], b[4];
+    e4m3x4_to_f16x2x2(rk[0], a[0], a[2]);
+    e4m3x4_to_f16x2x2(rk[1], a[1], a[3]);
+    e4m3x4_to_f16x2x2(__byte_perm(rv[0], 0u, 0x3120u), b[0], b[1]);
+    e4m3x4_to_f16x2x2(__byte_perm(rv[1], 0u, 0x3120u), b[2], b[3]);
+    mma_16816_f16(s[0], a, state.qf[0][2 * pair][0], state.qf[0][2 * pair][1]);
+    mma_16816_f16(state.o[0][2 * pair], b, pb[0][0], pb[0][1]);
+    e4m3x4_to_f16x2x2(rk[2], a[0], a[2]);
+    e4m3x4_to_f16x2x2(rk[3], a[1], a[3]);
+    e4m3x4_to_f16x2x2(__byte_perm(rv[2], 0u, 0x3120u), b[0], b[1]);
+    e4m3x4_to_f16x2x2(__byte_perm(rv[3], 0u, 0x3120u), b[2], b[3]);
+    mma_16816_f16(s[0], a, state.qf[0][2 * pair + 1][0], state.qf[0][2 * pair + 1][1]);
+    mma_16816_f16(state.o[0][2 * pair + 1], b, pb[0][0], pb[0][1]);
+  }
 }
 
 template <bool kFp8, int kD>
@@ -325,8 +368,43 @@ decode_stream_split_kernel(const DecodeParams p, const __grid_constant__ CUtenso
   if (p.early_metadata) loom_launch::grid_dependency_wait();
   begin_item();
 
+  static_assert(kFp8 && !kFp8KeyByAlu, "the merged product is written for the converted FP8 path");
+  // The value product of a chunk is deferred to the next chunk's score product, so that the two run
+  // as one instruction stream; `pending` says that `pb` holds probabilities whose V tile (slot
+  // pending_v, pending_rows live rows) has not been used yet.
+  uint32_t pb[kNT][2];
+  bool pending = false;
+  uint32_t pending_v = 0, pending_rows = 0;
+  auto clear_dead_rows = [&](uint32_t v_tile, uint32_t live_rows) {
+    // rows past the end of the sequence hold whatever the page held: clear them
+    constexpr uint32_t kPieces = 16 * Tile::kSegs;
+    for (uint32_t piece = lane; piece < kPieces; piece += 32) {
+      const uint32_t row = piece / Tile::kSegs;
+      if (row >= live_rows) {
+        asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};\n" ::"r"(
+                         v_tile + tile_offset<Tile::kSegs, true>(row, piece % Tile::kSegs)),
+                     "r"(0u)
+                     : "memory");
+      }
+    }
+    __syncwarp();
+  };
+  // the deferred value product on its own (end of an item, end of the range)
+  auto flush_pending = [&](uint32_t chunk) {
+    if (!pending) return;
+    pending = false;
+    wait_slot(pending_v, chunk);
+    if (!(phases & kAborted)) {
+      const uint32_t v_tile = ring_base + pending_v * Tile::kTileBytes;
+      if (pending_rows < 16u) clear_dead_rows(v_tile, pending_rows);
+      chunk_values<QT, kFp8, kD, kNT, true>(state, pb, v_tile, lane);
+    }
+    release_slot(pending_v);
+  };
+
   for (uint32_t chunk = 0; chunk < my_tiles; ++chunk) {
     if (chunk != 0 && consumer.tile == 0) {
+      flush_pending(chunk);
       finish_item();
       begin_item();
     }
@@ -338,41 +416,35 @@ decode_stream_split_kernel(const DecodeParams p, const __grid_constant__ CUtenso
     consume_slot = v_slot + 1 == (uint32_t)Ring::kSlots ? 0u : v_slot + 1;
 
     if (in_sequence) {
-      // ---- K tile ------------------------------------------------------------
-      uint32_t pb[kNT][2];
       wait_slot(k_slot, chunk);
-      const bool usable = !(phases & kAborted);
-      if (usable) {
-        float s[kNT][4];
-        chunk_scores<QT, kFp8, kD, kNT, true>(s, state, ring_base + k_slot * Tile::kTileBytes, lane);
-        chunk_softmax<QT, kFp8, kD, kNT>(pb, s, state, live_rows, g);
-      }
-      release_slot(k_slot);
-
-      // ---- V tile ------------------------------------------------------------
-      wait_slot(v_slot, chunk);
-      if (usable && !(phases & kAborted)) {
-        const uint32_t v_tile = ring_base + v_slot * Tile::kTileBytes;
-        if (live_rows < 16u) {
-          // rows past the end of the sequence hold whatever the page held: clear them
-          constexpr uint32_t kPieces = 16 * Tile::kSegs;
-          for (uint32_t piece = lane; piece < kPieces; piece += 32) {
-            const uint32_t row = piece / Tile::kSegs;
-            if (row >= live_rows) {
-              asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};\n" ::"r"(
-                               v_tile + tile_offset<Tile::kSegs, true>(row, piece % Tile::kSegs)),
-                           "r"(0u)
-                           : "memory");
-            }
-          }
-          __syncwarp();
+      float s[kNT][4];
+      if (pending) {
+        wait_slot(pending_v, chunk);
+        if (!(phases & kAborted)) {
+          const uint32_t v_tile = ring_base + pending_v * Tile::kTileBytes;
+          if (pending_rows < 16u) clear_dead_rows(v_tile, pending_rows);
+          chunk_scores_and_values<QT, kD>(s, state, ring_base + k_slot * Tile::kTileBytes, pb, v_tile, lane);
         }
-        chunk_values<QT, kFp8, kD, kNT, true>(state, pb, v_tile, lane);
+        __syncwarp();
+        if (lane == 0) {
+          mbarrier_release(empty + pending_v * 8);
+          mbarrier_release(empty + k_slot * 8);
+        }
+      } else {
+        if (!(phases & kAborted)) {
+          chunk_scores<QT, kFp8, kD, kNT, true>(s, state, ring_base + k_slot * Tile::kTileBytes, lane);
+        }
+        release_slot(k_slot);
       }
-      release_slot(v_slot);
+      if (!(phases & kAborted)) chunk_softmax<QT, kFp8, kD, kNT>(pb, s, state, live_rows, g);
+      pending = !(phases & kAborted);
+      pending_v = v_slot;
+      pending_rows = live_rows;
+      if (!pending) release_slot(v_slot);
     }
     if (chunk + 1 < my_tiles) advance(consumer);
   }
+  flush_pending(my_tiles);
   finish_item();
   if (*aborted) {
     // copies issued before the expiry may still be on their way into this CTA's shared memory
