@@ -402,11 +402,48 @@ decode_stream_split_kernel(const DecodeParams p, const __grid_constant__ CUtenso
     release_slot(pending_v);
   };
 
-  for (uint32_t chunk = 0; chunk < my_tiles; ++chunk) {
+  for (uint32_t chunk = 0; chunk < my_tiles;) {
     if (chunk != 0 && consumer.tile == 0) {
       flush_pending(chunk);
       finish_item();
       begin_item();
+    }
+    // A run of plain tiles - same work item, inside this CTA's range, this warp's 16 tokens all
+    // inside the sequence, a value product pending - goes through a loop that carries none of the
+    // general case's tests (about a seventh fewer instructions per chunk).
+    if (pending && !(phases & kAborted)) {
+      const uint32_t full_tiles =
+          consumer.length >= warp_token + 16u ? (consumer.length - warp_token - 16u) / kTileTokens + 1u : 0u;
+      const uint32_t item_end = min(full_tiles, consumer.tiles);
+      const uint32_t run = min(item_end > consumer.tile ? item_end - consumer.tile : 0u, my_tiles - chunk);
+      if (run > 1u) {
+        uint32_t done = 0;
+        for (; done < run; ++done) {
+          const uint32_t k_slot = consume_slot;
+          const uint32_t v_slot = k_slot + 1 == (uint32_t)Ring::kSlots ? 0u : k_slot + 1;
+          wait_slot(k_slot, chunk + done);
+          wait_slot(pending_v, chunk + done);
+          if (phases & kAborted) break;  // the general path below walks on without waiting or computing
+          float s[kNT][4];
+          chunk_scores_and_values<QT, kD>(s, state, ring_base + k_slot * Tile::kTileBytes, pb,
+                                          ring_base + pending_v * Tile::kTileBytes, lane);
+          __syncwarp();
+          if (lane == 0) {
+            mbarrier_release(empty + pending_v * 8);
+            mbarrier_release(empty + k_slot * 8);
+          }
+          chunk_softmax<QT, kFp8, kD, kNT>(pb, s, state, 16u, g);
+          pending_v = v_slot;
+          consume_slot = v_slot + 1 == (uint32_t)Ring::kSlots ? 0u : v_slot + 1;
+        }
+        if (done != 0u) {
+          pending_rows = 16u;
+          chunk += done;
+          consumer.tile += done - 1u;
+          if (chunk < my_tiles) advance(consumer);
+          continue;
+        }
+      }
     }
     const uint32_t token0 = consumer.tile * kTileTokens + warp_token;
     const bool in_sequence = token0 < consumer.length;  // warp-uniform; the copy side uses the same test
@@ -443,6 +480,7 @@ decode_stream_split_kernel(const DecodeParams p, const __grid_constant__ CUtenso
       if (!pending) release_slot(v_slot);
     }
     if (chunk + 1 < my_tiles) advance(consumer);
+    ++chunk;
   }
   flush_pending(my_tiles);
   finish_item();
