@@ -40,6 +40,7 @@
 #include <type_traits>
 
 #include "../../include/loom_launch.h"
+#include "decode_block_tile.cuh"
 #include "decode_common.cuh"
 #include "decode_merge.cuh"
 #include "decode_mma.cuh"
@@ -228,7 +229,7 @@ __global__ void __launch_bounds__(kMergeThreads)
 merge_stream_kernel(const float* __restrict__ slots, const uint32_t* __restrict__ item_meta,
                     const int32_t* __restrict__ sequence_lengths, uint32_t query_heads, uint32_t group,
                     uint32_t heads_per_item, uint32_t value_head_size, uint32_t max_sequence_length,
-                    void* output, uint32_t emit_state) {
+                    void* output, uint32_t emit_state, uint32_t heads_together) {
   loom_launch::grid_dependency_wait();
   const uint32_t row = blockIdx.x;
   const uint32_t seq = row / query_heads;
@@ -249,6 +250,13 @@ merge_stream_kernel(const float* __restrict__ slots, const uint32_t* __restrict_
     return;
   }
   if (parts <= 1) return;
+  if (heads_together != 0) {
+    // the kernel whose tile holds `heads_together` KV heads: slot = heads_together * (item group + CTA) + head
+    const uint64_t slot = (item / heads_together + first_cta) * heads_together + item % heads_together;
+    merge_row<OT>(slots + (slot * heads_per_item + head_in_group % heads_per_item) * stride, parts,
+                  (uint64_t)heads_together * heads_per_item * stride, value_head_size, row, output, emit_state);
+    return;
+  }
   const float* base = slots + ((item + first_cta) * heads_per_item + head_in_group % heads_per_item) * stride;
   merge_row<OT>(base, parts, (uint64_t)heads_per_item * stride, value_head_size, row, output, emit_state);
 }
@@ -431,6 +439,48 @@ bool build_cache_maps(const LoomDecodeArgs& a, bool fp8, CacheMaps* maps) {
          encode_cache_map(&maps->value, a.value_cache, row_bytes, sizes, value_strides, order);
 }
 
+// The cache as (row bytes, page, head, block) whatever the order of its strides: a box of
+// [128 bytes, 16 pages, 8 heads, 1 block] then lands in shared memory as eight per-head tiles.
+bool encode_block_map(CUtensorMap* map, const void* base, uint32_t row_bytes, uint64_t kv_heads,
+                      uint64_t block_size, uint64_t num_blocks, uint64_t head_stride, uint64_t page_stride,
+                      uint64_t block_stride) {
+  const EncodeTiled encode = tensor_map_encoder();
+  if (encode == nullptr || row_bytes != 128) return false;
+  cuuint64_t dims[4] = {row_bytes, block_size, kv_heads, num_blocks};
+  cuuint64_t strides[3] = {page_stride, head_stride, block_stride};
+  cuuint32_t box[4] = {128, 16, 8, 1};
+  cuuint32_t element_strides[4] = {1, 1, 1, 1};
+  for (const cuuint64_t stride : strides) {
+    if (stride % 16 != 0 || stride >= (1ull << 40)) return false;
+  }
+  // a block's rows touch along one of the two inner axes in both usual layouts
+  const bool rows_touch = head_stride == row_bytes || page_stride == row_bytes;
+  return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(base), dims, strides, box,
+                element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                rows_touch ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool build_block_maps(const LoomDecodeArgs& a, CacheMaps* maps) {
+  return encode_block_map(&maps->key, a.key_cache, a.head_size, a.kv_heads, a.block_size, a.num_blocks,
+                          a.key_head_stride, a.key_page_stride, a.key_block_stride) &&
+         encode_block_map(&maps->value, a.value_cache, a.value_head_size, a.kv_heads, a.block_size, a.num_blocks,
+                          a.value_head_stride, a.value_page_stride, a.value_block_stride);
+}
+
+// The balanced kernel whose tile is one 16-token block of eight KV heads (FP8 caches).
+template <typename QT>
+int launch_block_tile(const DecodeParams& p, uint32_t ctas, const CacheMaps& maps, cudaStream_t stream) {
+  static std::atomic<uint64_t> configured{0};
+  using Ring = BlockRing<128>;
+  auto kernel = decode_block_tile_kernel<QT, 128>;
+  if (const cudaError_t limit = ensure_smem(kernel, Ring::kSmemBytes, configured); limit != cudaSuccess) {
+    return launched(limit, "shared-memory limit of a decode kernel (cudaFuncSetAttribute)");
+  }
+  return launched(loom_launch::launch(kernel, dim3(ctas), dim3(Ring::kThreads), Ring::kSmemBytes, stream, p, maps.key,
+                                      maps.value));
+}
+
 template <typename QT, bool kFp8, int kD, int kNT>
 int launch_stream_tma(const DecodeParams& p, uint32_t ctas, const CacheMaps& maps, cudaStream_t stream) {
   static std::atomic<uint64_t> configured_masks[2];  // one per instantiation (plain, with options)
@@ -592,6 +642,28 @@ bool stream_shape(uint32_t sequences, uint32_t query_heads, uint32_t kv_heads, u
   return true;
 }
 
+// Does the kernel whose tile holds eight KV heads apply to this shape? (The cache encoding and the
+// layout are not part of a workspace query; the launch checks them.)
+bool block_tile_shape(uint32_t query_heads, uint32_t kv_heads, uint32_t head_size, uint32_t value_head_size) {
+  return kv_heads != 0 && kv_heads % 8 == 0 && query_heads % kv_heads == 0 && query_heads / kv_heads <= 8 &&
+         head_size == 128 && value_head_size == 128;
+}
+
+// Its workspace: eight state slots per (group of eight items + CTA), then the item table.
+bool block_tile_workspace(uint32_t sequences, uint32_t kv_heads, uint32_t value_head_size, uint32_t ctas,
+                          StreamShape* shape) {
+  shape->heads_per_item = 8;
+  uint64_t groups = 0, per_slot = 0, slots = 0, meta = 0;
+  if (!mul_checked(sequences, kv_heads / 8, &groups) || groups > std::numeric_limits<uint64_t>::max() - ctas ||
+      !mul_checked(groups + ctas, 8, &slots) || !mul_checked(8, (uint64_t)value_head_size + 2, &per_slot) ||
+      !mul_checked(slots, per_slot, &shape->slot_elements) || !mul_checked(sequences, kv_heads, &shape->items) ||
+      !mul_checked(shape->items, 2, &meta) || shape->slot_elements > std::numeric_limits<uint64_t>::max() - meta) {
+    return false;
+  }
+  shape->total_elements = shape->slot_elements + meta;
+  return true;
+}
+
 // Size that serves whichever partitioned kernel the launch then picks.
 uint64_t auto_workspace_elements(uint32_t sequences, uint32_t query_heads, uint32_t kv_heads,
                                  uint32_t value_head_size, uint32_t max_sequence_length) {
@@ -602,7 +674,14 @@ uint64_t auto_workspace_elements(uint32_t sequences, uint32_t query_heads, uint3
   if (fixed == 0 || !stream_shape(sequences, query_heads, kv_heads, value_head_size, stream_ctas_for_sizing(), &shape)) {
     return 0;
   }
-  return fixed > shape.total_elements ? fixed : shape.total_elements;
+  uint64_t needed = fixed > shape.total_elements ? fixed : shape.total_elements;
+  // head_size is not part of the query: the value head size stands for both (the launch checks)
+  StreamShape block{};
+  if (block_tile_shape(query_heads, kv_heads, value_head_size, value_head_size)) {
+    if (!block_tile_workspace(sequences, kv_heads, value_head_size, stream_ctas_for_sizing(), &block)) return 0;
+    if (block.total_elements > needed) needed = block.total_elements;
+  }
+  return needed;
 }
 
 bool product_fits_u64(std::initializer_list<uint64_t> dims) {
@@ -688,6 +767,7 @@ int launch_decode(const LoomDecodeArgs& a) {
   const CacheMaps* tma = nullptr;
   bool umma = false;
   bool split = false;  // the balanced kernel with a copy-issuing warp
+  bool block_tile = false;  // the balanced kernel whose tile is one block of eight KV heads
   if (partitioned) {
     if (a.workspace == nullptr || (reinterpret_cast<uintptr_t>(a.workspace) & 3u) != 0) {
       return LOOM_CUDA_INVALID_ARGUMENT;
@@ -710,11 +790,30 @@ int launch_decode(const LoomDecodeArgs& a) {
       // issued by a warp of their own (copy engine 2 keeps the unsplit kernel, for comparisons)
       split = tma != nullptr && !umma && fp8 && p.group <= 8 && a.sliding_window == 0 &&
               a.logits_soft_cap == 0.0f && g_copy_engine.load(std::memory_order_relaxed) != 2;
+      // ... and with KV heads in multiples of eight and head size 128 the kernel that copies a whole
+      // block of eight heads at a time (copy engine 4 keeps the one-head-per-tile kernel)
+      CacheMaps block_maps;
+      StreamShape block_shape{};
+      const uint32_t block_ctas = stream_ctas_for_launch((uint32_t)BlockRing<128>::kCtasPerSm);
+      if (split && g_copy_engine.load(std::memory_order_relaxed) == 0 && block_ctas != 0 &&
+          block_tile_shape(a.query_heads, a.kv_heads, a.head_size, a.value_head_size) &&
+          block_tile_workspace(a.sequences, a.kv_heads, a.value_head_size, block_ctas, &block_shape) &&
+          a.workspace_elements >= block_shape.total_elements && build_block_maps(a, &block_maps)) {
+        block_tile = true;
+        split = false;
+        maps = block_maps;
+        shape = block_shape;
+        stream_ctas = block_ctas;
+        p.item_meta = reinterpret_cast<uint32_t*>(a.workspace + shape.slot_elements);
+        p.partition_tokens = 16;
+        p.max_partitions = 1;
+      }
       const uint32_t ctas = stream_ctas_for_launch(
           umma    ? (uint32_t)kUmmaCtasPerSm
           : split ? 2u
                   : (tma != nullptr && p.group <= 8 ? (fp8 ? 4u : 3u) : kStreamCtasPerSm));
-      if (ctas != 0 && stream_shape(a.sequences, a.query_heads, a.kv_heads, a.value_head_size, ctas, &shape) &&
+      if (!block_tile && ctas != 0 &&
+          stream_shape(a.sequences, a.query_heads, a.kv_heads, a.value_head_size, ctas, &shape) &&
           a.workspace_elements >= shape.total_elements) {
         stream_ctas = ctas;
         p.item_meta = reinterpret_cast<uint32_t*>(a.workspace + shape.slot_elements);
@@ -744,6 +843,7 @@ int launch_decode(const LoomDecodeArgs& a) {
       tma = nullptr;
       umma = false;
       split = false;
+      block_tile = false;
     }
     // the caller's promise only matters to the balanced TMA-fed mma.sync kernel
     const bool promises_apply = tma != nullptr && !umma;
@@ -752,6 +852,10 @@ int launch_decode(const LoomDecodeArgs& a) {
       g_last_route = "umma-fp8-balanced-tma";
       status = a.dtype == 1 ? launch_umma_fp8<__half>(p, stream_ctas, maps, stream)
                             : launch_umma_fp8<__nv_bfloat16>(p, stream_ctas, maps, stream);
+    } else if (block_tile) {
+      g_last_route = "mma16-fp8-balanced-block-tma";
+      status = a.dtype == 1 ? launch_block_tile<__half>(p, stream_ctas, maps, stream)
+                            : launch_block_tile<__nv_bfloat16>(p, stream_ctas, maps, stream);
     } else if (split) {
       g_last_route = "mma16-fp8-balanced-producer-tma";
       if (a.head_size == 128) {
@@ -803,7 +907,7 @@ int launch_decode(const LoomDecodeArgs& a) {
       merge_stream_kernel<type>, dim3(grid), dim3(kMergeThreads), 0, stream,                          \
       static_cast<const float*>(p.partials), static_cast<const uint32_t*>(p.item_meta),               \
       static_cast<const int32_t*>(p.sequence_lengths), p.query_heads, p.group, shape.heads_per_item, \
-      p.value_head_size, p.max_sequence_length, p.output, p.emit_state)
+      p.value_head_size, p.max_sequence_length, p.output, p.emit_state, block_tile ? 8u : 0u)
     if (p.emit_state || a.dtype == 0) LOOM_MERGE(float);
     else if (a.dtype == 1) LOOM_MERGE(__half);
     else LOOM_MERGE(__nv_bfloat16);
@@ -1084,7 +1188,7 @@ extern "C" uint64_t loom_cuda_plain_launch_retries(void) {
 }
 
 extern "C" int loom_cuda_set_decode_copy_engine(uint32_t engine) {
-  if (engine > 3) return LOOM_CUDA_INVALID_ARGUMENT;
+  if (engine > 4) return LOOM_CUDA_INVALID_ARGUMENT;
   loom_decode::g_copy_engine.store(engine, std::memory_order_relaxed);
   return LOOM_CUDA_SUCCESS;
 }

@@ -65,11 +65,13 @@ def set_programmatic_launch(mode: int) -> None:
 
 def set_decode_copy_engine(engine: str) -> None:
     """How the balanced kernel is fed: ``"tma"`` (default; over an FP8 cache the
-    copies are issued by a warp of their own), ``"cp_async"`` (per-lane copies),
-    ``"tma-mma"`` (TMA with every computing warp feeding its own ring) or
+    copies are issued by a warp of their own, a whole block of eight KV heads at
+    a time where the KV heads come in eights), ``"cp_async"`` (per-lane copies),
+    ``"tma-mma"`` (TMA with every computing warp feeding its own ring),
     ``"tma-umma"`` (TMA, and the tcgen05 kernel where it applies: FP8 cache,
-    head size 128, up to 8 query heads per KV head)."""
-    code = {"tma": 0, "cp_async": 1, "tma-mma": 2, "tma-umma": 3}[engine]
+    head size 128, up to 8 query heads per KV head) or ``"tma-head"`` (as
+    ``"tma"``, but always one KV head per tile)."""
+    code = {"tma": 0, "cp_async": 1, "tma-mma": 2, "tma-umma": 3, "tma-head": 4}[engine]
     if library().loom_cuda_set_decode_copy_engine(code) != 0:
         raise RuntimeError("could not select the decode copy engine")
 

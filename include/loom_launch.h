@@ -288,8 +288,11 @@ uint64_t loom_cuda_plain_launch_retries(void);
  * (every computing warp feeds its own ring); 3 is 0 plus the tcgen05 kernel
  * (E4M3 operands read by the tensor cores straight from shared memory,
  * accumulators in tensor memory) for FP8 caches with head size 128 and up to 8
- * query heads per KV head. Process-wide; meant for comparisons and as a switch
- * to fall back on.
+ * query heads per KV head; 4 is 0 without the kernel that, where the KV heads
+ * come in multiples of eight (head size 128, FP8 cache, a workspace of the size
+ * the workspace query returns), copies one 16-token block of eight KV heads per
+ * copy and gives each computing warp one KV head. Process-wide; meant for
+ * comparisons and as a switch to fall back on.
  */
 int loom_cuda_set_decode_copy_engine(uint32_t engine);
 

@@ -467,6 +467,61 @@ def test_tcgen05_kernel_emits_states_that_merge(ops):
     assert ops.decode_timeout_flag() == 0
 
 
+# ---- the kernel whose tile is one 16-token block of eight KV heads (FP8 caches, KV heads in eights) ----
+
+@pytest.mark.parametrize("layout", ["NHD", "HND"])
+@pytest.mark.parametrize("query_heads,kv_heads", [(64, 8), (32, 16), (8, 8)])
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+def test_block_of_eight_heads_per_tile(ops, layout, query_heads, kv_heads, dtype):
+    # one token, partial last blocks, whole blocks, items split over CTAs
+    config = workloads.DecodeConfig("t", 9, query_heads, kv_heads, head_size=128, dtype=dtype, cache="fp8",
+                                    fp8_granularity="head", layout=layout,
+                                    lengths=("fixed", [1, 15, 16, 17, 33, 3000, 4097, 640, 48]))
+    case = workloads.build_case(config, DEVICE, seed=41)
+    key_cache, value_cache = case.cache_views()
+    scales = dict(key_scales=case.key_scales, value_scales=case.value_scales)
+    torch_dtype = config.torch_dtype
+    expected = helpers.oracle_decode(case.query, key_cache, value_cache, case.block_tables, case.sequence_lengths,
+                                     scale=case.scale, max_sequence_length=case.max_sequence_length, **scales)
+    # stale contents after the end of each sequence must not matter (0x7f is the E4M3 NaN)
+    poisoned_k, poisoned_v = key_cache.clone(), value_cache.clone()
+    for s, length in enumerate(case.lengths.tolist()):
+        if length % 16:
+            block = int(case.block_tables[s, (length - 1) // 16])
+            poisoned_k[block, length % 16:] = 0x7F
+            poisoned_v[block, length % 16:] = 0x7F
+    outputs = {}
+    for engine in ("tma", "tma-head"):
+        ops.set_decode_copy_engine(engine)
+        try:
+            outputs[engine] = ops.paged_decode_attention_ex(
+                case.query, poisoned_k, poisoned_v, case.block_tables, case.sequence_lengths,
+                max_sequence_length=case.max_sequence_length, scale=case.scale, split=True, **scales)
+            route = ops.last_decode_route()
+        finally:
+            ops.set_decode_copy_engine("tma")
+        assert route == ("mma16-fp8-balanced-block-tma" if engine == "tma" else "mma16-fp8-balanced-producer-tma")
+        helpers.assert_close(outputs[engine], expected, torch_dtype, f"{engine} {layout} {query_heads}/{kv_heads}")
+    assert ops.decode_timeout_flag() == 0
+
+
+def test_block_of_eight_heads_emits_states_that_merge(ops):
+    config = workloads.DecodeConfig("t", 6, 48, 8, head_size=128, dtype="bf16", cache="fp8", fp8_granularity="tensor",
+                                    lengths=("fixed", [3, 128, 129, 64, 700, 2100]))
+    case = workloads.build_case(config, DEVICE, seed=43)
+    key_cache, value_cache = case.cache_views()
+    scales = dict(key_scales=case.key_scales, value_scales=case.value_scales)
+    expected = helpers.oracle_decode(case.query, key_cache, value_cache, case.block_tables, case.sequence_lengths,
+                                     scale=case.scale, max_sequence_length=case.max_sequence_length, **scales)
+    states = ops.paged_decode_attention_ex(case.query, key_cache, value_cache, case.block_tables,
+                                           case.sequence_lengths, max_sequence_length=case.max_sequence_length,
+                                           scale=case.scale, split=True, emit_state=True, **scales)
+    assert ops.last_decode_route() == "mma16-fp8-balanced-block-tma" and states.dtype == torch.float32
+    merged = ops.merge_decode_states(states.reshape(1, -1, states.shape[-1]).contiguous(), torch.bfloat16)
+    helpers.assert_close(merged.reshape(expected.shape), expected, torch.bfloat16, "states of the block-tile kernel")
+    assert ops.decode_timeout_flag() == 0
+
+
 # ---- sliding window and logits soft cap (options beyond the reference's contract; parity unpinned:
 # the expectation is the oracle's F64 attention restricted to the window / with capped scores) -------
 
