@@ -30,9 +30,10 @@ def ops():
     module.kv_block_move_timeout_flag(reset=True)
 
 
-@pytest.mark.parametrize("name,engine", [("cfg2", "tma"), ("cfg4", "tma"), ("cfg4", "tma-mma")])
+@pytest.mark.parametrize("name,engine", [("cfg2", "tma"), ("cfg4", "tma"), ("cfg4", "tma-head"), ("cfg4", "tma-mma")])
 def test_an_expired_wait_of_the_decode_kernel_sets_the_flag_and_returns(ops, name, engine):
-    # cfg4 / tma: the FP8 kernel whose copies are issued by a warp of their own; tma-mma: every warp feeds itself
+    # cfg4 / tma: the FP8 kernel that copies a block of eight KV heads per tile; tma-head: one KV head per
+    # tile, copies issued by a warp of their own; tma-mma: every warp feeds itself
     ops.set_decode_copy_engine(engine)
     config = workloads.scaled(workloads.CONFIGS[name], batch=3, lengths=("fixed", [700, 64, 300]))
     case = workloads.build_case(config, DEVICE, seed=9)
@@ -52,7 +53,8 @@ def test_an_expired_wait_of_the_decode_kernel_sets_the_flag_and_returns(ops, nam
     helpers.assert_close(decode(), expected, config.torch_dtype, "before")
     route = ops.last_decode_route()
     assert "balanced" in route and route.endswith("-tma")
-    assert ("producer" in route) == (name == "cfg4" and engine == "tma")
+    assert ("producer" in route) == (name == "cfg4" and engine == "tma-head")
+    assert ("block" in route) == (name == "cfg4" and engine == "tma")
     assert ops.decode_timeout_flag() == 0
 
     ops.set_wait_policy(attempts=400, unmatched_bytes=16)
