@@ -55,6 +55,9 @@ NCU_DRAM_TRAFFIC_BYTES = {"kv-move": 537_019_136 + 486_040_832, "kv-swap": 1_073
 # token count, so a full launch is this ratio times its KV bytes
 # (profiles/decode_dram_traffic_all_configs.md).
 NCU_DRAM_TRAFFIC_PER_KV_BYTE = {"cfg2": 1.0267, "cfg3": 1.0170, "cfg4": 1.0137, "cfg5": 1.0056}
+# The kernel that copies a block of eight KV heads per tile (cfg4 on one GPU): reads 1.0056 x the KV
+# bytes plus 9.1 MB of partial states per launch, whatever the size (profiles/decode_block_tile_fp8_cfg4.md).
+NCU_BLOCK_TILE_READ_PER_KV_BYTE, NCU_BLOCK_TILE_WRITTEN_BYTES = 1.0056, 9_123_072
 
 
 def reference_kernels_baseline(case, config, cache_views, steps):
@@ -653,6 +656,8 @@ def measure_workload(args, ranks, name, steps, headline):
     local_decode_us = decode_ms / steps * 1e3
     achieved = shard.kv_bytes / (local_decode_us * 1e-6) / 1e9 if shard.kv_bytes else 0.0
     traffic = NCU_DRAM_TRAFFIC_PER_KV_BYTE.get(name)
+    if traffic is not None and "block" in route and shard.kv_bytes:
+        traffic = NCU_BLOCK_TILE_READ_PER_KV_BYTE + NCU_BLOCK_TILE_WRITTEN_BYTES / shard.kv_bytes
     record.update({
         "workload": f"{config.name}: {config.description}", "sharding": mode, "n_gpus": world, "steps": steps,
         "us_per_step": us, "value": global_bytes / (us * 1e-6) / 1e9, "unit": UNIT,
@@ -667,7 +672,7 @@ def measure_workload(args, ranks, name, steps, headline):
             "traffic": None if traffic is None else int(traffic * shard.kv_bytes),
             "traffic_source": None if traffic is None else
             "ncu dram__bytes_read.sum + dram__bytes_write.sum of one decode launch on a cut of the workload, "
-            "scaled by KV bytes (profiles/decode_dram_traffic_all_configs.md)",
+            "scaled by KV bytes (profiles/decode_dram_traffic_all_configs.md, profiles/decode_block_tile_fp8_cfg4.md)",
         },
         "exchange": (None if not shard.exchange else
                      "push + merge kernels over NVLink peer memory" if step.peer_exchange is not None else
