@@ -897,10 +897,26 @@ def run_multi_token(args):
         step()
     torch.cuda.synchronize()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        step()
+    stop.record()
+    torch.cuda.synchronize()
+    eager_ms = start.elapsed_time(stop) / args.steps
+    # the same K steps as one CUDA graph, like the single-token benchmark
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            for _ in range(args.steps):
+                step()
+    torch.cuda.synchronize()
+    graph.replay()
+    torch.cuda.synchronize()
     with ClockSampler(local_rank) as sampler:
         start.record()
-        for _ in range(args.steps):
-            step()
+        graph.replay()
         stop.record()
         torch.cuda.synchronize()
     ms = start.elapsed_time(stop) / args.steps
@@ -912,7 +928,8 @@ def run_multi_token(args):
         "scaling": "weak", "vs_baseline": None, "dtype": config.dtype if not fp8 else "u8", "data": "synthetic",
         "config": {"workload": f"{config.name}: {config.description}", "query_tokens": args.query_tokens,
                    "form": "expanded" if args.expanded else "one pass", "distinct_kv_bytes_per_step": case.kv_bytes,
-                   "launch": "eager operator calls, CUDA events around K steps",
+                   "launch": "one CUDA graph of K operator calls, CUDA events around its replay",
+                   "eager_ms_per_step": eager_ms,
                    "l2": "KV of %.2f GB per step" % (case.kv_bytes / 1e9)},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": UNIT, "frac": achieved / peak,
                      "peak_source": f"{source} copy bandwidth", "algorithmic_bytes_per_launch": case.kv_bytes,
