@@ -107,6 +107,23 @@ def test_workspace_rule_matches_the_sizing_function(lib):
     assert "multiple of 16" in _native.last_error()
 
 
+def test_workspace_covers_the_layout_of_the_eight_heads_per_tile_kernel(lib):
+    # KV heads in eights, head size 128, up to 8 query heads per KV head: eight state slots of
+    # 8 x 130 floats per (sequence + CTA), two CTAs per SM of at least 148 SMs, then two words per item
+    elements = ctypes.c_uint64(0)
+    assert lib.loom_cuda_bridge_paged_decode_workspace_elements(2, 128, 64, 8, 128, 128, 80000, 16, 1024, 16384, 0.1,
+                                                                elements) == 0
+    block_tiles = (128 * (8 // 8) + 2 * 148) * 8 * 8 * 130 + 2 * 128 * 8
+    assert elements.value >= block_tiles
+    # a group of 16 query heads per KV head is not served by that kernel: the other layouts alone decide
+    assert lib.loom_cuda_bridge_paged_decode_workspace_elements(2, 128, 128, 8, 128, 128, 80000, 16, 1024, 16384, 0.1,
+                                                                elements) == 0
+    per_item_slots = (128 * 8 + 4 * 148) * 16 * 130 + 2 * 128 * 8
+    tokens = lib.loom_cuda_paged_decode_default_partition_tokens(128, 8, 16384)
+    fixed = 128 * 128 * ((16384 + tokens - 1) // tokens) * 130
+    assert elements.value == max(per_item_slots, fixed)
+
+
 def rope_call(lib, **overrides):
     a = dict(dtype=0, encoding=0, query=0x10000, query_elements=2 * 3 * 8, key=0x20000, key_elements=2 * 1 * 8,
              value=0x30000, value_elements=2 * 1 * 8, positions=0x40000, cos_sin=0x50000, cos_sin_elements=4 * 8,
