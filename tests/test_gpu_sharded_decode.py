@@ -146,6 +146,36 @@ def test_long_context_rank_steps_merge_to_the_oracle(ranks):
     assert_close(merged.cpu(), expected, config.torch_dtype, f"long context x{ranks}")
 
 
+# ---- the merge of partial states itself: few parts (eight per round trip) and many (four groups of
+# 32 threads, from 17 parts on), against the log-sum-exp merge written out in F64 ------------------------
+
+@pytest.mark.parametrize("parts", [1, 3, 16, 17, 40, 131])
+@pytest.mark.parametrize("dim", [64, 128, 256])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_merge_of_states_matches_the_log_sum_exp_merge(parts, dim, out_dtype):
+    from attnarc_b200 import ops
+
+    rows = 37
+    generator = torch.Generator(device="cuda:0").manual_seed(parts * 1000 + dim)
+    states = torch.randn((parts, rows, dim + 2), device="cuda:0", generator=generator)
+    states[..., dim] = states[..., dim] * 6.0                       # maxima in natural-log units
+    states[..., dim + 1] = states[..., dim + 1].abs() + 0.1         # sums of exponentials
+    if parts > 2:
+        # parts that saw no token: sum 0, maximum -inf, whatever in O (must not matter)
+        states[1, ::3, dim + 1] = 0.0
+        states[1, ::3, dim] = float("-inf")
+        states[parts - 1, 5, dim + 1] = 0.0
+    merged = ops.merge_decode_states(states.contiguous(), out_dtype)
+    wide = states.double().cpu()
+    live = wide[..., dim + 1] > 0
+    maxima = torch.where(live, wide[..., dim], torch.full_like(wide[..., dim], float("-inf")))
+    top = maxima.max(dim=0).values
+    factor = torch.where(live, torch.exp(maxima - top), torch.zeros_like(maxima))
+    total = (wide[..., dim + 1] * factor).sum(dim=0)
+    expected = (wide[..., :dim] * factor.unsqueeze(-1)).sum(dim=0) / total.unsqueeze(-1)
+    assert_close(merged.cpu(), expected.float(), out_dtype, f"{parts} parts, Dv {dim}")
+
+
 # ---- the exchange over peer memory (multi_gpu.PeerExchange), ranks emulated on one GPU ---------------
 #
 # Kernels that wait for each other must not run as separate launches on one device. The emulation
