@@ -505,6 +505,24 @@ def test_block_of_eight_heads_per_tile(ops, layout, query_heads, kv_heads, dtype
     assert ops.decode_timeout_flag() == 0
 
 
+@pytest.mark.parametrize("block_size", [32, 64])
+def test_block_of_eight_heads_with_larger_cache_blocks(ops, block_size):
+    # a tile is 16 tokens, so a cache block of 32 or 64 tokens is copied in two or four pieces
+    config = workloads.DecodeConfig("t", 5, 40, 8, head_size=128, block_size=block_size, dtype="bf16", cache="fp8",
+                                    fp8_granularity="head", lengths=("fixed", [block_size - 1, block_size + 17, 1000, 16, 2500]))
+    case = workloads.build_case(config, DEVICE, seed=47)
+    key_cache, value_cache = case.cache_views()
+    scales = dict(key_scales=case.key_scales, value_scales=case.value_scales)
+    expected = helpers.oracle_decode(case.query, key_cache, value_cache, case.block_tables, case.sequence_lengths,
+                                     scale=case.scale, max_sequence_length=case.max_sequence_length, **scales)
+    actual = ops.paged_decode_attention_ex(case.query, key_cache, value_cache, case.block_tables,
+                                           case.sequence_lengths, max_sequence_length=case.max_sequence_length,
+                                           scale=case.scale, split=True, **scales)
+    assert ops.last_decode_route() == "mma16-fp8-balanced-block-tma"
+    helpers.assert_close(actual, expected, torch.bfloat16, f"block size {block_size}")
+    assert ops.decode_timeout_flag() == 0
+
+
 def test_block_of_eight_heads_emits_states_that_merge(ops):
     config = workloads.DecodeConfig("t", 6, 48, 8, head_size=128, dtype="bf16", cache="fp8", fp8_granularity="tensor",
                                     lengths=("fixed", [3, 128, 129, 64, 700, 2100]))
