@@ -665,8 +665,12 @@ bool block_tile_workspace(uint32_t sequences, uint32_t kv_heads, uint32_t value_
 }
 
 // Size that serves whichever partitioned kernel the launch then picks.
+// `every_layout` = false leaves out the (larger) layout of the eight-heads-per-tile kernel: the size
+// below which no partitioned kernel can run, since the launch falls back to the other kernels when
+// the workspace does not hold that layout.
 uint64_t auto_workspace_elements(uint32_t sequences, uint32_t query_heads, uint32_t kv_heads,
-                                 uint32_t value_head_size, uint32_t max_sequence_length) {
+                                 uint32_t value_head_size, uint32_t max_sequence_length,
+                                 bool every_layout = true) {
   const uint64_t fixed = fixed_workspace_elements(
       sequences, query_heads, value_head_size, max_sequence_length,
       default_partition_tokens(sequences, kv_heads, max_sequence_length));
@@ -677,7 +681,7 @@ uint64_t auto_workspace_elements(uint32_t sequences, uint32_t query_heads, uint3
   uint64_t needed = fixed > shape.total_elements ? fixed : shape.total_elements;
   // head_size is not part of the query: the value head size stands for both (the launch checks)
   StreamShape block{};
-  if (block_tile_shape(query_heads, kv_heads, value_head_size, value_head_size)) {
+  if (every_layout && block_tile_shape(query_heads, kv_heads, value_head_size, value_head_size)) {
     if (!block_tile_workspace(sequences, kv_heads, value_head_size, stream_ctas_for_sizing(), &block)) return 0;
     if (block.total_elements > needed) needed = block.total_elements;
   }
@@ -1250,7 +1254,7 @@ extern "C" int loom_cuda_paged_decode_attention_built_in_scratch(const LoomDecod
   const uint64_t needed =
       args->partition_tokens == 0
           ? auto_workspace_elements(args->sequences, args->query_heads, args->kv_heads, args->value_head_size,
-                                    args->max_sequence_length)
+                                    args->max_sequence_length, /*every_layout=*/false)
           : fixed_workspace_elements(args->sequences, args->query_heads, args->value_head_size,
                                      args->max_sequence_length, args->partition_tokens);
   if (needed == 0) {
