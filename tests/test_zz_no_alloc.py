@@ -69,10 +69,14 @@ def decode_args(case, query, output, partition_tokens=0):
 @pytest.fixture(scope="module")
 def lib():
     library = _native.library()
+    # this file binds the entry points to its own (shorter, first-version) mirror of the struct;
+    # the package's bindings come back afterwards whatever the order of the test files
+    before = library.loom_cuda_paged_decode_attention_ex.argtypes
     library.loom_cuda_paged_decode_attention_ex.argtypes = [ctypes.POINTER(LoomDecodeArgs)]
     library.loom_cuda_paged_decode_attention_built_in_scratch.argtypes = [
         ctypes.POINTER(LoomDecodeArgs), ctypes.c_char_p, u64]
-    return library
+    yield library
+    library.loom_cuda_paged_decode_attention_ex.argtypes = before
 
 
 @pytest.mark.gpu
