@@ -272,7 +272,23 @@ decode_stream_split_kernel(const DecodeParams p, const __grid_constant__ CUtenso
         } else {
           slot = slot + 2 >= (uint32_t)Ring::kSlots ? slot + 2 - Ring::kSlots : slot + 2;
         }
-        if (tile + 1 < my_tiles) advance(cursor);
+        if (tile + 1 < my_tiles) {
+          advance(cursor);
+          // a new work item starts with the next tile: its query rows go to L1 now, two to three tiles
+          // before the computing warps ask for them (a 128-byte line per lane and pass)
+          if (cursor.tile == 0) {
+            constexpr uint32_t kLinesPerRow = (kD * sizeof(QT) + 127) / 128;
+            const uint32_t kv_head = cursor.head / head_chunks;
+            const uint32_t first_head = (cursor.head % head_chunks) * kHeads;
+            const uint32_t live = min((uint32_t)kHeads, p.group - first_head);
+            for (uint32_t line = lane; line < live * kLinesPerRow; line += (uint32_t)kC) {
+              const QT* row = static_cast<const QT*>(p.query) + (uint64_t)cursor.seq * p.q_token +
+                              ((uint64_t)kv_head * p.group + first_head + line / kLinesPerRow) * p.q_head;
+              asm volatile("prefetch.global.L1 [%0];\n" ::"l"(reinterpret_cast<const char*>(row) +
+                                                              (line % kLinesPerRow) * 128));
+            }
+          }
+        }
       }
     }
     return;

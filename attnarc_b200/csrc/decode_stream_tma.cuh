@@ -295,6 +295,21 @@ decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorM
     if (issue_value && issue_left != 0) {
       advance(producer);
       fetch_block();
+      // The copy side reaches a new work item one to two tiles before the computing side does:
+      // its query rows are pulled into L1 now, so that begin_item finds them there instead of
+      // waiting for L2 at every item boundary (one warp per CTA, a 128-byte line per lane).
+      if (producer.tile == 0 && warp == 0) {
+        constexpr uint32_t kLinesPerRow = (kD * sizeof(QT) + 127) / 128;
+        const uint32_t kv_head = producer.head / head_chunks;
+        const uint32_t first_head = (producer.head % head_chunks) * kHeads;
+        const uint32_t live = min((uint32_t)kHeads, p.group - first_head);
+        for (uint32_t line = lane; line < live * kLinesPerRow; line += 32) {
+          const QT* row = static_cast<const QT*>(p.query) + (uint64_t)producer.seq * p.q_token +
+                          ((uint64_t)kv_head * p.group + first_head + line / kLinesPerRow) * p.q_head;
+          asm volatile("prefetch.global.L1 [%0];\n" ::"l"(reinterpret_cast<const char*>(row) +
+                                                          (line % kLinesPerRow) * 128));
+        }
+      }
     }
     issue_value = !issue_value;
   };

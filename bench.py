@@ -133,7 +133,7 @@ def parse_args():
                         help="override the workload's batch size (smaller cases for profiler captures)")
     parser.add_argument("--copies", type=int, default=0, help="cache copies rotated between steps (0 = auto)")
     parser.add_argument("--no-cpu-baseline", action="store_true")
-    parser.add_argument("--copy-engine", choices=["tma", "cp_async", "tma-mma", "tma-umma"], default=None,
+    parser.add_argument("--copy-engine", choices=["tma", "cp_async", "tma-mma", "tma-umma", "tma-head"], default=None,
                         help="how the balanced decode kernel is fed (default: the library's choice)")
     parser.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
                         help="long-context mode at N > 1: this library's push/merge kernels over peer memory "
