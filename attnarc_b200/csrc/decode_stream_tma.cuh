@@ -35,6 +35,9 @@
 
 namespace loom_decode {
 
+// Empty units the balanced line counts in front of every work item's tiles (decode_stream_tma_kernel).
+constexpr uint32_t kItemSetupUnits = 1;
+
 __device__ unsigned int g_decode_timeout_flag = 0;
 // Which wait expired first: (wait kind + 1) << 20 | local tile index << 1; 0 if none.
 __device__ unsigned int g_decode_timeout_where = 0;
@@ -155,7 +158,13 @@ decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorM
   // prologue runs while that kernel (the step's RoPE + KV write) is still at work.
   if (!p.early_metadata) loom_launch::grid_dependency_wait();
 
-  // ---- tiles per sequence, exclusive prefix sum -----------------------------
+  // ---- units per sequence, exclusive prefix sum -----------------------------
+  // The line that is cut into equal shares counts, per work item, its tiles plus kItemSetupUnits
+  // empty units in front of them: a boundary between two items costs a CTA about half a tile's
+  // time (the warps' states are merged and stored, the next item's queries loaded), and a share
+  // that holds a batch's shortest sequences crosses many. A unit below kItemSetupUnits of its item
+  // is nothing to copy or compute, like a chunk past the end of a sequence.
+  auto item_units = [](uint32_t tiles) -> uint32_t { return tiles ? tiles + kItemSetupUnits : 0u; };
   {
     const uint32_t per_thread = (p.sequences + kMmaThreads - 1) / kMmaThreads;
     const uint32_t begin = min(threadIdx.x * per_thread, p.sequences);
@@ -163,7 +172,7 @@ decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorM
     uint32_t local = 0;
     for (uint32_t s = begin; s < end; ++s) {
       const uint32_t length = clamp_length(__ldg(p.sequence_lengths + s), p.max_sequence_length);
-      local += stream_tiles(length, kOptions ? p.sliding_window : 0u);
+      local += item_units(stream_tiles(length, kOptions ? p.sliding_window : 0u));
     }
     uint32_t inclusive = local;
 #pragma unroll
@@ -178,7 +187,7 @@ decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorM
     for (uint32_t s = begin; s < end; ++s) {
       prefix[s] = running;
       const uint32_t length = clamp_length(__ldg(p.sequence_lengths + s), p.max_sequence_length);
-      running += stream_tiles(length, kOptions ? p.sliding_window : 0u);
+      running += item_units(stream_tiles(length, kOptions ? p.sliding_window : 0u));
     }
     if (threadIdx.x == kMmaThreads - 1) prefix[p.sequences] = running;
     __syncthreads();
@@ -237,10 +246,12 @@ decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorM
   // first token of this warp's 16-token chunk of a cursor's tile, and whether the chunk holds a
   // token the query sees
   auto chunk_token = [&](const StreamCursor& c) -> uint32_t {
+    if (c.tile < kItemSetupUnits) return 0xffffffffu;  // a setup unit: no token, never live
+    const uint32_t tile = c.tile - kItemSetupUnits;
     if constexpr (kOptions) {
-      return (stream_first_tile(c.length, p.sliding_window) + c.tile) * kStreamTileTokens + warp_token;
+      return (stream_first_tile(c.length, p.sliding_window) + tile) * kStreamTileTokens + warp_token;
     } else {
-      return c.tile * kStreamTileTokens + warp_token;
+      return tile * kStreamTileTokens + warp_token;
     }
   };
   auto chunk_live = [&](uint32_t token0, const StreamCursor& c) -> bool {
@@ -345,8 +356,10 @@ decode_stream_tma_kernel(const DecodeParams p, const __grid_constant__ CUtensorM
     const uint32_t first_head = (item_head % head_chunks) * kHeads;
     const uint32_t live_heads = min((uint32_t)kHeads, p.group - first_head);
     const uint64_t item = (uint64_t)item_seq * heads + item_head;
-    const uint64_t item_begin = (uint64_t)heads * prefix[item_seq] + (uint64_t)item_head * item_tiles;
-    const uint64_t item_end = item_begin + item_tiles;
+    // the item's tiles on the line (its setup units lie in front of them)
+    const uint64_t item_end = (uint64_t)heads * prefix[item_seq] + (uint64_t)(item_head + 1) * item_tiles;
+    const uint64_t item_begin = item_end - (item_tiles - kItemSetupUnits);
+    if (range_begin >= item_end || range_end <= item_begin) return;  // only setup units of it are in this share
     const uint32_t first_cta = cta_of(item_begin);
     const uint32_t last_cta = cta_of(item_end - 1);
     const uint32_t parts = last_cta - first_cta + 1;
