@@ -423,6 +423,9 @@ class Ranks:
         torch.cuda.set_device(self.local_rank)
         self.device = torch.device("cuda", self.local_rank)
         if self.world > 1:
+            # stdout carries the one JSON line and nothing else: NCCL's own log (its version line
+            # under NCCL_DEBUG=VERSION, more under INFO) goes to stderr unless the caller named a file
+            os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
             dist.init_process_group("nccl", device_id=self.device)
 
     def barrier(self):
