@@ -37,6 +37,28 @@ import time
 
 import numpy as np
 
+# stdout carries the one JSON line and nothing else. Libraries write to it too (NCCL prints its
+# version line there at the first communicator), so a multi-rank run moves file descriptor 1 over
+# to stderr for its lifetime and keeps the real stdout for emit().
+_REAL_STDOUT = None
+
+
+def keep_stdout_for_the_json_line():
+    global _REAL_STDOUT
+    if _REAL_STDOUT is None:
+        sys.stdout.flush()
+        _REAL_STDOUT = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(line: dict):
+    text = json.dumps(line) + "\n"
+    if _REAL_STDOUT is None:
+        sys.stdout.write(text)
+        sys.stdout.flush()
+    else:
+        os.write(_REAL_STDOUT, text.encode())
+
 ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
@@ -403,7 +425,7 @@ def run_reference(args):
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # ------------------------------------------------------------------ GPU arm
@@ -423,9 +445,7 @@ class Ranks:
         torch.cuda.set_device(self.local_rank)
         self.device = torch.device("cuda", self.local_rank)
         if self.world > 1:
-            # stdout carries the one JSON line and nothing else: NCCL's own log (its version line
-            # under NCCL_DEBUG=VERSION, more under INFO) goes to stderr unless the caller named a file
-            os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+            keep_stdout_for_the_json_line()
             dist.init_process_group("nccl", device_id=self.device)
 
     def barrier(self):
@@ -738,7 +758,7 @@ def run_b200(args):
             line["reference_gpu_baseline"] = head["reference_gpu_baseline"]
         if ranks.world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(config, args.seed, args.cpu_seconds, host_threads())
-        print(json.dumps(line), flush=True)
+        emit(line)
     ranks.close()
 
 
@@ -860,7 +880,7 @@ def run_kv_move(args):
         seconds = (time.perf_counter() - begin) / repeats
         line["cpu_baseline"] = {"value": 2 * sample * block_bytes / seconds / 1e9, "unit": UNIT, "cores": 1,
                                 "kind": "port", "sample": f"{sample} pairs of {block_bytes // 1024} KB blocks, numpy"}
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # ------------------------------------------------------------------ multi-token queries
